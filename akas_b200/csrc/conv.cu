@@ -1,0 +1,91 @@
+// LFM2's gated causal depthwise short convolution over a flat batch, with per-request state.
+//
+// Per token t of request r (local index j = t - cu_seqlens[r]) and channel c:
+//   u[t]   = B[t] * x[t]                      (bcx row = [B | C | x], three parts of width C)
+//   s[t]   = sum_{i<L} u_i * taps[c, i]       u_i = u of local index j - (L-1-i), taken from this
+//                                             step's rows when that index is >= 0, else from the
+//                                             request's state (its last L-1 values of u, oldest first)
+//   out[t] = C[t] * (s[t] + bias[c])
+// and afterwards state[r] = the last L-1 values of u of (state ++ this step's u). Products, sums and
+// the state are float32. Two launches: the forward reads the old state, the update then rewrites it;
+// both are per-token/per-request parallel, so a prompt portion is not walked serially.
+#include "common.cuh"
+
+using namespace akas;
+
+#define AKAS_CONV_MAX_TAPS 16
+
+template <typename T>
+__global__ void short_conv_forward_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
+                                          const float* __restrict__ bias, const float* __restrict__ state,
+                                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token,
+                                          const int* __restrict__ slots, T* __restrict__ out, int C, int L) {
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int r = seq_of_token[t];
+  const int slot = r >= 0 ? slots[r] : -1;
+  if (slot < 0) {
+    out[(size_t)t * C + c] = from_f32<T>(0.f);
+    return;
+  }
+  const int j = t - cu_seqlens[r];
+  float acc = 0.f;
+  for (int i = 0; i < L; ++i) {
+    const int back = L - 1 - i;  // how many tokens before t
+    float u;
+    if (j - back >= 0) {
+      const T* row = bcx + (size_t)(t - back) * 3 * C;
+      u = to_f32(row[c]) * to_f32(row[2 * C + c]);
+    } else {
+      u = state[((size_t)slot * (L - 1) + (j + i)) * C + c];
+    }
+    acc = fmaf(u, taps[(size_t)c * L + i], acc);
+  }
+  if (bias) acc += bias[c];
+  out[(size_t)t * C + c] = from_f32<T>(to_f32(bcx[(size_t)t * 3 * C + C + c]) * acc);
+}
+
+template <typename T>
+__global__ void short_conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
+                                        const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int C,
+                                        int L) {
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int slot = slots[r];
+  const int start = cu_seqlens[r];
+  const int n = cu_seqlens[r + 1] - start;
+  if (slot < 0 || n <= 0) return;
+  float next[AKAS_CONV_MAX_TAPS - 1];
+  float* rows = state + (size_t)slot * (L - 1) * C + c;
+  for (int i = 0; i < L - 1; ++i) {
+    const int j = n - (L - 1) + i;  // local index of the token whose u becomes state row i
+    if (j >= 0) {
+      const T* row = bcx + (size_t)(start + j) * 3 * C;
+      next[i] = to_f32(row[c]) * to_f32(row[2 * C + c]);
+    } else {
+      next[i] = rows[(size_t)(n + i) * C];
+    }
+  }
+  for (int i = 0; i < L - 1; ++i) rows[(size_t)i * C] = next[i];
+}
+
+AKAS_API int akas_short_conv(const void* bcx, const float* taps, const float* bias, float* state,
+                             const int* cu_seqlens, const int* seq_of_token, const int* slots, void* out, int N,
+                             int R, int C, int L, int dtype, cudaStream_t stream) {
+  if (L < 2 || L > AKAS_CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
+  if (N <= 0 || R <= 0) return 0;
+  const int threads = 128;
+  const dim3 fwd(N, (C + threads - 1) / threads), upd(R, (C + threads - 1) / threads);
+  if (dtype == AKAS_F32) {
+    short_conv_forward_kernel<float><<<fwd, threads, 0, stream>>>((const float*)bcx, taps, bias, state, cu_seqlens,
+                                                                  seq_of_token, slots, (float*)out, C, L);
+    short_conv_state_kernel<float><<<upd, threads, 0, stream>>>((const float*)bcx, state, cu_seqlens, slots, C, L);
+  } else {
+    short_conv_forward_kernel<bf16><<<fwd, threads, 0, stream>>>((const bf16*)bcx, taps, bias, state, cu_seqlens,
+                                                                 seq_of_token, slots, (bf16*)out, C, L);
+    short_conv_state_kernel<bf16><<<upd, threads, 0, stream>>>((const bf16*)bcx, state, cu_seqlens, slots, C, L);
+  }
+  return launch_status();
+}

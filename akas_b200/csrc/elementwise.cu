@@ -1,0 +1,101 @@
+// Embedding gather, RMSNorm (optionally of gathered rows), SwiGLU and the reset of state rows.
+//
+// The residual stream is float32 in both precisions: the embedding writes float32, RMSNorm reads
+// it and writes the compute dtype that the next matrix product takes. All sums are float32.
+#include "common.cuh"
+
+using namespace akas;
+
+// out[n, :] = float(table[token[n], :])
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                 float* __restrict__ out, int C) {
+  const int n = blockIdx.x;
+  const T* row = table + (size_t)tokens[n] * C;
+  float* dst = out + (size_t)n * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) dst[c] = to_f32(row[c]);
+}
+
+AKAS_API int akas_embedding(const int* tokens, const void* table, float* out, int N, int C, int dtype,
+                            cudaStream_t stream) {
+  if (N <= 0) return 0;
+  const int threads = C >= 1024 ? 256 : 128;
+  if (dtype == AKAS_F32)
+    embedding_kernel<float><<<N, threads, 0, stream>>>(tokens, (const float*)table, out, C);
+  else
+    embedding_kernel<bf16><<<N, threads, 0, stream>>>(tokens, (const bf16*)table, out, C);
+  return launch_status();
+}
+
+// y[i, :] = x[row(i), :] * rsqrt(mean(x^2) + eps) * (w or 1 + w); row(i) = rows[i] if rows else i.
+// One block per row; the row is read twice (the second read hits L1/L2).
+template <typename TI, typename TO>
+__global__ void rmsnorm_kernel(const TI* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
+                               const int* __restrict__ rows, int C, float eps, int zero_centered) {
+  __shared__ float scratch[32];
+  const int i = blockIdx.x;
+  const TI* src = x + (size_t)(rows ? rows[i] : i) * C;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float v = to_f32(src[c]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)C + eps);
+  TO* dst = y + (size_t)i * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float g = zero_centered ? 1.f + w[c] : w[c];
+    dst[c] = from_f32<TO>(to_f32(src[c]) * inv * g);
+  }
+}
+
+AKAS_API int akas_rmsnorm(const void* x, const float* w, void* y, const int* rows, int M, int C, float eps,
+                          int zero_centered, int in_dtype, int out_dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  const int threads = C >= 2048 ? 512 : C >= 512 ? 256 : 128;
+#define AKAS_NORM(TI, TO) \
+  rmsnorm_kernel<TI, TO><<<M, threads, 0, stream>>>((const TI*)x, w, (TO*)y, rows, C, eps, zero_centered)
+  if (in_dtype == AKAS_F32 && out_dtype == AKAS_F32) AKAS_NORM(float, float);
+  else if (in_dtype == AKAS_F32) AKAS_NORM(float, bf16);
+  else if (out_dtype == AKAS_F32) AKAS_NORM(bf16, float);
+  else AKAS_NORM(bf16, bf16);
+#undef AKAS_NORM
+  return launch_status();
+}
+
+// out[n, f] = silu(gu[n, f]) * gu[n, F + f], silu(g) = g / (1 + exp(-g)), in float32
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t n = i / F;
+  const int f = (int)(i - n * F);
+  const float g = to_f32(gu[n * 2 * F + f]);
+  const float u = to_f32(gu[n * 2 * F + F + f]);
+  out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+}
+
+AKAS_API int akas_swiglu(const void* gu, void* out, int N, int F, int dtype, cudaStream_t stream) {
+  const size_t total = (size_t)N * F;
+  if (total == 0) return 0;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  if (dtype == AKAS_F32)
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, F, total);
+  else
+    swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, F, total);
+  return launch_status();
+}
+
+// state[slot, :] = 0 for one slot of a [slots, row] float32 tensor
+__global__ void zero_row_kernel(float* __restrict__ state, size_t row, int slot) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < row) state[(size_t)slot * row + i] = 0.f;
+}
+
+AKAS_API int akas_zero_row(float* state, long long row_elems, int slot, cudaStream_t stream) {
+  if (row_elems <= 0) return 0;
+  const int threads = 256;
+  zero_row_kernel<<<(unsigned)((row_elems + threads - 1) / threads), threads, 0, stream>>>(state, (size_t)row_elems, slot);
+  return launch_status();
+}

@@ -1,0 +1,168 @@
+// Sampling from float32 logits [M, V]: greedy, and temperature with optional top-k and top-p.
+//
+// argmax: ties go to the lowest index (kreasof-ai/akas, src/akas/ops/vocabulary/kernel.py:146-150).
+//
+// sample, per row with temperature T, top_k k, top_p p and a uniform u in [0, 1) from the caller:
+//   T <= 0: the argmax. Else w_i = exp((x_i - max x) / T) and token i is kept iff
+//     fewer than k tokens have a larger logit (k <= 0 or k >= V: no limit; ties stay together), and
+//     the kept tokens with a larger logit hold at most p of the kept mass (p >= 1: no limit);
+//   the result is the first kept i, in index order, whose running kept mass exceeds u * (kept mass).
+// The reference's only stochastic sampler (its audio model's `codebook_sample`,
+// src/akas/ops/vocabulary/kernel.py:515-671) has the same stages: top-k, exp((v - peak) / T), a
+// top-p cut on the mass before a token, inverse CDF with a supplied uniform, T <= 0 greedy. Here
+// no sort is needed: both cuts are thresholds on the logit, found by bisection over the ordered
+// bit patterns of float32 with one counting or summing pass over the row per step.
+// One block of 1024 threads per row. Softmax terms and sums are float32.
+#include <math.h>
+
+#include "common.cuh"
+
+using namespace akas;
+
+#define AKAS_SAMPLE_THREADS 1024
+
+__device__ __forceinline__ uint32_t ordered_key(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+
+// (value, index) of the row maximum with the lowest index among equals; every thread gets it.
+__device__ void block_argmax(const float* __restrict__ x, int V, float& best_out, int& idx_out) {
+  __shared__ float vals[32];
+  __shared__ int idxs[32];
+  float best = -INFINITY;
+  int idx = V;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = x[i];
+    if (v > best || idx == V) { best = v; idx = i; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+  }
+  if (lane == 0) { vals[warp] = best; idxs[warp] = idx; }
+  __syncthreads();
+  const int warps = (blockDim.x + 31) >> 5;
+  best = lane < warps ? vals[lane] : -INFINITY;
+  idx = lane < warps ? idxs[lane] : V;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+  }
+  best_out = best;
+  idx_out = idx;
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(AKAS_SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+  float best;
+  int idx;
+  block_argmax(logits + (size_t)blockIdx.x * V, V, best, idx);
+  if (threadIdx.x == 0) out[blockIdx.x] = idx;
+}
+
+AKAS_API int akas_argmax(const float* logits, int* out, int M, int V, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  argmax_kernel<<<M, AKAS_SAMPLE_THREADS, 0, stream>>>(logits, out, V);
+  return launch_status();
+}
+
+__global__ void __launch_bounds__(AKAS_SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
+              int* __restrict__ out, int V) {
+  __shared__ float scratch[32];
+  __shared__ float warp_tot[32];
+  __shared__ int pick, last_kept;
+  const int row = blockIdx.x;
+  const float* x = logits + (size_t)row * V;
+  float top;
+  int top_idx;
+  block_argmax(x, V, top, top_idx);
+  const float T = temperature[row];
+  if (!(T > 0.f)) {
+    if (threadIdx.x == 0) out[row] = top_idx;
+    return;
+  }
+  const float inv_t = 1.f / T;
+  uint32_t thr = 0u;  // keep tokens whose ordered key is >= thr
+
+  const int k = top_k[row];
+  if (k > 0 && k < V) {
+    uint32_t lo = 0u, hi = 0xffffffffu;  // smallest t with count(key > t) < k
+    while (lo < hi) {
+      const uint32_t mid = lo + (hi - lo) / 2u;
+      float c = 0.f;
+      for (int i = threadIdx.x; i < V; i += blockDim.x) c += ordered_key(x[i]) > mid ? 1.f : 0.f;
+      c = block_sum(c, scratch);  // exact: counts stay far below 2^24
+      if (c < (float)k) hi = mid; else lo = mid + 1u;
+    }
+    thr = lo;
+  }
+
+  const float p = top_p[row];
+  if (p < 1.f) {
+    float mass = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x)
+      if (ordered_key(x[i]) >= thr) mass += expf((x[i] - top) * inv_t);
+    mass = block_sum(mass, scratch);
+    const float limit = p * mass;
+    uint32_t lo = thr, hi = 0xffffffffu;  // smallest t >= thr with mass(key > t) <= limit
+    while (lo < hi) {
+      const uint32_t mid = lo + (hi - lo) / 2u;
+      float g = 0.f;
+      for (int i = threadIdx.x; i < V; i += blockDim.x)
+        if (ordered_key(x[i]) > mid) g += expf((x[i] - top) * inv_t);
+      g = block_sum(g, scratch);
+      if (g <= limit) hi = mid; else lo = mid + 1u;
+    }
+    thr = lo;
+  }
+
+  // inverse CDF in index order: thread t owns the contiguous indices [t * chunk, (t + 1) * chunk)
+  const int chunk = (V + blockDim.x - 1) / blockDim.x;
+  const int begin = min(V, (int)threadIdx.x * chunk), end = min(V, begin + chunk);
+  float local = 0.f;
+  int my_last = -1;
+  for (int i = begin; i < end; ++i)
+    if (ordered_key(x[i]) >= thr) { local += expf((x[i] - top) * inv_t); my_last = i; }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (threadIdx.x == 0) { pick = V; last_kept = -1; }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  float before = 0.f, total = 0.f;  // mass of the warps before mine, and of the whole row
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+    if (w < warp) before += warp_tot[w];
+    total += warp_tot[w];
+  }
+  const float target = uniform[row] * total;
+  float run = before + incl - local;
+  for (int i = begin; i < end; ++i) {
+    if (ordered_key(x[i]) >= thr) {
+      run += expf((x[i] - top) * inv_t);
+      if (run > target) { atomicMin(&pick, i); break; }
+    }
+  }
+  if (my_last >= 0) atomicMax(&last_kept, my_last);
+  __syncthreads();
+  if (threadIdx.x == 0) out[row] = pick < V ? pick : last_kept;
+}
+
+AKAS_API int akas_sample(const float* logits, const float* temperature, const int* top_k, const float* top_p,
+                         const float* uniform, int* out, int M, int V, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  sample_kernel<<<M, AKAS_SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_k, top_p, uniform, out, V);
+  return launch_status();
+}

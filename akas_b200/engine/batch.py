@@ -1,0 +1,124 @@
+"""One step's batch: flat arrays that every kernel reads, built on the host and uploaded in one copy.
+
+kreasof-ai/akas uploads a padded rectangle ``rows x chunk`` of one phase with
+``mapping``, ``positions`` and ``lengths`` per row (src/akas/execution/batch.py:21-48)
+and expands per-token positions on the device (src/akas/ops/sequence/kernel.py:289-312).
+Here a step is a flat run of tokens: portions of prompts of some requests beside
+single decoded tokens of others, cut anywhere.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request and the places among them whose logits are wanted."""
+
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepContext:
+    """Device views of the batch plus a few host-known sizes; parts read it, none writes it.
+
+    ``seq_of_token`` is ``-1`` and ``slots`` is ``-1`` for padding (a captured decode
+    step is padded up to its bucket); kernels touch no cache for those.
+    """
+
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor  # int32 [N]
+    positions: torch.Tensor  # int32 [N] absolute position of each token in its request
+    seq_of_token: torch.Tensor  # int32 [N] row of the request in slots / block tables
+    cu_seqlens: torch.Tensor  # int32 [R + 1]
+    slots: torch.Tensor  # int32 [R] state slot of each request
+    logit_rows: torch.Tensor  # int32 [M] flat token index of each wanted row
+    num_logit_rows: int
+    block_tables: List[torch.Tensor]  # per group: int32 [R, max_blocks]
+    max_query_len: int
+    max_context: int  # largest position + 1 in the batch
+    decode_only: bool  # every request brings exactly one token
+    memo: Dict = field(default_factory=dict)  # per-step results shared between layers (rotary tables)
+
+    def block_table(self, group: int) -> torch.Tensor:
+        return self.block_tables[group]
+
+
+class BatchLayout:
+    """Offsets (in int32 elements) of each array inside the staging buffer for a batch of N tokens, R requests."""
+
+    def __init__(self, n: int, r: int, m: int, groups: int, max_blocks: int):
+        self.n, self.r, self.m = n, r, m
+        off = 0
+
+        def take(count):
+            nonlocal off
+            start = off
+            off += (count + 3) // 4 * 4  # keep every array 16-byte aligned
+            return start
+
+        self.token_ids = take(n)
+        self.positions = take(n)
+        self.seq_of_token = take(n)
+        self.cu_seqlens = take(r + 1)
+        self.slots = take(r)
+        self.logit_rows = take(max(m, 1))
+        self.tables = [take(r * max_blocks) for _ in range(groups)]
+        self.size = off
+
+
+def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntry], cache, pad_to: int = 0):
+    """Writes the arrays of ``entries`` into ``host`` (int32) at ``layout``'s offsets.
+
+    ``pad_to``: for a decode-only step, the bucket size; padding tokens get request -1.
+    Returns (max_query_len, max_context).
+    """
+    n, r = layout.n, layout.r
+    tok = host[layout.token_ids : layout.token_ids + n]
+    pos = host[layout.positions : layout.positions + n]
+    seq = host[layout.seq_of_token : layout.seq_of_token + n]
+    cu = host[layout.cu_seqlens : layout.cu_seqlens + r + 1]
+    slots = host[layout.slots : layout.slots + r]
+    rows = host[layout.logit_rows : layout.logit_rows + max(layout.m, 1)]
+    max_blocks = cache.max_blocks
+    at = 0
+    row_at = 0
+    max_q = max_ctx = 0
+    for i, e in enumerate(entries):
+        k = len(e.tokens)
+        start = cache.length(e.request)
+        tok[at : at + k] = e.tokens
+        pos[at : at + k] = np.arange(start, start + k, dtype=np.int32)
+        seq[at : at + k] = i
+        cu[i] = at
+        slots[i] = cache.slot(e.request)
+        for w in e.want:
+            rows[row_at] = at + w
+            row_at += 1
+        for g, offset in enumerate(layout.tables):
+            blocks = cache.blocks(e.request, g)
+            row = host[offset + i * max_blocks : offset + (i + 1) * max_blocks]
+            row[: len(blocks)] = blocks
+            row[len(blocks) :] = -1
+        at += k
+        max_q = max(max_q, k)
+        max_ctx = max(max_ctx, start + k)
+    cu[len(entries)] = at
+    if pad_to:
+        tok[at:n] = 0
+        pos[at:n] = 0
+        seq[at:n] = -1
+        for i in range(len(entries), r):
+            cu[i + 1] = at
+            slots[i] = -1
+            for offset in layout.tables:
+                host[offset + i * max_blocks : offset + (i + 1) * max_blocks] = -1
+    return max_q, max_ctx

@@ -1,0 +1,210 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+``ModelRunner`` owns the model, the cache manager and the staging of a step's
+arrays. ``step`` runs only the tokens it is given, as one batch, from what earlier
+steps left in the cache; it is the only writer of pages and state slots. Generation,
+the scheduler and trace replay all go through it.
+
+kreasof-ai/akas's counterpart is ``Executor`` with ``Batch.prepare/run``
+(src/akas/execution/executor.py:360-374, src/akas/execution/batch.py:21-134): one
+captured CUDA graph per compiled ``rows x chunk`` geometry, prefill and decode in
+separate launches. Here any mix runs eagerly, and steps that only decode replay a
+CUDA graph captured per batch-size bucket (the reference's device for decode
+latency too: src/akas/execution/forward.py:41-45).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.engine import EngineConfig
+from ..config.registry import load_config
+from ..models.decoder import Decoder
+from ..parts.base import Runtime
+from ..weights.loader import load_weights
+from .batch import BatchLayout, StepContext, StepEntry, fill_batch
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+_GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+def default_ops(device: torch.device, dtype: torch.dtype):
+    """The compiled sm_100a kernels. There is no other product path: anything else fails here."""
+    if device.type != "cuda":
+        raise RuntimeError(
+            f"akas_b200 runs on CUDA devices only (got {device}); pass ops=akas_b200.ops.reference "
+            "explicitly to exercise host logic without kernels"
+        )
+    from ..ops import cuda as cuda_ops
+
+    cuda_ops.require(cuda_ops.libraries_for(dtype))
+    return cuda_ops
+
+
+class ModelRunner:
+    def __init__(self, model_dir, config: Optional[EngineConfig] = None, ops=None, model_config=None):
+        self.config = config or EngineConfig()
+        self.device = torch.device(self.config.device)
+        self.dtype = _DTYPES[self.config.dtype]
+        self.ops = ops if ops is not None else default_ops(self.device, self.dtype)
+        self.model_config = model_config if model_config is not None else load_config(model_dir)
+        spec = self.model_config.model_spec()
+        self.runtime = Runtime(self.dtype, self.device, self.ops)
+        self.model = Decoder(spec, self.runtime)
+        self.weight_bytes = load_weights(self.model, model_dir)
+        self.vocab_size = spec.vocab_size
+        self.cache = CacheManager(
+            self.model.cache_specs(), self.config.page_size, self.config.pool_tokens, self.config.max_requests,
+            self.config.context, dtype=self.dtype, device=self.device,
+        )
+        self._host = None  # pinned int32 staging
+        self._dev = None
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self.steps = 0
+        self.launches_hint = 0
+
+    # ------------------------------------------------------------------ requests
+
+    def admit(self, request: Hashable) -> int:
+        return self.cache.admit(request, zero=getattr(self.ops, "zero_rows", None))
+
+    def release(self, request: Hashable) -> None:
+        self.cache.release(request)
+
+    # ------------------------------------------------------------------ staging
+
+    def _staging(self, size: int):
+        if self._host is None or self._host.numel() < size:
+            cap = max(size, 1 << 14)
+            cap = 1 << (cap - 1).bit_length()
+            pinned = self.device.type == "cuda"
+            self._host = torch.empty(cap, dtype=torch.int32, pin_memory=pinned)
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        return self._host, self._dev
+
+    def _context(self, dev: torch.Tensor, lay: BatchLayout, max_q: int, max_ctx: int, decode_only: bool):
+        mb = self.cache.max_blocks
+        return StepContext(
+            num_tokens=lay.n,
+            num_seqs=lay.r,
+            token_ids=dev[lay.token_ids : lay.token_ids + lay.n],
+            positions=dev[lay.positions : lay.positions + lay.n],
+            seq_of_token=dev[lay.seq_of_token : lay.seq_of_token + lay.n],
+            cu_seqlens=dev[lay.cu_seqlens : lay.cu_seqlens + lay.r + 1],
+            slots=dev[lay.slots : lay.slots + lay.r],
+            logit_rows=dev[lay.logit_rows : lay.logit_rows + lay.m],
+            num_logit_rows=lay.m,
+            block_tables=[dev[o : o + lay.r * mb].view(lay.r, mb) for o in lay.tables],
+            max_query_len=max_q,
+            max_context=max_ctx,
+            decode_only=decode_only,
+        )
+
+    # ------------------------------------------------------------------ the step
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs one batch. Returns float32 logits ``[sum(len(e.want)), vocab]`` on the device, in the
+        order of the entries and of their ``want``. Unknown requests are admitted; pages are taken
+        first (``OutOfPages`` leaves the cache as it was before the step, but for pages already
+        reserved, which stay with their requests)."""
+        entries = [e for e in entries if len(e.tokens)]
+        if not entries:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        seen = set()
+        for e in entries:
+            if e.request in seen:
+                raise ValueError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
+            if bad:
+                raise ValueError(f"request {e.request!r}: token ids {bad[:4]} outside [0, {self.vocab_size})")
+            if any(not 0 <= w < len(e.tokens) for w in e.want):
+                raise ValueError(f"request {e.request!r}: wanted places {list(e.want)} outside its {len(e.tokens)} tokens")
+            if e.request not in self.cache:
+                self.admit(e.request)
+        for e in entries:
+            self.cache.reserve(e.request, len(e.tokens))
+
+        decode_only = all(len(e.tokens) == 1 for e in entries)
+        all_wanted = all(list(e.want) == [0] for e in entries)
+        if decode_only and all_wanted and self.config.cuda_graphs and self.device.type == "cuda":
+            logits = self._decode_graph_step(entries)
+        else:
+            n = sum(len(e.tokens) for e in entries)
+            m = sum(len(e.want) for e in entries)
+            lay = BatchLayout(n, len(entries), m, len(self.cache.groups), self.cache.max_blocks)
+            host, dev = self._staging(lay.size)
+            max_q, max_ctx = fill_batch(host.numpy(), lay, entries, self.cache)
+            dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
+            ctx = self._context(dev, lay, max_q, max_ctx, decode_only)
+            logits = self.model.forward(ctx, self.cache.views)
+        for e in entries:
+            self.cache.advance(e.request, len(e.tokens))
+        self.steps += 1
+        return logits
+
+    # ------------------------------------------------------------------ captured decode
+
+    def _decode_graph_step(self, entries):
+        count = len(entries)
+        bucket = next((b for b in _GRAPH_BUCKETS if b >= count), None)
+        if bucket is None:
+            bucket = -(-count // 64) * 64
+        graph = self._graphs.get(bucket)
+        if graph is None:
+            graph = self._graphs[bucket] = _DecodeGraph(self, bucket)
+        return graph.run(entries)
+
+
+class _DecodeGraph:
+    """One captured decode step for ``bucket`` requests of one token each.
+
+    The batch arrays live at fixed addresses; a replay copies the step's arrays in
+    and launches the graph. Requests short of the bucket are padding (request -1).
+    Launch shapes inside depend on the bucket only; lengths are read on the device.
+    """
+
+    def __init__(self, runner: ModelRunner, bucket: int):
+        self.runner = runner
+        self.bucket = bucket
+        cache = runner.cache
+        self.layout = BatchLayout(bucket, bucket, bucket, len(cache.groups), cache.max_blocks)
+        self.host = torch.empty(self.layout.size, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.zeros(self.layout.size, dtype=torch.int32, device=runner.device)
+        self.graph = None
+        self.logits = None
+
+    def _fill(self, entries):
+        fill_batch(self.host.numpy(), self.layout, entries, self.runner.cache, pad_to=self.bucket)
+        rows = self.host.numpy()[self.layout.logit_rows : self.layout.logit_rows + self.bucket]
+        rows[:] = np.arange(self.bucket, dtype=np.int32)
+        self.dev.copy_(self.host, non_blocking=True)
+
+    def run(self, entries):
+        runner = self.runner
+        if self.graph is None:
+            # Warm-up and capture run on a batch of padding only: they must leave pages and state alone.
+            # The context's host-side sizes are upper bounds so that the captured launches fit every replay.
+            self._fill([])
+            ctx = runner._context(self.dev, self.layout, 1, runner.config.context, True)
+            ctx.memo["captured"] = True
+            stream = torch.cuda.Stream(device=runner.device)
+            stream.wait_stream(torch.cuda.current_stream(runner.device))
+            with torch.cuda.stream(stream):
+                for _ in range(2):  # warm up: library handles, heuristics and workspaces before capture
+                    ctx.memo = {"captured": True}
+                    runner.model.forward(ctx, runner.cache.views)
+            torch.cuda.current_stream(runner.device).wait_stream(stream)
+            torch.cuda.synchronize(runner.device)
+            graph = torch.cuda.CUDAGraph()
+            ctx.memo = {"captured": True}
+            with torch.cuda.graph(graph):
+                self.logits = runner.model.forward(ctx, runner.cache.views)
+            self.graph = graph
+        self._fill(entries)
+        self.graph.replay()
+        return self.logits[: len(entries)]

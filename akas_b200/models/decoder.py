@@ -1,0 +1,77 @@
+"""The generic decoder that every registered architecture is built as.
+
+Embedding, the blocks of ``ModelSpec.layers`` in the order of ``ModelSpec.schedule``
+(a list that may name a layer twice or let an entry read another entry's cache),
+the final norm on the rows whose logits are wanted, and the head (the checkpoint's
+head tensor when it has one, else the embedding:
+src/akas/models/lfm2/weights.py:399-402 and _composition.py:363-380 in kreasof-ai/akas).
+It holds weights and computes; caches belong to the cache manager and reach the
+blocks through ``caches[entry]``.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from ..config.specs import ModelSpec
+from ..parts.base import Param, Runtime, build_part
+from ..parts.block import Block
+
+
+class Decoder:
+    def __init__(self, spec: ModelSpec, runtime: Runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.blocks: List[Block] = [Block(layer, runtime) for layer in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, runtime)
+        self.schedule = spec.run_order()
+        for i, entry in enumerate(self.schedule):
+            if not 0 <= entry.layer < len(self.blocks):
+                raise ValueError(f"schedule entry {i} names layer {entry.layer}; there are {len(self.blocks)}")
+            if entry.cache is not None:
+                owner = self.schedule[entry.cache] if 0 <= entry.cache < i else None
+                if owner is None or owner.cache is not None:
+                    raise ValueError(f"schedule entry {i} reads cache {entry.cache}, which is no earlier owning entry")
+        self.embedding = None
+        self.head = None
+
+    # ------------------------------------------------------------------ weights
+
+    def params(self) -> Dict[str, Param]:
+        s = self.spec
+        out = {s.embedding_name: Param((s.vocab_size, s.hidden_size))}
+        (norm_param,) = self.final_norm.params().values()
+        out[s.final_norm_name] = norm_param
+        if s.head_name is not None:
+            out[s.head_name] = Param((s.vocab_size, s.hidden_size), optional=s.head_optional)
+        for block in self.blocks:
+            out.update(block.params())
+        return out
+
+    def load(self, get: Callable[[str], torch.Tensor], has: Callable[[str], bool] = lambda name: True) -> None:
+        s = self.spec
+        self.embedding = get(s.embedding_name)
+        self.final_norm.load(lambda _name: get(s.final_norm_name))
+        self.head = get(s.head_name) if s.head_name is not None and has(s.head_name) else self.embedding
+        for block in self.blocks:
+            block.load(get)
+
+    # ------------------------------------------------------------------ compute
+
+    def cache_specs(self):
+        """For each schedule entry that owns a cache: what its mixer needs (or None)."""
+        return [self.blocks[e.layer].mixer.cache() if e.cache is None else None for e in self.schedule]
+
+    def forward(self, ctx, caches) -> torch.Tensor:
+        """Runs the tokens of ``ctx`` and returns float32 logits ``[len(ctx.logit_rows), vocab]``."""
+        ops = self.rt.ops
+        h = ops.embedding(ctx.token_ids, self.embedding)
+        for i, entry in enumerate(self.schedule):
+            owner = i if entry.cache is None else entry.cache
+            h = self.blocks[entry.layer].forward(h, ctx, caches[owner], write=entry.cache is None)
+        if ctx.num_logit_rows == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
+        x = self.final_norm.forward(h, rows=ctx.logit_rows)
+        return ops.linear(x, self.head, out_dtype=torch.float32)

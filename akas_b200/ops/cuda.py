@@ -1,0 +1,318 @@
+"""The compiled sm_100a kernels behind the signatures that the parts call.
+
+Every function takes torch CUDA tensors, allocates its output with torch, and
+launches the kernel of ``akas_b200/csrc`` on torch's current stream through the
+library's C entry point. ``akas_b200.ops.reference`` states the same functions in
+plain PyTorch. A missing compiler, a failed build or a launch error raises; there
+is no other path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Iterable, Optional
+
+import torch
+
+from . import build
+
+name = "cuda-sm100a"
+
+_F32, _BF16 = 0, 1
+_CODE = {torch.float32: _F32, torch.bfloat16: _BF16}
+_WORKSPACE_BYTES = 64 << 20
+_workspaces = {}
+launch_count = 0  # kernels launched through this module since import (library products count as one)
+
+_SIGNATURES = {
+    "elementwise": {
+        "akas_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+        "akas_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_zero_row": [c_void_p, c_longlong, c_int, c_void_p],
+    },
+    "conv": {
+        "akas_short_conv": [c_void_p] * 8 + [c_int] * 5 + [c_void_p],
+    },
+    "rope": {
+        "akas_rope_tables": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "akas_qk_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int,
+                                    c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                    c_int, c_int, c_int, c_void_p],
+        "akas_kv_store": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                          c_int, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "attention": {
+        "akas_paged_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_paged_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, c_void_p],
+    },
+    "sgemm": {
+        "akas_sgemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    },
+    "gemm_bf16": {
+        "akas_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
+                           c_void_p],
+    },
+    "sampling": {
+        "akas_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "akas_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    },
+}
+
+_functions = {}
+
+
+def libraries_for(dtype: torch.dtype) -> list:
+    """The kernel files a model of this compute dtype needs."""
+    names = ["elementwise", "conv", "rope", "attention", "sampling"]
+    names.append("sgemm" if dtype == torch.float32 else "gemm_bf16")
+    return names
+
+
+def require(names: Optional[Iterable[str]] = None) -> None:
+    """Builds (if need be) and loads the named kernel files, or all of them; raises if that fails."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device: akas_b200's kernels run on an NVIDIA B200 (sm_100a) only")
+    names = list(names) if names is not None else list(_SIGNATURES)
+    build.ensure_built(names)
+    for n in names:
+        _bind(n)
+
+
+def _bind(lib_name: str) -> None:
+    lib = build.library(lib_name)
+    for fn_name, argtypes in _SIGNATURES[lib_name].items():
+        if fn_name not in _functions:
+            fn = getattr(lib, fn_name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+            _functions[fn_name] = fn
+
+
+def _fn(lib_name: str, fn_name: str):
+    fn = _functions.get(fn_name)
+    if fn is None:
+        _bind(lib_name)
+        fn = _functions[fn_name]
+    return fn
+
+
+def _check(err: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if err:
+        if err >= 2000:
+            detail = f"cuBLASLt found no algorithm (status {err - 2000})"
+        elif err >= 1000:
+            detail = f"cuBLAS status {err - 1000}"
+        else:
+            detail = f"CUDA error {err}"
+        raise RuntimeError(f"{what} failed: {detail}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _CODE[t.dtype]
+    except KeyError:
+        raise TypeError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}") from None
+
+
+def _dense(t: torch.Tensor, what: str) -> torch.Tensor:
+    if not t.is_contiguous():
+        raise ValueError(f"{what} must be contiguous")
+    return t
+
+
+# --------------------------------------------------------------------------- elementwise
+
+
+def embedding(token_ids, table):
+    n, c = token_ids.numel(), table.shape[1]
+    out = torch.empty((n, c), dtype=torch.float32, device=table.device)
+    _check(_fn("elementwise", "akas_embedding")(_ptr(token_ids), _ptr(_dense(table, "table")), _ptr(out), n, c,
+                                               _code(table), _stream()), "embedding")
+    return out
+
+
+def rmsnorm(x, weight, eps, zero_centered, out_dtype, rows=None):
+    c = x.shape[-1]
+    _dense(x, "x")
+    lead = x.shape[:-1]
+    m = rows.numel() if rows is not None else x.numel() // c
+    out_shape = (m, c) if rows is not None else (*lead, c)
+    out = torch.empty(out_shape, dtype=out_dtype, device=x.device)
+    _check(_fn("elementwise", "akas_rmsnorm")(_ptr(x), _ptr(weight), _ptr(out), _ptr(rows), m, c, float(eps),
+                                             int(bool(zero_centered)), _code(x), _CODE[out_dtype], _stream()),
+           "rmsnorm")
+    return out
+
+
+def swiglu(gate_up):
+    n, f2 = gate_up.shape
+    out = torch.empty((n, f2 // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _check(_fn("elementwise", "akas_swiglu")(_ptr(_dense(gate_up, "gate_up")), _ptr(out), n, f2 // 2, _code(gate_up),
+                                            _stream()), "swiglu")
+    return out
+
+
+def zero_rows(state, slot):
+    row = state[0].numel()
+    if state.dtype != torch.float32:
+        state[slot].zero_()
+        return
+    _check(_fn("elementwise", "akas_zero_row")(_ptr(state), row, int(slot), _stream()), "zero_rows")
+
+
+# --------------------------------------------------------------------------- matrix products
+
+
+def _workspace(device):
+    ws = _workspaces.get(device)
+    if ws is None:
+        ws = _workspaces[device] = torch.empty(_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+    return ws
+
+
+def linear(x, w, out_dtype=None, residual=None):
+    """x [N, K] times w [O, K] transposed. With ``residual`` (float32 [N, O]) the product is added into it."""
+    n, k = x.shape
+    o = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError(f"linear: x has {k} columns, w has {w.shape[1]}")
+    _dense(x, "x")
+    _dense(w, "w")
+    if x.dtype != w.dtype:
+        raise TypeError(f"linear: x is {x.dtype}, w is {w.dtype}")
+    if residual is not None:
+        if residual.dtype != torch.float32 or residual.shape != (n, o) or not residual.is_contiguous():
+            raise ValueError("linear: residual must be contiguous float32 [N, O]")
+    if x.dtype == torch.float32:
+        out = residual if residual is not None else torch.empty((n, o), dtype=torch.float32, device=x.device)
+        _check(_fn("sgemm", "akas_sgemm")(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), n, o, k, _stream()), "sgemm")
+        if residual is None and out_dtype not in (None, torch.float32):
+            out = out.to(out_dtype)
+        return out
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"linear takes float32 or bfloat16, got {x.dtype}")
+    if k % 8:
+        raise ValueError(f"bfloat16 matrix products need an inner size that is a multiple of 8, got {k}")
+    if residual is not None:
+        out, out_f32, acc = residual, 1, 1
+    else:
+        target = out_dtype or torch.bfloat16
+        out = torch.empty((n, o), dtype=target, device=x.device)
+        out_f32, acc = int(target == torch.float32), 0
+    ws = _workspace(x.device)
+    _check(_fn("gemm_bf16", "akas_gemm_bf16")(_ptr(x), _ptr(w), _ptr(out), n, o, k, out_f32, acc, _ptr(ws),
+                                             ws.numel(), _stream()), f"bfloat16 product [{n}x{k}] x [{o}x{k}]^T")
+    return out
+
+
+# --------------------------------------------------------------------------- mixers
+
+
+def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots):
+    n, c3 = bcx.shape
+    c, l = c3 // 3, taps.shape[1]
+    out = torch.empty((n, c), dtype=bcx.dtype, device=bcx.device)
+    _check(_fn("conv", "akas_short_conv")(_ptr(_dense(bcx, "bcx")), _ptr(taps), _ptr(bias), _ptr(state),
+                                         _ptr(cu_seqlens), _ptr(seq_of_token), _ptr(slots), _ptr(out), n,
+                                         slots.numel(), c, l, _code(bcx), _stream()), "short_conv")
+    return out
+
+
+def rope_tables(positions, inv_freq):
+    n, half = positions.numel(), inv_freq.numel()
+    cos = torch.empty((n, half), dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    _check(_fn("rope", "akas_rope_tables")(_ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), n, half, _stream()),
+           "rope_tables")
+    return cos, sin
+
+
+def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_weight, k_weight, eps, zero_centered, cos, sin,
+                       k_pool, v_pool, block_table, seq_of_token, positions, page_size):
+    n = qkv.shape[0]
+    _dense(qkv, "qkv")
+    if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+        raise ValueError("qkv width does not match (heads + 2 kv_heads) * head_dim")
+    q = torch.empty((n, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    rotary = 2 * cos.shape[1] if cos is not None else 0
+    _check(_fn("rope", "akas_qk_norm_rope_store")(
+        _ptr(qkv), _ptr(q), _ptr(q_weight), _ptr(k_weight), float(eps), int(bool(zero_centered)), _ptr(cos), _ptr(sin),
+        rotary, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
+        _ptr(positions), page_size, n, heads, kv_heads, head_dim, _code(qkv), _stream()), "qk_norm_rope_store")
+    return q
+
+
+def kv_store(k, v, k_pool, v_pool, block_table, seq_of_token, positions, page_size):
+    n = k.shape[0]
+    kh, d = k_pool.shape[1], k_pool.shape[3]
+    if k.stride(1) != 1 or v.stride(1) != 1 or k.stride(0) != v.stride(0):
+        raise ValueError("kv_store: k and v must be rows of one buffer with unit inner stride")
+    _check(_fn("rope", "akas_kv_store")(_ptr(k), _ptr(v), k.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                       block_table.shape[1], _ptr(seq_of_token), _ptr(positions), page_size, n, kh, d,
+                                       _code(k_pool), _stream()), "kv_store")
+
+
+def decode_splits(num_tokens: int, kv_heads: int, head_tiles: int, max_context: int) -> int:
+    """How many parts the keys of a decoding request are cut into, from sizes known on the host."""
+    blocks = max(1, num_tokens * kv_heads * head_tiles)
+    want = -(-2 * 148 // blocks)  # about two blocks per SM
+    most = max(1, -(-max_context // 256))  # at least 256 keys per part
+    return max(1, min(want, most, 64))
+
+
+def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, page_size, ctx=None):
+    n = q.shape[0]
+    kh, d = k_pool.shape[1], k_pool.shape[3]
+    heads = q.shape[1] // d
+    _dense(q, "q")
+    out = torch.empty_like(q)
+    win = int(window) if window else 0
+    if ctx is not None and ctx.decode_only:
+        group = heads // kh
+        gt = 8 if group >= 8 else 4 if group > 2 else group
+        splits = decode_splits(n, kh, -(-group // gt), win if win else ctx.max_context)
+        part_o = torch.empty((n, heads, splits, d), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
+        _check(_fn("attention", "akas_paged_attention_decode")(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
+            _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
+            splits, _code(q), _stream()), "paged_attention_decode")
+        return out
+    _check(_fn("attention", "akas_paged_attention")(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
+        _ptr(positions), _ptr(out), float(scale), win, page_size, n, heads, kh, d, _code(q), _stream()),
+        "paged_attention")
+    return out
+
+
+# --------------------------------------------------------------------------- sampling
+
+
+def argmax(logits):
+    m, v = logits.shape
+    out = torch.empty((m,), dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "akas_argmax")(_ptr(_dense(logits, "logits")), _ptr(out), m, v, _stream()), "argmax")
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, uniform):
+    m, v = logits.shape
+    out = torch.empty((m,), dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "akas_sample")(_ptr(_dense(logits, "logits")), _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                                         _ptr(uniform), _ptr(out), m, v, _stream()), "sample")
+    return out

@@ -1,0 +1,138 @@
+"""What every part is, and the registries that map a spec's ``kind`` to a part.
+
+A part is a mixer, a feed-forward, a norm or a position encoding. It is built
+from its spec alone (``Part(spec, runtime)``), says which tensors it wants
+(``params()``), takes them (``load()``), and computes (``forward()``). No part
+knows which model it is in: names of checkpoint tensors reach it through the
+prefix that the block passes, and sizes through its spec.
+
+Interfaces (duck-typed; these base classes only document and give defaults):
+
+* Norm: ``params()``, ``load(get)``, ``forward(x, out_dtype=None, rows=None)``.
+* PositionEncoding: ``prepare(ctx)`` once per step, ``tables(ctx)`` -> (cos, sin)
+  for the fused rotary kernel, or ``apply(q, k, ctx)`` for any other encoding.
+* Mixer: ``params()``, ``load(get)``, ``cache()`` -> the cache it needs (a
+  ``PagedKVSpec``, a ``StateSpec`` or ``None``), ``forward(x, ctx, cache, residual,
+  write)``.
+* FeedForward: ``params()``, ``load(get)``, ``forward(x, ctx, residual)``.
+
+``forward`` of a mixer or feed-forward gets the normed activations ``x`` ``[N, C]``
+in the compute dtype and, when ``residual`` is given (float32 ``[N, C]``), returns
+``residual + result`` in float32 (it may add in place; the fused kernels do).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class Param:
+    """A tensor a part wants from the checkpoint.
+
+    ``role`` decides the dtype it is held in: a ``"matrix"`` is an operand of a
+    matrix product and takes the compute dtype; a ``"vector"`` (norm weights,
+    convolution taps, biases) is held in float32; ``"table"`` is an integer table
+    held in int32. ``optional`` tensors may be absent from the checkpoint. ``mean``
+    is the mean that the random-weights mode draws the tensor around (1 for norm
+    weights).
+    """
+
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+    optional: bool = False
+    mean: float = 0.0
+
+
+@dataclass(frozen=True)
+class PagedKVSpec:
+    """Keys and values of every position (or of the last ``window``), in pages."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size: one row of ``shape`` per request slot, zero at admission."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class Runtime:
+    """What a part needs to know about where it runs: compute dtype, device, kernels."""
+
+    dtype: torch.dtype
+    device: torch.device
+    ops: Any
+
+
+class Part:
+    def __init__(self, spec, runtime: Runtime):
+        self.spec = spec
+        self.rt = runtime
+
+    def params(self) -> Dict[str, Param]:
+        return {}
+
+    def load(self, get: Callable[[str], torch.Tensor]) -> None:
+        pass
+
+
+class Mixer(Part):
+    def cache(self):
+        return None
+
+    def forward(self, x, ctx, cache=None, residual=None, write=True):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, ctx, residual=None):
+        raise NotImplementedError
+
+
+_REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "ffn": {}, "norm": {}, "position": {}}
+
+
+def _register(family: str, kind: str, cls: type) -> None:
+    _REGISTRIES[family][kind] = cls
+
+
+def register_mixer(kind: str, cls: type) -> None:
+    _register("mixer", kind, cls)
+
+
+def register_ffn(kind: str, cls: type) -> None:
+    _register("ffn", kind, cls)
+
+
+def register_norm(kind: str, cls: type) -> None:
+    _register("norm", kind, cls)
+
+
+def register_position(kind: str, cls: type) -> None:
+    _register("position", kind, cls)
+
+
+def build_part(family: str, spec, runtime: Runtime):
+    """The part that ``spec.kind`` names in the registry of ``family``; ``None`` for a ``None`` spec."""
+    if spec is None:
+        return None
+    table = _REGISTRIES[family]
+    kind = getattr(spec, "kind", None)
+    if kind not in table:
+        raise KeyError(f"no {family} registered for kind {kind!r}; registered: {sorted(table)}")
+    return table[kind](spec, runtime)
+
+
+def renamed(spec, local: str) -> str:
+    """The checkpoint's name for a part's local parameter name (``spec.names`` overrides)."""
+    names = getattr(spec, "names", None) or {}
+    return names.get(local, local)

@@ -1,0 +1,57 @@
+"""LFM2's short-convolution mixer.
+
+BCx = x W_in^T gives, per token, three parts in the order B, C, x. u = B * x;
+s[t] = sum_j hist[j] * w[:, j] + u[t] * w[:, L-1] (+ bias), hist being the previous
+L-1 values of u of this request, oldest first, zero where the request began;
+y = C * s; out = y W_out^T. The state of a request is its last L-1 values of u, in
+float32. kreasof-ai/akas: src/akas/ops/convolution/kernel.py:43-91, and :318-333
+for where a bias is added; the checkpoint's taps are [C, 1, L]
+(src/akas/models/lfm2/weights.py:405-407).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .base import Mixer, Param, StateSpec, register_mixer, renamed
+
+
+class ShortConv(Mixer):
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        if not 2 <= spec.kernel_size <= 16:
+            raise ValueError(f"short-conv kernel_size {spec.kernel_size} must be from 2 to 16")
+        self.w_in = self.w_out = self.taps = self.bias = None
+
+    def _n(self, local):
+        return renamed(self.spec, local)
+
+    def params(self):
+        c, l = self.spec.hidden_size, self.spec.kernel_size
+        p = {
+            self._n("in_proj.weight"): Param((3 * c, c)),
+            self._n("conv.weight"): Param((c, 1, l), role="vector"),
+            self._n("out_proj.weight"): Param((c, c)),
+        }
+        if self.spec.bias:
+            p[self._n("conv.bias")] = Param((c,), role="vector")
+        return p
+
+    def load(self, get):
+        c, l = self.spec.hidden_size, self.spec.kernel_size
+        self.w_in = get(self._n("in_proj.weight"))
+        self.taps = get(self._n("conv.weight")).reshape(c, l).contiguous()
+        self.w_out = get(self._n("out_proj.weight"))
+        self.bias = get(self._n("conv.bias")) if self.spec.bias else None
+
+    def cache(self):
+        return StateSpec((self.spec.kernel_size - 1, self.spec.hidden_size), torch.float32)
+
+    def forward(self, x, ctx, cache=None, residual=None, write=True):
+        ops = self.rt.ops
+        bcx = ops.linear(x, self.w_in)
+        y = ops.short_conv(bcx, self.taps, self.bias, cache.state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots)
+        return ops.linear(y, self.w_out, residual=residual)
+
+
+register_mixer("short_conv", ShortConv)

@@ -1,0 +1,297 @@
+"""Each kernel alone against its plain PyTorch statement, at sizes other than the engine's.
+
+Sizes are chosen to hit tails: widths and vocabularies that are no power of two, head sizes 16 to 256
+in steps of 16, group sizes 1 to 8 and odd ones, pages of 8 to 64, padding tokens, empty requests.
+"""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from akas_b200.ops import cuda, reference
+
+    cuda.require()
+    return cuda, reference
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def _close(a, b, dtype, what=""):
+    tol = 2e-6 if dtype == torch.float32 else 1e-2
+    a, b = a.double(), b.double()
+    scale = max(b.abs().max().item(), 1e-6)
+    err = (a - b).abs().max().item() / scale
+    assert err <= tol, f"{what}: relative error {err:.3g} > {tol}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(ops, dtype):
+    cuda, ref = ops
+    table = _rand((37, 50), dtype, 1)
+    ids = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32, device=DEV)
+    assert torch.equal(cuda.embedding(ids, table), ref.embedding(ids, table))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("c", [16, 48, 100, 2048, 3000])
+def test_rmsnorm(ops, dtype, c):
+    cuda, ref = ops
+    x = _rand((7, c), torch.float32, 2, 3.0)
+    w = _rand((c,), torch.float32, 3) + 1
+    for zero_centered in (False, True):
+        _close(cuda.rmsnorm(x, w, 1e-6, zero_centered, dtype), ref.rmsnorm(x, w, 1e-6, zero_centered, dtype), dtype)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    _close(cuda.rmsnorm(x, w, 1e-5, False, dtype, rows), ref.rmsnorm(x, w, 1e-5, False, dtype, rows), dtype)
+    xt = x.to(dtype)  # input in the compute dtype too
+    _close(cuda.rmsnorm(xt, w, 1e-5, False, dtype), ref.rmsnorm(xt, w, 1e-5, False, dtype), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(ops, dtype):
+    cuda, ref = ops
+    gu = _rand((5, 2 * 33), dtype, 4, 4.0)
+    _close(cuda.swiglu(gu), ref.swiglu(gu), dtype)
+
+
+@pytest.mark.parametrize("n,k,o", [(1, 64, 50), (17, 100, 37), (70, 52, 130), (200, 96, 192), (3, 50, 9), (129, 257, 65)])
+def test_linear_float32(ops, n, k, o):
+    cuda, ref = ops
+    x, w = _rand((n, k), torch.float32, 5), _rand((o, k), torch.float32, 6)
+    want = x.double() @ w.double().T
+    _close(cuda.linear(x, w), want, torch.float32, "product")
+    res = _rand((n, o), torch.float32, 7)
+    got = cuda.linear(x, w, residual=res.clone())
+    _close(got, res.double() + want, torch.float32, "product + residual")
+
+
+def test_linear_float32_rows_do_not_depend_on_the_batch(ops):
+    cuda, _ = ops
+    x, w = _rand((300, 96), torch.float32, 8), _rand((130, 96), torch.float32, 9)
+    whole = cuda.linear(x, w)
+    for rows in (slice(0, 1), slice(5, 22), slice(100, 164), slice(299, 300)):
+        assert torch.equal(cuda.linear(x[rows].contiguous(), w), whole[rows])
+
+
+@pytest.mark.parametrize("n,k,o", [(1, 64, 50), (17, 104, 37), (70, 56, 130), (300, 96, 192), (8, 2048, 321)])
+def test_linear_bfloat16(ops, n, k, o):
+    cuda, ref = ops
+    x, w = _rand((n, k), torch.bfloat16, 5), _rand((o, k), torch.bfloat16, 6)
+    want = x.double() @ w.double().T
+    _close(cuda.linear(x, w), want, torch.bfloat16, "bf16 out")
+    _close(cuda.linear(x, w, out_dtype=torch.float32), want, torch.float32, "f32 out")
+    res = _rand((n, o), torch.float32, 7)
+    _close(cuda.linear(x, w, residual=res.clone()), res.double() + want, torch.float32, "accumulate")
+    with pytest.raises(ValueError):
+        cuda.linear(x[:, :60].contiguous(), w[:, :60].contiguous())
+
+
+def _batch(lengths, pad=0):
+    """cu_seqlens, seq_of_token, for requests of the given lengths, plus ``pad`` padding tokens."""
+    cu = [0]
+    seq = []
+    for r, n in enumerate(lengths):
+        cu.append(cu[-1] + n)
+        seq += [r] * n
+    seq += [-1] * pad
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    return t(cu), t(seq)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("taps,bias", [(2, False), (3, False), (4, True), (7, True)])
+def test_short_conv(ops, dtype, taps, bias):
+    cuda, ref = ops
+    c = 72
+    lengths = [5, 1, 0, 2, 9, 1]
+    cu, seq = _batch(lengths, pad=2)
+    n = sum(lengths) + 2
+    slots = torch.tensor([3, 0, 5, 6, 1, -1], dtype=torch.int32, device=DEV)
+    bcx = _rand((n, 3 * c), dtype, 10)
+    w = _rand((c, taps), torch.float32, 11)
+    b = _rand((c,), torch.float32, 12) if bias else None
+    state = _rand((8, taps - 1, c), torch.float32, 13)
+    s1, s2 = state.clone(), state.clone()
+    got = cuda.short_conv(bcx, w, b, s1, cu, seq, slots)
+    want = ref.short_conv(bcx, w, b, s2, cu, seq, slots)
+    _close(got, want, dtype, "output")
+    _close(s1, s2, torch.float32, "state")
+    for untouched in (2, 4, 5, 7):  # slots of no live request, and of the request with no tokens
+        assert torch.equal(s1[untouched], state[untouched])
+
+
+def test_rope_tables(ops):
+    cuda, ref = ops
+    pos = torch.tensor([0, 1, 77, 4095, 131071], dtype=torch.int32, device=DEV)
+    for theta, rot in ((1e4, 16), (1e6, 64), (5e5, 48)):
+        inv = (torch.tensor(theta, dtype=torch.float64) ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).to(DEV)
+        c1, s1 = cuda.rope_tables(pos, inv)
+        c2, s2 = ref.rope_tables(pos, inv)
+        assert (c1 - c2).abs().max() <= 1.2e-7 and (s1 - s2).abs().max() <= 1.2e-7
+
+
+def _pools(pages, kh, page, d, dtype, seed):
+    return _rand((pages, kh, page, d), dtype, seed), _rand((pages, kh, page, d), dtype, seed + 1)
+
+
+def _tables(contexts, page, pages, seed, max_blocks=None):
+    """A block table whose pages are a random permutation: neighbouring positions lie in far pages."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(pages, generator=g).tolist()
+    need = [-(-c // page) for c in contexts]
+    max_blocks = max_blocks or max(need) + 1
+    bt = torch.full((len(contexts), max_blocks), -1, dtype=torch.int32)
+    for r, n in enumerate(need):
+        for b in range(n):
+            bt[r, b] = perm.pop()
+    return bt.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("h,kh,d,rot,page", [(6, 2, 48, 32, 8), (4, 4, 16, 16, 16), (8, 1, 128, 128, 64), (3, 1, 256, 64, 8)])
+def test_qk_norm_rope_store(ops, dtype, h, kh, d, rot, page):
+    cuda, ref = ops
+    lengths, starts = [3, 1, 6], [5, 40, 0]
+    cu, seq = _batch(lengths, pad=1)
+    pos = torch.tensor([s + j for s, n in zip(starts, lengths) for j in range(n)] + [0], dtype=torch.int32, device=DEV)
+    n = pos.numel()
+    bt = _tables([s + l for s, l in zip(starts, lengths)], page, 40, 3)
+    qkv = _rand((n, (h + 2 * kh) * d), dtype, 20)
+    qw, kw = _rand((d,), torch.float32, 21) + 1, _rand((d,), torch.float32, 22) + 1
+    inv = (torch.tensor(1e4, dtype=torch.float64) ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).to(DEV)
+    cos, sin = ref.rope_tables(pos, inv)
+    for norm, rope in ((True, True), (False, True), (True, False)):
+        k1, v1 = _pools(40, kh, page, d, dtype, 30)
+        k2, v2 = k1.clone(), v1.clone()
+        a, b = qkv.clone(), qkv.clone()
+        args = (h, kh, d, qw if norm else None, kw if norm else None, 1e-5, False, cos if rope else None, sin if rope else None)
+        q1 = cuda.qk_norm_rope_store(a, *args, k1, v1, bt, seq, pos, page)
+        q2 = ref.qk_norm_rope_store(b, *args, k2, v2, bt, seq, pos, page)
+        _close(q1, q2, dtype, "q")
+        _close(a[:-1], b[:-1], dtype, "k in place")
+        _close(k1, k2, dtype, "key pages")
+        assert torch.equal(v1, v2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("h,kh,d,page,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (8, 8, 64, 64, None), (6, 2, 48, 8, 37), (16, 2, 128, 32, None),
+    (5, 1, 80, 16, 100), (32, 8, 64, 64, None), (7, 7, 256, 8, None),
+])
+def test_paged_attention(ops, dtype, h, kh, d, page, window):
+    cuda, ref = ops
+    # a prompt portion that starts mid-page, two decoded tokens with long and short contexts, a first token
+    lengths, starts = [37, 1, 1, 1, 70], [29, 333, 64, 0, 0]
+    cu, seq = _batch(lengths, pad=2)
+    pos = torch.tensor([s + j for s, n in zip(starts, lengths) for j in range(n)] + [0, 0], dtype=torch.int32, device=DEV)
+    contexts = [s + l for s, l in zip(starts, lengths)]
+    pages = sum(-(-c // page) for c in contexts) + 3
+    bt = _tables(contexts, page, pages, 4)
+    k, v = _pools(pages, kh, page, d, dtype, 40)
+    q = _rand((pos.numel(), h * d), dtype, 42)
+    scale = d ** -0.5
+    want = ref.paged_attention(q, k, v, bt, seq, pos, scale, window, page)
+    got = cuda.paged_attention(q, k, v, bt, seq, pos, scale, window, page)
+    _close(got, want, dtype, "mixed batch")
+
+
+class _Decode:
+    decode_only = True
+
+    def __init__(self, max_context):
+        self.max_context = max_context
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("h,kh,d,page,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (32, 8, 64, 64, None), (6, 1, 48, 8, 300), (16, 2, 128, 32, None),
+    (24, 1, 64, 16, None), (5, 5, 256, 64, None),
+])
+def test_paged_attention_decode_split(ops, dtype, h, kh, d, page, window):
+    cuda, ref = ops
+    contexts = [1, 2, 33, 700, 1500, 257]
+    cu, seq = _batch([1] * len(contexts), pad=2)
+    pos = torch.tensor([c - 1 for c in contexts] + [0, 0], dtype=torch.int32, device=DEV)
+    pages = sum(-(-c // page) for c in contexts) + 3
+    bt = _tables(contexts, page, pages, 6)
+    k, v = _pools(pages, kh, page, d, dtype, 50)
+    q = _rand((pos.numel(), h * d), dtype, 52)
+    scale = d ** -0.5
+    want = ref.paged_attention(q, k, v, bt, seq, pos, scale, window, page)
+    got = cuda.paged_attention(q, k, v, bt, seq, pos, scale, window, page, _Decode(max(contexts)))
+    _close(got, want, dtype, "split decode")
+    assert torch.equal(got[-2:], torch.zeros_like(got[-2:]))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(ops, dtype):
+    """One key among a thousand, far back and in a page of its own, is made to dominate: random values
+    would hide a kernel that drops it."""
+    cuda, ref = ops
+    h, kh, d, page = 4, 2, 64, 16
+    ctx, far = 1000, 131
+    cu, seq = _batch([1, 5])
+    pos = torch.tensor([ctx - 1] + list(range(ctx - 5, ctx)), dtype=torch.int32, device=DEV)
+    pages = 2 * (-(-ctx // page)) + 2
+    bt = _tables([ctx, ctx], page, pages, 8)
+    k, v = _pools(pages, kh, page, d, dtype, 60)
+    q = _rand((6, h * d), dtype, 62)
+    for r in range(2):
+        pg, off = int(bt[r, far // page]), far % page
+        for kvh in range(kh):
+            qh = q[0 if r == 0 else 3, kvh * 2 * d : kvh * 2 * d + d].float()
+            k[pg, kvh, off] = (qh / qh.norm() * 40).to(dtype)
+            v[pg, kvh, off] = 7.0
+    scale = d ** -0.5
+    want = ref.paged_attention(q, k, v, bt, seq, pos, scale, None, page)
+    assert want[0, :d].float().mean() > 6  # the far key does dominate
+    _close(cuda.paged_attention(q, k, v, bt, seq, pos, scale, None, page), want, dtype, "generic")
+    one = cuda.paged_attention(q[:1].contiguous(), k, v, bt[:1].contiguous(), seq[:1], pos[:1], scale, None, page, _Decode(ctx))
+    _close(one, want[:1], dtype, "split decode")
+
+
+def test_argmax_ties_go_to_the_lowest_index(ops):
+    cuda, ref = ops
+    x = _rand((5, 1000), torch.float32, 70)
+    x[0, 17] = x[0, 900] = 50.0
+    x[1, 999] = 60.0
+    x[2, 0] = x[2, 1] = 70.0
+    x[3] = 1.0
+    assert cuda.argmax(x).tolist() == ref.argmax(x).tolist() == [17, 999, 0, 0, int(x[4].argmax())]
+    big = _rand((3, 65536 + 3), torch.float32, 71)
+    assert cuda.argmax(big).tolist() == big.argmax(dim=-1).tolist()
+
+
+def test_sample(ops):
+    cuda, ref = ops
+    v = 777
+    logits = _rand((6, v), torch.float32, 80, 2.0)
+    t = lambda vals, dt: torch.tensor(vals, dtype=dt, device=DEV)
+    temp = t([0.0, 1.0, 0.7, 1.3, 1.0, 1.0], torch.float32)
+    top_k = t([0, 0, 5, 0, 1, 50], torch.int32)
+    top_p = t([1.0, 1.0, 1.0, 0.6, 1.0, 0.9], torch.float32)
+    for seed in range(20):
+        u = torch.rand(6, generator=torch.Generator().manual_seed(seed)).to(DEV)
+        got, want = cuda.sample(logits, temp, top_k, top_p, u), ref.sample(logits, temp, top_k, top_p, u)
+        assert got.tolist() == want.tolist(), (seed, got.tolist(), want.tolist())
+    assert cuda.sample(logits, temp, top_k, top_p, u)[0] == logits[0].argmax()
+    assert cuda.sample(logits, temp, top_k, top_p, u)[4] == logits[4].argmax()
+    # frequencies follow softmax(logits / T)
+    small = torch.tensor([[0.0, 1.0, 2.0, -1.0]], device=DEV).repeat(4096, 1)
+    u = torch.rand(4096, generator=torch.Generator().manual_seed(1)).to(DEV)
+    ones = torch.ones(4096, device=DEV)
+    picks = cuda.sample(small, ones * 0.8, torch.zeros(4096, dtype=torch.int32, device=DEV), ones, u)
+    freq = torch.bincount(picks.long(), minlength=4).float() / 4096
+    want = torch.softmax(small[0] / 0.8, dim=-1)
+    assert (freq - want).abs().max() < 0.03

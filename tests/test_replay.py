@@ -1,0 +1,94 @@
+"""The step function against the plain implementation, under every way of cutting and batching.
+
+The same tests run twice: on a CPU with the plain PyTorch statements of the kernels (they check the
+host logic: batches, pages, slots), and, marked ``gpu``, with the compiled kernels in float32 and in
+bfloat16. Tolerances are fixed: float32 results agree with the float64 plain model to rounding;
+bfloat16 results carry the rounding of activations to 8 bits of mantissa between kernels.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as plain
+import tiny
+import traces
+
+# largest |difference| over largest |reference logit|, per dtype
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+LENGTHS = {"a": [1, 40, 33, 70, 17, 100, 64, 129], "b": [70, 1, 5, 96, 48, 130, 9]}
+
+
+def _runner(folder, dtype, device, page, max_tokens, ops=None, max_requests=4, context=None):
+    from akas_b200.config import EngineConfig
+    from akas_b200.engine.runner import ModelRunner
+
+    cfg = EngineConfig(dtype=dtype, device=device, page_size=page, max_tokens=max_tokens, max_requests=max_requests,
+                       context=context or max_tokens, cuda_graphs=False)
+    return ModelRunner(folder, cfg, ops=ops)
+
+
+def _setup(key, dtype, tmp_path):
+    folder = tiny.make_folder(tiny.CONFIGS[key], seed=11 if key == "a" else 12, dtype=dtype, folder=tmp_path / key)
+    cfg, w = plain.load_folder(folder)
+    reqs = {f"r{i}": p for i, p in enumerate(tiny.prompts(cfg["vocab_size"], LENGTHS[key], seed=5))}
+    want = {rid: plain.forward(cfg, w, toks).numpy() for rid, toks in reqs.items()}
+    return folder, reqs, want
+
+
+def _check(got, want, dtype, what):
+    for rid in want:
+        err, l2 = traces.worst(got[rid], want[rid])
+        bad = traces.first_bad(got[rid], want[rid], TOL[dtype])
+        assert bad is None, f"{what}: request {rid} first differs at position {bad} (max {err:.3g}, L2 {l2:.3g})"
+
+
+def _run_modes(key, dtype, device, ops, tmp_path, modes):
+    folder, reqs, want = _setup(key, dtype, tmp_path)
+    page = tiny.PAGE[key]
+    longest = -(-max(len(t) for t in reqs.values()) // page) * page
+    for mode in modes:
+        if mode == "mixed":
+            prompt_lens = {rid: max(1, len(t) - 9) for rid, t in reqs.items()}
+            steps, peak = traces.mixed(reqs, prompt_lens, seed=3, live=4, page=page)
+            runner = _runner(folder, dtype, device, page, peak, ops, context=longest)
+        else:
+            steps = getattr(traces, mode)(reqs)
+            runner = _runner(folder, dtype, device, page, longest, ops)
+        got = traces.replay(runner, steps)
+        assert not runner.cache.live()
+        assert runner.cache.min_free_pages() == runner.cache.num_pages
+        _check(got, want, dtype, f"{key}/{dtype}/{mode}")
+
+
+MODES = ["whole", "tail_decoded", "portions", "mixed"]
+
+
+@pytest.mark.parametrize("key", ["a", "b"])
+def test_replay_host_logic_on_cpu(key, tmp_path):
+    from akas_b200.ops import reference
+
+    _run_modes(key, "float32", "cpu", reference, tmp_path, MODES)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["a", "b"])
+@pytest.mark.parametrize("mode", MODES)
+def test_replay_gpu(key, dtype, mode, tmp_path):
+    _run_modes(key, dtype, "cuda:0", None, tmp_path, [mode])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_ways_of_cutting_agree_with_each_other(dtype, tmp_path):
+    """Whole, decoded, portioned and mixed runs of the same request differ by rounding only."""
+    folder, reqs, want = _setup("a", dtype, tmp_path)
+    page = tiny.PAGE["a"]
+    longest = -(-max(len(t) for t in reqs.values()) // page) * page
+    base = traces.replay(_runner(folder, dtype, "cuda:0", page, longest), traces.whole(reqs))
+    tol = 5e-6 if dtype == "float32" else TOL[dtype]
+    for mode in ("tail_decoded", "portions"):
+        got = traces.replay(_runner(folder, dtype, "cuda:0", page, longest), getattr(traces, mode)(reqs))
+        for rid in reqs:
+            assert traces.first_bad(got[rid], base[rid], tol) is None, (mode, rid, traces.worst(got[rid], base[rid]))
