@@ -188,6 +188,15 @@ class CacheManager:
         end = req.length + tokens
         return [max(0, -(-end // self.page_size) - len(group.blocks[request])) for group in self.groups]
 
+    def room(self, request) -> int:
+        """How many more tokens of ``request`` could be reserved now: the rest of its last page plus the
+        free pages of the fullest group, and never past the context."""
+        req = self._requests[request]
+        if not self.groups:
+            return self.context - req.length
+        held = min(len(g.blocks[request]) for g in self.groups) * self.page_size
+        return min(max(0, held - req.length) + self.min_free_pages() * self.page_size, self.context - req.length)
+
     def reserve(self, request, tokens: int) -> None:
         """Takes pages in every group for the next ``tokens`` positions; all groups or none."""
         req = self._requests[request]

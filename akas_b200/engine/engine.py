@@ -1,0 +1,149 @@
+"""The request API: submit token ids, step the engine, read what it generated.
+
+``Engine`` has the surface of kreasof-ai/akas's engine (src/akas/engine.py:10-110): ``submit(prompt,
+max_tokens=)`` returns a ``Request`` whose ``output`` grows, ``step()`` runs one scheduler turn and says
+whether work is left, ``cancel``, ``run``, ``close``; requests are validated at submission; the engine
+runs on the thread that made it. ``generate`` is the Python entry point for whole batches of prompts:
+host token ids in, host token ids out.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import replace
+from threading import get_ident
+from typing import List, Optional, Sequence
+
+from ..config.engine import EngineConfig
+from ..sampling.sampler import Sampler
+from .request import Request
+from .runner import ModelRunner
+from .scheduler import Scheduler
+
+
+class Engine:
+    def __init__(self, model, *, config: Optional[EngineConfig] = None, publish=None, ops=None):
+        """``model``: a model folder (config.json + model.safetensors), or a ready ``ModelRunner``."""
+        self.thread = get_ident()
+        if isinstance(model, ModelRunner):
+            self.runner = model
+            self.config = model.config
+        else:
+            self.config = config or EngineConfig()
+            self.runner = ModelRunner(model, self.config, ops=ops)
+        self.sampler = Sampler(self.runner.ops, self.runner.device)
+        self.events = deque()
+        self.closed = False
+        self.scheduler = Scheduler(
+            self.runner.cache,
+            self._execute,
+            publish if publish is not None else self.events.extend,
+            prefill_chunk=self.config.prefill_chunk,
+            prefill_requests=self.config.prefill_requests,
+            prefill_token_budget=self.config.prefill_token_budget,
+            decode_prefill_token_budget=self.config.decode_prefill_token_budget,
+            admit=self.runner.admit,
+        )
+
+    @classmethod
+    def from_checkpoint(cls, checkpoint, *, config: Optional[EngineConfig] = None, publish=None, **options):
+        """Loads the model folder ``checkpoint``; ``options`` override fields of ``config``."""
+        config = replace(config or EngineConfig(), **options)
+        return cls(checkpoint, config=config, publish=publish)
+
+    # ------------------------------------------------------------------ properties of the model
+
+    @property
+    def context(self) -> int:
+        return min(self.config.context, self.runner.cache.num_pages * self.config.page_size)
+
+    @property
+    def capacity(self) -> int:
+        return self.config.max_requests
+
+    @property
+    def stats(self) -> dict:
+        return self.scheduler.stats
+
+    # ------------------------------------------------------------------ requests
+
+    def submit(self, prompt, *, max_tokens, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
+               seed: Optional[int] = None, eos_token_id: Optional[int] = None) -> Request:
+        prompt = list(prompt)
+        vocab = self.runner.vocab_size
+        if not prompt or any(type(t) is not int or t < 0 or t >= vocab for t in prompt):
+            raise ValueError("prompt must contain valid integer token IDs")
+        if type(max_tokens) is not int or max_tokens < 1:
+            raise ValueError("max_tokens must be positive")
+        if len(prompt) + max_tokens > self.context:
+            raise ValueError("generation exceeds context capacity")
+        if not 0.0 < top_p <= 1.0 or top_k < 0 or temperature < 0:
+            raise ValueError("need temperature >= 0, top_k >= 0 and 0 < top_p <= 1")
+        request = Request(prompt, max_tokens, temperature=float(temperature), top_k=int(top_k), top_p=float(top_p),
+                          seed=seed, eos_token_id=eos_token_id)
+        self.scheduler.submit(request)
+        return request
+
+    def _execute(self, entries, requests) -> List[int]:
+        logits = self.runner.step(entries)
+        return self.sampler.sample(logits, requests)
+
+    def _check_thread(self):
+        if get_ident() != self.thread:
+            raise RuntimeError("engine must run on its owner thread")
+
+    def step(self) -> bool:
+        self._check_thread()
+        if self.closed:
+            raise RuntimeError("engine is closed")
+        return self.scheduler.turn()
+
+    def cancel(self, request: Request) -> None:
+        request.cancelled.set()
+
+    def run(self) -> None:
+        self._check_thread()
+        try:
+            self.scheduler.run()
+        finally:
+            self.close()
+
+    def close(self) -> None:
+        self._check_thread()
+        if self.closed:
+            return
+        self.scheduler.stopped.set()
+        self.scheduler.shutdown()
+        self.closed = True
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *error):
+        self.close()
+
+    # ------------------------------------------------------------------ whole batches
+
+    def generate(self, prompts: Sequence[Sequence[int]], *, max_tokens: int = 128, temperature: float = 0.0,
+                 top_k: int = 0, top_p: float = 1.0, seed: Optional[int] = None,
+                 eos_token_id: Optional[int] = None) -> List[dict]:
+        """Generates for every prompt (token ids) and returns, per prompt, what the reference's
+        ``generate`` returns (src/akas/generation/greedy.py:110-114): ``prompt_tokens``,
+        ``generated_tokens`` and ``text`` (``None``: this engine holds no tokenizer), plus ``finish_reason``.
+        A single prompt may be given as a flat list of ids."""
+        single = bool(prompts) and isinstance(prompts[0], int)
+        batch = [prompts] if single else list(prompts)
+        requests = [
+            self.submit(p, max_tokens=max_tokens, temperature=temperature, top_k=top_k, top_p=top_p,
+                        seed=None if seed is None else seed + i, eos_token_id=eos_token_id)
+            for i, p in enumerate(batch)
+        ]
+        while self.step():
+            pass
+        self.events.clear()
+        results = [
+            dict(prompt_tokens=list(r.prompt), generated_tokens=list(r.output), text=None,
+                 finish_reason=r.finish_reason)
+            for r in requests
+        ]
+        return results[0] if single else results

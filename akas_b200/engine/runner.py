@@ -65,7 +65,7 @@ class ModelRunner:
         self._dev = None
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self.steps = 0
-        self.launches_hint = 0
+        self.kernels_per_decode_step: Dict[int, int] = {}  # bucket -> kernels inside its captured graph
 
     # ------------------------------------------------------------------ requests
 
@@ -202,8 +202,10 @@ class _DecodeGraph:
             torch.cuda.synchronize(runner.device)
             graph = torch.cuda.CUDAGraph()
             ctx.memo = {"captured": True}
+            before = getattr(runner.ops, "launch_count", 0)
             with torch.cuda.graph(graph):
                 self.logits = runner.model.forward(ctx, runner.cache.views)
+            runner.kernels_per_decode_step[self.bucket] = getattr(runner.ops, "launch_count", 0) - before
             self.graph = graph
         self._fill(entries)
         self.graph.replay()

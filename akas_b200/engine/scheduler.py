@@ -1,0 +1,254 @@
+"""Continuous admission, portions of prompts under a token budget, decoding, finishing and freeing.
+
+The budgets carry the names and meanings of kreasof-ai/akas's scheduler
+(src/akas/scheduling/scheduler.py:15-52, 112-194): each turn every decoding request gets one token,
+and at most ``prefill_requests`` requests get a portion of their prompt, none more than
+``prefill_chunk`` tokens, all together at most ``prefill_token_budget`` (default chunk x requests)
+and at most ``decode_prefill_token_budget`` while any request decodes. Two things differ.
+The reference launches decode and prefill separately in one turn; here both are one batch of one
+step. And the reference reserves a whole context per slot, so it cannot run out of cache; here pages
+are taken as tokens are written, so they can run out, and what happens then is decided:
+
+* a request is admitted only while a slot is free and the free pages cover its first portion;
+* a portion is shortened to the pages that are free (a request that can get none waits);
+* when a decoding request needs a page and none is free, the most recently admitted request that
+  holds cache is preempted: its pages and slot are given back, and it returns to the front of the
+  waiting queue, to be recomputed from its prompt and the tokens it has generated so far. The
+  oldest request is never preempted, so the engine always makes progress; a request that could not
+  fit in the pool even alone is refused when it is submitted.
+
+The scheduler never touches the device: it plans with the cache manager's host-side counts and
+hands the batch to ``execute(entries, requests) -> tokens``.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from queue import Empty, Queue
+from threading import Event
+from typing import Callable, List, Optional, Sequence
+
+from ..cache.manager import CacheManager, OutOfPages
+from .batch import StepEntry
+from .request import Request
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, execute: Callable, publish: Callable, *, prefill_chunk=2048,
+                 prefill_requests=32, prefill_token_budget=None, decode_prefill_token_budget=None,
+                 admit: Optional[Callable] = None):
+        if prefill_chunk <= 0 or prefill_requests <= 0:
+            raise ValueError("invalid prefill budget")
+        for name, value in (("prefill token budget", prefill_token_budget),
+                            ("decode prefill token budget", decode_prefill_token_budget)):
+            if value is not None and (type(value) is not int or value < 1):
+                raise ValueError(f"{name} must be a positive integer")
+        self.cache = cache
+        self.execute = execute
+        self.publish = publish
+        self.admit_request = admit or cache.admit
+        self.prefill_chunk = prefill_chunk
+        self.prefill_requests = prefill_requests
+        self.prefill_token_budget = prefill_token_budget
+        self.decode_prefill_token_budget = decode_prefill_token_budget
+        self.incoming: Queue = Queue()
+        self.pending: deque = deque()  # waiting for a slot and pages
+        self.running: List[Request] = []  # hold cache, in order of admission
+        self.stopped = Event()
+        self.stats = dict(
+            tokens=0, completed=0, cancelled=0, steps=0, decode_rounds=0, prefill_rounds=0, decode_rows=0,
+            max_active=0, prefill_tokens=0, max_prefill_tokens_per_turn=0, max_prefill_tokens_with_decoding=0,
+            max_tokens_per_step=0, preemptions=0, pages_in_use_max=0,
+        )
+
+    # ------------------------------------------------------------------ requests in and out
+
+    def submit(self, request: Request) -> None:
+        if self.stopped.is_set():
+            raise RuntimeError("scheduler stopped")
+        self.incoming.put(request)
+
+    @property
+    def prefilling(self) -> List[Request]:
+        return [r for r in self.running if r.pending_tokens() > 1]
+
+    @property
+    def decoding(self) -> List[Request]:
+        return [r for r in self.running if r.pending_tokens() == 1]
+
+    def _release(self, request: Request) -> None:
+        if request.slot is not None:
+            self.cache.release(request.id)
+            request.slot = None
+
+    def _finish(self, request: Request, reason: str) -> None:
+        self._release(request)
+        request.finish_reason = reason
+        self.stats["cancelled" if reason == "cancelled" else "completed"] += 1
+
+    def _preempt(self, request: Request) -> None:
+        """Gives back everything ``request`` holds; it will be recomputed from prompt + output."""
+        self._release(request)
+        request.offset = 0
+        request.preemptions += 1
+        self.running.remove(request)
+        self.pending.appendleft(request)
+        self.stats["preemptions"] += 1
+
+    def _event(self, request: Request) -> tuple:
+        finished = request.finished
+        return (request, dict(
+            output_ids=list(request.output),
+            meta_info=dict(
+                prompt_tokens=len(request.prompt),
+                completion_tokens=len(request.output),
+                finish_reason=dict(type=request.finish_reason, length=request.limit) if finished else None,
+            ),
+        ))
+
+    # ------------------------------------------------------------------ one turn
+
+    def plan(self) -> List[tuple]:
+        """Decides this turn's batch: [(request, number of tokens)], decoding requests first.
+
+        Takes the pages the batch needs (so the step cannot run out), preempting if a decoding request
+        would otherwise stall, and admits waiting requests into free slots.
+        """
+        cache = self.cache
+        batch: List[tuple] = []
+        # 1. every decoding request gets its token; make room by preempting the youngest if need be
+        for request in list(self.decoding):
+            if request not in self.running:
+                continue  # preempted a moment ago
+            while True:
+                try:
+                    cache.reserve(request.id, 1)
+                    batch.append((request, 1))
+                    break
+                except OutOfPages as error:
+                    victim = self.running[-1]
+                    if victim is request and len(self.running) == 1:
+                        raise RuntimeError("the page pool cannot hold a single request") from error
+                    if victim is request:
+                        # the youngest itself is the one that stalls: it waits, recomputed later
+                        self._preempt(request)
+                        break
+                    batch = [(r, n) for r, n in batch if r is not victim]
+                    self._preempt(victim)
+        decoding_now = bool(batch)
+        # 2. admission: a slot and pages for a first portion
+        budget = self.prefill_token_budget
+        remaining = budget if budget is not None else self.prefill_chunk * self.prefill_requests
+        if decoding_now and self.decode_prefill_token_budget is not None:
+            remaining = min(remaining, self.decode_prefill_token_budget)
+        while self.pending and cache.free_slots() > 0:
+            request = self.pending[0]
+            if request.cancelled.is_set():
+                self.pending.popleft()
+                self._finish(request, "cancelled")
+                continue
+            first = min(self.prefill_chunk, request.pending_tokens())
+            if -(-first // cache.page_size) > cache.min_free_pages() and self.running:
+                break  # wait until running requests finish and give pages back
+            self.pending.popleft()
+            request.slot = self.admit_request(request.id)
+            self.running.append(request)
+        # 3. portions of prompts, oldest first
+        selected = 0
+        for request in self.prefilling:
+            if selected >= self.prefill_requests or remaining <= 0:
+                break
+            count = min(self.prefill_chunk, remaining, request.pending_tokens())
+            count = min(count, cache.room(request.id))  # shortened to the pages that are free
+            if count <= 0:
+                continue
+            cache.reserve(request.id, count)
+            batch.append((request, count))
+            remaining -= count
+            selected += 1
+        return batch
+
+    def turn(self) -> bool:
+        """One step of the engine. Returns whether any request is still waiting or running."""
+        while True:
+            try:
+                self.pending.append(self.incoming.get_nowait())
+            except Empty:
+                break
+        for request in list(self.running):
+            if request.cancelled.is_set():
+                self.running.remove(request)
+                self._finish(request, "cancelled")
+        batch = self.plan()
+        self.stats["max_active"] = max(self.stats["max_active"], len(self.running))
+        self.stats["pages_in_use_max"] = max(self.stats["pages_in_use_max"], self.cache.peak_pages)
+        if not batch:
+            if self.running and not self.pending:
+                raise RuntimeError("running requests can make no progress: the page pool is too small")
+            return bool(self.pending or self.running)
+
+        entries, sampled = [], []
+        for request, count in batch:
+            tokens = request.tokens()[request.offset:request.offset + count]
+            last = request.offset + count == len(request.prompt) + len(request.output)
+            entries.append(StepEntry(request.id, tokens, (count - 1,) if last else ()))
+            if last:
+                sampled.append(request)
+        new_tokens = self.execute(entries, sampled)
+        if len(new_tokens) != len(sampled):
+            raise ValueError("missing generated request result")
+
+        decode_rows = sum(1 for r, n in batch if n == 1 and r.pending_tokens() == 1)
+        prefill_tokens = sum(n for r, n in batch) - decode_rows
+        st = self.stats
+        st["steps"] += 1
+        st["max_tokens_per_step"] = max(st["max_tokens_per_step"], decode_rows + prefill_tokens)
+        if decode_rows:
+            st["decode_rounds"] += 1
+            st["decode_rows"] += decode_rows
+        if prefill_tokens:
+            st["prefill_rounds"] += 1
+            st["prefill_tokens"] += prefill_tokens
+            st["max_prefill_tokens_per_turn"] = max(st["max_prefill_tokens_per_turn"], prefill_tokens)
+            if decode_rows:
+                st["max_prefill_tokens_with_decoding"] = max(st["max_prefill_tokens_with_decoding"], prefill_tokens)
+
+        for request, count in batch:
+            request.offset += count
+        events = []
+        for request, token in zip(sampled, new_tokens):
+            request.output.append(int(token))
+            st["tokens"] += 1
+            if request.eos_token_id is not None and int(token) == request.eos_token_id:
+                reason = "stop"
+            elif len(request.output) >= request.limit:
+                reason = "length"
+            else:
+                reason = None
+            if reason:
+                self.running.remove(request)
+                self._finish(request, reason)
+            # the first token at once, later ones in groups of four, the last always (as the reference publishes)
+            if request.published == 0 or len(request.output) - request.published >= 4 or reason:
+                events.append(self._event(request))
+                request.published = len(request.output)
+        if events:
+            self.publish(events)
+        return bool(self.pending or self.running)
+
+    def run(self) -> None:
+        try:
+            while not self.stopped.is_set():
+                if not self.turn():
+                    try:
+                        self.pending.append(self.incoming.get(timeout=0.01))
+                    except Empty:
+                        pass
+        finally:
+            self.shutdown()
+
+    def shutdown(self) -> None:
+        for request in list(self.running):
+            self._finish(request, "cancelled")
+        self.running.clear()
+        self.pending.clear()

@@ -101,9 +101,9 @@ def _fn(lib_name: str, fn_name: str):
     return fn
 
 
-def _check(err: int, what: str) -> None:
+def _check(err: int, what: str, kernels: int = 1) -> None:
     global launch_count
-    launch_count += 1
+    launch_count += kernels
     if err:
         if err >= 2000:
             detail = f"cuBLASLt found no algorithm (status {err - 2000})"
@@ -229,7 +229,7 @@ def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots):
     out = torch.empty((n, c), dtype=bcx.dtype, device=bcx.device)
     _check(_fn("conv", "akas_short_conv")(_ptr(_dense(bcx, "bcx")), _ptr(taps), _ptr(bias), _ptr(state),
                                          _ptr(cu_seqlens), _ptr(seq_of_token), _ptr(slots), _ptr(out), n,
-                                         slots.numel(), c, l, _code(bcx), _stream()), "short_conv")
+                                         slots.numel(), c, l, _code(bcx), _stream()), "short_conv", kernels=2)
     return out
 
 
@@ -291,7 +291,7 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
         _check(_fn("attention", "akas_paged_attention_decode")(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
             _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
-            splits, _code(q), _stream()), "paged_attention_decode")
+            splits, _code(q), _stream()), "paged_attention_decode", kernels=2)
         return out
     _check(_fn("attention", "akas_paged_attention")(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),

@@ -1,0 +1,32 @@
+"""From the logits of a step to one token per request: greedy, or temperature with top-k and top-p.
+
+kreasof-ai/akas samples LFM2 greedily on the device, ties to the lowest id
+(src/akas/ops/vocabulary/kernel.py:112-153). Temperature, top-k and top-p follow the stages of its one
+stochastic sampler (src/akas/ops/vocabulary/kernel.py:515-671): the uniform number comes from the host,
+one per (request, generated index), so results do not depend on batch composition.
+"""
+
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+
+class Sampler:
+    def __init__(self, ops, device):
+        self.ops = ops
+        self.device = device
+
+    def sample(self, logits: torch.Tensor, requests: Sequence) -> List[int]:
+        """``logits``: float32 [M, vocab], one row per request in order. Returns M token ids (host ints)."""
+        if logits.shape[0] == 0:
+            return []
+        if all(r.temperature <= 0 for r in requests):
+            return self.ops.argmax(logits).tolist()
+        params = torch.tensor(
+            [[r.temperature, float(r.top_k), r.top_p, r.uniform() if r.temperature > 0 else 0.0] for r in requests],
+            dtype=torch.float32,
+        ).t().contiguous().to(self.device, non_blocking=True)
+        top_k = params[1].to(torch.int32)
+        return self.ops.sample(logits, params[0], top_k, params[2], params[3]).tolist()
