@@ -136,11 +136,29 @@ class Scheduler:
                     batch = [(r, n) for r, n in batch if r is not victim]
                     self._preempt(victim)
         decoding_now = bool(batch)
-        # 2. admission: a slot and pages for a first portion
         budget = self.prefill_token_budget
         remaining = budget if budget is not None else self.prefill_chunk * self.prefill_requests
         if decoding_now and self.decode_prefill_token_budget is not None:
             remaining = min(remaining, self.decode_prefill_token_budget)
+        selected = 0
+
+        def portion(request) -> None:
+            """Gives ``request`` the next portion of its prompt, shortened to the budget and the free pages."""
+            nonlocal remaining, selected
+            if selected >= self.prefill_requests or remaining <= 0:
+                return
+            count = min(self.prefill_chunk, remaining, request.pending_tokens(), cache.room(request.id))
+            if count <= 0:
+                return
+            cache.reserve(request.id, count)
+            batch.append((request, count))
+            remaining -= count
+            selected += 1
+
+        # 2. portions of the prompts that are under way, oldest first
+        for request in self.prefilling:
+            portion(request)
+        # 3. admission: a free slot, and free pages for a first portion; the admitted request starts at once
         while self.pending and cache.free_slots() > 0:
             request = self.pending[0]
             if request.cancelled.is_set():
@@ -153,19 +171,7 @@ class Scheduler:
             self.pending.popleft()
             request.slot = self.admit_request(request.id)
             self.running.append(request)
-        # 3. portions of prompts, oldest first
-        selected = 0
-        for request in self.prefilling:
-            if selected >= self.prefill_requests or remaining <= 0:
-                break
-            count = min(self.prefill_chunk, remaining, request.pending_tokens())
-            count = min(count, cache.room(request.id))  # shortened to the pages that are free
-            if count <= 0:
-                continue
-            cache.reserve(request.id, count)
-            batch.append((request, count))
-            remaining -= count
-            selected += 1
+            portion(request)
         return batch
 
     def turn(self) -> bool:

@@ -1,0 +1,165 @@
+"""Generation through the entry point, long decoding through captured graphs, the first tokens of a
+sequence, sampling that does not depend on the batch, and bin/trace_run as a user runs it."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as plain
+import tiny
+import traces
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+
+
+def _engine(folder, dtype, page, **kw):
+    from akas_b200 import Engine, EngineConfig
+
+    options = dict(dtype=dtype, device="cuda:0", page_size=page, max_requests=4, context=512, max_tokens=2048)
+    options.update(kw)
+    return Engine(str(folder), config=EngineConfig(**options))
+
+
+@pytest.mark.parametrize("key", ["a", "b"])
+def test_greedy_generation_equals_plain_recomputation(key, tmp_path):
+    folder = tiny.make_folder(tiny.CONFIGS[key], seed=21, dtype="float32", folder=tmp_path / key)
+    cfg, w = plain.load_folder(folder)
+    prompts = tiny.prompts(cfg["vocab_size"], [1, 7, 40, 23, 64, 3], seed=2)
+    with _engine(folder, "float32", tiny.PAGE[key], prefill_chunk=13, prefill_requests=2) as engine:
+        results = engine.generate(prompts, max_tokens=12)
+        stats = dict(engine.stats)
+    for prompt, result in zip(prompts, results):
+        assert result["prompt_tokens"] == prompt and result["finish_reason"] == "length"
+        assert result["generated_tokens"] == plain.greedy(cfg, w, prompt, 12)
+    assert stats["completed"] == 6 and stats["max_active"] == 4 and stats["max_prefill_tokens_with_decoding"] > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_through_captured_graphs(dtype, tmp_path):
+    """300 decoded tokens for three requests of different lengths (graph replay, bucket of 4 with one row of
+    padding): the logits of every step against one whole pass of the plain model over the final sequences."""
+    from akas_b200 import StepEntry
+
+    folder = tiny.make_folder(tiny.TINY_A, seed=22, dtype=dtype, folder=tmp_path / "m")
+    cfg, w = plain.load_folder(folder)
+    prompts = tiny.prompts(cfg["vocab_size"], [5, 70, 33], seed=3)
+    feed = tiny.prompts(cfg["vocab_size"], [300, 300, 300], seed=4)
+    with _engine(folder, dtype, 16) as engine:
+        runner = engine.runner
+        runner.step([StepEntry(i, p, ()) for i, p in enumerate(prompts)])
+        rows = [[] for _ in prompts]
+        for t in range(300):
+            logits = runner.step([StepEntry(i, (feed[i][t],), (0,)) for i in range(3)]).float().cpu().numpy()
+            for i in range(3):
+                rows[i].append(logits[i])
+        assert 4 in runner._graphs and runner.kernels_per_decode_step[4] > 0
+    for i, p in enumerate(prompts):
+        want = plain.forward(cfg, w, p + feed[i]).numpy()[len(p):]
+        bad = traces.first_bad(np.stack(rows[i]), want, TOL[dtype])
+        assert bad is None, (i, bad, traces.worst(np.stack(rows[i]), want))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(dtype, tmp_path):
+    """Positions 0, 1, 2: empty state, a cache of one page, a single key."""
+    from akas_b200 import StepEntry
+
+    folder = tiny.make_folder(tiny.TINY_B, seed=23, dtype=dtype, folder=tmp_path / "m")
+    cfg, w = plain.load_folder(folder)
+    with _engine(folder, dtype, 8) as engine:
+        for prompt in ([5], [5, 5], [300, 0, 319]):
+            want = plain.forward(cfg, w, prompt).numpy()
+            got = engine.runner.step([StepEntry("x", prompt, range(len(prompt)))]).float().cpu().numpy()
+            engine.runner.release("x")
+            one = np.concatenate([engine.runner.step([StepEntry("y", (t,), (0,))]).float().cpu().numpy() for t in prompt])
+            engine.runner.release("y")
+            assert traces.first_bad(got, want, TOL[dtype]) is None and traces.first_bad(one, want, TOL[dtype]) is None
+
+
+def test_sampling_does_not_depend_on_the_batch(tmp_path):
+    folder = tiny.make_folder(tiny.TINY_A, seed=24, dtype="float32", std=0.3, folder=tmp_path / "m")
+    prompts = tiny.prompts(256, [9, 30, 2, 17], seed=5)
+    with _engine(folder, "float32", 16) as engine:
+        together = engine.generate(prompts, max_tokens=20, temperature=0.9, top_k=40, top_p=0.95, seed=100)
+        alone = [engine.generate(p, max_tokens=20, temperature=0.9, top_k=40, top_p=0.95, seed=100 + i)
+                 for i, p in enumerate(prompts)]
+        again = engine.generate(prompts, max_tokens=20, temperature=0.9, top_k=40, top_p=0.95, seed=101)
+    assert [r["generated_tokens"] for r in together] == [r["generated_tokens"] for r in alone]
+    assert [r["generated_tokens"] for r in together] != [r["generated_tokens"] for r in again]
+    assert len({tuple(r["generated_tokens"]) for r in together}) == 4
+
+
+def test_preemption_on_the_device_recomputes_exactly(tmp_path):
+    """A pool too small for three growing requests: the youngest is preempted and recomputed; every output
+    still equals the plain greedy continuation."""
+    folder = tiny.make_folder(tiny.TINY_A, seed=25, dtype="float32", folder=tmp_path / "m")
+    cfg, w = plain.load_folder(folder)
+    prompts = tiny.prompts(256, [20, 20, 20], seed=6)
+    with _engine(folder, "float32", 16, max_tokens=128, context=64, max_requests=3) as engine:
+        results = engine.generate(prompts, max_tokens=40)
+        assert engine.stats["preemptions"] > 0
+    for prompt, result in zip(prompts, results):
+        assert result["generated_tokens"] == plain.greedy(cfg, w, prompt, 40)
+
+
+def test_submit_validates(tmp_path):
+    folder = tiny.make_folder(tiny.TINY_A, seed=26, dtype="float32", folder=tmp_path / "m")
+    with _engine(folder, "float32", 16, context=32, max_tokens=64) as engine:
+        for bad in ([], [256], [-1], [1.5]):
+            with pytest.raises(ValueError):
+                engine.submit(bad, max_tokens=2)
+        with pytest.raises(ValueError):
+            engine.submit([1], max_tokens=0)
+        with pytest.raises(ValueError):
+            engine.submit([1] * 30, max_tokens=3)
+        request = engine.submit([1, 2], max_tokens=3)
+        engine.cancel(request)
+        while engine.step():
+            pass
+        assert request.finish_reason == "cancelled"
+    with pytest.raises(RuntimeError):
+        engine.step()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tmp_path):
+    """bin/trace_run as a user calls it: steps on standard input, logits as files, `done <step>` lines."""
+    folder = tiny.make_folder(tiny.TINY_B, seed=27, dtype=dtype, folder=tmp_path / "m")
+    cfg, w = plain.load_folder(folder)
+    reqs = {f"q{i}": p for i, p in enumerate(tiny.prompts(cfg["vocab_size"], [50, 3, 71, 20, 64], seed=7))}
+    steps, peak = traces.mixed(reqs, {rid: max(1, len(t) - 5) for rid, t in reqs.items()}, seed=1, live=4, page=64)
+    steps.insert(2, dict(step=999, entries=[], end=[]))  # a step that brings nothing
+    for i, s in enumerate(steps):
+        s["step"] = i
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
+         "--max-tokens", str(peak)],
+        input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(len(steps))]
+    want = {rid: plain.forward(cfg, w, t).numpy() for rid, t in reqs.items()}
+    at = {rid: 0 for rid in reqs}
+    vocab = cfg["vocab_size"]
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        path = out / f"{s['step']}.f32"
+        if not wanted:
+            assert not path.exists()
+            continue
+        data = np.fromfile(path, dtype="<f4").reshape(wanted, vocab)
+        row = 0
+        for e in s["entries"]:
+            for k in e["want"]:
+                ref = want[e["id"]][at[e["id"]] + k]
+                assert np.abs(data[row] - ref).max() <= TOL[dtype] * np.abs(want[e["id"]]).max(), (s["step"], e["id"], k)
+                row += 1
+            at[e["id"]] += len(e["tokens"])

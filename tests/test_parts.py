@@ -1,0 +1,300 @@
+"""Each part alone against the plain functions, and a toy architecture built from outside the package.
+
+The toy architecture is defined here and registered through the public registries only; no file of the
+framework knows it. It holds a mixer with state of its own (an exponential moving average), an
+attention layer with a window (a page group of its own whose pages are given back as the window moves),
+a layer that runs twice, and a schedule entry that reads another entry's cache.
+"""
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as plain
+import tiny
+import traces
+from akas_b200.cache import CacheManager
+from akas_b200.config import (AttentionSpec, EngineConfig, LayerSpec, ModelSpec, PartSpec, RMSNormSpec, RopeSpec,
+                              ScheduleEntry, ShortConvSpec, SwiGLUSpec, register_architecture)
+from akas_b200.engine.batch import BatchLayout, StepEntry, fill_batch
+from akas_b200.engine.runner import ModelRunner
+from akas_b200.ops import reference
+from akas_b200.parts import (Block, Mixer, Param, Runtime, StateSpec, build_part, register_mixer)
+from akas_b200.weights import write_random_model
+
+
+def _devices():
+    out = [pytest.param("cpu", id="cpu-reference-ops")]
+    out.append(pytest.param("cuda:0", id="gpu", marks=pytest.mark.gpu))
+    return out
+
+
+def _runtime(device, dtype=torch.float32):
+    if device == "cpu":
+        return Runtime(dtype, torch.device("cpu"), reference)
+    from akas_b200.ops import cuda
+
+    cuda.require()
+    return Runtime(dtype, torch.device(device), cuda)
+
+
+def _context(rt, cache, lengths):
+    """A StepContext for fresh requests of the given lengths, each run whole."""
+    from akas_b200.engine.runner import ModelRunner as _R
+
+    entries = []
+    for i, n in enumerate(lengths):
+        cache.admit(i)
+        cache.reserve(i, n)
+        entries.append(StepEntry(i, [0] * n, ()))
+    lay = BatchLayout(sum(lengths), len(lengths), 0, len(cache.groups), cache.max_blocks)
+    host = torch.zeros(lay.size, dtype=torch.int32)
+    mq, mc = fill_batch(host.numpy(), lay, entries, cache)
+    dev = host.to(rt.device)
+    shim = type("S", (), {"cache": cache})()
+    return _R._context(shim, dev, lay, mq, mc, False)
+
+
+def _rel(got, want):
+    """Largest difference relative to the largest reference value (float32 results of size 40 carry 5e-6)."""
+    return ((got - want).abs().max() / want.abs().max()).item()
+
+
+def _rand(shape, seed, scale=1.0):
+    return torch.randn(shape, generator=torch.Generator().manual_seed(seed), dtype=torch.float64) * scale
+
+
+@pytest.mark.parametrize("device", _devices())
+def test_rmsnorm_part(device):
+    rt = _runtime(device)
+    for zero_centered in (False, True):
+        part = build_part("norm", RMSNormSpec(50, 1e-6, zero_centered), rt)
+        w = _rand((50,), 1)
+        part.load(lambda name: w.float().to(rt.device))
+        x = _rand((7, 50), 2, 3.0)
+        want = plain.rms_norm(x, w + 1 if zero_centered else w, 1e-6)
+        got = part.forward(x.float().to(rt.device), out_dtype=torch.float32).double().cpu()
+        assert _rel(got, want) < 1e-5
+
+
+@pytest.mark.parametrize("device", _devices())
+@pytest.mark.parametrize("taps,bias", [(3, False), (5, True)])
+def test_short_conv_part(device, taps, bias):
+    rt = _runtime(device)
+    c = 40
+    part = build_part("mixer", ShortConvSpec(c, taps, bias), rt)
+    w = {"in_proj.weight": _rand((3 * c, c), 1, 0.3), "conv.weight": _rand((c, 1, taps), 2), "out_proj.weight": _rand((c, c), 3, 0.3),
+         "conv.bias": _rand((c,), 4)}
+    assert set(part.params()) == set(w) - (set() if bias else {"conv.bias"})
+    part.load(lambda name: w[name].float().to(rt.device))
+    cache = CacheManager([part.cache()], 8, 64, 2, 32, device=rt.device)
+    lengths = [11, 4]
+    ctx = _context(rt, cache, lengths)
+    x = _rand((sum(lengths), c), 5)
+    got = part.forward(x.float().to(rt.device), ctx, cache.views[0]).double().cpu()
+    at = 0
+    for n in lengths:
+        want = plain.short_conv(x[at:at + n], w["in_proj.weight"], w["conv.weight"].reshape(c, taps),
+                                w["conv.bias"] if bias else None, w["out_proj.weight"])
+        assert _rel(got[at:at + n], want) < 1e-5
+        at += n
+
+
+@pytest.mark.parametrize("device", _devices())
+@pytest.mark.parametrize("heads,kv,dim,window,rotary", [(4, 2, 16, None, None), (3, 1, 32, 6, None), (2, 2, 48, None, 16)])
+def test_attention_part(device, heads, kv, dim, window, rotary):
+    rt = _runtime(device)
+    c = 40
+    spec = AttentionSpec(c, heads, kv, dim, qk_norm=RMSNormSpec(dim, 1e-6), position=RopeSpec(dim, 1e4, rotary), window=window)
+    part = build_part("mixer", spec, rt)
+    w = {"q_proj.weight": _rand((heads * dim, c), 1, 0.3), "k_proj.weight": _rand((kv * dim, c), 2, 0.3),
+         "v_proj.weight": _rand((kv * dim, c), 3, 0.3), "out_proj.weight": _rand((c, heads * dim), 4, 0.3),
+         "q_norm.weight": _rand((dim,), 5) + 1, "k_norm.weight": _rand((dim,), 6) + 1}
+    assert set(part.params()) == set(w)
+    part.load(lambda name: w[name].float().to(rt.device))
+    cache = CacheManager([part.cache()], 4, 64, 2, 32, device=rt.device)
+    lengths = [13, 6]
+    ctx = _context(rt, cache, lengths)
+    x = _rand((sum(lengths), c), 7)
+    h = torch.zeros((sum(lengths), c), dtype=torch.float32, device=rt.device)
+    got = part.forward(x.float().to(rt.device), ctx, cache.views[0], residual=h).double().cpu()
+    at = 0
+    for n in lengths:
+        if rotary is None:
+            want = plain.attention(x[at:at + n], w["q_proj.weight"], w["k_proj.weight"], w["v_proj.weight"],
+                                   w["out_proj.weight"], w["q_norm.weight"], w["k_norm.weight"], 1e-6, heads, kv, dim,
+                                   1e4, window)
+            assert _rel(got[at:at + n], want) < 1e-5
+        at += n
+    assert torch.isfinite(got).all()
+
+
+@pytest.mark.parametrize("device", _devices())
+def test_swiglu_part_and_block(device):
+    rt = _runtime(device)
+    c, f = 24, 56
+    w = {"ff.w1.weight": _rand((f, c), 1, 0.3), "ff.w3.weight": _rand((f, c), 2, 0.3), "ff.w2.weight": _rand((c, f), 3, 0.3),
+         "mix.in_proj.weight": _rand((3 * c, c), 4, 0.3), "mix.conv.weight": _rand((c, 1, 3), 5),
+         "mix.out_proj.weight": _rand((c, c), 6, 0.3), "n1": _rand((c,), 7) + 1, "n2": _rand((c,), 8) + 1}
+    spec = LayerSpec(ShortConvSpec(c, 3), SwiGLUSpec(c, f), RMSNormSpec(c, 1e-5), RMSNormSpec(c, 1e-5), "mix.", "ff.", "n1", "n2")
+    block = Block(spec, rt)
+    assert set(block.params()) == set(w)
+    block.load(lambda name: w[name].float().to(rt.device))
+    cache = CacheManager([block.mixer.cache()], 8, 64, 1, 32, device=rt.device)
+    ctx = _context(rt, cache, [9])
+    h = _rand((9, c), 9)
+    got = block.forward(h.float().to(rt.device), ctx, cache.views[0]).double().cpu()
+    x = plain.rms_norm(h, w["n1"], 1e-5)
+    h1 = h + plain.short_conv(x, w["mix.in_proj.weight"], w["mix.conv.weight"].reshape(c, 3), None, w["mix.out_proj.weight"])
+    want = h1 + plain.swiglu(plain.rms_norm(h1, w["n2"], 1e-5), w["ff.w1.weight"], w["ff.w3.weight"], w["ff.w2.weight"])
+    assert _rel(got, want) < 1e-5
+
+
+# --------------------------------------------------------------------------- a toy architecture
+
+
+class EmaMixer(Mixer):
+    """s_t = decay * s_{t-1} + x_t W^T, out_t = s_t: one vector of state per request."""
+
+    def params(self):
+        c = self.spec.options["width"]
+        return {"proj.weight": Param((c, c)), "decay": Param((c,), role="vector", mean=0.5)}
+
+    def load(self, get):
+        self.w, self.decay = get("proj.weight"), get("decay")
+
+    def cache(self):
+        return StateSpec((self.spec.options["width"],))
+
+    def forward(self, x, ctx, cache=None, residual=None, write=True):
+        u = self.rt.ops.linear(x, self.w, out_dtype=torch.float32)
+        out = torch.zeros_like(u)
+        cu, slots = ctx.cu_seqlens.tolist(), ctx.slots.tolist()
+        for r, slot in enumerate(slots):
+            if slot < 0:
+                continue
+            s = cache.state[slot].clone()
+            for t in range(cu[r], cu[r + 1]):
+                s = self.decay * s + u[t]
+                out[t] = s
+            cache.state[slot] = s
+        return residual.add_(out) if residual is not None else out.to(x.dtype)
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    width: int = 32
+    vocab: int = 50
+    window: int = 12
+    architecture = "ToyHybridForTests"
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(data["width"], data["vocab"], data["window"])
+
+    def to_dict(self):
+        return dict(architectures=[self.architecture], width=self.width, vocab=self.vocab, window=self.window)
+
+    def model_spec(self):
+        c = self.width
+        norm = RMSNormSpec(c, 1e-5)
+
+        def layer(i, mixer):
+            p = f"layers.{i}."
+            return LayerSpec(mixer, SwiGLUSpec(c, 48), norm, norm, p + "mixer.", p + "ffn.", p + "norm1", p + "norm2")
+
+        attn = dict(qk_norm=RMSNormSpec(16, 1e-5), position=RopeSpec(16, 1e4))
+        return ModelSpec(
+            architecture=self.architecture, hidden_size=c, vocab_size=self.vocab,
+            layers=(layer(0, PartSpec("ema_for_tests", {"width": c})),
+                    layer(1, AttentionSpec(c, 2, 1, 16, window=self.window, **attn)),
+                    layer(2, AttentionSpec(c, 2, 2, 16, **attn))),
+            final_norm=norm, embedding_name="embed", final_norm_name="final_norm", head_name=None,
+            # layer 1 runs twice, each time with a cache of its own; the last entry reads entry 2's keys and values
+            schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(1), ScheduleEntry(2, cache=2)),
+        )
+
+
+def _toy_plain(cfg, w, tokens):
+    """The toy model, whole sequence, float64, from the plain part functions."""
+    c, T = cfg.width, len(tokens)
+    h = w["embed"][torch.as_tensor(tokens)]
+    kept = {}
+
+    def attn(i, x, window, heads, kv, shared=None):
+        p = f"layers.{i}.mixer."
+        d = 16
+        q = plain.rms_norm((x @ w[p + "q_proj.weight"].T).reshape(T, heads, d), w[p + "q_norm.weight"], 1e-5)
+        cos, sin = plain.rope_tables(torch.arange(T), d, 1e4, torch.float64)
+        q = plain.apply_rope(q, cos, sin)
+        if shared is None:
+            k = plain.rms_norm((x @ w[p + "k_proj.weight"].T).reshape(T, kv, d), w[p + "k_norm.weight"], 1e-5)
+            k, v = plain.apply_rope(k, cos, sin), (x @ w[p + "v_proj.weight"].T).reshape(T, kv, d)
+        else:
+            k, v = shared
+        pos = torch.arange(T)
+        seen = pos[None, :] <= pos[:, None]
+        if window:
+            seen &= pos[None, :] > pos[:, None] - window
+        kk, vv = k.repeat_interleave(heads // kv, 1), v.repeat_interleave(heads // kv, 1)
+        score = (torch.einsum("thd,shd->hts", q, kk) * d ** -0.5).masked_fill(~seen[None], float("-inf"))
+        out = torch.einsum("hts,shd->thd", torch.softmax(score, -1), vv).reshape(T, heads * d)
+        return out @ w[p + "out_proj.weight"].T, (k, v)
+
+    for n, (i, shared) in enumerate(((0, None), (1, None), (2, None), (1, None), (2, 2))):
+        p = f"layers.{i}."
+        x = plain.rms_norm(h, w[p + "norm1"], 1e-5)
+        if i == 0:
+            u = x @ w[p + "mixer.proj.weight"].T
+            s, rows = torch.zeros(c, dtype=torch.float64), []
+            for t in range(T):
+                s = w[p + "mixer.decay"] * s + u[t]
+                rows.append(s)
+            mixed = torch.stack(rows)
+        else:
+            mixed, kept[n] = attn(i, x, cfg.window if i == 1 else None, 2, 1 if i == 1 else 2,
+                                  kept[shared] if shared is not None else None)
+        h = h + mixed
+        f = p + "ffn."
+        h = h + plain.swiglu(plain.rms_norm(h, w[p + "norm2"], 1e-5), w[f + "w1.weight"], w[f + "w3.weight"], w[f + "w2.weight"])
+    return plain.rms_norm(h, w["final_norm"], 1e-5) @ w["embed"].T
+
+
+@pytest.mark.parametrize("device", _devices())
+def test_toy_architecture_is_registered_built_and_stepped(device, tmp_path):
+    register_mixer("ema_for_tests", EmaMixer)
+    register_architecture(ToyConfig.architecture, ToyConfig)
+    cfg = ToyConfig()
+    folder = write_random_model(tmp_path / "toy", cfg, seed=3, std=0.2, dtype="float32")
+    from safetensors.torch import load_file
+
+    w = {k: v.double() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    reqs = {f"t{i}": p for i, p in enumerate(tiny.prompts(cfg.vocab, [41, 3, 30, 17, 26], seed=9))}
+    want = {rid: _toy_plain(cfg, w, toks).numpy() for rid, toks in reqs.items()}
+    ops = reference if device == "cpu" else None
+    page = 4
+
+    def runner(tokens):
+        config = EngineConfig(dtype="float32", device=device, page_size=page, max_tokens=tokens, max_requests=4,
+                              context=48, cuda_graphs=False)
+        return ModelRunner(folder, config, ops=ops)
+
+    r = runner(48)
+    assert len(r.cache.groups) == 2 and [type(v).__name__ for v in r.cache.views] == [
+        "StateCache", "PagedCache", "PagedCache", "PagedCache", "NoneType"]
+    steps, peak = traces.mixed(reqs, {rid: max(1, len(t) - 6) for rid, t in reqs.items()}, seed=2, live=3, page=page)
+    for name, trace, pool in (("whole", traces.whole(reqs), 48), ("portions", traces.portions(reqs), 48),
+                              ("tail", traces.tail_decoded(reqs, 8), 48), ("mixed", steps, peak)):
+        r = runner(pool)
+        got = traces.replay(r, trace)
+        for rid in reqs:
+            bad = traces.first_bad(got[rid], want[rid], 2e-5)
+            assert bad is None, f"{name}: {rid} first differs at {bad}: {traces.worst(got[rid], want[rid])}"
+        assert r.cache.min_free_pages() == r.cache.num_pages
+    # the windowed group gave pages back while the request was still running
+    r = runner(48)
+    r.step([StepEntry("w", reqs["t0"], ())])
+    full, win = r.cache.blocks("w", r.cache.views[2].group), r.cache.blocks("w", r.cache.views[1].group)
+    assert all(p >= 0 for p in full) and sum(p < 0 for p in win) == (41 - cfg.window + 1) // page

@@ -1,0 +1,197 @@
+"""The scheduler's decisions, with a fake step function (no device).
+
+The fake keeps, per request, a rolling hash of every token it was fed, in order; the token it "generates"
+is a function of that hash. Outputs are therefore sensitive to order, to lost or repeated tokens and to a
+wrong recomputation after a preemption, as the reference's FakeEngine is (tests/test_dense_scheduler.py:7-37).
+"""
+
+import pytest
+
+from akas_b200.cache import CacheManager
+from akas_b200.engine.request import Request
+from akas_b200.engine.scheduler import Scheduler
+from akas_b200.parts import PagedKVSpec, StateSpec
+
+VOCAB = 1000
+
+
+class FakeModel:
+    def __init__(self, page=4, tokens=64, requests=4, context=64):
+        self.cache = CacheManager([PagedKVSpec(1, 16), StateSpec((2, 4))], page, tokens, requests, context, storage=False)
+        self.hash = {}
+        self.batches = []
+
+    def admit(self, rid):
+        self.hash[rid] = 7
+        return self.cache.admit(rid)
+
+    def execute(self, entries, requests):
+        self.batches.append([(e.request, len(e.tokens)) for e in entries])
+        out = []
+        for e in entries:
+            assert len(e.tokens) > 0
+            self.cache.reserve(e.request, len(e.tokens))  # must already be covered by the plan
+            for t in e.tokens:
+                self.hash[e.request] = (self.hash[e.request] * 31 + t + 1) % 1000003
+            self.cache.advance(e.request, len(e.tokens))
+            if e.want:
+                assert list(e.want) == [len(e.tokens) - 1]
+                out.append(self.hash[e.request] % VOCAB)
+        self.cache.check()
+        return out
+
+
+def expected(prompt, n):
+    h, out = 7, []
+    for t in prompt:
+        h = (h * 31 + t + 1) % 1000003
+    for _ in range(n):
+        out.append(h % VOCAB)
+        h = (h * 31 + out[-1] + 1) % 1000003
+    return out
+
+
+def make(model, **kw):
+    events = []
+    s = Scheduler(model.cache, model.execute, events.extend, admit=model.admit, **kw)
+    return s, events
+
+
+def drain(s, limit=10000):
+    turns = 0
+    while s.turn():
+        turns += 1
+        assert turns < limit
+    return turns
+
+
+def test_batched_equals_sequential():
+    model = FakeModel(tokens=256, requests=4)
+    s, _ = make(model, prefill_chunk=5, prefill_requests=2)
+    reqs = [Request([i + 1] * n, 6) for i, n in enumerate((3, 11, 1, 8, 20, 2))]
+    for r in reqs:
+        s.submit(r)
+    drain(s)
+    for r in reqs:
+        assert r.output == expected(r.prompt, 6) and r.finish_reason == "length" and r.slot is None
+    assert not model.cache.live() and model.cache.free_pages() == 64
+    assert s.stats["completed"] == 6 and s.stats["tokens"] == 36 and s.stats["max_active"] == 4
+    # prompt portions and decoded tokens did share steps
+    assert any(any(n == 1 for _, n in b) and any(n > 1 for _, n in b) for b in model.batches)
+
+
+def test_budgets_are_kept():
+    model = FakeModel(tokens=4096, requests=8, context=512)
+    s, _ = make(model, prefill_chunk=16, prefill_requests=3, prefill_token_budget=40, decode_prefill_token_budget=8)
+    reqs = [Request([1] * 100, 4) for _ in range(6)]
+    for r in reqs:
+        s.submit(r)
+    drain(s)
+    assert all(r.output == expected(r.prompt, 4) for r in reqs)
+    for batch in model.batches:
+        portions = [n for _, n in batch if n > 1]
+        decodes = [n for _, n in batch if n == 1]
+        assert all(n <= 16 for n in portions) and len(portions) <= 3 and sum(portions) <= 40
+    st = s.stats
+    assert st["max_prefill_tokens_per_turn"] <= 40 and st["max_prefill_tokens_with_decoding"] <= 8
+    assert 594 <= st["prefill_tokens"] <= 600  # every prompt token ran once (a last single token counts as decoding)
+
+
+def test_default_budget_is_chunk_times_requests():
+    model = FakeModel(tokens=4096, requests=8, context=512)
+    s, _ = make(model, prefill_chunk=10, prefill_requests=2)
+    for _ in range(4):
+        s.submit(Request([1] * 50, 2))
+    s.turn()
+    assert sorted(n for _, n in model.batches[0]) == [10, 10]
+
+
+def test_cancel_frees_and_others_go_on():
+    model = FakeModel(tokens=256)
+    s, _ = make(model, prefill_chunk=4)
+    a, b = Request([1] * 10, 50), Request([2] * 3, 5)
+    s.submit(a), s.submit(b)
+    for _ in range(4):
+        s.turn()
+    a.cancelled.set()
+    drain(s)
+    assert a.finish_reason == "cancelled" and b.output == expected(b.prompt, 5)
+    assert s.stats["cancelled"] == 1 and not model.cache.live()
+    c = Request([3], 2)
+    c.cancelled.set()
+    s.submit(c)
+    drain(s)
+    assert c.finish_reason == "cancelled" and c.output == []
+
+
+def test_end_of_sequence_token_stops_a_request():
+    model = FakeModel(tokens=256)
+    s, _ = make(model)
+    want = expected([5, 6], 10)
+    r = Request([5, 6], 10, eos_token_id=want[3])
+    s.submit(r)
+    drain(s)
+    assert r.output == want[:4] and r.finish_reason == "stop"
+
+
+def test_pages_run_out_the_youngest_is_preempted_and_recomputed():
+    # 10 pages of 4 tokens; three requests that each grow to 24 tokens cannot all stay
+    model = FakeModel(page=4, tokens=40, requests=3, context=40)
+    s, _ = make(model, prefill_chunk=8)
+    reqs = [Request([i + 1] * 6, 18) for i in range(3)]
+    for r in reqs:
+        s.submit(r)
+    drain(s)
+    assert s.stats["preemptions"] > 0
+    for r in reqs:
+        assert r.output == expected(r.prompt, 18), "a preempted request must be recomputed, not resumed from stale state"
+    assert reqs[0].preemptions == 0, "the oldest request is never preempted"
+    assert not model.cache.live() and model.cache.free_pages() == 10 and s.stats["pages_in_use_max"] <= 10
+
+
+def test_admission_waits_for_pages():
+    model = FakeModel(page=4, tokens=16, requests=4, context=16)
+    s, _ = make(model, prefill_chunk=16)
+    a, b = Request([1] * 12, 2), Request([2] * 12, 2)
+    s.submit(a), s.submit(b)
+    s.turn()
+    assert [r for r, _ in model.batches[0]] == [a.id]  # b's first portion has no pages yet
+    drain(s)
+    assert a.output == expected(a.prompt, 2) and b.output == expected(b.prompt, 2)
+
+
+def test_a_portion_is_shortened_to_the_free_pages():
+    model = FakeModel(page=4, tokens=32, requests=2, context=32)
+    s, _ = make(model, prefill_chunk=32)
+    a, b = Request([1] * 20, 1), Request([2] * 5, 8)
+    s.submit(b)
+    s.turn()
+    s.submit(a)
+    s.turn()  # b holds 2 pages; 6 are free: a's first portion is 24 at most, it wants 20
+    assert (a.id, 20) in model.batches[1]
+    drain(s)
+    assert a.output == expected(a.prompt, 1) and b.output == expected(b.prompt, 8)
+
+
+def test_events_carry_ids_and_reasons():
+    model = FakeModel(tokens=256)
+    s, events = make(model)
+    r = Request([1, 2, 3], 6)
+    s.submit(r)
+    drain(s)
+    assert [len(e[1]["output_ids"]) for e in events] == [1, 5, 6]  # first token, a group of four, the end
+    last = events[-1][1]
+    assert last["meta_info"] == dict(prompt_tokens=3, completion_tokens=6, finish_reason=dict(type="length", length=6))
+    assert events[0][1]["meta_info"]["finish_reason"] is None
+
+
+def test_invalid_budgets():
+    model = FakeModel()
+    with pytest.raises(ValueError):
+        make(model, prefill_chunk=0)
+    with pytest.raises(ValueError):
+        make(model, prefill_token_budget=0)
+    s, _ = make(model)
+    s.stopped.set()
+    with pytest.raises(RuntimeError):
+        s.submit(Request([1], 1))
