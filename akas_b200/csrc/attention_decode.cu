@@ -1,0 +1,284 @@
+// Paged GQA attention for steps that only decode, bfloat16, keys split across blocks (flash-decoding).
+//
+// One block per (token, kv head x tile of up to 16 query heads of its group, split of the keys). The
+// query heads that share a kv head are the rows of one mma tile (rows beyond the group are zero), so
+// the K and V rows of a kv head are read once for the whole group. The block's share of the 64-key
+// tiles is streamed through a three-stage cp.async pipeline (48 KB of loads in flight per block at
+// head size 64); in every tile each of the 4 warps takes 16 of the 64 keys: S = Q.K^T (mma.sync
+// m16n8k16), mask by absolute position, running max/sum in float32, O += P.V. At the end the four
+// warps' (max, sum, O) are merged through shared memory. With one split the block writes the output;
+// otherwise it writes float32 partials [token, head, split] (+ max and sum), which
+// decode_merge_bf16_kernel combines by log-sum-exp.
+//
+// Launch shapes depend only on (tokens, heads, splits); lengths are read on the device, so the
+// kernel can sit in a captured graph. Tokens of request -1 (padding) write zeros and touch no page.
+#include <math.h>
+
+#include "common.cuh"
+#include "mma.cuh"
+
+using namespace akas;
+
+namespace {
+
+constexpr int BK = 64, WARPS = 4, STAGES = 3, ROWS = 16;
+
+template <int D>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_of_token,
+                        const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, float scale, int window, int page_size, int H, int KH,
+                        int row_tiles, int splits) {
+  constexpr int STRIDE = D + 8, CHUNKS = D / 8, KS = D / 16, NB = D / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);        // [ROWS][STRIDE]
+  bf16* k_s = q_s + ROWS * STRIDE;                      // [STAGES][BK][STRIDE]
+  bf16* v_s = k_s + STAGES * BK * STRIDE;               // [STAGES][BK][STRIDE]
+
+  const int tok = blockIdx.x, split = blockIdx.z;
+  const int kvh = blockIdx.y / row_tiles, row_tile = blockIdx.y % row_tiles;
+  const int G = H / KH;
+  const int g0 = row_tile * ROWS, gn = min(ROWS, G - g0);
+  const int head0 = kvh * G + g0;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int r = seq_of_token[tok];
+  if (r < 0) {
+    if (split == 0)
+      for (int i = tid; i < gn * D; i += WARPS * 32) out[((size_t)tok * H + head0) * D + i] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int pos = positions[tok];
+  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kt_first = first_key / BK, kt_last = pos / BK;
+  const int tiles = kt_last - kt_first + 1;
+  const int per_split = (tiles + splits - 1) / splits;
+  const int lo = kt_first + split * per_split, hi = min(lo + per_split, kt_last + 1);
+
+  auto load_tile = [&](int kt, int stage) {
+    bf16* ks_ = k_s + stage * BK * STRIDE;
+    bf16* vs_ = v_s + stage * BK * STRIDE;
+    for (int c = tid; c < BK * CHUNKS; c += WARPS * 32) {
+      const int row = c / CHUNKS, col = (c % CHUNKS) * 8;
+      const int key = kt * BK + row;
+      size_t at = 0;
+      int bytes = 0;
+      if (key >= first_key && key <= pos) {
+        const int page = block_table[(size_t)r * max_blocks + key / page_size];
+        if (page >= 0) {
+          at = (((size_t)page * KH + kvh) * page_size + key % page_size) * D + col;
+          bytes = 16;
+        }
+      }
+      cp_async16(ks_ + row * STRIDE + col, k_pool + at, bytes);
+      cp_async16(vs_ + row * STRIDE + col, v_pool + at, bytes);
+    }
+  };
+
+  // Q rows (one per query head of the group) and the first tiles, all in flight together
+  for (int c = tid; c < ROWS * CHUNKS; c += WARPS * 32) {
+    const int row = c / CHUNKS, col = (c % CHUNKS) * 8;
+    const bf16* src = q + ((size_t)tok * H + head0 + min(row, gn - 1)) * D + col;
+    cp_async16(q_s + row * STRIDE + col, src, row < gn ? 16 : 0);
+  }
+  cp_async_commit();
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (lo + s < hi) load_tile(lo + s, s);
+    cp_async_commit();
+  }
+
+  float o[NB][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) { o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float sl2 = scale * 1.4426950408889634f;
+  uint32_t qf[KS][4];
+
+  for (int kt = lo; kt < hi; ++kt) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();
+    if (kt == lo) {
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks)
+        ldmatrix_x4(qf[ks], q_s + (lane & 15) * STRIDE + ks * 16 + (lane >> 4) * 8);
+    }
+    const int next = kt + STAGES - 1;
+    if (next < hi) load_tile(next, (next - lo) % STAGES);
+    cp_async_commit();
+    const int stage = (kt - lo) % STAGES;
+    const bf16* ks_ = k_s + stage * BK * STRIDE + warp * 16 * STRIDE;  // this warp's 16 keys of the tile
+    const bf16* vs_ = v_s + stage * BK * STRIDE + warp * 16 * STRIDE;
+
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      uint32_t b[4];
+      ldmatrix_x4(b, ks_ + ((lane & 7) + (lane >> 4) * 8) * STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
+      mma_bf16(s[0], qf[ks], b[0], b[1]);
+      mma_bf16(s[1], qf[ks], b[2], b[3]);
+    }
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = kt * BK + warp * 16 + nb * 8 + 2 * t + (e & 1);
+        const bool seen = key <= pos && key >= first_key;
+        s[nb][e] = seen ? s[nb][e] * sl2 : -INFINITY;
+        m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nb][e]);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      m_new[h2] = fmaxf(m_new[h2], __shfl_xor_sync(0xffffffffu, m_new[h2], 1));
+      m_new[h2] = fmaxf(m_new[h2], __shfl_xor_sync(0xffffffffu, m_new[h2], 2));
+      m_use[h2] = m_new[h2] == -INFINITY ? 0.f : m_new[h2];
+      corr[h2] = exp2f(m_run[h2] - m_use[h2]);
+      m_run[h2] = m_new[h2];
+    }
+    uint32_t pf[4];
+    float l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      const float p0 = exp2f(s[nb][0] - m_use[0]), p1 = exp2f(s[nb][1] - m_use[0]);
+      const float p2 = exp2f(s[nb][2] - m_use[1]), p3 = exp2f(s[nb][3] - m_use[1]);
+      l_add[0] += p0 + p1;
+      l_add[1] += p2 + p3;
+      pf[nb * 2] = pack_bf16(p0, p1);
+      pf[nb * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) l_run[h2] = l_run[h2] * corr[h2] + l_add[h2];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      o[nb][0] *= corr[0]; o[nb][1] *= corr[0];
+      o[nb][2] *= corr[1]; o[nb][3] *= corr[1];
+    }
+#pragma unroll
+    for (int np = 0; np < NB / 2; ++np) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, vs_ + ((lane & 7) + ((lane >> 3) & 1) * 8) * STRIDE + np * 16 + (lane >> 4) * 8);
+      mma_bf16(o[2 * np], pf, b[0], b[1]);
+      mma_bf16(o[2 * np + 1], pf, b[2], b[3]);
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // all warps are done with the tiles: the stages become the merge buffers
+
+  // merge the four warps: (m, l) per row and O[16][D] per warp, in float32 through shared memory
+  float* o_s = reinterpret_cast<float*>(k_s);            // [WARPS][ROWS][D]
+  float* ml_s = o_s + WARPS * ROWS * D;                  // [WARPS][ROWS][2]
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 1);
+    l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 2);
+    const int row = g + h2 * 8;
+    if (t == 0) {
+      ml_s[(warp * ROWS + row) * 2] = m_run[h2];
+      ml_s[(warp * ROWS + row) * 2 + 1] = l_run[h2];
+    }
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      float* dst = o_s + ((size_t)warp * ROWS + row) * D + nb * 8 + 2 * t;
+      dst[0] = o[nb][h2 * 2];
+      dst[1] = o[nb][h2 * 2 + 1];
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < gn * D; i += WARPS * 32) {
+    const int row = i / D, e = i % D;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) top = fmaxf(top, ml_s[(w * ROWS + row) * 2]);
+    float sum = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float mw = ml_s[(w * ROWS + row) * 2];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - top);
+      sum = fmaf(ml_s[(w * ROWS + row) * 2 + 1], f, sum);
+      acc = fmaf(o_s[((size_t)w * ROWS + row) * D + e], f, acc);
+    }
+    const size_t head = (size_t)tok * H + head0 + row;
+    if (splits == 1) {
+      out[head * D + e] = __float2bfloat16_rn(acc / sum);
+    } else {
+      part_o[(head * splits + split) * D + e] = acc;
+      if (e == 0) {
+        part_ml[(head * splits + split) * 2] = top;  // in units of log2(e)
+        part_ml[(head * splits + split) * 2 + 1] = sum;
+      }
+    }
+  }
+}
+
+__global__ void decode_merge_bf16_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         const int* __restrict__ seq_of_token, bf16* __restrict__ out, int H, int D,
+                                         int splits) {
+  const int tok = blockIdx.x, head = blockIdx.y;
+  if (seq_of_token[tok] < 0) return;  // the split kernel wrote the zeros
+  const size_t base = ((size_t)tok * H + head) * splits;
+  float top = -INFINITY;
+  for (int s = 0; s < splits; ++s) top = fmaxf(top, part_ml[(base + s) * 2]);
+  for (int e = threadIdx.x; e < D; e += blockDim.x) {
+    float sum = 0.f, acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = part_ml[(base + s) * 2];
+      const float f = ms == -INFINITY ? 0.f : exp2f(ms - top);
+      sum = fmaf(part_ml[(base + s) * 2 + 1], f, sum);
+      acc = fmaf(part_o[(base + s) * D + e], f, acc);
+    }
+    out[((size_t)tok * H + head) * D + e] = __float2bfloat16_rn(acc / sum);
+  }
+}
+
+template <int D>
+int launch(const void* q, const void* k_pool, const void* v_pool, const int* block_table, int max_blocks,
+           const int* seq_of_token, const int* positions, void* out, float* part_o, float* part_ml, float scale,
+           int window, int page_size, int N, int H, int KH, int splits, cudaStream_t stream) {
+  constexpr int STRIDE = D + 8;
+  constexpr int tiles_bytes = (ROWS + 2 * STAGES * BK) * STRIDE * (int)sizeof(bf16);
+  constexpr int merge_bytes = ROWS * STRIDE * (int)sizeof(bf16) + WARPS * ROWS * (D + 2) * (int)sizeof(float);
+  constexpr int smem = tiles_bytes > merge_bytes ? tiles_bytes : merge_bytes;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int G = H / KH, row_tiles = (G + ROWS - 1) / ROWS;
+  decode_attention_kernel<D><<<dim3(N, KH * row_tiles, splits), WARPS * 32, smem, stream>>>(
+      (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, seq_of_token, positions,
+      (bf16*)out, part_o, part_ml, scale, window, page_size, H, KH, row_tiles, splits);
+  int err = launch_status();
+  if (err || splits == 1) return err;
+  decode_merge_bf16_kernel<<<dim3(N, H), D >= 64 ? 64 : 32, 0, stream>>>(part_o, part_ml, seq_of_token, (bf16*)out, H, D, splits);
+  return launch_status();
+}
+
+}  // namespace
+
+// Scratch (untouched when splits == 1): part_o float32 [N, H, splits, D], part_ml float32 [N, H, splits, 2].
+AKAS_API int akas_decode_attention_bf16(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
+                                        int max_blocks, const int* seq_of_token, const int* positions, void* out,
+                                        float* part_o, float* part_ml, float scale, int window, int page_size, int N,
+                                        int H, int KH, int D, int splits, cudaStream_t stream) {
+  if (H % KH || splits < 1 || splits > 65535 || (long long)KH * ((H / KH + ROWS - 1) / ROWS) > 65535)
+    return (int)cudaErrorInvalidValue;
+  if (N <= 0) return 0;
+#define AKAS_DECODE(DD)                                                                                             \
+  case DD:                                                                                                          \
+    return launch<DD>(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, part_o, part_ml,    \
+                      scale, window, page_size, N, H, KH, splits, stream)
+  switch (D) {
+    AKAS_DECODE(16);
+    AKAS_DECODE(32);
+    AKAS_DECODE(64);
+    AKAS_DECODE(128);
+    default:
+      return (int)cudaErrorInvalidValue;
+  }
+#undef AKAS_DECODE
+}

@@ -46,6 +46,7 @@ class StepContext:
     max_query_len: int
     max_context: int  # largest position + 1 in the batch
     decode_only: bool  # every request brings exactly one token
+    query_tiles: int = 0  # sum over requests of ceil(tokens / 64): the grid of the prompt-attention kernel
     memo: Dict = field(default_factory=dict)  # per-step results shared between layers (rotary tables)
 
     def block_table(self, group: int) -> torch.Tensor:

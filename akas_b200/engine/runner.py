@@ -141,6 +141,7 @@ class ModelRunner:
             max_q, max_ctx = fill_batch(host.numpy(), lay, entries, self.cache)
             dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
             ctx = self._context(dev, lay, max_q, max_ctx, decode_only)
+            ctx.query_tiles = sum(-(-len(e.tokens) // 64) for e in entries)
             logits = self.model.forward(ctx, self.cache.views)
         for e in entries:
             self.cache.advance(e.request, len(e.tokens))

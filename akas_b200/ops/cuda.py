@@ -50,6 +50,15 @@ _SIGNATURES = {
                                         c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                         c_int, c_void_p],
     },
+    "attention_prefill": {
+        "akas_prefill_attention_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "attention_decode": {
+        "akas_decode_attention_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_void_p],
+    },
     "sgemm": {
         "akas_sgemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
@@ -69,7 +78,7 @@ _functions = {}
 def libraries_for(dtype: torch.dtype) -> list:
     """The kernel files a model of this compute dtype needs."""
     names = ["elementwise", "conv", "rope", "attention", "sampling"]
-    names.append("sgemm" if dtype == torch.float32 else "gemm_bf16")
+    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "attention_prefill", "attention_decode"]
     return names
 
 
@@ -271,7 +280,7 @@ def decode_splits(num_tokens: int, kv_heads: int, head_tiles: int, max_context: 
     """How many parts the keys of a decoding request are cut into, from sizes known on the host."""
     blocks = max(1, num_tokens * kv_heads * head_tiles)
     want = -(-2 * 148 // blocks)  # about two blocks per SM
-    most = max(1, -(-max_context // 256))  # at least 256 keys per part
+    most = max(1, -(-max_context // 128))  # at least two 64-key tiles per part
     return max(1, min(want, most, 64))
 
 
@@ -284,14 +293,35 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
     win = int(window) if window else 0
     if ctx is not None and ctx.decode_only:
         group = heads // kh
+        keys = win if win else ctx.max_context
+        if q.dtype == torch.bfloat16 and d in (16, 32, 64, 128):
+            # tensor-core kernel: the query heads of a group are the rows of one tile
+            splits = decode_splits(n, kh, -(-group // 16), keys)
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = torch.empty((n, heads, splits, d), dtype=torch.float32, device=q.device)
+                part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
+            _check(_fn("attention_decode", "akas_decode_attention_bf16")(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
+                _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
+                splits, _stream()), "decode_attention", kernels=2 if splits > 1 else 1)
+            return out
         gt = 8 if group >= 8 else 4 if group > 2 else group
-        splits = decode_splits(n, kh, -(-group // gt), win if win else ctx.max_context)
+        splits = decode_splits(n, kh, -(-group // gt), keys)
         part_o = torch.empty((n, heads, splits, d), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
         _check(_fn("attention", "akas_paged_attention_decode")(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
             _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
             splits, _code(q), _stream()), "paged_attention_decode", kernels=2)
+        return out
+    tiles = getattr(ctx, "query_tiles", 0) if ctx is not None else 0
+    if q.dtype == torch.bfloat16 and d in (16, 32, 64, 128) and tiles > 0:
+        # prompt portions (and whatever decodes beside them): 64-query tiles on the tensor cores
+        _check(_fn("attention_prefill", "akas_prefill_attention_bf16")(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_seqlens),
+            _ptr(positions), _ptr(out), float(scale), win, page_size, tiles, heads, kh, d, ctx.cu_seqlens.numel() - 1,
+            _stream()), "prefill_attention")
         return out
     _check(_fn("attention", "akas_paged_attention")(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),

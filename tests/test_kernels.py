@@ -206,6 +206,39 @@ def test_paged_attention(ops, dtype, h, kh, d, page, window):
     _close(got, want, dtype, "mixed batch")
 
 
+class _Prompt:
+    decode_only = False
+
+    def __init__(self, cu, lengths):
+        self.cu_seqlens = cu
+        self.query_tiles = sum(-(-n // 64) for n in lengths)
+        self.max_context = 0
+
+
+@pytest.mark.parametrize("h,kh,d,page,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (8, 2, 64, 64, None), (6, 2, 64, 8, 37), (16, 2, 128, 32, None),
+    (5, 1, 128, 16, 100), (32, 8, 64, 64, 70), (2, 2, 16, 4, None),
+])
+def test_prompt_attention_on_tensor_cores(ops, h, kh, d, page, window):
+    """Portions that start mid-page and mid-tile, of 1 to 200 tokens, beside decoded tokens with long contexts."""
+    cuda, ref = ops
+    dtype = torch.bfloat16
+    lengths, starts = [37, 1, 200, 1, 64, 65, 0, 130], [29, 333, 0, 64, 64, 100, 5, 700]
+    cu, seq = _batch(lengths)
+    pos = torch.tensor([s + j for s, n in zip(starts, lengths) for j in range(n)], dtype=torch.int32, device=DEV)
+    contexts = [s + l for s, l in zip(starts, lengths)]
+    pages = sum(-(-c // page) for c in contexts) + 3
+    bt = _tables(contexts, page, pages, 4)
+    k, v = _pools(pages, kh, page, d, dtype, 40)
+    q = _rand((pos.numel(), h * d), dtype, 42)
+    scale = d ** -0.5
+    want = ref.paged_attention(q, k, v, bt, seq, pos, scale, window, page)
+    got = cuda.paged_attention(q, k, v, bt, seq, pos, scale, window, page, _Prompt(cu, lengths))
+    _close(got, want, dtype, "tensor-core prompt attention")
+    general = cuda.paged_attention(q, k, v, bt, seq, pos, scale, window, page)
+    _close(general, want, dtype, "general kernel")
+
+
 class _Decode:
     decode_only = True
 
