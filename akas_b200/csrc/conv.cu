@@ -71,6 +71,53 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, float* __rest
   for (int i = 0; i < L - 1; ++i) rows[(size_t)i * C] = next[i];
 }
 
+// Steps that only decode: token t is the single token of request seq_of_token[t]. One thread per (token,
+// channel) reads the state rows, forms the output and writes the shifted state: one launch instead of two.
+template <typename T>
+__global__ void short_conv_decode_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
+                                         const float* __restrict__ bias, float* __restrict__ state,
+                                         const int* __restrict__ seq_of_token, const int* __restrict__ slots,
+                                         T* __restrict__ out, int C, int L) {
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int r = seq_of_token[t];
+  const int slot = r >= 0 ? slots[r] : -1;
+  if (slot < 0) {
+    out[(size_t)t * C + c] = from_f32<T>(0.f);
+    return;
+  }
+  const T* row = bcx + (size_t)t * 3 * C;
+  const float u = to_f32(row[c]) * to_f32(row[2 * C + c]);
+  float* hist = state + (size_t)slot * (L - 1) * C + c;
+  float acc = 0.f;
+  for (int i = 0; i < L - 1; ++i) {
+    const float h = hist[(size_t)i * C];
+    acc = fmaf(h, taps[(size_t)c * L + i], acc);
+    if (i > 0) hist[(size_t)(i - 1) * C] = h;
+  }
+  acc = fmaf(u, taps[(size_t)c * L + L - 1], acc);
+  hist[(size_t)(L - 2) * C] = u;
+  if (bias) acc += bias[c];
+  out[(size_t)t * C + c] = from_f32<T>(to_f32(row[C + c]) * acc);
+}
+
+AKAS_API int akas_short_conv_decode(const void* bcx, const float* taps, const float* bias, float* state,
+                                    const int* seq_of_token, const int* slots, void* out, int N, int C, int L,
+                                    int dtype, cudaStream_t stream) {
+  if (L < 2 || L > AKAS_CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
+  if (N <= 0) return 0;
+  const int threads = 128;
+  const dim3 grid(N, (C + threads - 1) / threads);
+  if (dtype == AKAS_F32)
+    short_conv_decode_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, taps, bias, state, seq_of_token,
+                                                                  slots, (float*)out, C, L);
+  else
+    short_conv_decode_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, taps, bias, state, seq_of_token,
+                                                                 slots, (bf16*)out, C, L);
+  return launch_status();
+}
+
 AKAS_API int akas_short_conv(const void* bcx, const float* taps, const float* bias, float* state,
                              const int* cu_seqlens, const int* seq_of_token, const int* slots, void* out, int N,
                              int R, int C, int L, int dtype, cudaStream_t stream) {

@@ -16,7 +16,7 @@ from typing import Callable, Dict, List, Optional
 import torch
 
 from ..config.specs import ModelSpec
-from ..parts.base import Param, Runtime, build_part
+from ..parts.base import Param, Runtime, build_part, project
 from ..parts.block import Block
 
 
@@ -73,5 +73,8 @@ class Decoder:
             h = self.blocks[entry.layer].forward(h, ctx, caches[owner], write=entry.cache is None)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
-        x = self.final_norm.forward(h, rows=ctx.logit_rows)
-        return ops.linear(x, self.head, out_dtype=torch.float32)
+        if hasattr(self.final_norm, "lazy"):
+            x = self.final_norm.lazy(h, rows=ctx.logit_rows)
+        else:
+            x = self.final_norm.forward(h, rows=ctx.logit_rows)
+        return project(self.rt, x, self.head, out_dtype=torch.float32)

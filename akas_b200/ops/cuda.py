@@ -34,6 +34,7 @@ _SIGNATURES = {
     },
     "conv": {
         "akas_short_conv": [c_void_p] * 8 + [c_int] * 5 + [c_void_p],
+        "akas_short_conv_decode": [c_void_p] * 7 + [c_int] * 4 + [c_void_p],
     },
     "rope": {
         "akas_rope_tables": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -59,6 +60,10 @@ _SIGNATURES = {
                                        c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_void_p],
     },
+    "skinny_gemm": {
+        "akas_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                             c_int, c_int, c_void_p],
+    },
     "sgemm": {
         "akas_sgemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
@@ -78,7 +83,7 @@ _functions = {}
 def libraries_for(dtype: torch.dtype) -> list:
     """The kernel files a model of this compute dtype needs."""
     names = ["elementwise", "conv", "rope", "attention", "sampling"]
-    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "attention_prefill", "attention_decode"]
+    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "skinny_gemm", "attention_prefill", "attention_decode"]
     return names
 
 
@@ -215,6 +220,16 @@ def linear(x, w, out_dtype=None, residual=None):
         return out
     if x.dtype != torch.bfloat16:
         raise TypeError(f"linear takes float32 or bfloat16, got {x.dtype}")
+    if n <= _SKINNY_ROWS and k % 32 == 0:
+        # a handful of tokens: the weights are streamed once by the skinny kernel
+        if residual is not None:
+            out, mode = residual, _OUT_ACC
+        else:
+            target = out_dtype or torch.bfloat16
+            out = torch.empty((n, o), dtype=target, device=x.device)
+            mode = _OUT_F32 if target == torch.float32 else _OUT_BF16
+        _skinny(x, None, None, 0.0, False, w, out, n, o, k, 0, mode)
+        return out
     if k % 8:
         raise ValueError(f"bfloat16 matrix products need an inner size that is a multiple of 8, got {k}")
     if residual is not None:
@@ -229,13 +244,58 @@ def linear(x, w, out_dtype=None, residual=None):
     return out
 
 
+_SKINNY_ROWS = 16
+_OUT_BF16, _OUT_F32, _OUT_ACC, _OUT_SWIGLU = 0, 1, 2, 3
+
+
+def _skinny(x, rows, norm_w, eps, zero_centered, w, out, m, o, k, in_mode, out_mode):
+    _check(_fn("skinny_gemm", "akas_skinny_gemm")(_ptr(x), _ptr(rows), _ptr(norm_w), float(eps), int(bool(zero_centered)),
+                                                 _ptr(w), _ptr(out), m, o, k, in_mode, out_mode, _stream()),
+           f"skinny product [{m}x{k}] x [{o}x{k}]^T")
+
+
+def linear_swiglu(x, w_gate_up):
+    """swiglu(x . w^T) with w the stacked [2F, K] gate and up matrices: [N, F] in x's dtype."""
+    n, k = x.shape
+    f2 = w_gate_up.shape[0]
+    if x.dtype == torch.bfloat16 and n <= _SKINNY_ROWS and k % 32 == 0 and f2 % 2 == 0:
+        out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
+        _skinny(_dense(x, "x"), None, None, 0.0, False, _dense(w_gate_up, "w"), out, n, f2, k, 0, _OUT_SWIGLU)
+        return out
+    return swiglu(linear(x, w_gate_up))
+
+
+def norm_linear(h, norm_weight, eps, zero_centered, w, out_dtype=None, rows=None, swiglu_out=False):
+    """linear(rmsnorm(h[rows]), w), optionally through swiglu: the norm rides in the product for few tokens."""
+    m = rows.numel() if rows is not None else h.shape[0]
+    k, o = h.shape[1], w.shape[0]
+    if (w.dtype == torch.bfloat16 and h.dtype == torch.float32 and m <= _SKINNY_ROWS and k % 32 == 0
+            and h.is_contiguous() and (not swiglu_out or o % 2 == 0)):
+        if swiglu_out:
+            out = torch.empty((m, o // 2), dtype=torch.bfloat16, device=h.device)
+            mode = _OUT_SWIGLU
+        else:
+            target = out_dtype or torch.bfloat16
+            out = torch.empty((m, o), dtype=target, device=h.device)
+            mode = _OUT_F32 if target == torch.float32 else _OUT_BF16
+        _skinny(h, rows, norm_weight, eps, zero_centered, _dense(w, "w"), out, m, o, k, 1, mode)
+        return out
+    x = rmsnorm(h, norm_weight, eps, zero_centered, w.dtype, rows)
+    return linear_swiglu(x, w) if swiglu_out else linear(x, w, out_dtype=out_dtype)
+
+
 # --------------------------------------------------------------------------- mixers
 
 
-def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots):
+def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots, decode_only=False):
     n, c3 = bcx.shape
     c, l = c3 // 3, taps.shape[1]
     out = torch.empty((n, c), dtype=bcx.dtype, device=bcx.device)
+    if decode_only:
+        _check(_fn("conv", "akas_short_conv_decode")(_ptr(_dense(bcx, "bcx")), _ptr(taps), _ptr(bias), _ptr(state),
+                                                    _ptr(seq_of_token), _ptr(slots), _ptr(out), n, c, l, _code(bcx),
+                                                    _stream()), "short_conv_decode")
+        return out
     _check(_fn("conv", "akas_short_conv")(_ptr(_dense(bcx, "bcx")), _ptr(taps), _ptr(bias), _ptr(state),
                                          _ptr(cu_seqlens), _ptr(seq_of_token), _ptr(slots), _ptr(out), n,
                                          slots.numel(), c, l, _code(bcx), _stream()), "short_conv", kernels=2)

@@ -53,7 +53,16 @@ def swiglu(gate_up):
     return (g / (1 + torch.exp(-g)) * u).to(gate_up.dtype)
 
 
-def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots):
+def linear_swiglu(x, w_gate_up):
+    return swiglu(linear(x, w_gate_up))
+
+
+def norm_linear(h, norm_weight, eps, zero_centered, w, out_dtype=None, rows=None, swiglu_out=False):
+    x = rmsnorm(h, norm_weight, eps, zero_centered, w.dtype, rows)
+    return linear_swiglu(x, w) if swiglu_out else linear(x, w, out_dtype=out_dtype)
+
+
+def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots, decode_only=False):
     n, c3 = bcx.shape
     c = c3 // 3
     l = taps.shape[1]

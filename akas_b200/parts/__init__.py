@@ -3,12 +3,15 @@
 from .base import (
     FeedForward,
     Mixer,
+    Normed,
     PagedKVSpec,
     Param,
     Part,
     Runtime,
     StateSpec,
     build_part,
+    project,
+    project_swiglu,
     register_ffn,
     register_mixer,
     register_norm,
@@ -22,7 +25,7 @@ from .shortconv import ShortConv
 from .swiglu import SwiGLU
 
 __all__ = [
-    "ARRANGEMENTS", "Attention", "Block", "FeedForward", "Mixer", "PagedKVSpec", "Param", "Part", "RMSNorm",
-    "Rope", "Runtime", "ShortConv", "StateSpec", "SwiGLU", "build_part", "register_ffn", "register_mixer",
+    "ARRANGEMENTS", "Attention", "Block", "FeedForward", "Mixer", "Normed", "PagedKVSpec", "Param", "Part", "RMSNorm",
+    "Rope", "Runtime", "ShortConv", "StateSpec", "SwiGLU", "build_part", "project", "project_swiglu", "register_ffn", "register_mixer",
     "register_norm", "register_position",
 ]

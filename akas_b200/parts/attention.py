@@ -13,10 +13,12 @@ from __future__ import annotations
 
 import torch
 
-from .base import Mixer, PagedKVSpec, Param, build_part, register_mixer, renamed
+from .base import Mixer, PagedKVSpec, Param, build_part, project, register_mixer, renamed
 
 
 class Attention(Mixer):
+    takes_normed = True
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         s = spec
@@ -62,7 +64,7 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, cache=None, residual=None, write=True):
         s, ops = self.spec, self.rt.ops
-        qkv = ops.linear(x, self.w_qkv)
+        qkv = project(self.rt, x, self.w_qkv)
         fused = self.position is None or hasattr(self.position, "tables")
         cos = sin = None
         if self.position is not None and fused:
@@ -88,7 +90,7 @@ class Attention(Mixer):
             q, cache.k, cache.v, ctx.block_table(cache.group), ctx.seq_of_token, ctx.positions,
             self.scale, s.window, cache.page_size, ctx,
         )
-        return ops.linear(out, self.w_out, residual=residual)
+        return project(self.rt, out, self.w_out, residual=residual)
 
 
 register_mixer("attention", Attention)

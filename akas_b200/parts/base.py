@@ -8,7 +8,8 @@ prefix that the block passes, and sizes through its spec.
 
 Interfaces (duck-typed; these base classes only document and give defaults):
 
-* Norm: ``params()``, ``load(get)``, ``forward(x, out_dtype=None, rows=None)``.
+* Norm: ``params()``, ``load(get)``, ``forward(x, out_dtype=None, rows=None)``; optionally
+  ``lazy(h, rows=None)`` -> ``Normed`` so that a following product may absorb it.
 * PositionEncoding: ``prepare(ctx)`` once per step, ``tables(ctx)`` -> (cos, sin)
   for the fused rotary kernel, or ``apply(q, k, ctx)`` for any other encoding.
 * Mixer: ``params()``, ``load(get)``, ``cache()`` -> the cache it needs (a
@@ -73,7 +74,49 @@ class Runtime:
     ops: Any
 
 
+class Normed:
+    """The output of a norm that has not run yet: ``norm(h[rows])``.
+
+    A block hands it to parts that set ``takes_normed``; they pass it to ``project`` /
+    ``project_swiglu`` for their first matrix product, where the kernels may compute the norm inside
+    the product instead of in a pass of its own. ``tensor()`` runs the norm and gives the plain result.
+    """
+
+    def __init__(self, norm, h, rows=None):
+        self.norm, self.h, self.rows = norm, h, rows
+        self._tensor = None
+
+    def tensor(self):
+        if self._tensor is None:
+            self._tensor = self.norm.forward(self.h, rows=self.rows)
+        return self._tensor
+
+
+def project(rt: "Runtime", x, w, out_dtype=None, residual=None):
+    """``x . w^T`` for a tensor or a ``Normed``; with ``residual`` the product is added into it."""
+    if isinstance(x, Normed):
+        spec = x.norm.spec
+        if residual is None and getattr(spec, "kind", None) == "rmsnorm" and hasattr(rt.ops, "norm_linear"):
+            return rt.ops.norm_linear(x.h, x.norm.weight, spec.eps, spec.zero_centered, w, out_dtype, x.rows)
+        x = x.tensor()
+    return rt.ops.linear(x, w, out_dtype=out_dtype, residual=residual)
+
+
+def project_swiglu(rt: "Runtime", x, w_gate_up):
+    """``silu(x . w1^T) * (x . w3^T)`` for the stacked ``[w1; w3]``, for a tensor or a ``Normed``."""
+    if isinstance(x, Normed):
+        spec = x.norm.spec
+        if getattr(spec, "kind", None) == "rmsnorm" and hasattr(rt.ops, "norm_linear"):
+            return rt.ops.norm_linear(x.h, x.norm.weight, spec.eps, spec.zero_centered, w_gate_up, None, x.rows, True)
+        x = x.tensor()
+    if hasattr(rt.ops, "linear_swiglu"):
+        return rt.ops.linear_swiglu(x, w_gate_up)
+    return rt.ops.swiglu(rt.ops.linear(x, w_gate_up))
+
+
 class Part:
+    takes_normed = False  # True: forward accepts a ``Normed`` in place of the normed tensor
+
     def __init__(self, spec, runtime: Runtime):
         self.spec = spec
         self.rt = runtime

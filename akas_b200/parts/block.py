@@ -10,11 +10,16 @@ from __future__ import annotations
 from .base import Runtime, build_part
 
 
+def _normed(norm, part, h):
+    """The norm's output for ``part``: left to the part's first product when both sides can do that."""
+    if getattr(part, "takes_normed", False) and hasattr(norm, "lazy"):
+        return norm.lazy(h)
+    return norm.forward(h)
+
+
 def _pre_norm(block, h, ctx, cache, write):
-    x = block.mixer_norm.forward(h)
-    h = block.mixer.forward(x, ctx, cache, residual=h, write=write)
-    x = block.ffn_norm.forward(h)
-    return block.ffn.forward(x, ctx, residual=h)
+    h = block.mixer.forward(_normed(block.mixer_norm, block.mixer, h), ctx, cache, residual=h, write=write)
+    return block.ffn.forward(_normed(block.ffn_norm, block.ffn, h), ctx, residual=h)
 
 
 ARRANGEMENTS = {"pre_norm": _pre_norm}

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Param, Part, register_norm
+from .base import Normed, Param, Part, register_norm
 
 
 class RMSNorm(Part):
@@ -29,6 +29,10 @@ class RMSNorm(Part):
         return self.rt.ops.rmsnorm(
             x, self.weight, self.spec.eps, self.spec.zero_centered, out_dtype or self.rt.dtype, rows
         )
+
+
+    def lazy(self, h, rows=None) -> Normed:
+        return Normed(self, h, rows)
 
 
 register_norm("rmsnorm", RMSNorm)

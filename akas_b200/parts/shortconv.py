@@ -13,10 +13,12 @@ from __future__ import annotations
 
 import torch
 
-from .base import Mixer, Param, StateSpec, register_mixer, renamed
+from .base import Mixer, Param, StateSpec, project, register_mixer, renamed
 
 
 class ShortConv(Mixer):
+    takes_normed = True
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         if not 2 <= spec.kernel_size <= 16:
@@ -49,9 +51,10 @@ class ShortConv(Mixer):
 
     def forward(self, x, ctx, cache=None, residual=None, write=True):
         ops = self.rt.ops
-        bcx = ops.linear(x, self.w_in)
-        y = ops.short_conv(bcx, self.taps, self.bias, cache.state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots)
-        return ops.linear(y, self.w_out, residual=residual)
+        bcx = project(self.rt, x, self.w_in)
+        y = ops.short_conv(bcx, self.taps, self.bias, cache.state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots,
+                           decode_only=ctx.decode_only)
+        return project(self.rt, y, self.w_out, residual=residual)
 
 
 register_mixer("short_conv", ShortConv)

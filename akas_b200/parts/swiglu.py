@@ -10,10 +10,12 @@ from __future__ import annotations
 
 import torch
 
-from .base import FeedForward, Param, register_ffn, renamed
+from .base import FeedForward, Param, project, project_swiglu, register_ffn, renamed
 
 
 class SwiGLU(FeedForward):
+    takes_normed = True
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.w_gate_up = self.w_down = None
@@ -34,9 +36,8 @@ class SwiGLU(FeedForward):
         self.w_down = get(self._n("w2.weight"))
 
     def forward(self, x, ctx, residual=None):
-        ops = self.rt.ops
-        act = ops.swiglu(ops.linear(x, self.w_gate_up))
-        return ops.linear(act, self.w_down, residual=residual)
+        act = project_swiglu(self.rt, x, self.w_gate_up)
+        return project(self.rt, act, self.w_down, residual=residual)
 
 
 register_ffn("swiglu", SwiGLU)

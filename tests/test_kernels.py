@@ -97,6 +97,49 @@ def test_linear_bfloat16(ops, n, k, o):
         cuda.linear(_rand((n, 60), torch.bfloat16, 5), _rand((o, 60), torch.bfloat16, 6))
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("k,o", [(64, 50), (96, 320), (2048, 37), (8192, 64)])
+def test_skinny_products_for_few_tokens(ops, m, k, o):
+    """The decode-step product kernel: plain, float32 out, accumulate, SwiGLU, and with the norm riding along."""
+    cuda, ref = ops
+    x, w = _rand((m, k), torch.bfloat16, 5), _rand((o, k), torch.bfloat16, 6, 0.05)
+    want = x.double() @ w.double().T
+    _close(cuda.linear(x, w), want, torch.bfloat16, "bf16 out")
+    _close(cuda.linear(x, w, out_dtype=torch.float32), want, torch.float32, "f32 out")
+    res = _rand((m, o), torch.float32, 7)
+    _close(cuda.linear(x, w, residual=res.clone()), res.double() + want, torch.float32, "accumulate")
+    w2 = _rand((2 * o, k), torch.bfloat16, 8, 0.05)
+    _close(cuda.linear_swiglu(x, w2), ref.linear_swiglu(x, w2), torch.bfloat16, "swiglu")
+    # the norm inside the product: float32 rows of a larger residual stream, gathered by index
+    h = _rand((m + 5, k), torch.float32, 9, 3.0)
+    nw = _rand((k,), torch.float32, 10) + 1
+    rows = torch.arange(m + 4, 4, -1, dtype=torch.int32, device=DEV)[:m].contiguous()
+    for zero_centered in (False, True):
+        got = cuda.norm_linear(h, nw, 1e-6, zero_centered, w, torch.float32, rows)
+        _close(got, ref.norm_linear(h, nw, 1e-6, zero_centered, w, torch.float32, rows), torch.bfloat16, "norm + product")
+    got = cuda.norm_linear(h[:m].contiguous(), nw, 1e-5, False, w2, None, None, True)
+    _close(got, ref.norm_linear(h[:m].contiguous(), nw, 1e-5, False, w2, None, None, True), torch.bfloat16, "norm + swiglu")
+    # more tokens than the kernel takes: the library path gives the same
+    big = _rand((40, k), torch.float32, 11)
+    _close(cuda.norm_linear(big, nw, 1e-5, False, w), ref.norm_linear(big, nw, 1e-5, False, w), torch.bfloat16, "many tokens")
+
+
+def test_short_conv_decode_kernel_equals_the_general_one(ops):
+    cuda, ref = ops
+    c, taps = 72, 4
+    seq = torch.tensor([0, 1, 2, -1], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, 1, 2, 3, 3], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([5, 0, 2, -1], dtype=torch.int32, device=DEV)
+    for dtype in DTYPES:
+        bcx = _rand((4, 3 * c), dtype, 10)
+        w, b = _rand((c, taps), torch.float32, 11), _rand((c,), torch.float32, 12)
+        state = _rand((8, taps - 1, c), torch.float32, 13)
+        s1, s2 = state.clone(), state.clone()
+        got = cuda.short_conv(bcx, w, b, s1, cu, seq, slots, decode_only=True)
+        want = cuda.short_conv(bcx, w, b, s2, cu, seq, slots)
+        assert torch.equal(got, want) and torch.equal(s1, s2)
+
+
 def _batch(lengths, pad=0):
     """cu_seqlens, seq_of_token, for requests of the given lengths, plus ``pad`` padding tokens."""
     cu = [0]
