@@ -6,7 +6,9 @@
 // split K in 32-wide chunks; in a chunk, thread (g, t) of a warp loads 16 contiguous bytes of W rows g
 // and g + 8 and of the activations of token g at k = 32c + 8t. The 8 values feed two k-steps; the
 // product does not care which physical k sits in which k-slot as long as A and B agree, which is
-// what makes 16-byte loads possible. Partial sums of the 8 warps meet in shared memory.
+// what makes 16-byte loads possible. The weight rows arrive through a six-stage ring of 256-wide
+// chunks in shared memory filled by cp.async (40 KB of loads in flight per block, several blocks per
+// SM), the activations come from L1/L2 one chunk ahead. Partial sums of the 8 warps meet in shared memory.
 //
 // Input modes:   bf16   x is bfloat16 [M, K]
 //                norm   x is the float32 residual stream (rows optionally gathered by index); the kernel
@@ -25,38 +27,53 @@ using namespace akas;
 
 namespace {
 
-constexpr int WARPS = 8;
+constexpr int WARPS = 8, KC = 256, STAGES = 6, AS = KC + 32;  // AS: row stride of a stage, 16 words off a multiple of 32 banks
 enum { IN_BF16 = 0, IN_NORM = 1 };
 enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_ACC = 2, OUT_SWIGLU = 3 };
+
+template <int NT, int IN>
+struct BFrag {
+  uint4 raw[NT];        // IN_BF16: 8 bfloat16 of the token's activations
+  float4 lo[NT], hi[NT];  // IN_NORM: 8 float32 of the residual stream
+  float4 w_lo, w_hi;    // IN_NORM: 8 norm weights
+};
 
 template <int NT, int IN, int OUT>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const void* __restrict__ x_, const int* __restrict__ rows, const float* __restrict__ norm_w,
                    float eps, int zero_centered, const bf16* __restrict__ W, void* __restrict__ y_, int M, int O,
                    int K) {
-  __shared__ float red[WARPS][NT][16][8];
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* ring = reinterpret_cast<bf16*>(smem_raw);  // [STAGES][16][AS]
   __shared__ float ss_s[WARPS][NT * 8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  // weight rows of this block: output channels o0 .. o0+15, or 8 gate + 8 up rows
   const int F = O / 2;  // swiglu only: O is the stacked height 2F
-  int row_a, row_b;
-  bool ok_a, ok_b;
-  if (OUT == OUT_SWIGLU) {
-    const int f = blockIdx.x * 8 + g;
-    ok_a = ok_b = f < F;
-    row_a = ok_a ? f : 0;
-    row_b = ok_a ? F + f : 0;
-  } else {
-    row_a = blockIdx.x * 16 + g;
-    row_b = row_a + 8;
-    ok_a = row_a < O;
-    ok_b = row_b < O;
-    if (!ok_a) row_a = 0;
-    if (!ok_b) row_b = 0;
+
+  // weight row that stage row i of this block holds, or -1
+  auto weight_row = [&](int i) -> int {
+    if (OUT == OUT_SWIGLU) {
+      const int f = blockIdx.x * 8 + (i & 7);
+      return f < F ? (i < 8 ? f : F + f) : -1;
+    }
+    const int o = blockIdx.x * 16 + i;
+    return o < O ? o : -1;
+  };
+  const int chunks = (K + KC - 1) / KC;
+  auto load_stage = [&](int c) {
+    const int k0 = c * KC, len = min(KC, K - k0), per_row = len / 8;
+    bf16* dst = ring + (size_t)(c % STAGES) * 16 * AS;
+    for (int i = tid; i < 16 * per_row; i += WARPS * 32) {
+      const int row = i / per_row, col = (i % per_row) * 8;
+      const int wr = weight_row(row);
+      cp_async16(dst + row * AS + col, W + (size_t)max(wr, 0) * K + k0 + col, wr >= 0 ? 16 : 0);
+    }
+  };
+#pragma unroll
+  for (int c = 0; c < STAGES - 1; ++c) {
+    if (c < chunks) load_stage(c);
+    cp_async_commit();
   }
-  const bf16* wa = W + (size_t)row_a * K + 8 * t;
-  const bf16* wb = W + (size_t)row_b * K + 8 * t;
 
   // the token this thread feeds into B, per n-block
   const bf16* xb[NT];
@@ -70,60 +87,80 @@ skinny_gemm_kernel(const void* __restrict__ x_, const int* __restrict__ rows, co
     xb[j] = (const bf16*)x_ + src * K + 8 * t;
     xf[j] = (const float*)x_ + src * K + 8 * t;
   }
+  auto load_b = [&](BFrag<NT, IN>& f, int k) {  // k: first of this thread's 8 consecutive k
+    if (k >= K) return;
+    if (IN == IN_NORM) {
+      f.w_lo = *reinterpret_cast<const float4*>(norm_w + k + 8 * t);
+      f.w_hi = *reinterpret_cast<const float4*>(norm_w + k + 8 * t + 4);
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      if (!live[j]) continue;
+      if (IN == IN_BF16) {
+        f.raw[j] = *reinterpret_cast<const uint4*>(xb[j] + k);
+      } else {
+        f.lo[j] = *reinterpret_cast<const float4*>(xf[j] + k);
+        f.hi[j] = *reinterpret_cast<const float4*>(xf[j] + k + 4);
+      }
+    }
+  };
 
   float acc[NT][4];
   float ss[NT];
 #pragma unroll
   for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; ss[j] = 0.f; }
 
-  const int chunks = K / 32;
-#pragma unroll 4
-  for (int c = warp; c < chunks; c += WARPS) {
-    const int k = c * 32;
-    const uint4 a_lo = *reinterpret_cast<const uint4*>(wa + k);
-    const uint4 a_hi = *reinterpret_cast<const uint4*>(wb + k);
-    const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};  // first k-step
-    const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};  // second k-step
-    float nw[8];
-    if (IN == IN_NORM) {
-      const float4 w0 = *reinterpret_cast<const float4*>(norm_w + k + 8 * t);
-      const float4 w1 = *reinterpret_cast<const float4*>(norm_w + k + 8 * t + 4);
-      nw[0] = w0.x; nw[1] = w0.y; nw[2] = w0.z; nw[3] = w0.w;
-      nw[4] = w1.x; nw[5] = w1.y; nw[6] = w1.z; nw[7] = w1.w;
-      if (zero_centered) {
+  BFrag<NT, IN> cur, next;
+  load_b(cur, warp * 32);
+  for (int c = 0; c < chunks; ++c) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();  // chunk c has landed for everyone, and everyone is done with chunk c - 1
+    if (c + STAGES - 1 < chunks) load_stage(c + STAGES - 1);
+    cp_async_commit();
+    const int k = c * KC + warp * 32;  // this warp's 32 k of the chunk
+    load_b(next, k + KC);
+    if (k < K) {
+      const bf16* st = ring + (size_t)(c % STAGES) * 16 * AS + warp * 32 + 8 * t;
+      const uint4 a_lo = *reinterpret_cast<const uint4*>(st + g * AS);
+      const uint4 a_hi = *reinterpret_cast<const uint4*>(st + (g + 8) * AS);
+      const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};  // first k-step: this thread's k 0..3
+      const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};  // second k-step: its k 4..7
 #pragma unroll
-        for (int i = 0; i < 8; ++i) nw[i] += 1.f;
-      }
-    }
+      for (int j = 0; j < NT; ++j) {
+        uint32_t b[4] = {0u, 0u, 0u, 0u};
+        if (live[j]) {
+          if (IN == IN_BF16) {
+            b[0] = cur.raw[j].x; b[1] = cur.raw[j].y; b[2] = cur.raw[j].z; b[3] = cur.raw[j].w;
+          } else {
+            const float v[8] = {cur.lo[j].x, cur.lo[j].y, cur.lo[j].z, cur.lo[j].w,
+                                cur.hi[j].x, cur.hi[j].y, cur.hi[j].z, cur.hi[j].w};
+            float nw[8] = {cur.w_lo.x, cur.w_lo.y, cur.w_lo.z, cur.w_lo.w, cur.w_hi.x, cur.w_hi.y, cur.w_hi.z, cur.w_hi.w};
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      uint32_t b[4] = {0u, 0u, 0u, 0u};
-      if (live[j]) {
-        if (IN == IN_BF16) {
-          const uint4 v = *reinterpret_cast<const uint4*>(xb[j] + k);
-          b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w;
-        } else {
-          const float4 v0 = *reinterpret_cast<const float4*>(xf[j] + k);
-          const float4 v1 = *reinterpret_cast<const float4*>(xf[j] + k + 4);
-          const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            for (int i = 0; i < 8; ++i) {
+              ss[j] = fmaf(v[i], v[i], ss[j]);
+              if (zero_centered) nw[i] += 1.f;
+            }
 #pragma unroll
-          for (int i = 0; i < 8; ++i) ss[j] = fmaf(v[i], v[i], ss[j]);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) b[i] = pack_bf16(v[2 * i] * nw[2 * i], v[2 * i + 1] * nw[2 * i + 1]);
+            for (int i = 0; i < 4; ++i) b[i] = pack_bf16(v[2 * i] * nw[2 * i], v[2 * i + 1] * nw[2 * i + 1]);
+          }
         }
+        mma_bf16(acc[j], a1, b[0], b[1]);
+        mma_bf16(acc[j], a2, b[2], b[3]);
       }
-      mma_bf16(acc[j], a1, b[0], b[1]);
-      mma_bf16(acc[j], a2, b[2], b[3]);
     }
+    cur = next;
   }
+  cp_async_wait<0>();
+  __syncthreads();  // the ring is free: it becomes the buffer where the 8 warps' partial sums meet
 
-  // partial sums of the 8 warps -> shared memory
+  float* red = reinterpret_cast<float*>(smem_raw);  // [WARPS][NT][16][8]
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
-    red[warp][j][g][2 * t] = acc[j][0];
-    red[warp][j][g][2 * t + 1] = acc[j][1];
-    red[warp][j][g + 8][2 * t] = acc[j][2];
-    red[warp][j][g + 8][2 * t + 1] = acc[j][3];
+    float* r0 = red + (((size_t)warp * NT + j) * 16 + g) * 8 + 2 * t;
+    r0[0] = acc[j][0];
+    r0[1] = acc[j][1];
+    r0[64] = acc[j][2];  // row g + 8
+    r0[65] = acc[j][3];
     if (IN == IN_NORM) {
       float s = ss[j];
       s += __shfl_xor_sync(0xffffffffu, s, 1);
@@ -141,8 +178,9 @@ skinny_gemm_kernel(const void* __restrict__ x_, const int* __restrict__ rows, co
     float v = 0.f, u = 0.f;
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) {
-      v += red[w][j][row][tok];
-      if (OUT == OUT_SWIGLU) u += red[w][j][row + 8][tok];
+      const float* r0 = red + (((size_t)w * NT + j) * 16 + row) * 8 + tok;
+      v += r0[0];
+      if (OUT == OUT_SWIGLU) u += r0[64];
     }
     if (IN == IN_NORM) {
       float s = 0.f;
@@ -166,13 +204,24 @@ skinny_gemm_kernel(const void* __restrict__ x_, const int* __restrict__ rows, co
   }
 }
 
+constexpr int kSmemBytes = STAGES * 16 * AS * (int)sizeof(bf16);
+
 template <int NT, int IN>
 int launch_out(int out_mode, const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
                const void* W, void* y, int M, int O, int K, cudaStream_t stream) {
   const int threads = WARPS * 32;
 #define AKAS_SKINNY(OUTM, GRID)                                                                                   \
-  skinny_gemm_kernel<NT, IN, OUTM><<<GRID, threads, 0, stream>>>(x, rows, norm_w, eps, zero_centered,             \
-                                                                 (const bf16*)W, y, M, O, K)
+  {                                                                                                               \
+    static bool configured = false;                                                                               \
+    if (!configured) {                                                                                            \
+      const cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT, IN, OUTM>,                                \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);        \
+      if (e != cudaSuccess) return (int)e;                                                                        \
+      configured = true;                                                                                          \
+    }                                                                                                             \
+    skinny_gemm_kernel<NT, IN, OUTM><<<GRID, threads, kSmemBytes, stream>>>(x, rows, norm_w, eps, zero_centered,  \
+                                                                            (const bf16*)W, y, M, O, K);          \
+  }
   switch (out_mode) {
     case OUT_BF16: AKAS_SKINNY(OUT_BF16, (O + 15) / 16); break;
     case OUT_F32: AKAS_SKINNY(OUT_F32, (O + 15) / 16); break;
