@@ -186,3 +186,68 @@ def run_matrix(model_dir, config, batches=(1, 8), prompts=(2048,), generated=128
                              prefill_tokens_per_s=statistics.median(pp), decode_tokens_per_s=statistics.median(tg)))
     return dict(protocol="native-token-step-v2", dtype=config.dtype, seed=seed, repeats=repeats, warmup=warmup,
                 prefill_chunk=chunk, rows=rows)
+
+
+# --------------------------------------------------------------------------- single kernels
+
+
+def _time_kernel(fn, iters: int, flush_bytes: int = 256 << 20) -> float:
+    """Median milliseconds of ``fn()``; a buffer larger than L2 is rewritten before every timed call."""
+    flush = torch.empty(flush_bytes, dtype=torch.uint8, device="cuda")
+    times = []
+    for i in range(iters + 3):
+        flush.fill_(i & 1)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(start.elapsed_time(end))
+    return statistics.median(times)
+
+
+def bench_linear(m: int, o: int, k: int, mode: str, iters: int = 20) -> dict:
+    """One matrix product of the bfloat16 path, cold L2: mode is bf16 | f32 | acc | swiglu | norm | norm_swiglu."""
+    from .ops import cuda as ops
+
+    ops.require(ops.libraries_for(torch.bfloat16))
+    g = torch.Generator(device="cuda").manual_seed(0)
+    w = (torch.randn((o, k), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn((m, k), device="cuda", generator=g).to(torch.bfloat16)
+    h = torch.randn((m, k), device="cuda", generator=g)
+    nw = torch.ones(k, device="cuda")
+    res = torch.zeros((m, o), device="cuda")
+    fn = {
+        "bf16": lambda: ops.linear(x, w),
+        "f32": lambda: ops.linear(x, w, out_dtype=torch.float32),
+        "acc": lambda: ops.linear(x, w, residual=res),
+        "swiglu": lambda: ops.linear_swiglu(x, w),
+        "norm": lambda: ops.norm_linear(h, nw, 1e-5, False, w),
+        "norm_swiglu": lambda: ops.norm_linear(h, nw, 1e-5, False, w, None, None, True),
+    }[mode]
+    ms = _time_kernel(fn, iters)
+    nbytes = w.numel() * 2
+    return dict(kernel="linear", mode=mode, m=m, o=o, k=k, ms=round(ms, 5), weight_gb_s=round(nbytes / ms / 1e6, 1),
+                tflops=round(2.0 * m * o * k / ms / 1e9, 2))
+
+
+def _main():
+    import argparse
+    import json
+
+    ap = argparse.ArgumentParser(description="time single kernels of the bfloat16 path (cold L2, CUDA events)")
+    sub = ap.add_subparsers(dest="what", required=True)
+    lin = sub.add_parser("linear", help="y = x . w^T with one of the epilogues")
+    lin.add_argument("--m", type=int, nargs="+", default=[8])
+    lin.add_argument("--o", type=int, default=2048)
+    lin.add_argument("--k", type=int, default=2048)
+    lin.add_argument("--mode", default="bf16", choices=("bf16", "f32", "acc", "swiglu", "norm", "norm_swiglu"))
+    lin.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    for m in args.m:
+        print(json.dumps(bench_linear(m, args.o, args.k, args.mode, args.iters)))
+
+
+if __name__ == "__main__":
+    _main()
