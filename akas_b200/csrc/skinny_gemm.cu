@@ -6,9 +6,12 @@
 // split K in 32-wide chunks; in a chunk, thread (g, t) of a warp loads 16 contiguous bytes of W rows g
 // and g + 8 and of the activations of token g at k = 32c + 8t. The 8 values feed two k-steps; the
 // product does not care which physical k sits in which k-slot as long as A and B agree, which is
-// what makes 16-byte loads possible. The weight rows arrive through a six-stage ring of 256-wide
-// chunks in shared memory filled by cp.async (40 KB of loads in flight per block, several blocks per
-// SM), the activations come from L1/L2 one chunk ahead. Partial sums of the 8 warps meet in shared memory.
+// what makes 16-byte loads possible. Blocks are persistent: one or two per SM, each taking row tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ... The weight rows arrive through an eight-stage ring of
+// 256-wide chunks in shared memory filled by cp.async (56 KB of loads in flight per block) that runs
+// on across row tiles; the tokens' activations are put into shared memory once per block (converted
+// and weighted by the norm there, if the norm rides along), so the inner loop reads shared memory
+// only. At the end of a row tile the 8 warps' partial sums meet in shared memory.
 //
 // Input modes:   bf16   x is bfloat16 [M, K]
 //                norm   x is the float32 residual stream (rows optionally gathered by index); the kernel
@@ -27,210 +30,210 @@ using namespace akas;
 
 namespace {
 
-constexpr int WARPS = 8, KC = 256, STAGES = 6, AS = KC + 32;  // AS: row stride of a stage, 16 words off a multiple of 32 banks
+constexpr int WARPS = 8, KC = 256, STAGES = 8, AS = KC + 32;  // AS: row stride of a stage, 16 words off a multiple of 32 banks
 enum { IN_BF16 = 0, IN_NORM = 1 };
 enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_ACC = 2, OUT_SWIGLU = 3 };
-
-template <int NT, int IN>
-struct BFrag {
-  uint4 raw[NT];        // IN_BF16: 8 bfloat16 of the token's activations
-  float4 lo[NT], hi[NT];  // IN_NORM: 8 float32 of the residual stream
-  float4 w_lo, w_hi;    // IN_NORM: 8 norm weights
-};
 
 template <int NT, int IN, int OUT>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const void* __restrict__ x_, const int* __restrict__ rows, const float* __restrict__ norm_w,
                    float eps, int zero_centered, const bf16* __restrict__ W, void* __restrict__ y_, int M, int O,
-                   int K) {
+                   int K, int num_tiles) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* ring = reinterpret_cast<bf16*>(smem_raw);  // [STAGES][16][AS]
-  __shared__ float ss_s[WARPS][NT * 8];
+  bf16* ring = reinterpret_cast<bf16*>(smem_raw);               // [STAGES][16][AS]: weight rows, chunk by chunk
+  float* red = reinterpret_cast<float*>(ring + STAGES * 16 * AS);  // [WARPS][NT][16][8]: the warps' partial sums
+  bf16* xs = reinterpret_cast<bf16*>(red + WARPS * NT * 128);    // [NT * 8][XS]: the tokens' activations, whole K
+  const int XS = K + 32;
+  __shared__ float ss_s[NT * 8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int F = O / 2;  // swiglu only: O is the stacked height 2F
 
-  // weight row that stage row i of this block holds, or -1
-  auto weight_row = [&](int i) -> int {
+  // weight row that stage row i of row tile `tile` holds, or -1
+  auto weight_row = [&](int tile, int i) -> int {
     if (OUT == OUT_SWIGLU) {
-      const int f = blockIdx.x * 8 + (i & 7);
+      const int f = tile * 8 + (i & 7);
       return f < F ? (i < 8 ? f : F + f) : -1;
     }
-    const int o = blockIdx.x * 16 + i;
+    const int o = tile * 16 + i;
     return o < O ? o : -1;
   };
   const int chunks = (K + KC - 1) / KC;
-  auto load_stage = [&](int c) {
-    const int k0 = c * KC, len = min(KC, K - k0), per_row = len / 8;
-    bf16* dst = ring + (size_t)(c % STAGES) * 16 * AS;
-    for (int i = tid; i < 16 * per_row; i += WARPS * 32) {
-      const int row = i / per_row, col = (i % per_row) * 8;
-      const int wr = weight_row(row);
-      cp_async16(dst + row * AS + col, W + (size_t)max(wr, 0) * K + k0 + col, wr >= 0 ? 16 : 0);
-    }
-  };
+  // this block's row tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; its work is the sequence of their chunks
+  const int my_tiles = (num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int items = my_tiles * chunks;
+  int load_tile = blockIdx.x, load_chunk = 0, loaded = 0;  // the next item whose copies are to be issued
+  auto issue_next = [&]() {
+    if (loaded < items) {
+      const int k0 = load_chunk * KC, len = min(KC, K - k0);
+      bf16* dst = ring + (size_t)(loaded % STAGES) * 16 * AS;
+      if (len == KC) {  // the common case: two 16-byte copies per thread, no division
 #pragma unroll
-  for (int c = 0; c < STAGES - 1; ++c) {
-    if (c < chunks) load_stage(c);
-    cp_async_commit();
-  }
-
-  // the token this thread feeds into B, per n-block
-  const bf16* xb[NT];
-  const float* xf[NT];
-  bool live[NT];
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    const int m = 8 * j + g;
-    live[j] = m < M;
-    const size_t src = live[j] ? (size_t)(rows ? rows[m] : m) : 0;
-    xb[j] = (const bf16*)x_ + src * K + 8 * t;
-    xf[j] = (const float*)x_ + src * K + 8 * t;
-  }
-  auto load_b = [&](BFrag<NT, IN>& f, int k) {  // k: first of this thread's 8 consecutive k
-    if (k >= K) return;
-    if (IN == IN_NORM) {
-      f.w_lo = *reinterpret_cast<const float4*>(norm_w + k + 8 * t);
-      f.w_hi = *reinterpret_cast<const float4*>(norm_w + k + 8 * t + 4);
-    }
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      if (!live[j]) continue;
-      if (IN == IN_BF16) {
-        f.raw[j] = *reinterpret_cast<const uint4*>(xb[j] + k);
+        for (int i = tid; i < 16 * (KC / 8); i += WARPS * 32) {
+          const int row = i / (KC / 8), col = (i % (KC / 8)) * 8;
+          const int wr = weight_row(load_tile, row);
+          cp_async16(dst + row * AS + col, W + (size_t)max(wr, 0) * K + k0 + col, wr >= 0 ? 16 : 0);
+        }
       } else {
-        f.lo[j] = *reinterpret_cast<const float4*>(xf[j] + k);
-        f.hi[j] = *reinterpret_cast<const float4*>(xf[j] + k + 4);
+        const int per_row = len / 8;
+        for (int i = tid; i < 16 * per_row; i += WARPS * 32) {
+          const int row = i / per_row, col = (i % per_row) * 8;
+          const int wr = weight_row(load_tile, row);
+          cp_async16(dst + row * AS + col, W + (size_t)max(wr, 0) * K + k0 + col, wr >= 0 ? 16 : 0);
+        }
       }
+      ++loaded;
+      if (++load_chunk == chunks) { load_chunk = 0; load_tile += gridDim.x; }
     }
+    cp_async_commit();
   };
+
+  // Activations into shared memory, once per block. bfloat16 input rides in the first cp.async group.
+  if (IN == IN_BF16) {
+    const int per_row = K / 8;
+    for (int i = tid; i < NT * 8 * per_row; i += WARPS * 32) {
+      const int m = i / per_row, col = (i % per_row) * 8;
+      const size_t src = m < M ? (size_t)(rows ? rows[m] : m) : 0;
+      cp_async16(xs + (size_t)m * XS + col, (const bf16*)x_ + src * K + col, m < M ? 16 : 0);
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < STAGES - 1; ++c) issue_next();
+  if (IN == IN_NORM) {
+    // float32 residual rows -> bf16(x * norm weight); each warp owns tokens warp, warp + 8 and sums x^2
+    for (int m = warp; m < NT * 8; m += WARPS) {
+      float ss = 0.f;
+      bf16* dst = xs + (size_t)m * XS;
+      if (m < M) {
+        const float* src = (const float*)x_ + (size_t)(rows ? rows[m] : m) * K;
+#pragma unroll 4
+        for (int k = lane * 4; k < K; k += 128) {
+          const float4 v = *reinterpret_cast<const float4*>(src + k);
+          float4 w = *reinterpret_cast<const float4*>(norm_w + k);
+          if (zero_centered) { w.x += 1.f; w.y += 1.f; w.z += 1.f; w.w += 1.f; }
+          ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+          uint2 packed;
+          packed.x = pack_bf16(v.x * w.x, v.y * w.y);
+          packed.y = pack_bf16(v.z * w.z, v.w * w.w);
+          *reinterpret_cast<uint2*>(dst + k) = packed;
+        }
+        ss = warp_sum(ss);
+      } else {
+        for (int k = lane * 4; k < K; k += 128) *reinterpret_cast<uint2*>(dst + k) = make_uint2(0u, 0u);
+      }
+      if (lane == 0) ss_s[m] = ss;
+    }
+  }
 
   float acc[NT][4];
-  float ss[NT];
 #pragma unroll
-  for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; ss[j] = 0.f; }
+  for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
 
-  BFrag<NT, IN> cur, next;
-  load_b(cur, warp * 32);
-  for (int c = 0; c < chunks; ++c) {
+  int tile = blockIdx.x, c = 0;
+  for (int n = 0; n < items; ++n) {
     cp_async_wait<STAGES - 2>();
-    __syncthreads();  // chunk c has landed for everyone, and everyone is done with chunk c - 1
-    if (c + STAGES - 1 < chunks) load_stage(c + STAGES - 1);
-    cp_async_commit();
-    const int k = c * KC + warp * 32;  // this warp's 32 k of the chunk
-    load_b(next, k + KC);
+    __syncthreads();  // item n (and the activations) are there for everyone; everyone is done with item n - 1
+    issue_next();
+    const int k = c * KC + warp * 32 + 8 * t;  // this thread's 8 consecutive k of the chunk
     if (k < K) {
-      const bf16* st = ring + (size_t)(c % STAGES) * 16 * AS + warp * 32 + 8 * t;
+      const bf16* st = ring + (size_t)(n % STAGES) * 16 * AS + warp * 32 + 8 * t;
       const uint4 a_lo = *reinterpret_cast<const uint4*>(st + g * AS);
       const uint4 a_hi = *reinterpret_cast<const uint4*>(st + (g + 8) * AS);
       const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};  // first k-step: this thread's k 0..3
       const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};  // second k-step: its k 4..7
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        uint32_t b[4] = {0u, 0u, 0u, 0u};
-        if (live[j]) {
-          if (IN == IN_BF16) {
-            b[0] = cur.raw[j].x; b[1] = cur.raw[j].y; b[2] = cur.raw[j].z; b[3] = cur.raw[j].w;
-          } else {
-            const float v[8] = {cur.lo[j].x, cur.lo[j].y, cur.lo[j].z, cur.lo[j].w,
-                                cur.hi[j].x, cur.hi[j].y, cur.hi[j].z, cur.hi[j].w};
-            float nw[8] = {cur.w_lo.x, cur.w_lo.y, cur.w_lo.z, cur.w_lo.w, cur.w_hi.x, cur.w_hi.y, cur.w_hi.z, cur.w_hi.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              ss[j] = fmaf(v[i], v[i], ss[j]);
-              if (zero_centered) nw[i] += 1.f;
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) b[i] = pack_bf16(v[2 * i] * nw[2 * i], v[2 * i + 1] * nw[2 * i + 1]);
-          }
-        }
-        mma_bf16(acc[j], a1, b[0], b[1]);
-        mma_bf16(acc[j], a2, b[2], b[3]);
+        const uint4 b = *reinterpret_cast<const uint4*>(xs + (size_t)(8 * j + g) * XS + k);
+        mma_bf16(acc[j], a1, b.x, b.y);
+        mma_bf16(acc[j], a2, b.z, b.w);
       }
     }
-    cur = next;
+    if (++c < chunks) continue;
+
+    // the row tile is complete: the 8 warps' partial sums meet in shared memory, then the epilogue
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      float* r0 = red + (((size_t)warp * NT + j) * 16 + g) * 8 + 2 * t;
+      r0[0] = acc[j][0];
+      r0[1] = acc[j][1];
+      r0[64] = acc[j][2];  // row g + 8
+      r0[65] = acc[j][3];
+      acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    }
+    __syncthreads();  // (the next write to `red` is a whole item, and so a barrier, away)
+    constexpr int per_tile = OUT == OUT_SWIGLU ? 64 : 128;  // (row, token) pairs per n-block
+    for (int i = tid; i < NT * per_tile; i += WARPS * 32) {
+      const int j = i / per_tile, row = (i % per_tile) / 8, tok = i % 8;
+      const int m = 8 * j + tok;
+      if (m >= M) continue;
+      float v = 0.f, u = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float* r0 = red + (((size_t)w * NT + j) * 16 + row) * 8 + tok;
+        v += r0[0];
+        if (OUT == OUT_SWIGLU) u += r0[64];
+      }
+      if (IN == IN_NORM) {
+        const float inv = 1.f / sqrtf(ss_s[m] / (float)K + eps);
+        v *= inv;
+        u *= inv;
+      }
+      if (OUT == OUT_SWIGLU) {
+        const int f = tile * 8 + row;
+        if (f < F) ((bf16*)y_)[(size_t)m * F + f] = __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
+      } else {
+        const int o = tile * 16 + row;
+        if (o >= O) continue;
+        const size_t at = (size_t)m * O + o;
+        if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
+        else if (OUT == OUT_F32) ((float*)y_)[at] = v;
+        else ((float*)y_)[at] += v;
+      }
+    }
+    c = 0;
+    tile += gridDim.x;
   }
   cp_async_wait<0>();
-  __syncthreads();  // the ring is free: it becomes the buffer where the 8 warps' partial sums meet
-
-  float* red = reinterpret_cast<float*>(smem_raw);  // [WARPS][NT][16][8]
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    float* r0 = red + (((size_t)warp * NT + j) * 16 + g) * 8 + 2 * t;
-    r0[0] = acc[j][0];
-    r0[1] = acc[j][1];
-    r0[64] = acc[j][2];  // row g + 8
-    r0[65] = acc[j][3];
-    if (IN == IN_NORM) {
-      float s = ss[j];
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      if (t == 0) ss_s[warp][j * 8 + g] = s;
-    }
-  }
-  __syncthreads();
-
-  const int per_tile = OUT == OUT_SWIGLU ? 64 : 128;  // (row, token) pairs per n-block handled in the epilogue
-  for (int i = tid; i < NT * per_tile; i += WARPS * 32) {
-    const int j = i / per_tile, row = (i % per_tile) / 8, tok = i % 8;
-    const int m = 8 * j + tok;
-    if (m >= M) continue;
-    float v = 0.f, u = 0.f;
-#pragma unroll
-    for (int w = 0; w < WARPS; ++w) {
-      const float* r0 = red + (((size_t)w * NT + j) * 16 + row) * 8 + tok;
-      v += r0[0];
-      if (OUT == OUT_SWIGLU) u += r0[64];
-    }
-    if (IN == IN_NORM) {
-      float s = 0.f;
-#pragma unroll
-      for (int w = 0; w < WARPS; ++w) s += ss_s[w][j * 8 + tok];
-      const float inv = 1.f / sqrtf(s / (float)K + eps);
-      v *= inv;
-      u *= inv;
-    }
-    if (OUT == OUT_SWIGLU) {
-      const int f = blockIdx.x * 8 + row;
-      if (f < F) ((bf16*)y_)[(size_t)m * F + f] = __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
-    } else {
-      const int o = blockIdx.x * 16 + row;
-      if (o >= O) continue;
-      const size_t at = (size_t)m * O + o;
-      if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
-      else if (OUT == OUT_F32) ((float*)y_)[at] = v;
-      else ((float*)y_)[at] += v;
-    }
-  }
 }
 
-constexpr int kSmemBytes = STAGES * 16 * AS * (int)sizeof(bf16);
+constexpr int kMaxSmemBytes = 226 * 1024;  // the block also has a few bytes of static shared memory
+
+template <int NT>
+constexpr int fixed_smem() { return STAGES * 16 * AS * (int)sizeof(bf16) + WARPS * NT * 128 * (int)sizeof(float); }
+
+template <int NT, int IN, int OUTM>
+int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
+               const void* W, void* y, int M, int O, int K, cudaStream_t stream) {
+  const int smem = fixed_smem<NT>() + NT * 8 * (K + 32) * (int)sizeof(bf16);
+  if (smem > kMaxSmemBytes) return (int)cudaErrorInvalidValue;
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT, IN, OUTM>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
+    if (e != cudaSuccess) { sms = 0; return (int)e; }
+  }
+  const int per_sm = max(1, min(3, kMaxSmemBytes / (smem + 1024)));  // resident blocks per SM by shared memory
+  const int grid = min(num_tiles, sms * per_sm);
+  skinny_gemm_kernel<NT, IN, OUTM><<<grid, WARPS * 32, smem, stream>>>(x, rows, norm_w, eps, zero_centered,
+                                                                       (const bf16*)W, y, M, O, K, num_tiles);
+  return launch_status();
+}
 
 template <int NT, int IN>
 int launch_out(int out_mode, const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
                const void* W, void* y, int M, int O, int K, cudaStream_t stream) {
-  const int threads = WARPS * 32;
-#define AKAS_SKINNY(OUTM, GRID)                                                                                   \
-  {                                                                                                               \
-    static bool configured = false;                                                                               \
-    if (!configured) {                                                                                            \
-      const cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT, IN, OUTM>,                                \
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);        \
-      if (e != cudaSuccess) return (int)e;                                                                        \
-      configured = true;                                                                                          \
-    }                                                                                                             \
-    skinny_gemm_kernel<NT, IN, OUTM><<<GRID, threads, kSmemBytes, stream>>>(x, rows, norm_w, eps, zero_centered,  \
-                                                                            (const bf16*)W, y, M, O, K);          \
-  }
+  const int tiles = (O + 15) / 16;
   switch (out_mode) {
-    case OUT_BF16: AKAS_SKINNY(OUT_BF16, (O + 15) / 16); break;
-    case OUT_F32: AKAS_SKINNY(OUT_F32, (O + 15) / 16); break;
-    case OUT_ACC: AKAS_SKINNY(OUT_ACC, (O + 15) / 16); break;
-    case OUT_SWIGLU: AKAS_SKINNY(OUT_SWIGLU, (O / 2 + 7) / 8); break;
+    case OUT_BF16: return launch_one<NT, IN, OUT_BF16>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
+    case OUT_F32: return launch_one<NT, IN, OUT_F32>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
+    case OUT_ACC: return launch_one<NT, IN, OUT_ACC>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
+    case OUT_SWIGLU:
+      return launch_one<NT, IN, OUT_SWIGLU>((O / 2 + 7) / 8, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
     default: return (int)cudaErrorInvalidValue;
   }
-#undef AKAS_SKINNY
-  return launch_status();
 }
 
 }  // namespace
