@@ -106,7 +106,7 @@ skinny_gemm_kernel(const void* __restrict__ x_, const int* __restrict__ rows, co
       bf16* dst = xs + (size_t)m * XS;
       if (m < M) {
         const float* src = (const float*)x_ + (size_t)(rows ? rows[m] : m) * K;
-#pragma unroll 4
+#pragma unroll 8
         for (int k = lane * 4; k < K; k += 128) {
           const float4 v = *reinterpret_cast<const float4*>(src + k);
           float4 w = *reinterpret_cast<const float4*>(norm_w + k);

@@ -220,14 +220,11 @@ def linear(x, w, out_dtype=None, residual=None):
         return out
     if x.dtype != torch.bfloat16:
         raise TypeError(f"linear takes float32 or bfloat16, got {x.dtype}")
+    target = out_dtype or torch.bfloat16
+    mode = _OUT_ACC if residual is not None else _OUT_F32 if target == torch.float32 else _OUT_BF16
     if _skinny_fits(n, k):
         # a handful of tokens: the weights are streamed once by the skinny kernel
-        if residual is not None:
-            out, mode = residual, _OUT_ACC
-        else:
-            target = out_dtype or torch.bfloat16
-            out = torch.empty((n, o), dtype=target, device=x.device)
-            mode = _OUT_F32 if target == torch.float32 else _OUT_BF16
+        out = residual if residual is not None else torch.empty((n, o), dtype=target, device=x.device)
         _skinny(x, None, None, 0.0, False, w, out, n, o, k, 0, mode)
         return out
     if k % 8:
@@ -244,13 +241,14 @@ def linear(x, w, out_dtype=None, residual=None):
     return out
 
 
-_SKINNY_ROWS = 16
-
-
 def _skinny_fits(m: int, k: int) -> bool:
-    """The skinny kernel keeps the tokens' activations in shared memory beside its ring of weight chunks."""
+    """Whether the skinny kernel takes this product: few tokens, an inner size that is a multiple of 32, and
+    activations that fit in shared memory beside the ring of weight chunks."""
     tokens = 8 if m <= 8 else 16
     return m <= _SKINNY_ROWS and k % 32 == 0 and 8 * 16 * 288 * 2 + tokens * 512 + tokens * (k + 32) * 2 <= 226 * 1024
+
+
+_SKINNY_ROWS = 16
 _OUT_BF16, _OUT_F32, _OUT_ACC, _OUT_SWIGLU = 0, 1, 2, 3
 
 
@@ -264,7 +262,7 @@ def linear_swiglu(x, w_gate_up):
     """swiglu(x . w^T) with w the stacked [2F, K] gate and up matrices: [N, F] in x's dtype."""
     n, k = x.shape
     f2 = w_gate_up.shape[0]
-    if x.dtype == torch.bfloat16 and _skinny_fits(n, k) and f2 % 2 == 0:
+    if x.dtype == torch.bfloat16 and f2 % 2 == 0 and _skinny_fits(n, k):
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _skinny(_dense(x, "x"), None, None, 0.0, False, _dense(w_gate_up, "w"), out, n, f2, k, 0, _OUT_SWIGLU)
         return out
@@ -275,15 +273,11 @@ def norm_linear(h, norm_weight, eps, zero_centered, w, out_dtype=None, rows=None
     """linear(rmsnorm(h[rows]), w), optionally through swiglu: the norm rides in the product for few tokens."""
     m = rows.numel() if rows is not None else h.shape[0]
     k, o = h.shape[1], w.shape[0]
-    if (w.dtype == torch.bfloat16 and h.dtype == torch.float32 and _skinny_fits(m, k)
-            and h.is_contiguous() and (not swiglu_out or o % 2 == 0)):
-        if swiglu_out:
-            out = torch.empty((m, o // 2), dtype=torch.bfloat16, device=h.device)
-            mode = _OUT_SWIGLU
-        else:
-            target = out_dtype or torch.bfloat16
-            out = torch.empty((m, o), dtype=target, device=h.device)
-            mode = _OUT_F32 if target == torch.float32 else _OUT_BF16
+    target = torch.bfloat16 if swiglu_out else (out_dtype or torch.bfloat16)
+    mode = _OUT_SWIGLU if swiglu_out else _OUT_F32 if target == torch.float32 else _OUT_BF16
+    if (w.dtype == torch.bfloat16 and h.dtype == torch.float32 and h.is_contiguous() and _skinny_fits(m, k)
+            and (not swiglu_out or o % 2 == 0)):
+        out = torch.empty((m, o // 2 if swiglu_out else o), dtype=target, device=h.device)
         _skinny(h, rows, norm_weight, eps, zero_centered, _dense(w, "w"), out, m, o, k, 1, mode)
         return out
     x = rmsnorm(h, norm_weight, eps, zero_centered, w.dtype, rows)
