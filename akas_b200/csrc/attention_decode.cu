@@ -282,3 +282,74 @@ AKAS_API int akas_decode_attention_bf16(const void* q, const void* k_pool, const
   }
 #undef AKAS_DECODE
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// The same kernels for callers that cannot allocate: scratch inside the library. See noalloc.h.
+#include <mutex>
+
+#include "noalloc.h"
+
+namespace {
+
+// Partials of the key splits: [tokens, heads, splits, head_dim] sums, then [tokens, heads, splits, 2] (max, sum).
+// In host code this name is only a handle for cudaGetSymbolAddress, never a pointer a kernel may be given.
+static __device__ __align__(256) float g_decode_scratch[AKAS_DECODE_NOALLOC_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_decode_scratch_address[kMaxDevices] = {};  // device address of the array, per device ordinal
+std::mutex g_decode_scratch_mutex;
+
+// The device address of g_decode_scratch on the current device; looked up once per device.
+int decode_scratch(float** address) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= kMaxDevices) return AKAS_NOALLOC_NO_SYMBOL;
+  std::lock_guard<std::mutex> lock(g_decode_scratch_mutex);
+  if (g_decode_scratch_address[device] == nullptr) {
+    float* found = nullptr;
+    e = cudaGetSymbolAddress((void**)&found, g_decode_scratch);
+    if (e != cudaSuccess || found == nullptr) return e != cudaSuccess ? (int)e : AKAS_NOALLOC_NO_SYMBOL;
+    g_decode_scratch_address[device] = found;
+  }
+  *address = g_decode_scratch_address[device];
+  return 0;
+}
+
+}  // namespace
+
+long long akas_decode_attention_bf16_noalloc_needs(int tokens, int heads, int splits, int head_dim) {
+  if (tokens <= 0 || heads <= 0 || splits <= 1 || head_dim <= 0) return 0;  // a single split writes the output directly
+  return (long long)tokens * heads * splits * (head_dim + 2);
+}
+
+const char* akas_noalloc_error_string(int code) {
+  switch (code) {
+    case 0: return "no error";
+    case AKAS_NOALLOC_TOO_LARGE:
+      return "the call needs more than AKAS_DECODE_NOALLOC_FLOATS float32 of scratch (tokens * heads * splits * "
+             "(head_dim + 2)); use fewer splits or tokens, or akas_decode_attention_bf16 with scratch of your own";
+    case AKAS_NOALLOC_NO_SYMBOL: return "the device address of the library's scratch array could not be found";
+    case AKAS_NOALLOC_BAD_ARGUMENT: return "a size is out of range or a pointer is null";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+  }
+}
+
+int akas_decode_attention_bf16_noalloc(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
+                                       int max_blocks, const int* seq_of_token, const int* positions, void* out,
+                                       float scale, int window, int page_size, int tokens, int heads, int kv_heads,
+                                       int head_dim, int splits, cudaStream_t stream) {
+  if (tokens < 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || splits < 1 || page_size <= 0 || max_blocks <= 0 ||
+      !q || !k_pool || !v_pool || !block_table || !seq_of_token || !positions || !out)
+    return AKAS_NOALLOC_BAD_ARGUMENT;
+  const long long need = akas_decode_attention_bf16_noalloc_needs(tokens, heads, splits, head_dim);
+  if (need > (long long)AKAS_DECODE_NOALLOC_FLOATS) return AKAS_NOALLOC_TOO_LARGE;
+  float* scratch = nullptr;
+  const int err = decode_scratch(&scratch);
+  if (err) return err;
+  float* part_o = scratch;
+  float* part_ml = scratch + (size_t)tokens * heads * splits * head_dim;
+  return akas_decode_attention_bf16(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, part_o,
+                                    part_ml, scale, window, page_size, tokens, heads, kv_heads, head_dim, splits,
+                                    stream);
+}
