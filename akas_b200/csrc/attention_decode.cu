@@ -36,6 +36,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   bf16* k_s = q_s + ROWS * STRIDE;                      // [STAGES][BK][STRIDE]
   bf16* v_s = k_s + STAGES * BK * STRIDE;               // [STAGES][BK][STRIDE]
 
+  chain_release();
+  chain_wait();
   const int tok = blockIdx.x, split = blockIdx.z;
   const int kvh = blockIdx.y / row_tiles, row_tile = blockIdx.y % row_tiles;
   const int G = H / KH;
@@ -217,6 +219,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 __global__ void decode_merge_bf16_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const int* __restrict__ seq_of_token, bf16* __restrict__ out, int H, int D,
                                          int splits) {
+  chain_release();
+  chain_wait();
   const int tok = blockIdx.x, head = blockIdx.y;
   if (seq_of_token[tok] < 0) return;  // the split kernel wrote the zeros
   const size_t base = ((size_t)tok * H + head) * splits;
@@ -249,13 +253,13 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* blo
     configured = true;
   }
   const int G = H / KH, row_tiles = (G + ROWS - 1) / ROWS;
-  decode_attention_kernel<D><<<dim3(N, KH * row_tiles, splits), WARPS * 32, smem, stream>>>(
-      (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, seq_of_token, positions,
-      (bf16*)out, part_o, part_ml, scale, window, page_size, H, KH, row_tiles, splits);
-  int err = launch_status();
+  int err = launch_chained(decode_attention_kernel<D>, dim3(N, KH * row_tiles, splits), dim3(WARPS * 32), smem, stream,
+                           (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks,
+                           seq_of_token, positions, (bf16*)out, part_o, part_ml, scale, window, page_size, H, KH,
+                           row_tiles, splits);
   if (err || splits == 1) return err;
-  decode_merge_bf16_kernel<<<dim3(N, H), D >= 64 ? 64 : 32, 0, stream>>>(part_o, part_ml, seq_of_token, (bf16*)out, H, D, splits);
-  return launch_status();
+  return launch_chained(decode_merge_bf16_kernel, dim3(N, H), dim3(D >= 64 ? 64 : 32), 0, stream,
+                        (const float*)part_o, (const float*)part_ml, seq_of_token, (bf16*)out, H, D, splits);
 }
 
 }  // namespace

@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define AKAS_API extern "C" __attribute__((visibility("default")))
 
@@ -65,10 +66,74 @@ __device__ __forceinline__ void load_vec(const bf16* p, float (&out)[8]) {
   }
 }
 
+// Stores 16 bytes' worth of elements (4 float32 or 8 bfloat16) from floats. `p` must be 16-byte aligned.
+__device__ __forceinline__ void store_vec(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store_vec(bf16* p, const float (&v)[8]) {
+  uint4 o;
+  uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(p) = o;
+}
+// Stores 8 consecutive elements from floats (two 16-byte stores for float32, one for bfloat16).
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) { store_vec(p, v); }
+// Loads 8 consecutive elements as floats.
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) { load_vec(p, v); }
+
 template <typename T> struct Vec;
 template <> struct Vec<float> { static constexpr int N = 4; };
 template <> struct Vec<bf16> { static constexpr int N = 8; };
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch. Kernels of a decode step follow one another on one stream; a kernel
+// launched with launch_chained may begin while its predecessor is still draining, as soon as every block of
+// the predecessor has executed chain_release(). Such a kernel must execute chain_wait() before it touches
+// anything an earlier kernel wrote or may still read; what it does before that (fetching weights, which no
+// kernel ever writes) overlaps the predecessor's tail. chain_wait() returns when all earlier kernels have
+// completed and their writes are visible; in a kernel that was launched the ordinary way both are no-ops.
+// Every chained kernel calls chain_wait() in every block before any exit, so that "my predecessor has
+// completed" implies "everything before it has completed" along the whole chain.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool chained_launches_enabled();  // AKAS_B200_CHAINED_LAUNCHES=0 turns the attribute off (ordinary launches)
+
+template <typename... Params, typename... Args>
+static inline int launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = chained_launches_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&config, kernel, Params(args)...);
+}
+
+inline bool chained_launches_enabled() {
+  static const bool enabled = [] {
+    const char* v = getenv("AKAS_B200_CHAINED_LAUNCHES");
+    return !(v && v[0] == '0');
+  }();
+  return enabled;
+}
 
 }  // namespace akas

@@ -46,6 +46,44 @@ __global__ void short_conv_forward_kernel(const T* __restrict__ bcx, const float
   out[(size_t)t * C + c] = from_f32<T>(to_f32(bcx[(size_t)t * 3 * C + C + c]) * acc);
 }
 
+// The forward for widths that are a multiple of 8: a thread owns 8 neighbouring channels of one token.
+template <typename T>
+__global__ void short_conv_forward8_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
+                                           const float* __restrict__ bias, const float* __restrict__ state,
+                                           const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token,
+                                           const int* __restrict__ slots, T* __restrict__ out, int C, int L) {
+  const int t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  const int r = seq_of_token[t];
+  const int slot = r >= 0 ? slots[r] : -1;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (slot >= 0) {
+    const int j = t - cu_seqlens[r];
+    for (int i = 0; i < L; ++i) {
+      const int back = L - 1 - i;
+      float u[8];
+      if (j - back >= 0) {
+        const T* row = bcx + (size_t)(t - back) * 3 * C;
+        float b[8], x[8];
+        load8(row + c, b);
+        load8(row + 2 * C + c, x);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) u[e] = b[e] * x[e];
+      } else {
+        load8(state + ((size_t)slot * (L - 1) + (j + i)) * C + c, u);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(u[e], taps[(size_t)(c + e) * L + i], acc[e]);
+    }
+    float gate[8];
+    load8(bcx + (size_t)t * 3 * C + C + c, gate);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = gate[e] * (bias ? acc[e] + bias[c + e] : acc[e]);
+  }
+  store8(out + (size_t)t * C + c, acc);
+}
+
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int C,
@@ -78,6 +116,8 @@ __global__ void short_conv_decode_kernel(const T* __restrict__ bcx, const float*
                                          const float* __restrict__ bias, float* __restrict__ state,
                                          const int* __restrict__ seq_of_token, const int* __restrict__ slots,
                                          T* __restrict__ out, int C, int L) {
+  chain_release();
+  chain_wait();
   const int t = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
@@ -110,12 +150,10 @@ AKAS_API int akas_short_conv_decode(const void* bcx, const float* taps, const fl
   const int threads = 128;
   const dim3 grid(N, (C + threads - 1) / threads);
   if (dtype == AKAS_F32)
-    short_conv_decode_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, taps, bias, state, seq_of_token,
-                                                                  slots, (float*)out, C, L);
-  else
-    short_conv_decode_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, taps, bias, state, seq_of_token,
-                                                                 slots, (bf16*)out, C, L);
-  return launch_status();
+    return launch_chained(short_conv_decode_kernel<float>, grid, dim3(threads), 0, stream, (const float*)bcx, taps, bias,
+                          state, seq_of_token, slots, (float*)out, C, L);
+  return launch_chained(short_conv_decode_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)bcx, taps, bias,
+                        state, seq_of_token, slots, (bf16*)out, C, L);
 }
 
 AKAS_API int akas_short_conv(const void* bcx, const float* taps, const float* bias, float* state,
@@ -125,13 +163,23 @@ AKAS_API int akas_short_conv(const void* bcx, const float* taps, const float* bi
   if (N <= 0 || R <= 0) return 0;
   const int threads = 128;
   const dim3 fwd(N, (C + threads - 1) / threads), upd(R, (C + threads - 1) / threads);
+  const bool wide = C % 8 == 0 && (uintptr_t)bcx % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)state % 16 == 0;
+  const dim3 fwd8(N, (C / 8 + threads - 1) / threads);
   if (dtype == AKAS_F32) {
-    short_conv_forward_kernel<float><<<fwd, threads, 0, stream>>>((const float*)bcx, taps, bias, state, cu_seqlens,
-                                                                  seq_of_token, slots, (float*)out, C, L);
+    if (wide)
+      short_conv_forward8_kernel<float><<<fwd8, threads, 0, stream>>>((const float*)bcx, taps, bias, state, cu_seqlens,
+                                                                      seq_of_token, slots, (float*)out, C, L);
+    else
+      short_conv_forward_kernel<float><<<fwd, threads, 0, stream>>>((const float*)bcx, taps, bias, state, cu_seqlens,
+                                                                    seq_of_token, slots, (float*)out, C, L);
     short_conv_state_kernel<float><<<upd, threads, 0, stream>>>((const float*)bcx, state, cu_seqlens, slots, C, L);
   } else {
-    short_conv_forward_kernel<bf16><<<fwd, threads, 0, stream>>>((const bf16*)bcx, taps, bias, state, cu_seqlens,
-                                                                 seq_of_token, slots, (bf16*)out, C, L);
+    if (wide)
+      short_conv_forward8_kernel<bf16><<<fwd8, threads, 0, stream>>>((const bf16*)bcx, taps, bias, state, cu_seqlens,
+                                                                     seq_of_token, slots, (bf16*)out, C, L);
+    else
+      short_conv_forward_kernel<bf16><<<fwd, threads, 0, stream>>>((const bf16*)bcx, taps, bias, state, cu_seqlens,
+                                                                   seq_of_token, slots, (bf16*)out, C, L);
     short_conv_state_kernel<bf16><<<upd, threads, 0, stream>>>((const bf16*)bcx, state, cu_seqlens, slots, C, L);
   }
   return launch_status();

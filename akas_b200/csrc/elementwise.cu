@@ -10,6 +10,8 @@ using namespace akas;
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                  float* __restrict__ out, int C) {
+  chain_release();
+  chain_wait();
   const int n = blockIdx.x;
   const T* row = table + (size_t)tokens[n] * C;
   float* dst = out + (size_t)n * C;
@@ -21,10 +23,8 @@ AKAS_API int akas_embedding(const int* tokens, const void* table, float* out, in
   if (N <= 0) return 0;
   const int threads = C >= 1024 ? 256 : 128;
   if (dtype == AKAS_F32)
-    embedding_kernel<float><<<N, threads, 0, stream>>>(tokens, (const float*)table, out, C);
-  else
-    embedding_kernel<bf16><<<N, threads, 0, stream>>>(tokens, (const bf16*)table, out, C);
-  return launch_status();
+    return launch_chained(embedding_kernel<float>, dim3(N), dim3(threads), 0, stream, tokens, (const float*)table, out, C);
+  return launch_chained(embedding_kernel<bf16>, dim3(N), dim3(threads), 0, stream, tokens, (const bf16*)table, out, C);
 }
 
 // y[i, :] = x[row(i), :] * rsqrt(mean(x^2) + eps) * (w or 1 + w); row(i) = rows[i] if rows else i.
@@ -49,9 +49,58 @@ __global__ void rmsnorm_kernel(const TI* __restrict__ x, const float* __restrict
   }
 }
 
+// The same for float32 rows whose width is a multiple of 8 and at most 8192: the row is read once, with
+// 16-byte loads, and stays in registers between the sum of squares and the scaling.
+template <typename TO, int PER_THREAD>  // PER_THREAD groups of 8 elements per thread, 256 threads
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
+                    const int* __restrict__ rows, int C, float eps, int zero_centered) {
+  __shared__ float scratch[32];
+  const int i = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[i] : i) * C;
+  float v[PER_THREAD][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int p = 0; p < PER_THREAD; ++p) {
+    const int c = (p * 256 + threadIdx.x) * 8;
+    if (c < C) {
+      const float4 a = *reinterpret_cast<const float4*>(src + c);
+      const float4 b = *reinterpret_cast<const float4*>(src + c + 4);
+      v[p][0] = a.x; v[p][1] = a.y; v[p][2] = a.z; v[p][3] = a.w;
+      v[p][4] = b.x; v[p][5] = b.y; v[p][6] = b.z; v[p][7] = b.w;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss = fmaf(v[p][e], v[p][e], ss);
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)C + eps);
+  TO* dst = y + (size_t)i * C;
+#pragma unroll
+  for (int p = 0; p < PER_THREAD; ++p) {
+    const int c = (p * 256 + threadIdx.x) * 8;
+    if (c < C) {
+      const float4 wa = *reinterpret_cast<const float4*>(w + c);
+      const float4 wb = *reinterpret_cast<const float4*>(w + c + 4);
+      const float g[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = v[p][e] * inv * (zero_centered ? 1.f + g[e] : g[e]);
+      store8(dst + c, o);
+    }
+  }
+}
+
 AKAS_API int akas_rmsnorm(const void* x, const float* w, void* y, const int* rows, int M, int C, float eps,
                           int zero_centered, int in_dtype, int out_dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
+  if (in_dtype == AKAS_F32 && C % 8 == 0 && C >= 1024 && C <= 8192 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
+#define AKAS_ROWS(TO, P) \
+  rmsnorm_rows_kernel<TO, P><<<M, 256, 0, stream>>>((const float*)x, w, (TO*)y, rows, C, eps, zero_centered)
+    if (out_dtype == AKAS_F32) { if (C <= 2048) AKAS_ROWS(float, 1); else if (C <= 4096) AKAS_ROWS(float, 2); else AKAS_ROWS(float, 4); }
+    else { if (C <= 2048) AKAS_ROWS(bf16, 1); else if (C <= 4096) AKAS_ROWS(bf16, 2); else AKAS_ROWS(bf16, 4); }
+#undef AKAS_ROWS
+    return launch_status();
+  }
   const int threads = C >= 2048 ? 512 : C >= 512 ? 256 : 128;
 #define AKAS_NORM(TI, TO) \
   rmsnorm_kernel<TI, TO><<<M, threads, 0, stream>>>((const TI*)x, w, (TO*)y, rows, C, eps, zero_centered)
@@ -75,10 +124,37 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
   out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
 }
 
+// Eight (bfloat16) or four (float32) neighbours per thread with 16-byte loads, for F a multiple of that.
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t groups) {
+  constexpr int V = Vec<T>::N;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= groups) return;
+  const int per_row = F / V;
+  const size_t n = i / per_row;
+  const int f = (int)(i - n * per_row) * V;
+  float g[V], u[V], o[V];
+  load_vec(gu + n * 2 * F + f, g);
+  load_vec(gu + n * 2 * F + F + f, u);
+#pragma unroll
+  for (int e = 0; e < V; ++e) o[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+  store_vec(out + n * F + f, o);
+}
+
 AKAS_API int akas_swiglu(const void* gu, void* out, int N, int F, int dtype, cudaStream_t stream) {
   const size_t total = (size_t)N * F;
   if (total == 0) return 0;
   const int threads = 256;
+  const int v = dtype == AKAS_F32 ? 4 : 8;
+  if (F % v == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)out % 16 == 0) {
+    const size_t groups = total / v;
+    const unsigned blocks = (unsigned)((groups + threads - 1) / threads);
+    if (dtype == AKAS_F32)
+      swiglu_vec_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, F, groups);
+    else
+      swiglu_vec_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, F, groups);
+    return launch_status();
+  }
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   if (dtype == AKAS_F32)
     swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, F, total);

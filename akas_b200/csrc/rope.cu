@@ -14,6 +14,8 @@ using namespace akas;
 
 __global__ void rope_tables_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                    float* __restrict__ cos_out, float* __restrict__ sin_out, int N, int half) {
+  chain_release();
+  chain_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)N * half) return;
   const int n = (int)(i / half), f = (int)(i % half);
@@ -27,8 +29,8 @@ AKAS_API int akas_rope_tables(const int* positions, const double* inv_freq, floa
                               int half, cudaStream_t stream) {
   const size_t total = (size_t)N * half;
   if (total == 0) return 0;
-  rope_tables_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(positions, inv_freq, cos_out, sin_out, N, half);
-  return launch_status();
+  return launch_chained(rope_tables_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, positions,
+                        inv_freq, cos_out, sin_out, N, half);
 }
 
 #define AKAS_ROPE_WARPS 4
@@ -42,6 +44,8 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, T* __restrict__ q
                                           int max_blocks, const int* __restrict__ seq_of_token,
                                           const int* __restrict__ positions, int page_size, int H, int KH, int D) {
   __shared__ float buf[AKAS_ROPE_WARPS][256];
+  chain_release();
+  chain_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int head = blockIdx.y * AKAS_ROPE_WARPS + warp;
@@ -107,14 +111,12 @@ AKAS_API int akas_qk_norm_rope_store(void* qkv, void* q_out, const float* q_w, c
   const dim3 grid(N, (H + 2 * KH + AKAS_ROPE_WARPS - 1) / AKAS_ROPE_WARPS);
   const int threads = 32 * AKAS_ROPE_WARPS;
   if (dtype == AKAS_F32)
-    qk_norm_rope_store_kernel<float><<<grid, threads, 0, stream>>>(
-        (float*)qkv, (float*)q_out, q_w, k_w, eps, zero_centered, cos_t, sin_t, rotary, (float*)k_pool,
-        (float*)v_pool, block_table, max_blocks, seq_of_token, positions, page_size, H, KH, D);
-  else
-    qk_norm_rope_store_kernel<bf16><<<grid, threads, 0, stream>>>(
-        (bf16*)qkv, (bf16*)q_out, q_w, k_w, eps, zero_centered, cos_t, sin_t, rotary, (bf16*)k_pool,
-        (bf16*)v_pool, block_table, max_blocks, seq_of_token, positions, page_size, H, KH, D);
-  return launch_status();
+    return launch_chained(qk_norm_rope_store_kernel<float>, grid, dim3(threads), 0, stream, (float*)qkv, (float*)q_out,
+                          q_w, k_w, eps, zero_centered, cos_t, sin_t, rotary, (float*)k_pool, (float*)v_pool,
+                          block_table, max_blocks, seq_of_token, positions, page_size, H, KH, D);
+  return launch_chained(qk_norm_rope_store_kernel<bf16>, grid, dim3(threads), 0, stream, (bf16*)qkv, (bf16*)q_out, q_w,
+                        k_w, eps, zero_centered, cos_t, sin_t, rotary, (bf16*)k_pool, (bf16*)v_pool, block_table,
+                        max_blocks, seq_of_token, positions, page_size, H, KH, D);
 }
 
 // k, v: [N, KH * D] rows (row stride `stride` elements) into the pages; for position encodings that

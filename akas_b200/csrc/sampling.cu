@@ -61,6 +61,8 @@ __device__ void block_argmax(const float* __restrict__ x, int V, float& best_out
 
 __global__ void __launch_bounds__(AKAS_SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+  chain_release();
+  chain_wait();
   float best;
   int idx;
   block_argmax(logits + (size_t)blockIdx.x * V, V, best, idx);
@@ -69,8 +71,7 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
 
 AKAS_API int akas_argmax(const float* logits, int* out, int M, int V, cudaStream_t stream) {
   if (M <= 0) return 0;
-  argmax_kernel<<<M, AKAS_SAMPLE_THREADS, 0, stream>>>(logits, out, V);
-  return launch_status();
+  return launch_chained(argmax_kernel, dim3(M), dim3(AKAS_SAMPLE_THREADS), 0, stream, logits, out, V);
 }
 
 __global__ void __launch_bounds__(AKAS_SAMPLE_THREADS)

@@ -88,7 +88,15 @@ skinny_gemm_kernel(const void* __restrict__ x_, const int* __restrict__ rows, co
     cp_async_commit();
   };
 
-  // Activations into shared memory, once per block. bfloat16 input rides in the first cp.async group.
+  // The weights do not depend on anything an earlier kernel wrote: their first chunks are requested before
+  // this kernel waits for its predecessor, whose tail they overlap.
+  chain_release();
+#pragma unroll
+  for (int c = 0; c < STAGES - 2; ++c) issue_next();
+  chain_wait();
+
+  // Activations into shared memory, once per block. bfloat16 input is a cp.async group of its own (empty
+  // when the norm rides along), then the last chunk of the prologue follows.
   if (IN == IN_BF16) {
     const int per_row = K / 8;
     for (int i = tid; i < NT * 8 * per_row; i += WARPS * 32) {
@@ -97,8 +105,8 @@ skinny_gemm_kernel(const void* __restrict__ x_, const int* __restrict__ rows, co
       cp_async16(xs + (size_t)m * XS + col, (const bf16*)x_ + src * K + col, m < M ? 16 : 0);
     }
   }
-#pragma unroll
-  for (int c = 0; c < STAGES - 1; ++c) issue_next();
+  cp_async_commit();
+  issue_next();
   if (IN == IN_NORM) {
     // float32 residual rows -> bf16(x * norm weight); each warp owns tokens warp, warp + 8 and sums x^2
     for (int m = warp; m < NT * 8; m += WARPS) {
@@ -131,7 +139,9 @@ skinny_gemm_kernel(const void* __restrict__ x_, const int* __restrict__ rows, co
 
   int tile = blockIdx.x, c = 0;
   for (int n = 0; n < items; ++n) {
-    cp_async_wait<STAGES - 2>();
+    // Groups in flight, oldest first: chunks 0 .. STAGES-3, the activations, chunk STAGES-2, ... The first
+    // item waits until only the newest is pending (so the activations are in); later ones keep STAGES-2 going.
+    if (n == 0) cp_async_wait<1>(); else cp_async_wait<STAGES - 2>();
     __syncthreads();  // item n (and the activations) are there for everyone; everyone is done with item n - 1
     issue_next();
     const int k = c * KC + warp * 32 + 8 * t;  // this thread's 8 consecutive k of the chunk
@@ -217,9 +227,8 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
   }
   const int per_sm = max(1, min(3, kMaxSmemBytes / (smem + 1024)));  // resident blocks per SM by shared memory
   const int grid = min(num_tiles, sms * per_sm);
-  skinny_gemm_kernel<NT, IN, OUTM><<<grid, WARPS * 32, smem, stream>>>(x, rows, norm_w, eps, zero_centered,
-                                                                       (const bf16*)W, y, M, O, K, num_tiles);
-  return launch_status();
+  return launch_chained(skinny_gemm_kernel<NT, IN, OUTM>, dim3(grid), dim3(WARPS * 32), (size_t)smem, stream, x, rows,
+                        norm_w, eps, zero_centered, (const bf16*)W, y, M, O, K, num_tiles);
 }
 
 template <int NT, int IN>
