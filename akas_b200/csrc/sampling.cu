@@ -59,19 +59,59 @@ __device__ void block_argmax(const float* __restrict__ x, int V, float& best_out
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(AKAS_SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+// Greedy token in two launches, so that a handful of rows still keeps many SMs busy: the vocabulary is cut
+// into `parts` slices, one block each; then one block per row picks the best of the slices' winners (the
+// larger value, and among equals the lower index, so ties go to the lowest id as in one pass).
+__global__ void __launch_bounds__(256)
+argmax_parts_kernel(const float* __restrict__ logits, float* __restrict__ part_val, int* __restrict__ part_idx, int V,
+                    int parts) {
   chain_release();
   chain_wait();
-  float best;
-  int idx;
-  block_argmax(logits + (size_t)blockIdx.x * V, V, best, idx);
-  if (threadIdx.x == 0) out[blockIdx.x] = idx;
+  const int row = blockIdx.x, part = blockIdx.y;
+  const int per = (V + parts - 1) / parts;
+  const int begin = min(V, part * per), count = min(V, begin + per) - begin;
+  float best = -INFINITY;
+  int idx = V;
+  if (count > 0) {
+    block_argmax(logits + (size_t)row * V + begin, count, best, idx);
+    idx += begin;
+  }
+  if (threadIdx.x == 0) {
+    part_val[row * parts + part] = count > 0 ? best : -INFINITY;
+    part_idx[row * parts + part] = count > 0 ? idx : V;
+  }
 }
 
-AKAS_API int akas_argmax(const float* logits, int* out, int M, int V, cudaStream_t stream) {
+__global__ void argmax_pick_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                   int* __restrict__ out, int parts) {
+  chain_release();
+  chain_wait();
+  const int row = blockIdx.x;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int p = threadIdx.x; p < parts; p += 32) {
+    const float v = part_val[row * parts + p];
+    const int i = part_idx[row * parts + p];
+    if (v > best || (v == best && i < idx) || idx == 0x7fffffff) { best = v; idx = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+  }
+  if (threadIdx.x == 0) out[row] = idx;
+}
+
+// Scratch: part_val float32 [M, parts], part_idx int32 [M, parts].
+AKAS_API int akas_argmax(const float* logits, int* out, float* part_val, int* part_idx, int M, int V, int parts,
+                         cudaStream_t stream) {
   if (M <= 0) return 0;
-  return launch_chained(argmax_kernel, dim3(M), dim3(AKAS_SAMPLE_THREADS), 0, stream, logits, out, V);
+  if (parts < 1 || parts > 1024 || V <= 0) return (int)cudaErrorInvalidValue;
+  int err = launch_chained(argmax_parts_kernel, dim3(M, parts), dim3(256), 0, stream, logits, part_val, part_idx, V, parts);
+  if (err) return err;
+  return launch_chained(argmax_pick_kernel, dim3(M), dim3(32), 0, stream, (const float*)part_val, (const int*)part_idx,
+                        out, parts);
 }
 
 __global__ void __launch_bounds__(AKAS_SAMPLE_THREADS)

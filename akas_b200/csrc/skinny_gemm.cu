@@ -226,7 +226,10 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
     if (e != cudaSuccess) { sms = 0; return (int)e; }
   }
   const int per_sm = max(1, min(3, kMaxSmemBytes / (smem + 1024)));  // resident blocks per SM by shared memory
-  const int grid = min(num_tiles, sms * per_sm);
+  // every block gets the same number of row tiles (to within one): blocks advance at the same rate, so a
+  // grid that leaves some blocks with one tile more than others would idle the rest of the GPU meanwhile
+  const int rounds = (num_tiles + sms * per_sm - 1) / (sms * per_sm);
+  const int grid = (num_tiles + rounds - 1) / rounds;
   return launch_chained(skinny_gemm_kernel<NT, IN, OUTM>, dim3(grid), dim3(WARPS * 32), (size_t)smem, stream, x, rows,
                         norm_w, eps, zero_centered, (const bf16*)W, y, M, O, K, num_tiles);
 }

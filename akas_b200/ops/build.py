@@ -122,6 +122,12 @@ def _compile(name: str, nvcc: str, digest: str, out_dir: Path, verbose: bool = F
     if verbose:
         _say(proc.stderr)
     os.replace(tmp, target)
+    for old in out_dir.glob(f"{name}-*.so"):  # earlier builds of this source
+        if old != target and len(old.stem) == len(target.stem):
+            try:
+                old.unlink()
+            except OSError:
+                pass
     return target
 
 

@@ -72,7 +72,7 @@ _SIGNATURES = {
                            c_void_p],
     },
     "sampling": {
-        "akas_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "akas_argmax": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     },
 }
@@ -337,10 +337,12 @@ def kv_store(k, v, k_pool, v_pool, block_table, seq_of_token, positions, page_si
 
 
 def decode_splits(num_tokens: int, kv_heads: int, head_tiles: int, max_context: int) -> int:
-    """How many parts the keys of a decoding request are cut into, from sizes known on the host."""
+    """How many parts the keys of a decoding request are cut into, from sizes known on the host: enough
+    blocks for several rounds over the SMs (a single round and a bit leaves most of the GPU idle in the
+    second), but at least four 64-key tiles per part."""
     blocks = max(1, num_tokens * kv_heads * head_tiles)
-    want = -(-2 * 148 // blocks)  # about two blocks per SM
-    most = max(1, -(-max_context // 128))  # at least two 64-key tiles per part
+    want = -(-1800 // blocks)
+    most = max(1, -(-max_context // 256))
     return max(1, min(want, most, 64))
 
 
@@ -396,7 +398,11 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
 def argmax(logits):
     m, v = logits.shape
     out = torch.empty((m,), dtype=torch.int32, device=logits.device)
-    _check(_fn("sampling", "akas_argmax")(_ptr(_dense(logits, "logits")), _ptr(out), m, v, _stream()), "argmax")
+    parts = max(1, min(64, v // 1024, 592 // max(m, 1)))  # slices of the vocabulary, at least 1024 entries each
+    part_val = torch.empty((m, parts), dtype=torch.float32, device=logits.device)
+    part_idx = torch.empty((m, parts), dtype=torch.int32, device=logits.device)
+    _check(_fn("sampling", "akas_argmax")(_ptr(_dense(logits, "logits")), _ptr(out), _ptr(part_val), _ptr(part_idx), m,
+                                         v, parts, _stream()), "argmax", kernels=2)
     return out
 
 
