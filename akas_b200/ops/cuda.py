@@ -10,6 +10,7 @@ is no other path.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Iterable, Optional
 
@@ -60,6 +61,10 @@ _SIGNATURES = {
                                        c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_void_p],
     },
+    "gemm_tcgen05": {
+        "akas_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_gemm_tcgen05_status": [],
+    },
     "skinny_gemm": {
         "akas_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_int, c_int, c_void_p],
@@ -83,7 +88,7 @@ _functions = {}
 def libraries_for(dtype: torch.dtype) -> list:
     """The kernel files a model of this compute dtype needs."""
     names = ["elementwise", "conv", "rope", "attention", "sampling"]
-    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "skinny_gemm", "attention_prefill", "attention_decode"]
+    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "skinny_gemm", "attention_prefill", "attention_decode"]
     return names
 
 
@@ -229,6 +234,13 @@ def linear(x, w, out_dtype=None, residual=None):
         return out
     if k % 8:
         raise ValueError(f"bfloat16 matrix products need an inner size that is a multiple of 8, got {k}")
+    if _tcgen05_takes(n, k) and (residual is not None or target == torch.bfloat16):
+        # prompt portions: the hand-written tcgen05 kernel, residual add fused into its read-out
+        out = residual if residual is not None else torch.empty((n, o), dtype=torch.bfloat16, device=x.device)
+        _check(_fn("gemm_tcgen05", "akas_gemm_tcgen05")(_ptr(x), _ptr(w), _ptr(out), n, o, k,
+                                                       1 if residual is not None else 0, _stream()),
+               f"tcgen05 product [{n}x{k}] x [{o}x{k}]^T")
+        return out
     if residual is not None:
         out, out_f32, acc = residual, 1, 1
     else:
@@ -249,6 +261,19 @@ def _skinny_fits(m: int, k: int) -> bool:
 
 
 _SKINNY_ROWS = 16
+library_products = os.environ.get("AKAS_B200_LIBRARY_PRODUCTS", "0") == "1"  # cuBLASLt instead of the tcgen05 kernel
+
+
+def _tcgen05_takes(n: int, k: int) -> bool:
+    """More tokens than the skinny kernel takes, a 16-byte row pitch, and the library not asked for."""
+    return n > _SKINNY_ROWS and k % 8 == 0 and not library_products
+
+
+def gemm_tcgen05_status() -> int:
+    """0 unless a bounded wait inside the tcgen05 product kernel has run out on this device. Synchronises."""
+    return int(_fn("gemm_tcgen05", "akas_gemm_tcgen05_status")())
+
+
 _OUT_BF16, _OUT_F32, _OUT_ACC, _OUT_SWIGLU = 0, 1, 2, 3
 
 
@@ -265,6 +290,12 @@ def linear_swiglu(x, w_gate_up):
     if x.dtype == torch.bfloat16 and f2 % 2 == 0 and _skinny_fits(n, k):
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _skinny(_dense(x, "x"), None, None, 0.0, False, _dense(w_gate_up, "w"), out, n, f2, k, 0, _OUT_SWIGLU)
+        return out
+    if x.dtype == torch.bfloat16 and _tcgen05_takes(n, k) and f2 % 16 == 0:
+        # SwiGLU in the read-out of the product: the [N, 2F] intermediate is never written
+        out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
+        _check(_fn("gemm_tcgen05", "akas_gemm_tcgen05")(_ptr(_dense(x, "x")), _ptr(_dense(w_gate_up, "w")), _ptr(out), n,
+                                                       f2, k, 2, _stream()), f"tcgen05 SwiGLU product [{n}x{k}]")
         return out
     return swiglu(linear(x, w_gate_up))
 

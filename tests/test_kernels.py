@@ -125,6 +125,22 @@ def test_skinny_products_for_few_tokens(ops, m, k, o):
     _close(cuda.norm_linear(big, nw, 1e-5, False, w), ref.norm_linear(big, nw, 1e-5, False, w), torch.bfloat16, "many tokens")
 
 
+@pytest.mark.parametrize("m,k,o", [(17, 64, 48), (64, 128, 256), (100, 96, 200), (128, 2048, 320), (300, 192, 1000),
+                                   (2048, 256, 512), (333, 2048, 2056)])
+def test_tensor_memory_products_for_prompt_portions(ops, m, k, o):
+    """The tcgen05 kernel (TMA in, accumulators in tensor memory) with its three read-outs, at sizes that leave
+    ragged tiles in every direction."""
+    cuda, ref = ops
+    x, w = _rand((m, k), torch.bfloat16, 5), _rand((o, k), torch.bfloat16, 6, 0.05)
+    want = x.double() @ w.double().T
+    _close(cuda.linear(x, w), want, torch.bfloat16, "bf16 out")
+    res = _rand((m, o), torch.float32, 7)
+    _close(cuda.linear(x, w, residual=res.clone()), res.double() + want, torch.float32, "accumulate", k)
+    w2 = _rand((2 * o, k), torch.bfloat16, 8, 0.05)
+    _close(cuda.linear_swiglu(x, w2), ref.linear_swiglu(x, w2), torch.bfloat16, "swiglu")
+    assert cuda.gemm_tcgen05_status() == 0
+
+
 def test_short_conv_decode_kernel_equals_the_general_one(ops):
     cuda, ref = ops
     c, taps = 72, 4
