@@ -127,17 +127,31 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
       }
     }
 
-    // scale, mask by absolute position, running softmax (rows g and g + 8 of the warp's 16)
+    // scale, mask by absolute position, running softmax (rows g and g + 8 of the warp's 16). Most tiles lie
+    // wholly before every query of the warp (and inside every window): those need no mask.
     float m_new[2] = {m_run[0], m_run[1]};
+    const int warp_first = pos0 + warp * 16, warp_last = warp_first + 15;
+    const bool whole = kt * BK + BK - 1 <= warp_first && (window <= 0 || kt * BK > warp_last - window);
+    if (whole) {
 #pragma unroll
-    for (int nb = 0; nb < BK / 8; ++nb) {
+      for (int nb = 0; nb < BK / 8; ++nb) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = kt * BK + nb * 8 + 2 * t + (e & 1);
-        const int qp = qpos[e >> 1];
-        const bool seen = key <= qp && (window <= 0 || key > qp - window);
-        s[nb][e] = seen ? s[nb][e] * sl2 : -INFINITY;
-        m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nb][e]);
+        for (int e = 0; e < 4; ++e) {
+          s[nb][e] *= sl2;
+          m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nb][e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int nb = 0; nb < BK / 8; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = kt * BK + nb * 8 + 2 * t + (e & 1);
+          const int qp = qpos[e >> 1];
+          const bool seen = key <= qp && (window <= 0 || key > qp - window);
+          s[nb][e] = seen ? s[nb][e] * sl2 : -INFINITY;
+          m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nb][e]);
+        }
       }
     }
     float corr[2], m_use[2];
@@ -146,15 +160,15 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
       m_new[h2] = fmaxf(m_new[h2], __shfl_xor_sync(0xffffffffu, m_new[h2], 1));
       m_new[h2] = fmaxf(m_new[h2], __shfl_xor_sync(0xffffffffu, m_new[h2], 2));
       m_use[h2] = m_new[h2] == -INFINITY ? 0.f : m_new[h2];  // a row that sees nothing yet
-      corr[h2] = exp2f(m_run[h2] - m_use[h2]);
+      corr[h2] = fast_exp2(m_run[h2] - m_use[h2]);
       m_run[h2] = m_new[h2];
     }
     float l_add[2] = {0.f, 0.f};
     uint32_t pf[BK / 16][4];
 #pragma unroll
     for (int nb = 0; nb < BK / 8; ++nb) {
-      const float p0 = exp2f(s[nb][0] - m_use[0]), p1 = exp2f(s[nb][1] - m_use[0]);
-      const float p2 = exp2f(s[nb][2] - m_use[1]), p3 = exp2f(s[nb][3] - m_use[1]);
+      const float p0 = fast_exp2(s[nb][0] - m_use[0]), p1 = fast_exp2(s[nb][1] - m_use[0]);
+      const float p2 = fast_exp2(s[nb][2] - m_use[1]), p3 = fast_exp2(s[nb][3] - m_use[1]);
       l_add[0] += p0 + p1;
       l_add[1] += p2 + p3;
       pf[nb >> 1][(nb & 1) * 2] = pack_bf16(p0, p1);

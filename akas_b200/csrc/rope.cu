@@ -101,6 +101,83 @@ __global__ void qk_norm_rope_store_kernel(T* __restrict__ qkv, T* __restrict__ q
   }
 }
 
+// The same for head sizes 32, 64, 128 and 256 (and a rotary width that is a multiple of 16): a thread owns 8
+// neighbouring channels, TPH = head_dim / 8 threads own a head, a warp 32 / TPH heads. Loads and stores are
+// 16 bytes (32 for float32); the sum of squares and the rotation partner travel by shuffle.
+template <typename T, int TPH>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_store8_kernel(T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_w,
+                           const float* __restrict__ k_w, float eps, int zero_centered,
+                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rotary,
+                           T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ block_table,
+                           int max_blocks, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                           int page_size, int H, int KH) {
+  constexpr int D = TPH * 8, HEADS_PER_BLOCK = 128 / TPH;
+  chain_release();
+  chain_wait();
+  const int t = blockIdx.x;
+  const int head = blockIdx.y * HEADS_PER_BLOCK + threadIdx.x / TPH;
+  const int j = threadIdx.x % TPH, e0 = j * 8;
+  const int total = H + 2 * KH;
+  const bool live = head < total;
+  const int hd = live ? head : total - 1;  // threads past the last head shadow it (shuffles need every lane)
+  const bool is_q = hd < H, is_k = !is_q && hd < H + KH;
+  T* src = qkv + (size_t)t * total * D + (size_t)hd * D + e0;
+  const int r = seq_of_token[t];
+
+  T* page_row = nullptr;
+  if (live && !is_q && k_pool != nullptr && r >= 0) {
+    const int pos = positions[t];
+    const int page = block_table[(size_t)r * max_blocks + pos / page_size];
+    if (page >= 0) {
+      const int kvh = is_k ? hd - H : hd - H - KH;
+      page_row = (is_k ? k_pool : v_pool) + (((size_t)page * KH + kvh) * page_size + pos % page_size) * D + e0;
+    }
+  }
+  float x[8];
+  load8(src, x);
+  if (!is_q && !is_k) {  // value head: copy into the page (every lane still takes part in the shuffles below)
+    if (page_row) store8(page_row, x);
+  }
+  const float* w = is_q ? q_w : k_w;
+  if (w != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
+#pragma unroll
+    for (int o = TPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.f / sqrtf(ss / (float)D + eps);
+    float g[8];
+    load8(w + e0, g);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * (zero_centered ? 1.f + g[e] : g[e]);
+  }
+  if (cos_t != nullptr) {
+    const int half = rotary / 2, shift = half / 8;  // the partner of channel e is e +- half: `shift` threads away
+    const bool low = e0 < half, rotated = e0 < rotary;
+    const int lane = threadIdx.x & 31;
+    const int partner = rotated ? (low ? lane + shift : lane - shift) : lane;
+    float other[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) other[e] = __shfl_sync(0xffffffffu, x[e], partner);
+    if (rotated) {
+      float c[8], sn[8];
+      const int f0 = low ? e0 : e0 - half;
+      load8(cos_t + (size_t)t * half + f0, c);
+      load8(sin_t + (size_t)t * half + f0, sn);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = low ? x[e] * c[e] - other[e] * sn[e] : other[e] * sn[e] + x[e] * c[e];
+    }
+  }
+  if (!live || (!is_q && !is_k)) return;
+  if (is_q) {
+    store8(q_out + (size_t)t * H * D + (size_t)hd * D + e0, x);
+  } else {
+    store8(src, x);
+    if (page_row) store8(page_row, x);
+  }
+}
+
 AKAS_API int akas_qk_norm_rope_store(void* qkv, void* q_out, const float* q_w, const float* k_w, float eps,
                                      int zero_centered, const float* cos_t, const float* sin_t, int rotary,
                                      void* k_pool, void* v_pool, const int* block_table, int max_blocks,
@@ -108,6 +185,28 @@ AKAS_API int akas_qk_norm_rope_store(void* qkv, void* q_out, const float* q_w, c
                                      int KH, int D, int dtype, cudaStream_t stream) {
   if (D > 256 || D <= 0 || rotary > D || (rotary & 1)) return (int)cudaErrorInvalidValue;
   if (N <= 0) return 0;
+  const bool wide = (D == 32 || D == 64 || D == 128 || D == 256) && rotary % 16 == 0 && (uintptr_t)qkv % 16 == 0 &&
+                    (uintptr_t)q_out % 16 == 0 && (k_pool == nullptr || ((uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0)) &&
+                    (cos_t == nullptr || ((uintptr_t)cos_t % 16 == 0 && (rotary / 2) % 8 == 0));
+  if (wide) {
+    const int tph = D / 8, per_block = 128 / tph;
+    const dim3 grid8(N, (H + 2 * KH + per_block - 1) / per_block);
+#define AKAS_QK8(T, TPH)                                                                                            \
+  return launch_chained(qk_norm_rope_store8_kernel<T, TPH>, grid8, dim3(128), 0, stream, (T*)qkv, (T*)q_out, q_w, k_w, \
+                        eps, zero_centered, cos_t, sin_t, rotary, (T*)k_pool, (T*)v_pool, block_table, max_blocks,      \
+                        seq_of_token, positions, page_size, H, KH)
+    if (dtype == AKAS_F32) {
+      if (tph == 4) AKAS_QK8(float, 4);
+      if (tph == 8) AKAS_QK8(float, 8);
+      if (tph == 16) AKAS_QK8(float, 16);
+      AKAS_QK8(float, 32);
+    }
+    if (tph == 4) AKAS_QK8(bf16, 4);
+    if (tph == 8) AKAS_QK8(bf16, 8);
+    if (tph == 16) AKAS_QK8(bf16, 16);
+    AKAS_QK8(bf16, 32);
+#undef AKAS_QK8
+  }
   const dim3 grid(N, (H + 2 * KH + AKAS_ROPE_WARPS - 1) / AKAS_ROPE_WARPS);
   const int threads = 32 * AKAS_ROPE_WARPS;
   if (dtype == AKAS_F32)

@@ -261,12 +261,18 @@ def _skinny_fits(m: int, k: int) -> bool:
 
 
 _SKINNY_ROWS = 16
-library_products = os.environ.get("AKAS_B200_LIBRARY_PRODUCTS", "0") == "1"  # cuBLASLt instead of the tcgen05 kernel
+# Which kernel runs the products of prompt portions (more than 16 tokens). "auto": the tcgen05 kernel where its
+# fused read-out saves a pass over memory (SwiGLU), cuBLASLt for the plain and residual products, which the
+# library's two-SM tiles still run faster; "tcgen05": the hand-written kernel everywhere; "library": cuBLASLt
+# everywhere (SwiGLU then runs as a kernel of its own).
+products = os.environ.get("AKAS_B200_PRODUCTS", "auto")
+if products not in ("auto", "tcgen05", "library"):
+    raise ValueError(f"AKAS_B200_PRODUCTS must be auto, tcgen05 or library, got {products!r}")
 
 
-def _tcgen05_takes(n: int, k: int) -> bool:
-    """More tokens than the skinny kernel takes, a 16-byte row pitch, and the library not asked for."""
-    return n > _SKINNY_ROWS and k % 8 == 0 and not library_products
+def _tcgen05_takes(n: int, k: int, fused: bool = False) -> bool:
+    """More tokens than the skinny kernel takes, a 16-byte row pitch, and the policy above."""
+    return n > _SKINNY_ROWS and k % 8 == 0 and (products == "tcgen05" or (products == "auto" and fused))
 
 
 def gemm_tcgen05_status() -> int:
@@ -291,7 +297,7 @@ def linear_swiglu(x, w_gate_up):
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _skinny(_dense(x, "x"), None, None, 0.0, False, _dense(w_gate_up, "w"), out, n, f2, k, 0, _OUT_SWIGLU)
         return out
-    if x.dtype == torch.bfloat16 and _tcgen05_takes(n, k) and f2 % 16 == 0:
+    if x.dtype == torch.bfloat16 and _tcgen05_takes(n, k, fused=True) and f2 % 16 == 0:
         # SwiGLU in the read-out of the product: the [N, 2F] intermediate is never written
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _check(_fn("gemm_tcgen05", "akas_gemm_tcgen05")(_ptr(_dense(x, "x")), _ptr(_dense(w_gate_up, "w")), _ptr(out), n,

@@ -133,11 +133,15 @@ def test_tensor_memory_products_for_prompt_portions(ops, m, k, o):
     cuda, ref = ops
     x, w = _rand((m, k), torch.bfloat16, 5), _rand((o, k), torch.bfloat16, 6, 0.05)
     want = x.double() @ w.double().T
-    _close(cuda.linear(x, w), want, torch.bfloat16, "bf16 out")
-    res = _rand((m, o), torch.float32, 7)
-    _close(cuda.linear(x, w, residual=res.clone()), res.double() + want, torch.float32, "accumulate", k)
-    w2 = _rand((2 * o, k), torch.bfloat16, 8, 0.05)
-    _close(cuda.linear_swiglu(x, w2), ref.linear_swiglu(x, w2), torch.bfloat16, "swiglu")
+    policy, cuda.products = cuda.products, "tcgen05"  # every read-out of the kernel, whatever the default policy
+    try:
+        _close(cuda.linear(x, w), want, torch.bfloat16, "bf16 out")
+        res = _rand((m, o), torch.float32, 7)
+        _close(cuda.linear(x, w, residual=res.clone()), res.double() + want, torch.float32, "accumulate", k)
+        w2 = _rand((2 * o, k), torch.bfloat16, 8, 0.05)
+        _close(cuda.linear_swiglu(x, w2), ref.linear_swiglu(x, w2), torch.bfloat16, "swiglu")
+    finally:
+        cuda.products = policy
     assert cuda.gemm_tcgen05_status() == 0
 
 
