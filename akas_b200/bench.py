@@ -232,6 +232,41 @@ def bench_linear(m: int, o: int, k: int, mode: str, iters: int = 20) -> dict:
                 tflops=round(2.0 * m * o * k / ms / 1e9, 2))
 
 
+def bench_attention(kind: str, batch: int, context: int, heads: int = 32, kv_heads: int = 8, dim: int = 64,
+                    page: int = 64, iters: int = 20) -> dict:
+    """Paged attention of the bfloat16 path, cold L2. ``decode``: ``batch`` requests of ``context`` cached tokens,
+    one query token each. ``prompt``: ``batch`` requests whose whole ``context`` tokens are queries."""
+    from types import SimpleNamespace
+
+    from .ops import cuda as ops
+
+    ops.require(ops.libraries_for(torch.bfloat16))
+    g = torch.Generator(device="cuda").manual_seed(0)
+    blocks = -(-context // page)
+    pages = batch * blocks
+    k = torch.randn((pages, kv_heads, page, dim), device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn((pages, kv_heads, page, dim), device="cuda", generator=g).to(torch.bfloat16)
+    table = torch.randperm(pages, device="cuda", generator=g).to(torch.int32).view(batch, blocks)
+    if kind == "decode":
+        n = batch
+        seq = torch.arange(batch, dtype=torch.int32, device="cuda")
+        pos = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
+        ctx = SimpleNamespace(decode_only=True, max_context=context, query_tiles=0, cu_seqlens=None)
+        flops = 4.0 * batch * context * heads * dim
+    else:
+        n = batch * context
+        seq = torch.arange(batch, dtype=torch.int32, device="cuda").repeat_interleave(context)
+        pos = torch.arange(context, dtype=torch.int32, device="cuda").repeat(batch)
+        cu = torch.arange(0, n + 1, context, dtype=torch.int32, device="cuda")
+        ctx = SimpleNamespace(decode_only=False, max_context=context, query_tiles=batch * -(-context // 64), cu_seqlens=cu)
+        flops = 4.0 * batch * context * (context + 1) / 2 * heads * dim
+    q = torch.randn((n, heads * dim), device="cuda", generator=g).to(torch.bfloat16)
+    ms = _time_kernel(lambda: ops.paged_attention(q, k, v, table, seq, pos, dim ** -0.5, None, page, ctx), iters)
+    kv_bytes = 2.0 * batch * context * kv_heads * dim * 2
+    return dict(kernel="attention", kind=kind, batch=batch, context=context, heads=heads, kv_heads=kv_heads, head_dim=dim,
+                ms=round(ms, 5), kv_gb_s=round(kv_bytes / ms / 1e6, 1), tflops=round(flops / ms / 1e9, 2))
+
+
 def _main():
     import argparse
     import json
@@ -244,7 +279,20 @@ def _main():
     lin.add_argument("--k", type=int, default=2048)
     lin.add_argument("--mode", default="bf16", choices=("bf16", "f32", "acc", "swiglu", "norm", "norm_swiglu"))
     lin.add_argument("--iters", type=int, default=20)
+    att = sub.add_parser("attention", help="paged attention over the cache")
+    att.add_argument("--kind", default="decode", choices=("decode", "prompt"))
+    att.add_argument("--batch", type=int, nargs="+", default=[8])
+    att.add_argument("--context", type=int, default=2048)
+    att.add_argument("--heads", type=int, default=32)
+    att.add_argument("--kv-heads", type=int, default=8)
+    att.add_argument("--head-dim", type=int, default=64)
+    att.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
+    if args.what == "attention":
+        for b in args.batch:
+            print(json.dumps(bench_attention(args.kind, b, args.context, args.heads, args.kv_heads, args.head_dim,
+                                             iters=args.iters)))
+        return
     for m in args.m:
         print(json.dumps(bench_linear(m, args.o, args.k, args.mode, args.iters)))
 
