@@ -1,27 +1,43 @@
 // Matrix products for a handful of tokens (decode steps): y[M, O] = f(x)[M, K] . W[O, K]^T with M <= 16,
-// bfloat16 weights streamed once from HBM, float32 accumulation on the tensor cores.
+// bfloat16 weights streamed once from HBM by TMA, float32 accumulation on the tensor cores.
 //
 // The weights are the A operand of mma.sync m16n8k16 (16 weight rows x 16 k), the tokens are the 8
-// columns of B, so one block turns 16 rows of W into 16 output channels for all tokens. Its 8 warps
-// split K in 32-wide chunks; in a chunk, thread (g, t) of a warp loads 16 contiguous bytes of W rows g
-// and g + 8 and of the activations of token g at k = 32c + 8t. The 8 values feed two k-steps; the
-// product does not care which physical k sits in which k-slot as long as A and B agree, which is
-// what makes 16-byte loads possible. Blocks are persistent: one or two per SM, each taking row tiles
-// blockIdx.x, blockIdx.x + gridDim.x, ... The weight rows arrive through an eight-stage ring of
-// 256-wide chunks in shared memory filled by cp.async (56 KB of loads in flight per block) that runs
-// on across row tiles; the tokens' activations are put into shared memory once per block (converted
-// and weighted by the norm there, if the norm rides along), so the inner loop reads shared memory
-// only. At the end of a row tile the 8 warps' partial sums meet in shared memory.
+// columns of B, so 16 rows of W become 16 output channels for all tokens. Blocks are persistent: one or
+// two per SM, each taking row tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+//
+// A block has one producer warp and 8 consumer warps. The producer streams the block's weight rows, in
+// 256-wide chunks, into an eight-stage ring in shared memory: two TMA tensor loads per stage (rows 0-7 and
+// rows 8-15 of the tile, each a box of 64 k x 8 rows x 4 groups of k from a three-dimensional view
+// [K/64][O][64] of the matrix, 128-byte swizzle), completion counted in bytes on the stage's "full" mbarrier.
+// It runs ahead across row tiles, held back only by the stages' "empty" mbarriers, on which the consumer
+// warps arrive when they have read a stage. So up to 64 KB of loads are in flight per block with one thread
+// issuing them, and the consumers' loop is: wait for the stage, three 16-byte reads from shared memory, two
+// products, arrive. The 8 consumer warps split a chunk 32 k each; in its 32 k, thread (g, t) reads 16
+// contiguous bytes of W rows g and g + 8 and of token g at k = 8t. These 8 values feed two k-steps: the
+// product does not care which physical k sits in which k-slot as long as A and B agree, which is what makes
+// 16-byte reads possible. The tokens' activations are put into shared memory once per block (converted and
+// weighted by the norm there, if the norm rides along). At the end of a row tile the consumers' partial sums
+// meet in shared memory (a barrier of the consumer warps only).
+//
+// The producer starts before the kernel waits for its predecessor (weights depend on nothing).
+// Every wait on an mbarrier is bounded: a wait that runs out sets a status flag that the host can read
+// (akas_skinny_gemm_status), everyone stops waiting and the block runs to its end; results of such a launch
+// are not valid.
 //
 // Input modes:   bf16   x is bfloat16 [M, K]
 //                norm   x is the float32 residual stream (rows optionally gathered by index); the kernel
-//                       forms bf16(x * norm_weight) for B, sums x^2 per token on the way and multiplies
-//                       the result by rsqrt(mean(x^2) + eps): RMSNorm without a pass of its own.
+//                       forms bf16(x * norm_weight), sums x^2 per token on the way and multiplies the
+//                       result by rsqrt(mean(x^2) + eps): RMSNorm without a pass of its own.
 // Output modes:  bf16 store | float32 store | float32 accumulate (y += ..., the residual stream) |
 //                swiglu: the block's 16 rows are gate rows f0..f0+7 and up rows F+f0..F+f0+7 of the
 //                stacked [2F, K] matrix, so silu(gate) * up is formed per thread and stored as bf16 [M, F].
-// Needs K % 32 == 0. Results do not depend on what else runs; summation order is fixed.
+// Needs K % 64 == 0. Results do not depend on what else runs; summation order is fixed.
+#include <cuda.h>
 #include <math.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #include "common.cuh"
 #include "mma.cuh"
@@ -30,186 +46,271 @@ using namespace akas;
 
 namespace {
 
-constexpr int WARPS = 8, KC = 256, STAGES = 8, AS = KC + 32;  // AS: row stride of a stage, 16 words off a multiple of 32 banks
+constexpr int CONSUMERS = 8, KC = 256, STAGES = 8;
+constexpr int STAGE_BYTES = 16 * KC * 2;  // two boxes of [4 groups of k][8 rows][128 bytes]
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr unsigned kSpinLimit = 1u << 22;  // try_wait calls before a wait gives up (each may block for a while)
 enum { IN_BF16 = 0, IN_NORM = 1 };
 enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_ACC = 2, OUT_SWIGLU = 3 };
 
+__device__ int g_skinny_status = 0;  // 0, or the code of a wait that ran out (1: a full stage, 2: an empty stage)
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Waits for the phase of the given parity to complete; false if the bounded wait ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+  const unsigned addr = smem_u32(bar);
+  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// One box of the weights: 64 k x 8 rows x 4 groups of k, starting at row `row` and k-group `group`.
+__device__ __forceinline__ void tma_load_box(void* smem_dst, const CUtensorMap* map, int row, int group, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(smem_u32(smem_dst)), "l"(map), "r"(0), "r"(row), "r"(group), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory"); }
+
 template <int NT, int IN, int OUT>
-__global__ void __launch_bounds__(WARPS * 32)
-skinny_gemm_kernel(const void* __restrict__ x_, const int* __restrict__ rows, const float* __restrict__ norm_w,
-                   float eps, int zero_centered, const bf16* __restrict__ W, void* __restrict__ y_, int M, int O,
+__global__ void __launch_bounds__(THREADS)
+skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __restrict__ x_, const int* __restrict__ rows,
+                   const float* __restrict__ norm_w, float eps, int zero_centered, void* __restrict__ y_, int M, int O,
                    int K, int num_tiles) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* ring = reinterpret_cast<bf16*>(smem_raw);               // [STAGES][16][AS]: weight rows, chunk by chunk
-  float* red = reinterpret_cast<float*>(ring + STAGES * 16 * AS);  // [WARPS][NT][16][8]: the warps' partial sums
-  bf16* xs = reinterpret_cast<bf16*>(red + WARPS * NT * 128);    // [NT * 8][XS]: the tokens' activations, whole K
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);  // [STAGES][STAGE_BYTES]
+  float* red = reinterpret_cast<float*>(ring + STAGES * STAGE_BYTES);   // [CONSUMERS][NT][16][8]: partial sums
+  bf16* xs = reinterpret_cast<bf16*>(red + CONSUMERS * NT * 128);       // [NT * 8][XS]: the tokens' activations
   const int XS = K + 32;
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES];
   __shared__ float ss_s[NT * 8];
+  __shared__ int abort_s;  // set by the first wait that runs out; from then on nobody waits on an mbarrier
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = lane >> 2, t = lane & 3;
   const int F = O / 2;  // swiglu only: O is the stacked height 2F
-
-  // weight row that stage row i of row tile `tile` holds, or -1
-  auto weight_row = [&](int tile, int i) -> int {
-    if (OUT == OUT_SWIGLU) {
-      const int f = tile * 8 + (i & 7);
-      return f < F ? (i < 8 ? f : F + f) : -1;
-    }
-    const int o = tile * 16 + i;
-    return o < O ? o : -1;
-  };
   const int chunks = (K + KC - 1) / KC;
-  // this block's row tiles: blockIdx.x, blockIdx.x + gridDim.x, ...; its work is the sequence of their chunks
   const int my_tiles = (num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-  const int items = my_tiles * chunks;
-  int load_tile = blockIdx.x, load_chunk = 0, loaded = 0;  // the next item whose copies are to be issued
-  auto issue_next = [&]() {
-    if (loaded < items) {
-      const int k0 = load_chunk * KC, len = min(KC, K - k0);
-      bf16* dst = ring + (size_t)(loaded % STAGES) * 16 * AS;
-      if (len == KC) {  // the common case: two 16-byte copies per thread, no division
-#pragma unroll
-        for (int i = tid; i < 16 * (KC / 8); i += WARPS * 32) {
-          const int row = i / (KC / 8), col = (i % (KC / 8)) * 8;
-          const int wr = weight_row(load_tile, row);
-          cp_async16(dst + row * AS + col, W + (size_t)max(wr, 0) * K + k0 + col, wr >= 0 ? 16 : 0);
-        }
-      } else {
-        const int per_row = len / 8;
-        for (int i = tid; i < 16 * per_row; i += WARPS * 32) {
-          const int row = i / per_row, col = (i % per_row) * 8;
-          const int wr = weight_row(load_tile, row);
-          cp_async16(dst + row * AS + col, W + (size_t)max(wr, 0) * K + k0 + col, wr >= 0 ? 16 : 0);
-        }
-      }
-      ++loaded;
-      if (++load_chunk == chunks) { load_chunk = 0; load_tile += gridDim.x; }
+  const int items = my_tiles * chunks;  // this block's work: the chunks of its row tiles, in order
+
+  if (tid == 0) {
+    abort_s = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], CONSUMERS);
     }
-    cp_async_commit();
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  chain_release();
+  // A bounded wait. When one runs out the launch is lost (the status flag says so), but every thread keeps
+  // following the same path through the barriers, so the block still ends.
+  auto wait_for = [&](uint64_t* bar, unsigned parity, int code) {
+    if (*(volatile int*)&abort_s) return;
+    if (!mbar_wait(bar, parity)) {
+      *(volatile int*)&abort_s = 1;
+      if (lane == 0) atomicExch(&g_skinny_status, code);
+    }
   };
 
-  // The weights do not depend on anything an earlier kernel wrote: their first chunks are requested before
-  // this kernel waits for its predecessor, whose tail they overlap.
-  chain_release();
-#pragma unroll
-  for (int c = 0; c < STAGES - 2; ++c) issue_next();
-  chain_wait();
-
-  // Activations into shared memory, once per block. bfloat16 input is a cp.async group of its own (empty
-  // when the norm rides along), then the last chunk of the prologue follows.
-  if (IN == IN_BF16) {
-    const int per_row = K / 8;
-    for (int i = tid; i < NT * 8 * per_row; i += WARPS * 32) {
-      const int m = i / per_row, col = (i % per_row) * 8;
-      const size_t src = m < M ? (size_t)(rows ? rows[m] : m) : 0;
-      cp_async16(xs + (size_t)m * XS + col, (const bf16*)x_ + src * K + col, m < M ? 16 : 0);
-    }
-  }
-  cp_async_commit();
-  issue_next();
-  if (IN == IN_NORM) {
-    // float32 residual rows -> bf16(x * norm weight); each warp owns tokens warp, warp + 8 and sums x^2
-    for (int m = warp; m < NT * 8; m += WARPS) {
-      float ss = 0.f;
-      bf16* dst = xs + (size_t)m * XS;
-      if (m < M) {
-        const float* src = (const float*)x_ + (size_t)(rows ? rows[m] : m) * K;
-#pragma unroll 8
-        for (int k = lane * 4; k < K; k += 128) {
-          const float4 v = *reinterpret_cast<const float4*>(src + k);
-          float4 w = *reinterpret_cast<const float4*>(norm_w + k);
-          if (zero_centered) { w.x += 1.f; w.y += 1.f; w.z += 1.f; w.w += 1.f; }
-          ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-          uint2 packed;
-          packed.x = pack_bf16(v.x * w.x, v.y * w.y);
-          packed.y = pack_bf16(v.z * w.z, v.w * w.w);
-          *reinterpret_cast<uint2*>(dst + k) = packed;
-        }
-        ss = warp_sum(ss);
-      } else {
-        for (int k = lane * 4; k < K; k += 128) *reinterpret_cast<uint2*>(dst + k) = make_uint2(0u, 0u);
+  if (warp == CONSUMERS) {
+    // ---------------------------------------------------------------- producer: one thread, two boxes per stage
+    if (lane == 0) {
+      int tile = blockIdx.x, chunk = 0;
+      for (int n = 0; n < items; ++n) {
+        const int s = n % STAGES;
+        if (n >= STAGES) wait_for(&empty_bar[s], ((n / STAGES) & 1) ^ 1, 2);
+        if (*(volatile int*)&abort_s) break;  // no more copies
+        // rows 0-7 and 8-15 of the tile: 16 consecutive weight rows, or 8 gate rows and the 8 up rows under them
+        const int row_lo = OUT == OUT_SWIGLU ? tile * 8 : tile * 16;
+        const int row_hi = OUT == OUT_SWIGLU ? F + tile * 8 : tile * 16 + 8;
+        unsigned char* dst = ring + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);  // rows or k past the matrix arrive as zeros and count too
+        tma_load_box(dst, &map_w, row_lo, chunk * (KC / 64), &full_bar[s]);
+        tma_load_box(dst + STAGE_BYTES / 2, &map_w, row_hi, chunk * (KC / 64), &full_bar[s]);
+        if (++chunk == chunks) { chunk = 0; tile += gridDim.x; }
       }
-      if (lane == 0) ss_s[m] = ss;
     }
-  }
+    // Copies may still be in flight: the block must not exit before they have landed. The consumers wait for
+    // every stage they read; the producer stays until they are through (the block-wide barrier below).
+  } else {
+    // ---------------------------------------------------------------- consumers
+    const int g = lane >> 2, t = lane & 3;
+    chain_wait();  // from here on the kernel reads what its predecessor wrote
+    if (IN == IN_BF16) {
+      const int per_row = K / 8;
+      for (int i = tid; i < NT * 8 * per_row; i += CONSUMERS * 32) {  // all copies in flight together
+        const int m = i / per_row, col = (i % per_row) * 8;
+        const size_t src = m < M ? (size_t)(rows ? rows[m] : m) : 0;
+        cp_async16(xs + (size_t)m * XS + col, (const bf16*)x_ + src * K + col, m < M ? 16 : 0);
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+    } else {
+      // float32 residual rows -> bf16(x * norm weight); each warp owns tokens warp, warp + 8 and sums x^2
+      for (int m = warp; m < NT * 8; m += CONSUMERS) {
+        float ss = 0.f;
+        bf16* dst = xs + (size_t)m * XS;
+        if (m < M) {
+          const float* src = (const float*)x_ + (size_t)(rows ? rows[m] : m) * K;
+#pragma unroll 8
+          for (int k = lane * 4; k < K; k += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(src + k);
+            float4 w = *reinterpret_cast<const float4*>(norm_w + k);
+            if (zero_centered) { w.x += 1.f; w.y += 1.f; w.z += 1.f; w.w += 1.f; }
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+            uint2 packed;
+            packed.x = pack_bf16(v.x * w.x, v.y * w.y);
+            packed.y = pack_bf16(v.z * w.z, v.w * w.w);
+            *reinterpret_cast<uint2*>(dst + k) = packed;
+          }
+          ss = warp_sum(ss);
+        } else {
+          for (int k = lane * 4; k < K; k += 128) *reinterpret_cast<uint2*>(dst + k) = make_uint2(0u, 0u);
+        }
+        if (lane == 0) ss_s[m] = ss;
+      }
+    }
+    consumer_barrier();  // the activations are in shared memory for every consumer warp
 
-  float acc[NT][4];
+    // Where this thread's 16 bytes of weight rows g and g + 8 lie inside a stage: box (rows 0-7 or 8-15), group of
+    // 64 k (warp / 2), row g, and the 16-byte unit ((warp & 1) * 4 + t) XOR g of the 128-byte swizzle.
+    const int a_off = ((warp >> 1) * 8 + g) * 128 + ((((warp & 1) * 4 + t) ^ g) << 4);
+    float acc[NT][4];
 #pragma unroll
-  for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+    for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+    int tile = blockIdx.x, c = 0;
+    for (int n = 0; n < items; ++n) {
+      const int s = n % STAGES;
+      wait_for(&full_bar[s], (n / STAGES) & 1, 1);
+      const int k = c * KC + warp * 32 + 8 * t;  // this thread's 8 consecutive k of the chunk
+      if (k < K) {
+        const unsigned char* st = ring + (size_t)s * STAGE_BYTES + a_off;
+        const uint4 a_lo = *reinterpret_cast<const uint4*>(st);
+        const uint4 a_hi = *reinterpret_cast<const uint4*>(st + STAGE_BYTES / 2);
+        const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};  // first k-step: this thread's k 0..3
+        const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};  // second k-step: its k 4..7
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          const uint4 b = *reinterpret_cast<const uint4*>(xs + (size_t)(8 * j + g) * XS + k);
+          mma_bf16(acc[j], a1, b.x, b.y);
+          mma_bf16(acc[j], a2, b.z, b.w);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);  // this warp has read the stage
+      if (++c < chunks) continue;
 
-  int tile = blockIdx.x, c = 0;
-  for (int n = 0; n < items; ++n) {
-    // Groups in flight, oldest first: chunks 0 .. STAGES-3, the activations, chunk STAGES-2, ... The first
-    // item waits until only the newest is pending (so the activations are in); later ones keep STAGES-2 going.
-    if (n == 0) cp_async_wait<1>(); else cp_async_wait<STAGES - 2>();
-    __syncthreads();  // item n (and the activations) are there for everyone; everyone is done with item n - 1
-    issue_next();
-    const int k = c * KC + warp * 32 + 8 * t;  // this thread's 8 consecutive k of the chunk
-    if (k < K) {
-      const bf16* st = ring + (size_t)(n % STAGES) * 16 * AS + warp * 32 + 8 * t;
-      const uint4 a_lo = *reinterpret_cast<const uint4*>(st + g * AS);
-      const uint4 a_hi = *reinterpret_cast<const uint4*>(st + (g + 8) * AS);
-      const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};  // first k-step: this thread's k 0..3
-      const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};  // second k-step: its k 4..7
+      // the row tile is complete: the consumer warps' partial sums meet in shared memory, then the epilogue
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        const uint4 b = *reinterpret_cast<const uint4*>(xs + (size_t)(8 * j + g) * XS + k);
-        mma_bf16(acc[j], a1, b.x, b.y);
-        mma_bf16(acc[j], a2, b.z, b.w);
+        float* r0 = red + (((size_t)warp * NT + j) * 16 + g) * 8 + 2 * t;
+        r0[0] = acc[j][0];
+        r0[1] = acc[j][1];
+        r0[64] = acc[j][2];  // row g + 8
+        r0[65] = acc[j][3];
+        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
       }
-    }
-    if (++c < chunks) continue;
-
-    // the row tile is complete: the 8 warps' partial sums meet in shared memory, then the epilogue
+      consumer_barrier();
+      constexpr int per_tile = OUT == OUT_SWIGLU ? 64 : 128;  // (row, token) pairs per n-block
+      for (int i = tid; i < NT * per_tile; i += CONSUMERS * 32) {
+        const int j = i / per_tile, row = (i % per_tile) / 8, tok = i % 8;
+        const int m = 8 * j + tok;
+        if (m >= M) continue;
+        float v = 0.f, u = 0.f;
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      float* r0 = red + (((size_t)warp * NT + j) * 16 + g) * 8 + 2 * t;
-      r0[0] = acc[j][0];
-      r0[1] = acc[j][1];
-      r0[64] = acc[j][2];  // row g + 8
-      r0[65] = acc[j][3];
-      acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        for (int w = 0; w < CONSUMERS; ++w) {
+          const float* r0 = red + (((size_t)w * NT + j) * 16 + row) * 8 + tok;
+          v += r0[0];
+          if (OUT == OUT_SWIGLU) u += r0[64];
+        }
+        if (IN == IN_NORM) {
+          const float inv = 1.f / sqrtf(ss_s[m] / (float)K + eps);
+          v *= inv;
+          u *= inv;
+        }
+        if (OUT == OUT_SWIGLU) {
+          const int f = tile * 8 + row;
+          if (f < F) ((bf16*)y_)[(size_t)m * F + f] = __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
+        } else {
+          const int o = tile * 16 + row;
+          if (o >= O) continue;
+          const size_t at = (size_t)m * O + o;
+          if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
+          else if (OUT == OUT_F32) ((float*)y_)[at] = v;
+          else ((float*)y_)[at] += v;
+        }
+      }
+      consumer_barrier();  // `red` is free again before the next tile's sums are written
+      c = 0;
+      tile += gridDim.x;
     }
-    __syncthreads();  // (the next write to `red` is a whole item, and so a barrier, away)
-    constexpr int per_tile = OUT == OUT_SWIGLU ? 64 : 128;  // (row, token) pairs per n-block
-    for (int i = tid; i < NT * per_tile; i += WARPS * 32) {
-      const int j = i / per_tile, row = (i % per_tile) / 8, tok = i % 8;
-      const int m = 8 * j + tok;
-      if (m >= M) continue;
-      float v = 0.f, u = 0.f;
-#pragma unroll
-      for (int w = 0; w < WARPS; ++w) {
-        const float* r0 = red + (((size_t)w * NT + j) * 16 + row) * 8 + tok;
-        v += r0[0];
-        if (OUT == OUT_SWIGLU) u += r0[64];
-      }
-      if (IN == IN_NORM) {
-        const float inv = 1.f / sqrtf(ss_s[m] / (float)K + eps);
-        v *= inv;
-        u *= inv;
-      }
-      if (OUT == OUT_SWIGLU) {
-        const int f = tile * 8 + row;
-        if (f < F) ((bf16*)y_)[(size_t)m * F + f] = __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
-      } else {
-        const int o = tile * 16 + row;
-        if (o >= O) continue;
-        const size_t at = (size_t)m * O + o;
-        if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
-        else if (OUT == OUT_F32) ((float*)y_)[at] = v;
-        else ((float*)y_)[at] += v;
-      }
-    }
-    c = 0;
-    tile += gridDim.x;
   }
-  cp_async_wait<0>();
+  if (*(volatile int*)&abort_s) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);  // a lost launch: give copies still in flight time to land
+  }
+  __syncthreads();  // nobody leaves while a copy into this block's shared memory may be in flight
 }
 
-constexpr int kMaxSmemBytes = 226 * 1024;  // the block also has a few bytes of static shared memory
+// ------------------------------------------------------------------------------------------------ host side
 
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (EncodeTiled)p;
+  }();
+  return fn;
+}
+
+std::mutex g_map_mutex;
+std::map<std::tuple<const void*, int, int>, CUtensorMap> g_maps;  // one map per weight matrix
+
+// The matrix [O, K] seen as [K / 64][O][64]: boxes of 64 k x 8 rows x 4 groups of k, 128-byte swizzle, zeros outside.
+int weight_map(CUtensorMap* out, const void* w, int O, int K) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  const auto key = std::make_tuple(w, O, K);
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) {
+    EncodeTiled fn = encode_tiled();
+    if (!fn) return 3001;
+    const cuuint64_t dims[3] = {64, (cuuint64_t)O, (cuuint64_t)(K / 64)};
+    const cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
+    const cuuint32_t box[3] = {64, 8, KC / 64};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMap map;
+    const CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 3000 + (int)r;
+    it = g_maps.emplace(key, map).first;
+  }
+  *out = it->second;
+  return 0;
+}
+
+constexpr int kMaxSmemBytes = 226 * 1024;  // the block also has a few hundred bytes of static shared memory
+
+// Shared memory of a block: alignment slack, the ring, the partial sums and the activations.
 template <int NT>
-constexpr int fixed_smem() { return STAGES * 16 * AS * (int)sizeof(bf16) + WARPS * NT * 128 * (int)sizeof(float); }
+constexpr int fixed_smem() { return 1024 + STAGES * STAGE_BYTES + CONSUMERS * NT * 128 * (int)sizeof(float); }
 
 template <int NT, int IN, int OUTM>
 int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
@@ -225,13 +326,16 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
     if (e != cudaSuccess) { sms = 0; return (int)e; }
   }
+  CUtensorMap map;
+  const int err = weight_map(&map, W, O, K);
+  if (err) return err;
   const int per_sm = max(1, min(3, kMaxSmemBytes / (smem + 1024)));  // resident blocks per SM by shared memory
   // every block gets the same number of row tiles (to within one): blocks advance at the same rate, so a
   // grid that leaves some blocks with one tile more than others would idle the rest of the GPU meanwhile
   const int rounds = (num_tiles + sms * per_sm - 1) / (sms * per_sm);
   const int grid = (num_tiles + rounds - 1) / rounds;
-  return launch_chained(skinny_gemm_kernel<NT, IN, OUTM>, dim3(grid), dim3(WARPS * 32), (size_t)smem, stream, x, rows,
-                        norm_w, eps, zero_centered, (const bf16*)W, y, M, O, K, num_tiles);
+  return launch_chained(skinny_gemm_kernel<NT, IN, OUTM>, dim3(grid), dim3(THREADS), (size_t)smem, stream, map, x, rows,
+                        norm_w, eps, zero_centered, y, M, O, K, num_tiles);
 }
 
 template <int NT, int IN>
@@ -252,16 +356,27 @@ int launch_out(int out_mode, const void* x, const int* rows, const float* norm_w
 
 // x: bfloat16 [M, K] (in_mode 0) or float32 [*, K] rows gathered by `rows` (or 0..M-1) with RMSNorm fused (in_mode 1).
 // W: bfloat16 [O, K]. y: [M, O] in the output mode's type, or bfloat16 [M, O / 2] for swiglu (out_mode 3).
+// Returns 0, a CUDA error code, or 3000 + a driver error from building the weights' tensor map.
 AKAS_API int akas_skinny_gemm(const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
                               const void* W, void* y, int M, int O, int K, int in_mode, int out_mode,
                               cudaStream_t stream) {
   if (M <= 0 || O <= 0) return 0;
-  if (M > 16 || K <= 0 || K % 32 || (out_mode == OUT_SWIGLU && O % 2)) return (int)cudaErrorInvalidValue;
+  if (M > 16 || K <= 0 || K % 64 || (out_mode == OUT_SWIGLU && O % 2)) return (int)cudaErrorInvalidValue;
   if (in_mode == IN_NORM && norm_w == nullptr) return (int)cudaErrorInvalidValue;
+  if ((uintptr_t)W % 16 || (uintptr_t)x % 16) return (int)cudaErrorInvalidValue;  // TMA and 16-byte loads
   if (M <= 8) {
     if (in_mode == IN_BF16) return launch_out<1, IN_BF16>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
     return launch_out<1, IN_NORM>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
   }
   if (in_mode == IN_BF16) return launch_out<2, IN_BF16>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
   return launch_out<2, IN_NORM>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
+}
+
+// 0 if no bounded wait of the kernel has ever run out on the current device, else the code of the last one
+// (1: consumers waited for a stage that never filled, 2: the producer waited for a stage that never emptied).
+// Synchronises with the device.
+AKAS_API int akas_skinny_gemm_status() {
+  int status = -1;
+  const cudaError_t e = cudaMemcpyFromSymbol(&status, g_skinny_status, sizeof(int));
+  return e == cudaSuccess ? status : -(int)e;
 }

@@ -68,6 +68,7 @@ _SIGNATURES = {
     "skinny_gemm": {
         "akas_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_int, c_int, c_void_p],
+        "akas_skinny_gemm_status": [],
     },
     "sgemm": {
         "akas_sgemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -254,10 +255,10 @@ def linear(x, w, out_dtype=None, residual=None):
 
 
 def _skinny_fits(m: int, k: int) -> bool:
-    """Whether the skinny kernel takes this product: few tokens, an inner size that is a multiple of 32, and
-    activations that fit in shared memory beside the ring of weight chunks."""
+    """Whether the skinny kernel takes this product: few tokens, an inner size that is a multiple of 64 (its TMA
+    boxes), and activations that fit in shared memory beside the ring of weight chunks."""
     tokens = 8 if m <= 8 else 16
-    return m <= _SKINNY_ROWS and k % 32 == 0 and 8 * 16 * 288 * 2 + tokens * 512 + tokens * (k + 32) * 2 <= 226 * 1024
+    return m <= _SKINNY_ROWS and k % 64 == 0 and 1024 + 8 * 8192 + tokens * 512 + tokens * (k + 32) * 2 <= 226 * 1024
 
 
 _SKINNY_ROWS = 16
@@ -287,6 +288,12 @@ def _skinny(x, rows, norm_w, eps, zero_centered, w, out, m, o, k, in_mode, out_m
     _check(_fn("skinny_gemm", "akas_skinny_gemm")(_ptr(x), _ptr(rows), _ptr(norm_w), float(eps), int(bool(zero_centered)),
                                                  _ptr(w), _ptr(out), m, o, k, in_mode, out_mode, _stream()),
            f"skinny product [{m}x{k}] x [{o}x{k}]^T")
+
+
+def skinny_status() -> int:
+    """0 unless a bounded wait inside the skinny product kernel has run out on this device (then its results
+    since are not valid). Synchronises with the device."""
+    return int(_fn("skinny_gemm", "akas_skinny_gemm_status")())
 
 
 def linear_swiglu(x, w_gate_up):

@@ -99,7 +99,7 @@ def test_linear_bfloat16(ops, n, k, o):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("k,o", [(64, 50), (96, 320), (2048, 37), (8192, 64)])
+@pytest.mark.parametrize("k,o", [(64, 50), (192, 320), (2048, 37), (8192, 64), (96, 40)])
 def test_skinny_products_for_few_tokens(ops, m, k, o):
     """The decode-step product kernel: plain, float32 out, accumulate, SwiGLU, and with the norm riding along."""
     cuda, ref = ops
@@ -123,6 +123,7 @@ def test_skinny_products_for_few_tokens(ops, m, k, o):
     # more tokens than the kernel takes: the library path gives the same
     big = _rand((40, k), torch.float32, 11)
     _close(cuda.norm_linear(big, nw, 1e-5, False, w), ref.norm_linear(big, nw, 1e-5, False, w), torch.bfloat16, "many tokens")
+    assert cuda.skinny_status() == 0  # no bounded wait inside the kernel ran out
 
 
 @pytest.mark.parametrize("m,k,o", [(17, 64, 48), (64, 128, 256), (100, 96, 200), (128, 2048, 320), (300, 192, 1000),
