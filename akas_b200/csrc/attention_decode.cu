@@ -58,23 +58,35 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   const int per_split = (tiles + splits - 1) / splits;
   const int lo = kt_first + split * per_split, hi = min(lo + per_split, kt_last + 1);
 
+  // A thread copies the same 16-byte column of rows tid / CHUNKS, + 128 / CHUNKS, ... of every tile. When pages hold
+  // whole tiles (page size a multiple of 64) a tile needs one look-up in the block table; else one per row.
+  constexpr int ROWS_PER_PASS = WARPS * 32 / CHUNKS;
+  const int my_row = tid / CHUNKS, my_col = (tid % CHUNKS) * 8;
+  const bool whole_pages = page_size % BK == 0;
   auto load_tile = [&](int kt, int stage) {
-    bf16* ks_ = k_s + stage * BK * STRIDE;
-    bf16* vs_ = v_s + stage * BK * STRIDE;
-    for (int c = tid; c < BK * CHUNKS; c += WARPS * 32) {
-      const int row = c / CHUNKS, col = (c % CHUNKS) * 8;
-      const int key = kt * BK + row;
+    bf16* ks_ = k_s + stage * BK * STRIDE + my_col;
+    bf16* vs_ = v_s + stage * BK * STRIDE + my_col;
+    const int key0 = kt * BK;
+    long long tile_row = -1;  // first pool row of the tile (in rows of D elements), if one page holds it
+    if (whole_pages) {
+      const int page = block_table[(size_t)r * max_blocks + key0 / page_size];
+      if (page >= 0) tile_row = ((long long)page * KH + kvh) * page_size + key0 % page_size;
+    }
+#pragma unroll
+    for (int row = my_row; row < BK; row += ROWS_PER_PASS) {
+      const int key = key0 + row;
       size_t at = 0;
       int bytes = 0;
       if (key >= first_key && key <= pos) {
-        const int page = block_table[(size_t)r * max_blocks + key / page_size];
-        if (page >= 0) {
-          at = (((size_t)page * KH + kvh) * page_size + key % page_size) * D + col;
-          bytes = 16;
+        if (whole_pages) {
+          if (tile_row >= 0) { at = (size_t)(tile_row + row) * D + my_col; bytes = 16; }
+        } else {
+          const int page = block_table[(size_t)r * max_blocks + key / page_size];
+          if (page >= 0) { at = (((size_t)page * KH + kvh) * page_size + key % page_size) * D + my_col; bytes = 16; }
         }
       }
-      cp_async16(ks_ + row * STRIDE + col, k_pool + at, bytes);
-      cp_async16(vs_ + row * STRIDE + col, v_pool + at, bytes);
+      cp_async16(ks_ + row * STRIDE, k_pool + at, bytes);
+      cp_async16(vs_ + row * STRIDE, v_pool + at, bytes);
     }
   };
 

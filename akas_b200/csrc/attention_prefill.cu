@@ -9,7 +9,7 @@
 // memory; scale, causal/window mask, running max and sum are float32 in registers; P is rounded to
 // bfloat16 for the second product, as the values it multiplies are.
 //
-// Tiles are found on the device: block b scans cu_seqlens for the request whose tiles contain b.
+// Tiles are found on the device: a block scans cu_seqlens for the request whose tiles contain its tile number.
 // Head sizes 16, 32, 64 and 128; others use the general kernel in attention.cu.
 #include <math.h>
 
@@ -36,8 +36,10 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
   bf16* k_s = reinterpret_cast<bf16*>(smem_raw);          // [2][BK][STRIDE]; stage 0 first holds Q
   bf16* v_s = k_s + 2 * BK * STRIDE;                      // [2][BK][STRIDE]
 
-  // which tile of which request is this block?
-  int tile = blockIdx.x, r = 0, n = 0;
+  // Which tile of which request is this block? Blocks are handed out with x fastest, so heads are x and tiles y,
+  // last tile first: the tiles with the most keys to walk (the ends of long portions) start first and the short
+  // ones fill the tail.
+  int tile = (int)gridDim.y - 1 - (int)blockIdx.y, r = 0, n = 0;
   for (; r < R; ++r) {
     n = cu_seqlens[r + 1] - cu_seqlens[r];
     const int tiles = (n + BQ - 1) / BQ;
@@ -45,7 +47,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     tile -= tiles;
   }
   if (r >= R) return;
-  const int head = blockIdx.y, kvh = head / (H / KH);
+  const int head = blockIdx.x, kvh = head / (H / KH);
   const int q0 = cu_seqlens[r] + tile * BQ;
   const int rows = min(BQ, n - tile * BQ);
   const int pos0 = positions[q0];
@@ -225,7 +227,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* blo
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  prefill_attention_kernel<D><<<dim3(tiles, H), WARPS * 32, smem, stream>>>(
+  prefill_attention_kernel<D><<<dim3(H, tiles), WARPS * 32, smem, stream>>>(
       (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_seqlens, positions,
       (bf16*)out, scale, window, page_size, H, KH, R);
   return launch_status();
@@ -238,7 +240,7 @@ AKAS_API int akas_prefill_attention_bf16(const void* q, const void* k_pool, cons
                                          int max_blocks, const int* cu_seqlens, const int* positions, void* out,
                                          float scale, int window, int page_size, int tiles, int H, int KH, int D, int R,
                                          cudaStream_t stream) {
-  if (H % KH || H > 65535 || R <= 0) return (int)cudaErrorInvalidValue;
+  if (H % KH || tiles > 65535 || R <= 0) return (int)cudaErrorInvalidValue;
   if (tiles <= 0) return 0;
 #define AKAS_PREFILL(DD)                                                                                          \
   case DD:                                                                                                        \

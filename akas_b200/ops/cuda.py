@@ -422,7 +422,7 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
             splits, _code(q), _stream()), "paged_attention_decode", kernels=2)
         return out
     tiles = getattr(ctx, "query_tiles", 0) if ctx is not None else 0
-    if q.dtype == torch.bfloat16 and d in (16, 32, 64, 128) and tiles > 0:
+    if q.dtype == torch.bfloat16 and d in (16, 32, 64, 128) and 0 < tiles <= 65535:
         # prompt portions (and whatever decodes beside them): 64-query tiles on the tensor cores
         _check(_fn("attention_prefill", "akas_prefill_attention_bf16")(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_seqlens),
