@@ -65,6 +65,12 @@ _SIGNATURES = {
         "akas_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "akas_gemm_tcgen05_status": [],
     },
+    "gemm_stream": {
+        "akas_stream_gemm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                             c_int, c_void_p],
+        "akas_stream_gemm_takes": [c_int, c_int, c_int, c_int, c_int],
+        "akas_stream_gemm_status": [],
+    },
     "skinny_gemm": {
         "akas_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_int, c_int, c_void_p],
@@ -89,7 +95,7 @@ _functions = {}
 def libraries_for(dtype: torch.dtype) -> list:
     """The kernel files a model of this compute dtype needs."""
     names = ["elementwise", "conv", "rope", "attention", "sampling"]
-    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "skinny_gemm", "attention_prefill", "attention_decode"]
+    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "gemm_stream", "skinny_gemm", "attention_prefill", "attention_decode"]
     return names
 
 
@@ -228,8 +234,12 @@ def linear(x, w, out_dtype=None, residual=None):
         raise TypeError(f"linear takes float32 or bfloat16, got {x.dtype}")
     target = out_dtype or torch.bfloat16
     mode = _OUT_ACC if residual is not None else _OUT_F32 if target == torch.float32 else _OUT_BF16
+    if _stream_takes(n, o, k, False, mode):
+        # few tokens: the weights are streamed once through the tensor cores
+        out = residual if residual is not None else torch.empty((n, o), dtype=target, device=x.device)
+        _stream_product(x, None, None, 0.0, False, False, w, out, n, o, k, mode)
+        return out
     if _skinny_fits(n, k):
-        # a handful of tokens: the weights are streamed once by the skinny kernel
         out = residual if residual is not None else torch.empty((n, o), dtype=target, device=x.device)
         _skinny(x, None, None, 0.0, False, w, out, n, o, k, 0, mode)
         return out
@@ -258,7 +268,7 @@ def _skinny_fits(m: int, k: int) -> bool:
     """Whether the skinny kernel takes this product: few tokens, an inner size that is a multiple of 64 (its TMA
     boxes), and activations that fit in shared memory beside the ring of weight chunks."""
     tokens = 8 if m <= 8 else 16
-    return m <= _SKINNY_ROWS and k % 64 == 0 and 1024 + 8 * 8192 + tokens * 512 + tokens * (k + 32) * 2 <= 226 * 1024
+    return decode_products == "skinny" and m <= _SKINNY_ROWS and k % 64 == 0 and 1024 + 8 * 8192 + tokens * 512 + tokens * (k + 32) * 2 <= 226 * 1024
 
 
 _SKINNY_ROWS = 16
@@ -284,6 +294,39 @@ def gemm_tcgen05_status() -> int:
 _OUT_BF16, _OUT_F32, _OUT_ACC, _OUT_SWIGLU = 0, 1, 2, 3
 
 
+# Which kernel runs the products of decode steps (few tokens): "skinny", the mma.sync kernel, for up to 16 tokens;
+# "stream", the tcgen05 kernel that streams the weights through the tensor cores (K split over a thread-block
+# cluster where output channels are few), for up to _STREAM_ROWS tokens. Measured on the 1.2B shape at 8 tokens
+# the skinny kernel is the faster one (1.01 ms a step against 1.35 ms), so it is the default; both are tested.
+decode_products = os.environ.get("AKAS_B200_DECODE_PRODUCTS", "skinny")
+if decode_products not in ("stream", "skinny"):
+    raise ValueError(f"AKAS_B200_DECODE_PRODUCTS must be stream or skinny, got {decode_products!r}")
+_STREAM_ROWS = 128
+_stream_answers = {}
+
+
+def _stream_takes(m: int, o: int, k: int, in_norm: bool, mode: int) -> bool:
+    if decode_products != "stream" or m > _STREAM_ROWS or k % 8:
+        return False
+    key = (m, o, k, in_norm, mode)
+    answer = _stream_answers.get(key)
+    if answer is None:
+        answer = _stream_answers[key] = bool(_fn("gemm_stream", "akas_stream_gemm_takes")(m, o, k, int(in_norm), mode))
+    return answer
+
+
+def _stream_product(x, rows, norm_w, eps, zero_centered, in_norm, w, out, m, o, k, mode):
+    _check(_fn("gemm_stream", "akas_stream_gemm")(_ptr(x), _ptr(rows), _ptr(norm_w), float(eps), int(bool(zero_centered)),
+                                                 int(in_norm), _ptr(w), _ptr(out), m, o, k, mode, _stream()),
+           f"streamed product [{m}x{k}] x [{o}x{k}]^T")
+
+
+def stream_status() -> int:
+    """0 unless a bounded wait inside the streamed product kernel has run out on this device (then its results
+    since are not valid). Synchronises with the device."""
+    return int(_fn("gemm_stream", "akas_stream_gemm_status")())
+
+
 def _skinny(x, rows, norm_w, eps, zero_centered, w, out, m, o, k, in_mode, out_mode):
     _check(_fn("skinny_gemm", "akas_skinny_gemm")(_ptr(x), _ptr(rows), _ptr(norm_w), float(eps), int(bool(zero_centered)),
                                                  _ptr(w), _ptr(out), m, o, k, in_mode, out_mode, _stream()),
@@ -300,6 +343,10 @@ def linear_swiglu(x, w_gate_up):
     """swiglu(x . w^T) with w the stacked [2F, K] gate and up matrices: [N, F] in x's dtype."""
     n, k = x.shape
     f2 = w_gate_up.shape[0]
+    if x.dtype == torch.bfloat16 and f2 % 2 == 0 and _stream_takes(n, f2, k, False, _OUT_SWIGLU):
+        out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
+        _stream_product(_dense(x, "x"), None, None, 0.0, False, False, _dense(w_gate_up, "w"), out, n, f2, k, _OUT_SWIGLU)
+        return out
     if x.dtype == torch.bfloat16 and f2 % 2 == 0 and _skinny_fits(n, k):
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _skinny(_dense(x, "x"), None, None, 0.0, False, _dense(w_gate_up, "w"), out, n, f2, k, 0, _OUT_SWIGLU)
@@ -319,8 +366,12 @@ def norm_linear(h, norm_weight, eps, zero_centered, w, out_dtype=None, rows=None
     k, o = h.shape[1], w.shape[0]
     target = torch.bfloat16 if swiglu_out else (out_dtype or torch.bfloat16)
     mode = _OUT_SWIGLU if swiglu_out else _OUT_F32 if target == torch.float32 else _OUT_BF16
-    if (w.dtype == torch.bfloat16 and h.dtype == torch.float32 and h.is_contiguous() and _skinny_fits(m, k)
-            and (not swiglu_out or o % 2 == 0)):
+    fusable = w.dtype == torch.bfloat16 and h.dtype == torch.float32 and h.is_contiguous() and (not swiglu_out or o % 2 == 0)
+    if fusable and _stream_takes(m, o, k, True, mode):
+        out = torch.empty((m, o // 2 if swiglu_out else o), dtype=target, device=h.device)
+        _stream_product(h, rows, norm_weight, eps, zero_centered, True, _dense(w, "w"), out, m, o, k, mode)
+        return out
+    if fusable and _skinny_fits(m, k):
         out = torch.empty((m, o // 2 if swiglu_out else o), dtype=target, device=h.device)
         _skinny(h, rows, norm_weight, eps, zero_centered, _dense(w, "w"), out, m, o, k, 1, mode)
         return out

@@ -100,9 +100,10 @@ def test_linear_bfloat16(ops, n, k, o):
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("k,o", [(64, 50), (192, 320), (2048, 37), (8192, 64), (96, 40)])
-def test_skinny_products_for_few_tokens(ops, m, k, o):
+def test_skinny_products_for_few_tokens(ops, m, k, o, monkeypatch):
     """The decode-step product kernel: plain, float32 out, accumulate, SwiGLU, and with the norm riding along."""
     cuda, ref = ops
+    monkeypatch.setattr(cuda, "decode_products", "skinny")
     x, w = _rand((m, k), torch.bfloat16, 5), _rand((o, k), torch.bfloat16, 6, 0.05)
     want = x.double() @ w.double().T
     _close(cuda.linear(x, w), want, torch.bfloat16, "bf16 out")
@@ -124,6 +125,43 @@ def test_skinny_products_for_few_tokens(ops, m, k, o):
     big = _rand((40, k), torch.float32, 11)
     _close(cuda.norm_linear(big, nw, 1e-5, False, w), ref.norm_linear(big, nw, 1e-5, False, w), torch.bfloat16, "many tokens")
     assert cuda.skinny_status() == 0  # no bounded wait inside the kernel ran out
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 40, 64, 128])
+@pytest.mark.parametrize("k,o", [(64, 50), (192, 320), (2048, 37), (8192, 64), (96, 40), (2048, 1000), (1024, 2048),
+                                 (520, 3000), (256, 20000)])
+def test_streamed_products_for_few_tokens(ops, m, k, o, monkeypatch):
+    """The decode-step product kernel on the tensor cores: plain, float32 out, accumulate, SwiGLU, and with the norm
+    riding along; one and several parts of K (few and many output channels), ragged edges in every direction."""
+    cuda, ref = ops
+    monkeypatch.setattr(cuda, "decode_products", "stream")
+    # the kernel itself answers, not the path behind it: every read-out with bfloat16 activations, and the fused norm
+    # where the normalised activations fit in shared memory
+    assert all(cuda._stream_takes(m, o, k, False, mode) for mode in (0, 1, 2)) and cuda._stream_takes(m, 2 * o, k, False, 3)
+    if m <= 16 and k <= 2048:
+        assert all(cuda._stream_takes(m, o, k, True, mode) for mode in (0, 1)) and cuda._stream_takes(m, 2 * o, k, True, 3)
+    x, w = _rand((m, k), torch.bfloat16, 5), _rand((o, k), torch.bfloat16, 6, 0.05)
+    want = x.double() @ w.double().T
+    _close(cuda.linear(x, w), want, torch.bfloat16, "bf16 out")
+    _close(cuda.linear(x, w, out_dtype=torch.float32), want, torch.float32, "f32 out", k)
+    res = _rand((m, o), torch.float32, 7)
+    _close(cuda.linear(x, w, residual=res.clone()), res.double() + want, torch.float32, "accumulate", k)
+    w2 = _rand((2 * o, k), torch.bfloat16, 8, 0.05)
+    _close(cuda.linear_swiglu(x, w2), ref.linear_swiglu(x, w2), torch.bfloat16, "swiglu")
+    h = _rand((m + 5, k), torch.float32, 9, 3.0)
+    nw = _rand((k,), torch.float32, 10) + 1
+    rows = torch.arange(m + 4, 4, -1, dtype=torch.int32, device=DEV)[:m].contiguous()
+    for zero_centered in (False, True):
+        got = cuda.norm_linear(h, nw, 1e-6, zero_centered, w, torch.float32, rows)
+        _close(got, ref.norm_linear(h, nw, 1e-6, zero_centered, w, torch.float32, rows), torch.bfloat16, "norm + product")
+    got = cuda.norm_linear(h[:m].contiguous(), nw, 1e-5, False, w, None, None)
+    _close(got, ref.norm_linear(h[:m].contiguous(), nw, 1e-5, False, w, None, None), torch.bfloat16, "norm + product, bf16")
+    got = cuda.norm_linear(h[:m].contiguous(), nw, 1e-5, False, w2, None, None, True)
+    _close(got, ref.norm_linear(h[:m].contiguous(), nw, 1e-5, False, w2, None, None, True), torch.bfloat16, "norm + swiglu")
+    # twice the same call gives the same bits: parts of K are added in a fixed order
+    a, b = cuda.linear(x, w, out_dtype=torch.float32), cuda.linear(x, w, out_dtype=torch.float32)
+    assert torch.equal(a, b)
+    assert cuda.stream_status() == 0  # no bounded wait inside the kernel ran out
 
 
 @pytest.mark.parametrize("m,k,o", [(17, 64, 48), (64, 128, 256), (100, 96, 200), (128, 2048, 320), (300, 192, 1000),
