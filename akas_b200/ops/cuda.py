@@ -281,9 +281,25 @@ if products not in ("auto", "tcgen05", "library"):
     raise ValueError(f"AKAS_B200_PRODUCTS must be auto, tcgen05 or library, got {products!r}")
 
 
-def _tcgen05_takes(n: int, k: int, fused: bool = False) -> bool:
-    """More tokens than the skinny kernel takes, a 16-byte row pitch, and the policy above."""
-    return n > _SKINNY_ROWS and k % 8 == 0 and (products == "tcgen05" or (products == "auto" and fused))
+def _tcgen05_takes(n: int, k: int, fused: bool = False, channels: int = 0) -> bool:
+    """More tokens than the decode kernels take, a 16-byte row pitch, and the policy above. Under "auto" the fused
+    product must also have a tile (128 tokens x 128 channels) for every SM: with fewer, reading the weights is the
+    cost, and the library's narrow tiles spread that over more SMs."""
+    if n <= _SKINNY_ROWS or k % 8:
+        return False
+    if products == "tcgen05":
+        return True
+    return products == "auto" and fused and -(-n // 128) * -(-channels // 128) >= _sm_count()
+
+
+_sms = 0
+
+
+def _sm_count() -> int:
+    global _sms
+    if not _sms:
+        _sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _sms
 
 
 def gemm_tcgen05_status() -> int:
@@ -351,7 +367,7 @@ def linear_swiglu(x, w_gate_up):
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _skinny(_dense(x, "x"), None, None, 0.0, False, _dense(w_gate_up, "w"), out, n, f2, k, 0, _OUT_SWIGLU)
         return out
-    if x.dtype == torch.bfloat16 and _tcgen05_takes(n, k, fused=True) and f2 % 16 == 0:
+    if x.dtype == torch.bfloat16 and _tcgen05_takes(n, k, fused=True, channels=f2 // 2) and f2 % 16 == 0:
         # SwiGLU in the read-out of the product: the [N, 2F] intermediate is never written
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _check(_fn("gemm_tcgen05", "akas_gemm_tcgen05")(_ptr(_dense(x, "x")), _ptr(_dense(w_gate_up, "w")), _ptr(out), n,
