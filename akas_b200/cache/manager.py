@@ -113,11 +113,24 @@ class CacheManager:
         self.max_blocks = -(-context // page_size)
         self.groups: List[_Group] = []
         self.views: List[Optional[object]] = []
-        self.state_tensors: List[torch.Tensor] = []
+        self.state_tensors: List[torch.Tensor] = []  # [layers of one state shape, slots, *shape]: zeroed per slot in one go
         self._group_of_window: Dict[Optional[int], int] = {}
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
         self._requests: Dict[Hashable, _Request] = {}
         self.peak_pages = 0
+        # states of one shape and type share an allocation, so that a slot is zeroed across layers by one launch
+        backing: Dict[tuple, torch.Tensor] = {}
+        taken: Dict[tuple, int] = {}
+        if storage:
+            count: Dict[tuple, int] = {}
+            for spec in cache_specs:
+                if isinstance(spec, StateSpec):
+                    key = (tuple(spec.shape), spec.dtype)
+                    count[key] = count.get(key, 0) + 1
+            for key, layers in count.items():
+                backing[key] = torch.zeros((layers, max_requests, *key[0]), dtype=key[1], device=device)
+                taken[key] = 0
+                self.state_tensors.append(backing[key])
         for spec in cache_specs:
             if spec is None:
                 self.views.append(None)
@@ -136,8 +149,9 @@ class CacheManager:
             elif isinstance(spec, StateSpec):
                 state = None
                 if storage:
-                    state = torch.zeros((max_requests, *spec.shape), dtype=spec.dtype, device=device)
-                    self.state_tensors.append(state)
+                    key = (tuple(spec.shape), spec.dtype)
+                    state = backing[key][taken[key]]
+                    taken[key] += 1
                 self.views.append(StateCache(state, spec))
             else:
                 raise TypeError(f"unknown cache spec {spec!r}")
@@ -166,7 +180,8 @@ class CacheManager:
         return min((g.allocator.free for g in self.groups), default=self.num_pages)
 
     def admit(self, request, zero=None) -> int:
-        """Gives ``request`` a slot and zeroes its state rows (``zero(tensor, slot)`` if given)."""
+        """Gives ``request`` a slot and zeroes its state rows (by ``zero(tensor, slot)`` if given, for a tensor
+        ``[layers, slots, ...]``)."""
         if request in self._requests:
             raise RuntimeError(f"request {request!r} is already admitted")
         if not self._free_slots:
@@ -179,7 +194,7 @@ class CacheManager:
             if zero is not None:
                 zero(state, slot)
             else:
-                state[slot].zero_()
+                state[:, slot].zero_()
         return slot
 
     def pages_needed(self, request, tokens: int) -> List[int]:

@@ -163,15 +163,19 @@ AKAS_API int akas_swiglu(const void* gu, void* out, int N, int F, int dtype, cud
   return launch_status();
 }
 
-// state[slot, :] = 0 for one slot of a [slots, row] float32 tensor
-__global__ void zero_row_kernel(float* __restrict__ state, size_t row, int slot) {
+// state[g, slot, :] = 0 for one slot of a [groups, slots, row] float32 tensor (groups: the layers whose states
+// of one shape share an allocation)
+__global__ void zero_row_kernel(float* __restrict__ state, size_t row, size_t group_stride, int slot) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < row) state[(size_t)slot * row + i] = 0.f;
+  if (i < row) state[blockIdx.y * group_stride + (size_t)slot * row + i] = 0.f;
 }
 
-AKAS_API int akas_zero_row(float* state, long long row_elems, int slot, cudaStream_t stream) {
-  if (row_elems <= 0) return 0;
+AKAS_API int akas_zero_row(float* state, long long row_elems, int slot, int groups, long long group_stride,
+                           cudaStream_t stream) {
+  if (row_elems <= 0 || groups <= 0) return 0;
+  if (groups > 65535) return (int)cudaErrorInvalidValue;
   const int threads = 256;
-  zero_row_kernel<<<(unsigned)((row_elems + threads - 1) / threads), threads, 0, stream>>>(state, (size_t)row_elems, slot);
+  zero_row_kernel<<<dim3((unsigned)((row_elems + threads - 1) / threads), groups), threads, 0, stream>>>(
+      state, (size_t)row_elems, (size_t)group_stride, slot);
   return launch_status();
 }

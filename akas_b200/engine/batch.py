@@ -76,10 +76,11 @@ class BatchLayout:
         self.size = off
 
 
-def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntry], cache, pad_to: int = 0):
+def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntry], cache, pad_to: int = 0, tokens=None):
     """Writes the arrays of ``entries`` into ``host`` (int32) at ``layout``'s offsets.
 
     ``pad_to``: for a decode-only step, the bucket size; padding tokens get request -1.
+    ``tokens``: the entries' token ids as arrays, if the caller has them already.
     Returns (max_query_len, max_context).
     """
     n, r = layout.n, layout.r
@@ -96,7 +97,7 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntr
     for i, e in enumerate(entries):
         k = len(e.tokens)
         start = cache.length(e.request)
-        tok[at : at + k] = e.tokens
+        tok[at : at + k] = e.tokens if tokens is None else tokens[i]
         pos[at : at + k] = np.arange(start, start + k, dtype=np.int32)
         seq[at : at + k] = i
         cu[i] = at

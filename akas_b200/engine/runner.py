@@ -115,13 +115,16 @@ class ModelRunner:
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         seen = set()
-        for e in entries:
+        arrays = [np.asarray(e.tokens, dtype=np.int64) for e in entries]  # converted once, checked and copied as arrays
+        for e, ids in zip(entries, arrays):
             if e.request in seen:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
-            bad = [t for t in e.tokens if not 0 <= int(t) < self.vocab_size]
-            if bad:
-                raise ValueError(f"request {e.request!r}: token ids {bad[:4]} outside [0, {self.vocab_size})")
+            if ids.ndim != 1:
+                raise ValueError(f"request {e.request!r}: tokens must be a flat sequence of ids")
+            if int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size:
+                bad = ids[(ids < 0) | (ids >= self.vocab_size)]
+                raise ValueError(f"request {e.request!r}: token ids {bad[:4].tolist()} outside [0, {self.vocab_size})")
             if any(not 0 <= w < len(e.tokens) for w in e.want):
                 raise ValueError(f"request {e.request!r}: wanted places {list(e.want)} outside its {len(e.tokens)} tokens")
             if e.request not in self.cache:
@@ -132,13 +135,13 @@ class ModelRunner:
         decode_only = all(len(e.tokens) == 1 for e in entries)
         all_wanted = all(list(e.want) == [0] for e in entries)
         if decode_only and all_wanted and self.config.cuda_graphs and self.device.type == "cuda":
-            logits = self._decode_graph_step(entries)
+            logits = self._decode_graph_step(entries, arrays)
         else:
             n = sum(len(e.tokens) for e in entries)
             m = sum(len(e.want) for e in entries)
             lay = BatchLayout(n, len(entries), m, len(self.cache.groups), self.cache.max_blocks)
             host, dev = self._staging(lay.size)
-            max_q, max_ctx = fill_batch(host.numpy(), lay, entries, self.cache)
+            max_q, max_ctx = fill_batch(host.numpy(), lay, entries, self.cache, tokens=arrays)
             dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
             ctx = self._context(dev, lay, max_q, max_ctx, decode_only)
             ctx.query_tiles = sum(-(-len(e.tokens) // 64) for e in entries)
@@ -150,7 +153,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ captured decode
 
-    def _decode_graph_step(self, entries):
+    def _decode_graph_step(self, entries, arrays=None):
         count = len(entries)
         bucket = next((b for b in _GRAPH_BUCKETS if b >= count), None)
         if bucket is None:
@@ -158,7 +161,7 @@ class ModelRunner:
         graph = self._graphs.get(bucket)
         if graph is None:
             graph = self._graphs[bucket] = _DecodeGraph(self, bucket)
-        return graph.run(entries)
+        return graph.run(entries, arrays)
 
 
 class _DecodeGraph:
@@ -179,13 +182,13 @@ class _DecodeGraph:
         self.graph = None
         self.logits = None
 
-    def _fill(self, entries):
-        fill_batch(self.host.numpy(), self.layout, entries, self.runner.cache, pad_to=self.bucket)
+    def _fill(self, entries, arrays=None):
+        fill_batch(self.host.numpy(), self.layout, entries, self.runner.cache, pad_to=self.bucket, tokens=arrays)
         rows = self.host.numpy()[self.layout.logit_rows : self.layout.logit_rows + self.bucket]
         rows[:] = np.arange(self.bucket, dtype=np.int32)
         self.dev.copy_(self.host, non_blocking=True)
 
-    def run(self, entries):
+    def run(self, entries, arrays=None):
         runner = self.runner
         if self.graph is None:
             # Warm-up and capture run on a batch of padding only: they must leave pages and state alone.
@@ -208,6 +211,6 @@ class _DecodeGraph:
                 self.logits = runner.model.forward(ctx, runner.cache.views)
             runner.kernels_per_decode_step[self.bucket] = getattr(runner.ops, "launch_count", 0) - before
             self.graph = graph
-        self._fill(entries)
+        self._fill(entries, arrays)
         self.graph.replay()
         return self.logits[: len(entries)]

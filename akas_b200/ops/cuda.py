@@ -31,7 +31,7 @@ _SIGNATURES = {
         "akas_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
         "akas_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-        "akas_zero_row": [c_void_p, c_longlong, c_int, c_void_p],
+        "akas_zero_row": [c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p],
     },
     "conv": {
         "akas_short_conv": [c_void_p] * 8 + [c_int] * 5 + [c_void_p],
@@ -140,7 +140,13 @@ def _check(err: int, what: str, kernels: int = 1) -> None:
         raise RuntimeError(f"{what} failed: {detail}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The handle of torch's current stream on the current device (every launch goes there)."""
+    if _raw_stream is not None:  # the same value as below without building a Stream object per launch
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -194,11 +200,13 @@ def swiglu(gate_up):
 
 
 def zero_rows(state, slot):
-    row = state[0].numel()
-    if state.dtype != torch.float32:
-        state[slot].zero_()
+    """state[:, slot] = 0 for a contiguous tensor [layers, slots, ...]."""
+    row = state[0, 0].numel()
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        state[:, slot].zero_()
         return
-    _check(_fn("elementwise", "akas_zero_row")(_ptr(state), row, int(slot), _stream()), "zero_rows")
+    _check(_fn("elementwise", "akas_zero_row")(_ptr(state), row, int(slot), state.shape[0], state[0].numel(), _stream()),
+           "zero_rows")
 
 
 # --------------------------------------------------------------------------- matrix products

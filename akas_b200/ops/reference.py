@@ -198,4 +198,4 @@ def sample(logits, temperature, top_k, top_p, uniform):
 
 
 def zero_rows(state, slot):
-    state[slot].zero_()
+    state[:, slot].zero_()
