@@ -84,6 +84,88 @@ __global__ void short_conv_forward8_kernel(const T* __restrict__ bcx, const floa
   store8(out + (size_t)t * C + c, acc);
 }
 
+// The forward for prompt portions, for the usual numbers of taps: a thread owns 8 neighbouring channels of TT
+// consecutive tokens and slides the window along them, so that every u = B * x is formed once, and the taps and
+// the bias are fetched once per thread. The sum runs in the same order as in the kernels above (tap 0 first), so
+// the results are the same bits.
+template <typename T, int L, int TT>
+__global__ void __launch_bounds__(128)
+short_conv_forward_run_kernel(const T* __restrict__ bcx, const float* __restrict__ taps, const float* __restrict__ bias,
+                              const float* __restrict__ state, const int* __restrict__ cu_seqlens,
+                              const int* __restrict__ seq_of_token, const int* __restrict__ slots, T* __restrict__ out,
+                              int N, int C) {
+  const int t0 = blockIdx.x * TT;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  float tap[8][L], bv[8], hist[L - 1][8];
+  {
+    float flat[8 * L];
+#pragma unroll
+    for (int i = 0; i < 8 * L; i += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(taps + (size_t)c * L + i);
+      flat[i] = v.x; flat[i + 1] = v.y; flat[i + 2] = v.z; flat[i + 3] = v.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+      for (int i = 0; i < L; ++i) tap[e][i] = flat[e * L + i];
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) bv[e] = bias ? bias[c + e] : 0.f;
+  bool have = false;  // hist holds the u of the L - 1 tokens before the current one
+#pragma unroll
+  for (int tt = 0; tt < TT; ++tt) {
+    const int t = t0 + tt;
+    if (t >= N) break;
+    const int r = seq_of_token[t];
+    const int slot = r >= 0 ? slots[r] : -1;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (slot < 0) {
+      have = false;
+      store8(out + (size_t)t * C + c, acc);
+      continue;
+    }
+    const int j = t - cu_seqlens[r];
+    if (!have || j == 0) {  // the first token of this thread's run or of a request: fetch the window
+#pragma unroll
+      for (int i = 0; i < L - 1; ++i) {
+        const int back = L - 1 - i;
+        if (j - back >= 0) {
+          const T* row = bcx + (size_t)(t - back) * 3 * C;
+          float b[8], x[8];
+          load8(row + c, b);
+          load8(row + 2 * C + c, x);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) hist[i][e] = b[e] * x[e];
+        } else {
+          load8(state + ((size_t)slot * (L - 1) + (j + i)) * C + c, hist[i]);
+        }
+      }
+    }
+    const T* row = bcx + (size_t)t * 3 * C;
+    float b[8], x[8], gate[8], u[8];
+    load8(row + c, b);
+    load8(row + 2 * C + c, x);
+    load8(row + C + c, gate);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      u[e] = b[e] * x[e];
+#pragma unroll
+      for (int i = 0; i < L - 1; ++i) acc[e] = fmaf(hist[i][e], tap[e][i], acc[e]);
+      acc[e] = fmaf(u[e], tap[e][L - 1], acc[e]);
+      acc[e] = gate[e] * (bias ? acc[e] + bv[e] : acc[e]);
+    }
+    store8(out + (size_t)t * C + c, acc);
+#pragma unroll
+    for (int i = 0; i + 1 < L - 1; ++i)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) hist[i][e] = hist[i + 1][e];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) hist[L - 2][e] = u[e];
+    have = true;
+  }
+}
+
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int C,
@@ -165,6 +247,23 @@ AKAS_API int akas_short_conv(const void* bcx, const float* taps, const float* bi
   const dim3 fwd(N, (C + threads - 1) / threads), upd(R, (C + threads - 1) / threads);
   const bool wide = C % 8 == 0 && (uintptr_t)bcx % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)state % 16 == 0;
   const dim3 fwd8(N, (C / 8 + threads - 1) / threads);
+  constexpr int TT = 4;
+  const dim3 run((N + TT - 1) / TT, (C / 8 + threads - 1) / threads);
+  const bool runs = wide && N >= 256 && L >= 2 && L <= 4 && (uintptr_t)taps % 16 == 0;
+#define AKAS_CONV_RUN(T, TAPS)                                                                                        \
+  short_conv_forward_run_kernel<T, TAPS, TT><<<run, threads, 0, stream>>>((const T*)bcx, taps, bias, state, cu_seqlens, \
+                                                                          seq_of_token, slots, (T*)out, N, C)
+  if (runs) {
+    if (dtype == AKAS_F32) {
+      if (L == 2) AKAS_CONV_RUN(float, 2); else if (L == 3) AKAS_CONV_RUN(float, 3); else AKAS_CONV_RUN(float, 4);
+      short_conv_state_kernel<float><<<upd, threads, 0, stream>>>((const float*)bcx, state, cu_seqlens, slots, C, L);
+    } else {
+      if (L == 2) AKAS_CONV_RUN(bf16, 2); else if (L == 3) AKAS_CONV_RUN(bf16, 3); else AKAS_CONV_RUN(bf16, 4);
+      short_conv_state_kernel<bf16><<<upd, threads, 0, stream>>>((const bf16*)bcx, state, cu_seqlens, slots, C, L);
+    }
+    return launch_status();
+  }
+#undef AKAS_CONV_RUN
   if (dtype == AKAS_F32) {
     if (wide)
       short_conv_forward8_kernel<float><<<fwd8, threads, 0, stream>>>((const float*)bcx, taps, bias, state, cu_seqlens,

@@ -234,6 +234,29 @@ def test_short_conv(ops, dtype, taps, bias):
         assert torch.equal(s1[untouched], state[untouched])
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("taps,bias", [(2, True), (3, False), (4, True), (5, False)])
+def test_short_conv_of_prompt_portions(ops, dtype, taps, bias):
+    """Many tokens: the sliding-window kernel (2 to 4 taps). Requests start and end inside a thread's run of
+    tokens, one has a single token, one is shorter than the window, and padding follows."""
+    cuda, ref = ops
+    c = 136
+    lengths = [130, 1, 3, 0, 77, 2, 61, 9]
+    cu, seq = _batch(lengths, pad=5)
+    n = sum(lengths) + 5
+    slots = torch.tensor([3, 0, 5, 6, 1, 7, -1, 2], dtype=torch.int32, device=DEV)
+    bcx = _rand((n, 3 * c), dtype, 10)
+    w = _rand((c, taps), torch.float32, 11)
+    b = _rand((c,), torch.float32, 12) if bias else None
+    state = _rand((8, taps - 1, c), torch.float32, 13)
+    s1, s2 = state.clone(), state.clone()
+    got = cuda.short_conv(bcx, w, b, s1, cu, seq, slots)
+    want = ref.short_conv(bcx, w, b, s2, cu, seq, slots)
+    _close(got, want, dtype, "output")
+    _close(s1, s2, torch.float32, "state")
+    assert torch.equal(s1[4], state[4]) and torch.equal(s1[6], state[6])  # no live request, no tokens
+
+
 def test_rope_tables(ops):
     cuda, ref = ops
     pos = torch.tensor([0, 1, 77, 4095, 131071], dtype=torch.int32, device=DEV)
