@@ -31,6 +31,13 @@
 // Output modes:  bf16 store | float32 store | float32 accumulate (y += ..., the residual stream) |
 //                swiglu: the block's 16 rows are gate rows f0..f0+7 and up rows F+f0..F+f0+7 of the
 //                stacked [2F, K] matrix, so silu(gate) * up is formed per thread and stored as bf16 [M, F].
+// Parts of K. A block must hold its tokens' activations for all the k it multiplies, and fetching them costs the
+// SM as much as fetching weights does; with a long K and few rows (the down projection of a feed-forward) they
+// are a third of what a block fetches, and they leave room for one block per SM only. Such a product is cut
+// along K as well: the `ksplit` blocks of a thread-block cluster take one part of K each for the same row
+// tiles, keep their sums in shared memory, and at the end send them to the cluster's first block
+// (st.shared::cluster, one arrival per block on its mbarrier), which adds the parts in rank order and writes
+// the result. Not for the SwiGLU read-out.
 // Needs K % 64 == 0. Results do not depend on what else runs; summation order is fixed.
 #include <cuda.h>
 #include <math.h>
@@ -47,6 +54,7 @@ using namespace akas;
 namespace {
 
 constexpr int CONSUMERS = 8, KC = 256, STAGES = 8;
+constexpr int MAX_KSPLIT = 8, SPLIT_TILES = 4;  // parts of K; row tiles a cluster may take when K is cut
 constexpr int STAGE_BYTES = 16 * KC * 2;  // two boxes of [4 groups of k][8 rows][128 bytes]
 constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr unsigned kSpinLimit = 1u << 22;  // try_wait calls before a wait gives up (each may block for a while)
@@ -84,23 +92,60 @@ __device__ __forceinline__ void tma_load_box(void* smem_dst, const CUtensorMap* 
 }
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory"); }
 
+__device__ __forceinline__ unsigned cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned peer_address(const void* local, unsigned rank) {  // the same location in block `rank`
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void peer_store(unsigned address, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(v) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, unsigned parity) {
+  const unsigned addr = smem_u32(bar);
+  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void cluster_meet() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 template <int NT, int IN, int OUT>
 __global__ void __launch_bounds__(THREADS)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __restrict__ x_, const int* __restrict__ rows,
                    const float* __restrict__ norm_w, float eps, int zero_centered, void* __restrict__ y_, int M, int O,
-                   int K, int num_tiles) {
+                   int K, int num_tiles, int ksplit) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);  // [STAGES][STAGE_BYTES]
   float* red = reinterpret_cast<float*>(ring + STAGES * STAGE_BYTES);   // [CONSUMERS][NT][16][8]: partial sums
-  bf16* xs = reinterpret_cast<bf16*>(red + CONSUMERS * NT * 128);       // [NT * 8][XS]: the tokens' activations
-  const int XS = K + 32;
-  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES];
+  // ksplit > 1: this block's sums of its row tiles, then (first block only) the other blocks' sums and sums of x^2
+  float* part = red + CONSUMERS * NT * 128;                              // [SPLIT_TILES][NT * 128]
+  float* peer = part + (ksplit > 1 ? SPLIT_TILES * NT * 128 : 0);        // [ksplit - 1][SPLIT_TILES][NT * 128]
+  float* peer_ss = peer + (ksplit > 1 ? (ksplit - 1) * SPLIT_TILES * NT * 128 : 0);  // [ksplit - 1][NT * 8]
+  bf16* xs = reinterpret_cast<bf16*>(peer_ss + (ksplit > 1 ? (ksplit - 1) * NT * 8 : 0));  // [NT * 8][XS]: activations
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], gathered;
   __shared__ float ss_s[NT * 8];
   __shared__ int abort_s;  // set by the first wait that runs out; from then on nobody waits on an mbarrier
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int F = O / 2;  // swiglu only: O is the stacked height 2F
-  const int chunks = (K + KC - 1) / KC;
-  const int my_tiles = (num_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int all_chunks = (K + KC - 1) / KC;
+  // this block's part of K: chunks [chunk0, chunk0 + chunks) of all_chunks, k from k0 on
+  const int rank = ksplit > 1 ? (int)cluster_rank() : 0;
+  const int chunk0 = all_chunks * rank / ksplit, chunks = all_chunks * (rank + 1) / ksplit - chunk0;
+  const int k0 = chunk0 * KC, k_len = min(K, (chunk0 + chunks) * KC) - k0;
+  const int XS = ((all_chunks + ksplit - 1) / ksplit) * KC + 32;
+  const int first_tile = (int)blockIdx.x / ksplit, tile_step = (int)gridDim.x / ksplit;  // of this block's cluster
+  const int my_tiles = first_tile < num_tiles ? (num_tiles - first_tile + tile_step - 1) / tile_step : 0;
   const int items = my_tiles * chunks;  // this block's work: the chunks of its row tiles, in order
 
   if (tid == 0) {
@@ -109,9 +154,11 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], CONSUMERS);
     }
+    mbar_init(&gathered, ksplit > 1 ? (unsigned)(ksplit - 1) : 1u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  if (ksplit > 1) cluster_meet();  // the first block's barrier exists before a peer arrives on it
   chain_release();
   // A bounded wait. When one runs out the launch is lost (the status flag says so), but every thread keeps
   // following the same path through the barriers, so the block still ends.
@@ -126,7 +173,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
   if (warp == CONSUMERS) {
     // ---------------------------------------------------------------- producer: one thread, two boxes per stage
     if (lane == 0) {
-      int tile = blockIdx.x, chunk = 0;
+      int tile = first_tile, chunk = 0;
       for (int n = 0; n < items; ++n) {
         const int s = n % STAGES;
         if (n >= STAGES) wait_for(&empty_bar[s], ((n / STAGES) & 1) ^ 1, 2);
@@ -136,9 +183,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
         const int row_hi = OUT == OUT_SWIGLU ? F + tile * 8 : tile * 16 + 8;
         unsigned char* dst = ring + (size_t)s * STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);  // rows or k past the matrix arrive as zeros and count too
-        tma_load_box(dst, &map_w, row_lo, chunk * (KC / 64), &full_bar[s]);
-        tma_load_box(dst + STAGE_BYTES / 2, &map_w, row_hi, chunk * (KC / 64), &full_bar[s]);
-        if (++chunk == chunks) { chunk = 0; tile += gridDim.x; }
+        tma_load_box(dst, &map_w, row_lo, (chunk0 + chunk) * (KC / 64), &full_bar[s]);
+        tma_load_box(dst + STAGE_BYTES / 2, &map_w, row_hi, (chunk0 + chunk) * (KC / 64), &full_bar[s]);
+        if (++chunk == chunks) { chunk = 0; tile += tile_step; }
       }
     }
     // Copies may still be in flight: the block must not exit before they have landed. The consumers wait for
@@ -148,11 +195,11 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
     const int g = lane >> 2, t = lane & 3;
     chain_wait();  // from here on the kernel reads what its predecessor wrote
     if (IN == IN_BF16) {
-      const int per_row = K / 8;
+      const int per_row = k_len / 8;
       for (int i = tid; i < NT * 8 * per_row; i += CONSUMERS * 32) {  // all copies in flight together
         const int m = i / per_row, col = (i % per_row) * 8;
         const size_t src = m < M ? (size_t)(rows ? rows[m] : m) : 0;
-        cp_async16(xs + (size_t)m * XS + col, (const bf16*)x_ + src * K + col, m < M ? 16 : 0);
+        cp_async16(xs + (size_t)m * XS + col, (const bf16*)x_ + src * K + k0 + col, m < M ? 16 : 0);
       }
       cp_async_commit();
       cp_async_wait<0>();
@@ -162,11 +209,11 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
         float ss = 0.f;
         bf16* dst = xs + (size_t)m * XS;
         if (m < M) {
-          const float* src = (const float*)x_ + (size_t)(rows ? rows[m] : m) * K;
+          const float* src = (const float*)x_ + (size_t)(rows ? rows[m] : m) * K + k0;
 #pragma unroll 8
-          for (int k = lane * 4; k < K; k += 128) {
+          for (int k = lane * 4; k < k_len; k += 128) {
             const float4 v = *reinterpret_cast<const float4*>(src + k);
-            float4 w = *reinterpret_cast<const float4*>(norm_w + k);
+            float4 w = *reinterpret_cast<const float4*>(norm_w + k0 + k);
             if (zero_centered) { w.x += 1.f; w.y += 1.f; w.z += 1.f; w.w += 1.f; }
             ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
             uint2 packed;
@@ -176,7 +223,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           }
           ss = warp_sum(ss);
         } else {
-          for (int k = lane * 4; k < K; k += 128) *reinterpret_cast<uint2*>(dst + k) = make_uint2(0u, 0u);
+          for (int k = lane * 4; k < k_len; k += 128) *reinterpret_cast<uint2*>(dst + k) = make_uint2(0u, 0u);
         }
         if (lane == 0) ss_s[m] = ss;
       }
@@ -189,12 +236,12 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
-    int tile = blockIdx.x, c = 0;
+    int tile = first_tile, c = 0, tiles_done = 0;
     for (int n = 0; n < items; ++n) {
       const int s = n % STAGES;
       wait_for(&full_bar[s], (n / STAGES) & 1, 1);
-      const int k = c * KC + warp * 32 + 8 * t;  // this thread's 8 consecutive k of the chunk
-      if (k < K) {
+      const int k = c * KC + warp * 32 + 8 * t;  // this thread's 8 consecutive k of the chunk, counted from k0
+      if (k < k_len) {
         const unsigned char* st = ring + (size_t)s * STAGE_BYTES + a_off;
         const uint4 a_lo = *reinterpret_cast<const uint4*>(st);
         const uint4 a_hi = *reinterpret_cast<const uint4*>(st + STAGE_BYTES / 2);
@@ -234,6 +281,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           v += r0[0];
           if (OUT == OUT_SWIGLU) u += r0[64];
         }
+        if (ksplit > 1) {  // a part of K: kept until the parts meet
+          part[tiles_done * NT * 128 + i] = v;
+          continue;
+        }
         if (IN == IN_NORM) {
           const float inv = 1.f / sqrtf(ss_s[m] / (float)K + eps);
           v *= inv;
@@ -253,13 +304,53 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
       }
       consumer_barrier();  // `red` is free again before the next tile's sums are written
       c = 0;
-      tile += gridDim.x;
+      tile += tile_step;
+      ++tiles_done;
+    }
+
+    if (ksplit > 1 && OUT != OUT_SWIGLU) {
+      // ---------------------------------------------------------------- the parts of K meet in the first block
+      const int count = my_tiles * NT * 128;
+      if (rank > 0) {
+        const unsigned to = peer_address(peer, 0) + (unsigned)((rank - 1) * SPLIT_TILES * NT * 128 * 4);
+        for (int i = tid; i < count; i += CONSUMERS * 32) peer_store(to + (unsigned)i * 4u, part[i]);
+        if (IN == IN_NORM && tid < NT * 8) peer_store(peer_address(peer_ss, 0) + (unsigned)(((rank - 1) * NT * 8 + tid) * 4), ss_s[tid]);
+        consumer_barrier();  // all of this block's sums are on their way; one thread tells the first block
+        if (tid == 0) {
+          asm volatile("fence.acq_rel.cluster;" ::: "memory");
+          asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_address(&gathered, 0)) : "memory");
+        }
+      } else {
+        if (!*(volatile int*)&abort_s && !mbar_wait_cluster(&gathered, 0)) {
+          *(volatile int*)&abort_s = 1;
+          if (lane == 0) atomicExch(&g_skinny_status, 3);
+        }
+        if (!*(volatile int*)&abort_s) {
+          for (int i = tid; i < count; i += CONSUMERS * 32) {
+            const int tl = i / (NT * 128), e = i % (NT * 128);
+            const int j = e / 128, row = (e % 128) / 8, tok = e % 8;
+            const int m = 8 * j + tok, o = (first_tile + tl * tile_step) * 16 + row;
+            if (m >= M || o >= O) continue;
+            float v = part[i], ss = IN == IN_NORM ? ss_s[m] : 0.f;
+            for (int r = 0; r < ksplit - 1; ++r) {  // in rank order
+              v += peer[(r * SPLIT_TILES + tl) * NT * 128 + e];
+              if (IN == IN_NORM) ss += peer_ss[r * NT * 8 + m];
+            }
+            if (IN == IN_NORM) v *= 1.f / sqrtf(ss / (float)K + eps);
+            const size_t at = (size_t)m * O + o;
+            if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
+            else if (OUT == OUT_F32) ((float*)y_)[at] = v;
+            else ((float*)y_)[at] += v;
+          }
+        }
+      }
     }
   }
   if (*(volatile int*)&abort_s) {
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);  // a lost launch: give copies still in flight time to land
   }
   __syncthreads();  // nobody leaves while a copy into this block's shared memory may be in flight
+  if (ksplit > 1) cluster_meet();  // nor while a peer may still write its sums there
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -308,34 +399,124 @@ int weight_map(CUtensorMap* out, const void* w, int O, int K) {
 
 constexpr int kMaxSmemBytes = 226 * 1024;  // the block also has a few hundred bytes of static shared memory
 
-// Shared memory of a block: alignment slack, the ring, the partial sums and the activations.
+// Shared memory of a block with `ksplit` parts of K: alignment slack, the ring, the consumers' partial sums, the
+// parts' meeting place, and the activations of this block's part of K.
 template <int NT>
-constexpr int fixed_smem() { return 1024 + STAGES * STAGE_BYTES + CONSUMERS * NT * 128 * (int)sizeof(float); }
+int block_smem(int K, int ksplit) {
+  const int chunks = (K + KC - 1) / KC, part_k = (chunks + ksplit - 1) / ksplit * KC;
+  int bytes = 1024 + STAGES * STAGE_BYTES + CONSUMERS * NT * 128 * (int)sizeof(float) + NT * 8 * (part_k + 32) * (int)sizeof(bf16);
+  if (ksplit > 1) bytes += (ksplit * SPLIT_TILES * NT * 128 + (ksplit - 1) * NT * 8) * (int)sizeof(float);
+  return bytes;
+}
+
+struct SplitPlan {
+  int ksplit, grid, smem;
+};
 
 template <int NT, int IN, int OUTM>
 int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
                const void* W, void* y, int M, int O, int K, cudaStream_t stream) {
-  const int smem = fixed_smem<NT>() + NT * 8 * (K + 32) * (int)sizeof(bf16);
-  if (smem > kMaxSmemBytes) return (int)cudaErrorInvalidValue;
+  auto kernel = skinny_gemm_kernel<NT, IN, OUTM>;
+  if (block_smem<NT>(K, 1) > kMaxSmemBytes && (OUTM == OUT_SWIGLU || block_smem<NT>(K, MAX_KSPLIT) > kMaxSmemBytes))
+    return (int)cudaErrorInvalidValue;
   static int sms = 0;
-  if (sms == 0) {
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    const cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT, IN, OUTM>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
-    if (e != cudaSuccess) { sms = 0; return (int)e; }
+  static std::mutex mutex;
+  static std::map<std::tuple<int, int>, SplitPlan> plans;  // (tiles, K) -> how the product is cut
+  static std::map<std::tuple<int, int>, int> cluster_room;  // (ksplit, smem) -> clusters resident at once
+  SplitPlan plan;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (sms == 0) {
+      int device = 0;
+      cudaGetDevice(&device);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+      const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
+      if (e != cudaSuccess) { sms = 0; return (int)e; }
+    }
+    const auto key = std::make_tuple(num_tiles, K);
+    auto found = plans.find(key);
+    if (found == plans.end()) {
+      // What the busiest SM must fetch, in bytes, if the product is cut into `ksplit` parts of K: its blocks' weights
+      // and activations. A cut costs an exchange at the end that grows with the number of parts, counted as the
+      // bytes the SM could have fetched meanwhile (12 KB a part); an SM with a single block streams about 30 % slower
+      // than one with two. On the 1.2B shape this picks 4 parts for the down projection, which measured best among
+      // 1, 2, 4 and 8 parts: 0.950 ms a decode step against 1.035, 1.10 and 0.965.
+      const int chunks = (K + KC - 1) / KC;
+      long long best = -1;
+      plan = SplitPlan{1, 0, 0};
+      for (int ksplit = 1; ksplit <= MAX_KSPLIT; ksplit *= 2) {
+        if (ksplit > 1 && (OUTM == OUT_SWIGLU || ksplit > chunks)) break;
+        const int smem = block_smem<NT>(K, ksplit);
+        if (smem > kMaxSmemBytes) continue;
+        const int per_sm = max(1, min(3, kMaxSmemBytes / (smem + 1024)));
+        int clusters = sms * per_sm / ksplit;
+        if (ksplit > 1) {
+          const auto room_key = std::make_tuple(ksplit, smem);
+          if (!cluster_room.count(room_key)) {
+            cudaLaunchConfig_t config = {};
+            config.gridDim = dim3(ksplit * 64);
+            config.blockDim = dim3(THREADS);
+            config.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attribute[1];
+            attribute[0].id = cudaLaunchAttributeClusterDimension;
+            attribute[0].val.clusterDim.x = ksplit;
+            attribute[0].val.clusterDim.y = 1;
+            attribute[0].val.clusterDim.z = 1;
+            config.attrs = attribute;
+            config.numAttrs = 1;
+            int room = 0;
+            if (cudaOccupancyMaxActiveClusters(&room, kernel, &config) != cudaSuccess) { cudaGetLastError(); room = 0; }
+            cluster_room[room_key] = room;
+          }
+          clusters = min(clusters, cluster_room[room_key]);
+          if (clusters < 1) continue;
+        }
+        clusters = min(clusters, num_tiles);
+        // every cluster gets the same number of row tiles (to within one)
+        const int rounds = (num_tiles + clusters - 1) / clusters;
+        if (ksplit > 1 && rounds > SPLIT_TILES) continue;
+        clusters = (num_tiles + rounds - 1) / rounds;
+        const int blocks = clusters * ksplit, on_busiest_sm = (blocks + sms - 1) / sms;
+        const long long part_k = (long long)(chunks + ksplit - 1) / ksplit * KC;
+        long long fetched = on_busiest_sm * (rounds * 16 * part_k * 2 + NT * 8 * part_k * 2);
+        if (on_busiest_sm == 1) fetched += fetched * 3 / 10;  // one ring per SM keeps too few bytes in flight
+        if (ksplit > 1) fetched += 12000 * ksplit;
+        if (best < 0 || fetched < best) {
+          best = fetched;
+          plan = SplitPlan{ksplit, blocks, smem};
+        }
+      }
+      if (best < 0) return (int)cudaErrorInvalidValue;
+      plans[key] = plan;
+    } else {
+      plan = found->second;
+    }
   }
   CUtensorMap map;
   const int err = weight_map(&map, W, O, K);
   if (err) return err;
-  const int per_sm = max(1, min(3, kMaxSmemBytes / (smem + 1024)));  // resident blocks per SM by shared memory
-  // every block gets the same number of row tiles (to within one): blocks advance at the same rate, so a
-  // grid that leaves some blocks with one tile more than others would idle the rest of the GPU meanwhile
-  const int rounds = (num_tiles + sms * per_sm - 1) / (sms * per_sm);
-  const int grid = (num_tiles + rounds - 1) / rounds;
-  return launch_chained(skinny_gemm_kernel<NT, IN, OUTM>, dim3(grid), dim3(THREADS), (size_t)smem, stream, map, x, rows,
-                        norm_w, eps, zero_centered, y, M, O, K, num_tiles);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(plan.grid);
+  config.blockDim = dim3(THREADS);
+  config.dynamicSmemBytes = plan.smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  int n = 0;
+  if (chained_launches_enabled()) {
+    attribute[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (plan.ksplit > 1) {
+    attribute[n].id = cudaLaunchAttributeClusterDimension;
+    attribute[n].val.clusterDim.x = plan.ksplit;
+    attribute[n].val.clusterDim.y = 1;
+    attribute[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  config.attrs = attribute;
+  config.numAttrs = n;
+  return (int)cudaLaunchKernelEx(&config, kernel, map, x, rows, norm_w, eps, zero_centered, y, M, O, K, num_tiles, plan.ksplit);
 }
 
 template <int NT, int IN>
