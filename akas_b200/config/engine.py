@@ -36,6 +36,7 @@ class EngineConfig:
     dtype: str = "bfloat16"  # "bfloat16" or "float32"
     device: str = "cuda:0"
     cuda_graphs: bool = True  # replay captured graphs for steps that only decode
+    run_ahead: bool = True  # launch the next decode step before the tokens of the one in flight are read
 
     def __post_init__(self):
         for name in ("prefill_chunk", "prefill_requests", "max_requests", "context", "page_size"):

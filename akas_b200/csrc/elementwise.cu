@@ -179,3 +179,20 @@ AKAS_API int akas_zero_row(float* state, long long row_elems, int slot, int grou
       state, (size_t)row_elems, (size_t)group_stride, slot);
   return launch_status();
 }
+
+// token_ids[i] = previous[source[i]] where source[i] >= 0: tokens that the step before sampled and that never
+// went to the host.
+__global__ void take_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ source,
+                                   const int* __restrict__ previous, int previous_count, int N) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  const int s = source[i];
+  if (s >= 0 && s < previous_count) token_ids[i] = previous[s];
+}
+
+AKAS_API int akas_take_tokens(int* token_ids, const int* source, const int* previous, int previous_count, int N,
+                              cudaStream_t stream) {
+  if (N <= 0) return 0;
+  take_tokens_kernel<<<(N + 255) / 256, 256, 0, stream>>>(token_ids, source, previous, previous_count, N);
+  return launch_status();
+}

@@ -23,6 +23,9 @@ class StepEntry:
     request: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    # For a single token that is not known on the host yet: its place among the tokens sampled by the step before
+    # (the step function then takes it from the device; ``tokens`` holds any valid id). -1: ``tokens`` is the token.
+    source: int = -1
 
 
 @dataclass
@@ -67,6 +70,7 @@ class BatchLayout:
             return start
 
         self.token_ids = take(n)
+        self.token_src = take(n)
         self.positions = take(n)
         self.seq_of_token = take(n)
         self.cu_seqlens = take(r + 1)
@@ -85,6 +89,7 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntr
     """
     n, r = layout.n, layout.r
     tok = host[layout.token_ids : layout.token_ids + n]
+    src = host[layout.token_src : layout.token_src + n]
     pos = host[layout.positions : layout.positions + n]
     seq = host[layout.seq_of_token : layout.seq_of_token + n]
     cu = host[layout.cu_seqlens : layout.cu_seqlens + r + 1]
@@ -98,6 +103,11 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntr
         k = len(e.tokens)
         start = cache.length(e.request)
         tok[at : at + k] = e.tokens if tokens is None else tokens[i]
+        src[at : at + k] = -1
+        if e.source >= 0:
+            if k != 1:
+                raise ValueError("only a single token can come from the step before")
+            src[at] = e.source
         pos[at : at + k] = np.arange(start, start + k, dtype=np.int32)
         seq[at : at + k] = i
         cu[i] = at
@@ -116,6 +126,7 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntr
     cu[len(entries)] = at
     if pad_to:
         tok[at:n] = 0
+        src[at:n] = -1
         pos[at:n] = 0
         seq[at:n] = -1
         for i in range(len(entries), r):

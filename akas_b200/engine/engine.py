@@ -14,11 +14,39 @@ from dataclasses import replace
 from threading import get_ident
 from typing import List, Optional, Sequence
 
+import torch
+
 from ..config.engine import EngineConfig
 from ..sampling.sampler import Sampler
 from .request import Request
 from .runner import ModelRunner
 from .scheduler import Scheduler
+
+
+class _Sampled:
+    """The tokens a launched step sampled: on the device (the next step may take its inputs from there), and on
+    their way to pinned host memory by a copy on a stream of its own. A copy on the step's stream would queue
+    behind whatever was launched after the step, and reading it would wait for that too."""
+
+    def __init__(self, tokens: torch.Tensor, copy_stream, host: Optional[torch.Tensor] = None):
+        self.tokens = tokens
+        if tokens.device.type != "cuda":
+            self.host, self.done = tokens, None
+            return
+        self.host = host[: tokens.numel()] if host is not None else torch.empty(tokens.shape, dtype=tokens.dtype, pin_memory=True)
+        ready = torch.cuda.Event()
+        ready.record()
+        copy_stream.wait_event(ready)
+        with torch.cuda.stream(copy_stream):
+            self.host.copy_(tokens, non_blocking=True)
+            self.done = torch.cuda.Event()
+            self.done.record()
+        tokens.record_stream(copy_stream)
+
+    def read(self) -> List[int]:
+        if self.done is not None:
+            self.done.synchronize()
+        return self.host.tolist()
 
 
 class Engine:
@@ -32,6 +60,11 @@ class Engine:
             self.config = config or EngineConfig()
             self.runner = ModelRunner(model, self.config, ops=ops)
         self.sampler = Sampler(self.runner.ops, self.runner.device)
+        on_gpu = self.runner.device.type == "cuda"
+        self._copy_stream = torch.cuda.Stream(self.runner.device) if on_gpu else None
+        self._token_buffers = [torch.empty(max(self.config.max_requests, 1), dtype=torch.int32, pin_memory=True)
+                               for _ in range(4)] if on_gpu else []
+        self._token_turn = 0
         self.events = deque()
         self.closed = False
         self.scheduler = Scheduler(
@@ -43,6 +76,8 @@ class Engine:
             prefill_token_budget=self.config.prefill_token_budget,
             decode_prefill_token_budget=self.config.decode_prefill_token_budget,
             admit=self.runner.admit,
+            launch=self._launch if self.config.run_ahead else None,
+            collect=self._collect if self.config.run_ahead else None,
         )
 
     @classmethod
@@ -87,6 +122,23 @@ class Engine:
     def _execute(self, entries, requests) -> List[int]:
         logits = self.runner.step(entries)
         return self.sampler.sample(logits, requests)
+
+    def _launch(self, entries, requests, previous=None):
+        """A step without waiting for it: the sampled tokens stay on the device (``_collect`` reads them).
+        ``previous``: what ``_launch`` returned for the step before, for entries that take their token from it."""
+        logits = self.runner.step(entries, previous=None if previous is None else previous.tokens)
+        if not len(requests):
+            return None
+        # pinned buffers are taken in turn; at most two steps' tokens are unread at any time
+        self._token_turn = (self._token_turn + 1) % len(self._token_buffers) if self._token_buffers else 0
+        host = self._token_buffers[self._token_turn] if self._token_buffers else None
+        if host is not None and host.numel() < len(requests):
+            host = None
+        return _Sampled(self.sampler.launch(logits, requests), self._copy_stream, host)
+
+    @staticmethod
+    def _collect(handle) -> List[int]:
+        return [] if handle is None else handle.read()
 
     def _check_thread(self):
         if get_ident() != self.thread:

@@ -34,6 +34,7 @@ class Request:
     eos_token_id: Optional[int] = None
     finish_reason: Optional[str] = None  # "length", "stop" (end-of-sequence token) or "cancelled"
     preemptions: int = 0
+    inflight: int = 0  # tokens sampled by steps that were launched and not read back yet
     id: int = field(default_factory=lambda: next(_ids))
     _uniforms: Optional[np.ndarray] = None
 
@@ -46,7 +47,8 @@ class Request:
         return self.prompt + self.output
 
     def pending_tokens(self) -> int:
-        return len(self.prompt) + len(self.output) - self.offset
+        """Tokens the cache does not hold yet; a token that is still in flight counts as the last of them."""
+        return len(self.prompt) + len(self.output) + self.inflight - self.offset
 
     def uniform(self) -> float:
         """The uniform number for the next generated token: a function of (seed, index of that token) only,
@@ -54,4 +56,4 @@ class Request:
         if self._uniforms is None:
             seed = self.seed if self.seed is not None else np.random.SeedSequence().entropy
             self._uniforms = np.random.default_rng(seed).random(self.limit, dtype=np.float32)
-        return float(self._uniforms[len(self.output)])
+        return float(self._uniforms[len(self.output) + self.inflight])

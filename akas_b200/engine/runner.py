@@ -78,11 +78,13 @@ class ModelRunner:
     # ------------------------------------------------------------------ staging
 
     def _staging(self, size: int):
-        if self._host is None or self._host.numel() < size:
+        """A pinned host buffer and a device buffer for one step's arrays. The copy between them is asynchronous
+        and nothing makes the host wait for a step, so host buffers are taken in turn from a small ring, and one is
+        reused only after the copy that last read it has run (``_Pinned.take`` waits for that copy's event)."""
+        if self._dev is None or self._dev.numel() < size:
             cap = max(size, 1 << 14)
             cap = 1 << (cap - 1).bit_length()
-            pinned = self.device.type == "cuda"
-            self._host = torch.empty(cap, dtype=torch.int32, pin_memory=pinned)
+            self._host = _Pinned(cap, self.device)
             self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         return self._host, self._dev
 
@@ -106,16 +108,19 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], previous: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs one batch. Returns float32 logits ``[sum(len(e.want)), vocab]`` on the device, in the
         order of the entries and of their ``want``. Unknown requests are admitted; pages are taken
         first (``OutOfPages`` leaves the cache as it was before the step, but for pages already
-        reserved, which stay with their requests)."""
+        reserved, which stay with their requests). ``previous``: the int32 device tensor of tokens that the
+        step before sampled, for entries that name a ``source`` in it."""
         entries = [e for e in entries if len(e.tokens)]
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         seen = set()
         arrays = [np.asarray(e.tokens, dtype=np.int64) for e in entries]  # converted once, checked and copied as arrays
+        if previous is None and any(e.source >= 0 for e in entries):
+            raise ValueError("an entry takes its token from the step before, but no such tokens were given")
         for e, ids in zip(entries, arrays):
             if e.request in seen:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
@@ -135,15 +140,19 @@ class ModelRunner:
         decode_only = all(len(e.tokens) == 1 for e in entries)
         all_wanted = all(list(e.want) == [0] for e in entries)
         if decode_only and all_wanted and self.config.cuda_graphs and self.device.type == "cuda":
-            logits = self._decode_graph_step(entries, arrays)
+            logits = self._decode_graph_step(entries, arrays, previous)
         else:
             n = sum(len(e.tokens) for e in entries)
             m = sum(len(e.want) for e in entries)
             lay = BatchLayout(n, len(entries), m, len(self.cache.groups), self.cache.max_blocks)
-            host, dev = self._staging(lay.size)
+            ring, dev = self._staging(lay.size)
+            host = ring.take()
             max_q, max_ctx = fill_batch(host.numpy(), lay, entries, self.cache, tokens=arrays)
             dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
+            ring.copied()
             ctx = self._context(dev, lay, max_q, max_ctx, decode_only)
+            if previous is not None:
+                self.ops.take_tokens(ctx.token_ids, dev[lay.token_src : lay.token_src + lay.n], previous)
             ctx.query_tiles = sum(-(-len(e.tokens) // 64) for e in entries)
             logits = self.model.forward(ctx, self.cache.views)
         for e in entries:
@@ -153,7 +162,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ captured decode
 
-    def _decode_graph_step(self, entries, arrays=None):
+    def _decode_graph_step(self, entries, arrays=None, previous=None):
         count = len(entries)
         bucket = next((b for b in _GRAPH_BUCKETS if b >= count), None)
         if bucket is None:
@@ -161,7 +170,37 @@ class ModelRunner:
         graph = self._graphs.get(bucket)
         if graph is None:
             graph = self._graphs[bucket] = _DecodeGraph(self, bucket)
-        return graph.run(entries, arrays)
+            # A batch shrinks as requests end: the smaller buckets are captured now, together, rather than each
+            # in the middle of serving when it is first needed (a capture holds the device for tens of ms).
+            for smaller in _GRAPH_BUCKETS:
+                if smaller < bucket and smaller not in self._graphs:
+                    self._graphs[smaller] = _DecodeGraph(self, smaller)
+                    self._graphs[smaller].capture()
+        return graph.run(entries, arrays, previous)
+
+
+class _Pinned:
+    """A ring of pinned int32 host buffers, each with the event of the last copy that read it."""
+
+    def __init__(self, size: int, device, count: int = 4):
+        self.cuda = device.type == "cuda"
+        self.buffers = [torch.empty(size, dtype=torch.int32, pin_memory=self.cuda) for _ in range(count)]
+        self.events = [None] * count
+        self.at = -1
+
+    def take(self) -> torch.Tensor:
+        """The next buffer, once the copy that last read it has run."""
+        self.at = (self.at + 1) % len(self.buffers)
+        if self.events[self.at] is not None:
+            self.events[self.at].synchronize()
+        return self.buffers[self.at]
+
+    def copied(self) -> None:
+        """Call after enqueueing the copy out of the buffer that ``take`` gave last."""
+        if self.cuda:
+            event = self.events[self.at] or torch.cuda.Event()
+            event.record()
+            self.events[self.at] = event
 
 
 class _DecodeGraph:
@@ -177,18 +216,20 @@ class _DecodeGraph:
         self.bucket = bucket
         cache = runner.cache
         self.layout = BatchLayout(bucket, bucket, bucket, len(cache.groups), cache.max_blocks)
-        self.host = torch.empty(self.layout.size, dtype=torch.int32, pin_memory=True)
+        self.ring = _Pinned(self.layout.size, runner.device)
         self.dev = torch.zeros(self.layout.size, dtype=torch.int32, device=runner.device)
         self.graph = None
         self.logits = None
 
     def _fill(self, entries, arrays=None):
-        fill_batch(self.host.numpy(), self.layout, entries, self.runner.cache, pad_to=self.bucket, tokens=arrays)
-        rows = self.host.numpy()[self.layout.logit_rows : self.layout.logit_rows + self.bucket]
+        host = self.ring.take()
+        fill_batch(host.numpy(), self.layout, entries, self.runner.cache, pad_to=self.bucket, tokens=arrays)
+        rows = host.numpy()[self.layout.logit_rows : self.layout.logit_rows + self.bucket]
         rows[:] = np.arange(self.bucket, dtype=np.int32)
-        self.dev.copy_(self.host, non_blocking=True)
+        self.dev.copy_(host, non_blocking=True)
+        self.ring.copied()
 
-    def run(self, entries, arrays=None):
+    def capture(self) -> None:
         runner = self.runner
         if self.graph is None:
             # Warm-up and capture run on a batch of padding only: they must leave pages and state alone.
@@ -211,6 +252,14 @@ class _DecodeGraph:
                 self.logits = runner.model.forward(ctx, runner.cache.views)
             runner.kernels_per_decode_step[self.bucket] = getattr(runner.ops, "launch_count", 0) - before
             self.graph = graph
+
+    def run(self, entries, arrays=None, previous=None):
+        runner = self.runner
+        self.capture()
         self._fill(entries, arrays)
+        if previous is not None:
+            lay = self.layout
+            runner.ops.take_tokens(self.dev[lay.token_ids : lay.token_ids + lay.n],
+                                   self.dev[lay.token_src : lay.token_src + lay.n], previous)
         self.graph.replay()
         return self.logits[: len(entries)]

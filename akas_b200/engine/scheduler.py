@@ -19,6 +19,15 @@ are taken as tokens are written, so they can run out, and what happens then is d
 
 The scheduler never touches the device: it plans with the cache manager's host-side counts and
 hands the batch to ``execute(entries, requests) -> tokens``.
+
+One step ahead. Given ``launch(entries, requests, previous) -> handle`` and ``collect(handle) -> tokens`` instead,
+a turn leaves its step in flight and the next turn reads it. While every running request decodes, the next turn
+goes further: it launches the following decode step *before* it reads the tokens of the one in flight (each
+entry names the place of its input token among those, and the step function takes it from the device), so the
+host's work for a step (planning, batch arrays, bookkeeping of the tokens read) runs while the device computes.
+What the host cannot know yet is only whether a request has just produced its end-of-sequence token; such a
+request runs one step too many, whose result is dropped when it lands. Everything else (admission, portions of
+prompts, preemption, a request that reaches its limit) is decided as before, after the step in flight has landed.
 """
 
 from __future__ import annotations
@@ -33,10 +42,21 @@ from .batch import StepEntry
 from .request import Request
 
 
+class _Flight:
+    """A step that was launched and whose sampled tokens have not been read: the requests it samples for, in
+    order, what ``launch`` returned, and whether it was a step of single decoded tokens only."""
+
+    __slots__ = ("requests", "handle", "decode_only")
+
+    def __init__(self, requests, handle, decode_only):
+        self.requests, self.handle, self.decode_only = requests, handle, decode_only
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, execute: Callable, publish: Callable, *, prefill_chunk=2048,
                  prefill_requests=32, prefill_token_budget=None, decode_prefill_token_budget=None,
-                 admit: Optional[Callable] = None):
+                 admit: Optional[Callable] = None, launch: Optional[Callable] = None,
+                 collect: Optional[Callable] = None):
         if prefill_chunk <= 0 or prefill_requests <= 0:
             raise ValueError("invalid prefill budget")
         for name, value in (("prefill token budget", prefill_token_budget),
@@ -45,6 +65,10 @@ class Scheduler:
                 raise ValueError(f"{name} must be a positive integer")
         self.cache = cache
         self.execute = execute
+        if (launch is None) != (collect is None):
+            raise ValueError("launch and collect come as a pair")
+        self.launch, self.collect = launch, collect
+        self.flight: Optional[_Flight] = None
         self.publish = publish
         self.admit_request = admit or cache.admit
         self.prefill_chunk = prefill_chunk
@@ -58,7 +82,7 @@ class Scheduler:
         self.stats = dict(
             tokens=0, completed=0, cancelled=0, steps=0, decode_rounds=0, prefill_rounds=0, decode_rows=0,
             max_active=0, prefill_tokens=0, max_prefill_tokens_per_turn=0, max_prefill_tokens_with_decoding=0,
-            max_tokens_per_step=0, preemptions=0, pages_in_use_max=0,
+            max_tokens_per_step=0, preemptions=0, pages_in_use_max=0, steps_ahead=0,
         )
 
     # ------------------------------------------------------------------ requests in and out
@@ -175,7 +199,7 @@ class Scheduler:
         return batch
 
     def turn(self) -> bool:
-        """One step of the engine. Returns whether any request is still waiting or running."""
+        """One step of the engine. Returns whether anything is still waiting, running or in flight."""
         while True:
             try:
                 self.pending.append(self.incoming.get_nowait())
@@ -185,6 +209,17 @@ class Scheduler:
             if request.cancelled.is_set():
                 self.running.remove(request)
                 self._finish(request, "cancelled")
+
+        if self.flight is not None:
+            ahead = self._plan_ahead()
+            if ahead is not None:
+                following = self._launch_ahead(ahead)
+                self._land(self.flight)
+                self.flight = following
+                return True
+            self._land(self.flight)
+            self.flight = None
+
         batch = self.plan()
         self.stats["max_active"] = max(self.stats["max_active"], len(self.running))
         self.stats["pages_in_use_max"] = max(self.stats["pages_in_use_max"], self.cache.peak_pages)
@@ -200,10 +235,27 @@ class Scheduler:
             entries.append(StepEntry(request.id, tokens, (count - 1,) if last else ()))
             if last:
                 sampled.append(request)
+        decode_only = all(count == 1 for _, count in batch) and len(sampled) == len(batch)
+        self._account(batch)
+        if self.launch is not None:
+            handle = self.launch(entries, sampled, None)
+            for request, count in batch:
+                request.offset += count
+            for request in sampled:
+                request.inflight += 1
+            self.flight = _Flight(sampled, handle, decode_only)
+            return True
         new_tokens = self.execute(entries, sampled)
         if len(new_tokens) != len(sampled):
             raise ValueError("missing generated request result")
+        for request, count in batch:
+            request.offset += count
+        for request in sampled:
+            request.inflight += 1
+        self._take(sampled, new_tokens)
+        return bool(self.pending or self.running)
 
+    def _account(self, batch) -> None:
         decode_rows = sum(1 for r, n in batch if n == 1 and r.pending_tokens() == 1)
         prefill_tokens = sum(n for r, n in batch) - decode_rows
         st = self.stats
@@ -219,10 +271,14 @@ class Scheduler:
             if decode_rows:
                 st["max_prefill_tokens_with_decoding"] = max(st["max_prefill_tokens_with_decoding"], prefill_tokens)
 
-        for request, count in batch:
-            request.offset += count
+    def _take(self, sampled: Sequence[Request], new_tokens: Sequence[int]) -> None:
+        """Gives each request the token a step sampled for it; finishes and publishes."""
+        st = self.stats
         events = []
         for request, token in zip(sampled, new_tokens):
+            if request.finished:
+                continue  # ended while the step was in flight: this token comes after its last
+            request.inflight -= 1
             request.output.append(int(token))
             st["tokens"] += 1
             if request.eos_token_id is not None and int(token) == request.eos_token_id:
@@ -240,12 +296,58 @@ class Scheduler:
                 request.published = len(request.output)
         if events:
             self.publish(events)
-        return bool(self.pending or self.running)
+
+    # ------------------------------------------------------------------ one step ahead
+
+    def _land(self, flight: _Flight) -> None:
+        new_tokens = self.collect(flight.handle)
+        if len(new_tokens) != len(flight.requests):
+            raise ValueError("missing generated request result")
+        self._take(flight.requests, new_tokens)
+
+    def _plan_ahead(self) -> Optional[List[Request]]:
+        """The requests of the next decode step, if it can be launched before the step in flight has been read:
+        the one in flight decodes only, nobody waits who could be admitted, every running request is in it with
+        nothing but its coming token outstanding, and pages are free for all without preempting. Requests that
+        reach their limit with the token in flight are left out. ``None``: plan in full after landing."""
+        flight, cache = self.flight, self.cache
+        if not flight.decode_only or (self.pending and cache.free_slots() > 0):
+            return None
+        members = {id(r) for r in flight.requests}
+        ahead = []
+        for request in self.running:
+            if id(request) not in members or request.inflight != 1 or request.pending_tokens() != 1:
+                return None
+            if len(request.output) + request.inflight < request.limit:
+                ahead.append(request)
+        if not ahead:
+            return None
+        need = [0] * len(cache.groups)
+        for request in ahead:
+            for group, pages in enumerate(cache.pages_needed(request.id, 1)):
+                need[group] += pages
+        if any(pages > cache.free_pages(group) for group, pages in enumerate(need)):
+            return None
+        return ahead
+
+    def _launch_ahead(self, ahead: List[Request]) -> _Flight:
+        place = {id(r): i for i, r in enumerate(self.flight.requests)}
+        entries = []
+        for request in ahead:
+            self.cache.reserve(request.id, 1)
+            entries.append(StepEntry(request.id, (0,), (0,), source=place[id(request)]))
+        self._account([(request, 1) for request in ahead])
+        handle = self.launch(entries, ahead, self.flight.handle)
+        self.stats["steps_ahead"] += 1
+        for request in ahead:
+            request.offset += 1
+            request.inflight += 1
+        return _Flight(ahead, handle, True)
 
     def run(self) -> None:
         try:
             while not self.stopped.is_set():
-                if not self.turn():
+                if not self.turn() and self.flight is None:
                     try:
                         self.pending.append(self.incoming.get(timeout=0.01))
                     except Empty:
@@ -254,6 +356,9 @@ class Scheduler:
             self.shutdown()
 
     def shutdown(self) -> None:
+        if self.flight is not None:
+            self.collect(self.flight.handle)  # wait for the step in flight; its tokens are dropped
+            self.flight = None
         for request in list(self.running):
             self._finish(request, "cancelled")
         self.running.clear()

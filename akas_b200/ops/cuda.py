@@ -31,6 +31,7 @@ _SIGNATURES = {
         "akas_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
         "akas_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_take_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "akas_zero_row": [c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p],
     },
     "conv": {
@@ -176,6 +177,12 @@ def embedding(token_ids, table):
     _check(_fn("elementwise", "akas_embedding")(_ptr(token_ids), _ptr(_dense(table, "table")), _ptr(out), n, c,
                                                _code(table), _stream()), "embedding")
     return out
+
+
+def take_tokens(token_ids, source, previous):
+    """token_ids[i] = previous[source[i]] where source[i] >= 0 (all int32, in place)."""
+    _check(_fn("elementwise", "akas_take_tokens")(_ptr(token_ids), _ptr(source), _ptr(previous), previous.numel(),
+                                                 token_ids.numel(), _stream()), "take_tokens")
 
 
 def rmsnorm(x, weight, eps, zero_centered, out_dtype, rows=None):

@@ -197,5 +197,10 @@ def sample(logits, temperature, top_k, top_p, uniform):
     return out
 
 
+def take_tokens(token_ids, source, previous):
+    live = source >= 0
+    token_ids[live] = previous[source[live].long()]
+
+
 def zero_rows(state, slot):
     state[:, slot].zero_()

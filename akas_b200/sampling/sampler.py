@@ -22,11 +22,16 @@ class Sampler:
         """``logits``: float32 [M, vocab], one row per request in order. Returns M token ids (host ints)."""
         if logits.shape[0] == 0:
             return []
+        return self.launch(logits, requests).tolist()
+
+    def launch(self, logits: torch.Tensor, requests: Sequence) -> torch.Tensor:
+        """The same without waiting for the device: the M token ids as an int32 device tensor. The uniform number
+        of a request is the one of the token it is about to generate, counting tokens that are still in flight."""
         if all(r.temperature <= 0 for r in requests):
-            return self.ops.argmax(logits).tolist()
+            return self.ops.argmax(logits)
         params = torch.tensor(
             [[r.temperature, float(r.top_k), r.top_p, r.uniform() if r.temperature > 0 else 0.0] for r in requests],
             dtype=torch.float32,
         ).t().contiguous().to(self.device, non_blocking=True)
         top_k = params[1].to(torch.int32)
-        return self.ops.sample(logits, params[0], top_k, params[2], params[3]).tolist()
+        return self.ops.sample(logits, params[0], top_k, params[2], params[3])

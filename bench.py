@@ -15,6 +15,7 @@ than L2, so no flush is needed between timed steps.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -135,7 +136,7 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    args.steps = max(1, min(args.steps, CONTEXT - PROMPT - args.warmup - 1))
+    args.steps = max(1, min(args.steps, CONTEXT - PROMPT - args.warmup - 17))
 
     import torch
 
@@ -180,16 +181,26 @@ def main():
         engine = Engine(runner)
         prompts = synthetic_prompts(BATCH, PROMPT, model_config.vocab_size)
         e2e_steps = args.steps
-        requests = [engine.submit(p, max_tokens=args.warmup + e2e_steps + 1) for p in prompts]
+        requests = [engine.submit(p, max_tokens=args.warmup + e2e_steps + 16) for p in prompts]  # nobody ends inside the timed steps
         while any(len(r.output) < args.warmup for r in requests):
             engine.step()
         torch.cuda.synchronize()
+        # what is alive now (model, prompts, graphs) stays alive: keep the collector from walking it in mid-run
+        gc.collect()
+        gc.freeze()
         before = sum(len(r.output) for r in requests)
         t1 = time.perf_counter()
+        turns = []
         for _ in range(e2e_steps):
+            t_turn = time.perf_counter()
             engine.step()
+            turns.append(time.perf_counter() - t_turn)
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t1
+        if os.environ.get("AKAS_BENCH_DEBUG"):
+            worst = sorted(range(len(turns)), key=lambda i: -turns[i])[:6]
+            print("e2e turns (index, ms):", [(i, round(turns[i] * 1e3, 2)) for i in sorted(worst)], "sync tail ms",
+                  round((e2e_s - sum(turns)) * 1e3, 2), engine.stats, file=sys.stderr)
         produced = sum(len(r.output) for r in requests) - before
         for r in requests:
             engine.cancel(r)

@@ -3,6 +3,10 @@
 The fake keeps, per request, a rolling hash of every token it was fed, in order; the token it "generates"
 is a function of that hash. Outputs are therefore sensitive to order, to lost or repeated tokens and to a
 wrong recomputation after a preemption, as the reference's FakeEngine is (tests/test_dense_scheduler.py:7-37).
+
+Every test runs twice: with the plain ``execute`` callback, and with the ``launch`` / ``collect`` pair, where
+the scheduler leaves a step in flight and, while all requests decode, launches the next one before it has read
+the tokens of the last (the fake then takes those tokens from the handle of the step before, as the device does).
 """
 
 import pytest
@@ -20,18 +24,32 @@ class FakeModel:
         self.cache = CacheManager([PagedKVSpec(1, 16), StateSpec((2, 4))], page, tokens, requests, context, storage=False)
         self.hash = {}
         self.batches = []
+        self.ahead = 0  # steps launched before the tokens of the step before them were read
 
     def admit(self, rid):
         self.hash[rid] = 7
         return self.cache.admit(rid)
 
-    def execute(self, entries, requests):
+    def launch(self, entries, requests, previous):
+        self.ahead += previous is not None
+        assert len(requests) == sum(1 for e in entries if e.want)
+        return self.execute(entries, requests, previous)
+
+    @staticmethod
+    def collect(handle):
+        return list(handle)
+
+    def execute(self, entries, requests, previous=None):
         self.batches.append([(e.request, len(e.tokens)) for e in entries])
         out = []
         for e in entries:
             assert len(e.tokens) > 0
             self.cache.reserve(e.request, len(e.tokens))  # must already be covered by the plan
-            for t in e.tokens:
+            tokens = e.tokens
+            if e.source >= 0:  # the token that the step before sampled and the host has not seen
+                assert len(tokens) == 1 and previous is not None
+                tokens = [previous[e.source]]
+            for t in tokens:
                 self.hash[e.request] = (self.hash[e.request] * 31 + t + 1) % 1000003
             self.cache.advance(e.request, len(e.tokens))
             if e.want:
@@ -51,8 +69,21 @@ def expected(prompt, n):
     return out
 
 
+MODE = "sync"
+
+
+@pytest.fixture(params=["sync", "ahead"], autouse=True)
+def mode(request):
+    global MODE
+    MODE = request.param
+    yield request.param
+    MODE = "sync"
+
+
 def make(model, **kw):
     events = []
+    if MODE == "ahead":
+        kw.update(launch=model.launch, collect=model.collect)
     s = Scheduler(model.cache, model.execute, events.extend, admit=model.admit, **kw)
     return s, events
 
@@ -195,3 +226,39 @@ def test_invalid_budgets():
     s.stopped.set()
     with pytest.raises(RuntimeError):
         s.submit(Request([1], 1))
+
+
+def test_decoding_runs_a_step_ahead(mode):
+    """With launch / collect, steady decoding launches each step before the one before it has been read; a request
+    that meets its end-of-sequence token has then run one step too many, which is dropped."""
+    model = FakeModel(tokens=256, requests=4)
+    s, _ = make(model, prefill_chunk=8)
+    stop = expected([9, 9, 9], 12)
+    reqs = [Request([i + 1] * n, 12) for i, n in enumerate((5, 2, 7))] + [Request([9, 9, 9], 12, eos_token_id=stop[5])]
+    for r in reqs:
+        s.submit(r)
+    drain(s)
+    for r in reqs[:3]:
+        assert r.output == expected(r.prompt, 12) and r.finish_reason == "length"
+    assert reqs[3].output == stop[:6] and reqs[3].finish_reason == "stop"
+    assert not model.cache.live() and s.flight is None
+    assert all(r.inflight == 0 for r in reqs[:3])
+    if mode == "ahead":
+        assert model.ahead >= 8  # most decode steps were launched ahead
+        decodes = [b for b in model.batches if all(n == 1 for _, n in b)]
+        assert sum(1 for b in decodes for rid, _ in b if rid == reqs[3].id) == 6  # five inputs and the dropped step
+    else:
+        assert model.ahead == 0
+
+
+def test_a_late_arrival_is_admitted_between_steps_ahead(mode):
+    model = FakeModel(tokens=256, requests=2)
+    s, _ = make(model, prefill_chunk=4)
+    a, b, c = Request([1] * 6, 20), Request([2] * 3, 4), Request([3] * 9, 5)
+    s.submit(a), s.submit(b)
+    for _ in range(6):
+        s.turn()
+    s.submit(c)  # no slot is free until b ends
+    drain(s)
+    assert a.output == expected(a.prompt, 20) and b.output == expected(b.prompt, 4) and c.output == expected(c.prompt, 5)
+    assert not model.cache.live()
