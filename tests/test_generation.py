@@ -97,6 +97,30 @@ def test_sampling_does_not_depend_on_the_batch(tmp_path):
     assert len({tuple(r["generated_tokens"]) for r in together}) == 4
 
 
+def test_a_step_ahead_changes_nothing(tmp_path):
+    """The engine that launches each decode step before it has read the last one's tokens (they go from step to step
+    on the device) generates what the engine that waits for every step generates: greedy and sampled, with requests
+    that stop at an end-of-sequence token in mid-flight, with and without captured graphs."""
+    folder = tiny.make_folder(tiny.TINY_B, seed=27, dtype="float32", std=0.3, folder=tmp_path / "m")
+    prompts = tiny.prompts(tiny.TINY_B["vocab_size"], [9, 30, 2, 17], seed=8)
+    runs = {}
+    for ahead in (False, True):
+        for graphs in (True, False):
+            with _engine(folder, "float32", 8, run_ahead=ahead, cuda_graphs=graphs) as engine:
+                greedy = engine.generate(prompts, max_tokens=24)
+                stop = greedy[1]["generated_tokens"][7]  # request 1 meets this token at its 8th place at the latest
+                stopped = engine.generate(prompts, max_tokens=24, eos_token_id=stop)
+                sampled = engine.generate(prompts, max_tokens=24, temperature=0.8, top_k=50, top_p=0.9, seed=3)
+                runs[ahead, graphs] = [[r["generated_tokens"] for r in out] for out in (greedy, stopped, sampled)]
+                reasons = [r["finish_reason"] for r in stopped]
+                if ahead:
+                    assert engine.stats["steps_ahead"] > 30
+                else:
+                    assert engine.stats["steps_ahead"] == 0
+            assert reasons[1] == "stop" and len(runs[ahead, graphs][1][1]) <= 8
+    assert runs[True, True] == runs[False, True] == runs[True, False] == runs[False, False]
+
+
 def test_preemption_on_the_device_recomputes_exactly(tmp_path):
     """A pool too small for three growing requests: the youngest is preempted and recomputed; every output
     still equals the plain greedy continuation."""
