@@ -267,11 +267,111 @@ def bench_attention(kind: str, batch: int, context: int, heads: int = 32, kv_hea
                 ms=round(ms, 5), kv_gb_s=round(kv_bytes / ms / 1e6, 1), tflops=round(flops / ms / 1e9, 2))
 
 
+SHAPES = {
+    # the dense LFM2 sizes named by the benchmark configurations (config.json keys; everything else at its default)
+    "350m": dict(hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, intermediate_size=6656),
+    "700m": dict(hidden_size=1536, num_attention_heads=24, num_key_value_heads=8, intermediate_size=10240),
+    "1.2b": dict(hidden_size=2048, num_attention_heads=32, num_key_value_heads=8, intermediate_size=12288),
+}
+
+
+def shape_config(name: str) -> dict:
+    base = dict(architectures=["Lfm2ForCausalLM"], model_type="lfm2", num_hidden_layers=16,
+                full_attn_idxs=[2, 5, 8, 10, 12, 14], vocab_size=65536, rope_theta=1000000.0, norm_eps=1e-5,
+                conv_L_cache=3, conv_bias=False, block_auto_adjust_ff_dim=True, block_multiple_of=256,
+                block_ffn_dim_multiplier=1.0, tie_embedding=True, max_position_embeddings=128000)
+    base.update(SHAPES[name])
+    return base
+
+
+def _random_engine(shape: str, **options):
+    import tempfile
+
+    from . import Engine, EngineConfig
+    from .config import config_from_dict
+    from .weights import write_random_model
+
+    with tempfile.TemporaryDirectory(prefix="akas-bench-") as folder:
+        write_random_model(folder, config_from_dict(shape_config(shape)), seed=0, dtype="bfloat16")
+        return Engine(folder, config=EngineConfig(dtype="bfloat16", **options))
+
+
+def bench_serving(shape: str = "350m", requests: int = 256, shortest: int = 128, longest: int = 2048, generated: int = 128,
+                  chunk: int = 512, seed: int = 17) -> dict:
+    """Many requests at once through the engine: random prompt lengths, prompts cut into portions of ``chunk``
+    that share steps with decoding requests. Wall time from the first submit to the last token."""
+    import time
+
+    rng = np.random.default_rng(seed)
+    lengths = rng.integers(shortest, longest + 1, requests).tolist()
+    vocab = shape_config(shape)["vocab_size"]
+    prompts = [rng.integers(0, vocab, n).tolist() for n in lengths]
+    pool = sum(-(-(n + generated) // 64) * 64 for n in lengths)
+    engine = _random_engine(shape, max_requests=requests, context=longest + generated + 64, max_tokens=pool + 64 * requests,
+                            prefill_chunk=chunk, prefill_requests=32, prefill_token_budget=8192)
+    with engine:
+        engine.generate(prompts[:4], max_tokens=8)  # warm up: kernels, library handles, the first graphs
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        results = engine.generate(prompts, max_tokens=generated)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        stats = dict(engine.stats)
+    out = sum(len(r["generated_tokens"]) for r in results)
+    return dict(bench="serving", shape=shape, requests=requests, prompt_tokens=sum(lengths), generated_tokens=out,
+                seconds=round(seconds, 3), output_tokens_per_s=round(out / seconds, 1),
+                total_tokens_per_s=round((out + sum(lengths)) / seconds, 1), steps=stats["steps"],
+                steps_ahead=stats["steps_ahead"], preemptions=stats["preemptions"], max_active=stats["max_active"])
+
+
+def bench_long_context(shape: str = "700m", requests: int = 8, prompt: int = 30000, generated: int = 256,
+                       chunk: int = 2048, seed: int = 17) -> dict:
+    """A few very long prompts, then decoding: the paged cache and the split-key decode attention under load."""
+    vocab = shape_config(shape)["vocab_size"]
+    context = -(-(prompt + generated + 64) // 64) * 64
+    engine = _random_engine(shape, max_requests=requests, context=context, max_tokens=requests * context,
+                            prefill_chunk=chunk, prefill_token_budget=8192)
+    runner = engine.runner
+    prompts = synthetic_prompts(requests, prompt, vocab, seed)
+    pre = []
+    for rep in range(2):
+        ids = [f"w{rep}-{i}" for i in range(requests)]
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for rid, tokens in zip(ids, prompts):
+            for at in range(0, prompt, chunk):
+                part = tokens[at:at + chunk]
+                runner.step([StepEntry(rid, part, (len(part) - 1,) if at + chunk >= prompt else ())])
+        stop.record()
+        torch.cuda.synchronize()
+        pre.append(start.elapsed_time(stop))
+        if rep == 0:
+            for rid in ids:
+                runner.release(rid)
+    feed = np.random.default_rng(seed + 1).integers(0, vocab, (generated + 8, requests)).tolist()
+
+    def step(i):
+        logits = runner.step([StepEntry(rid, (feed[i][j],), (0,)) for j, rid in enumerate(ids)])
+        return runner.ops.argmax(logits)
+
+    for i in range(8):
+        step(i)
+    ms = _event_ms(lambda: [step(8 + i) for i in range(generated)])
+    contexts = [prompt + 8 + generated // 2] * requests
+    nbytes = decode_bytes(runner, contexts)
+    engine.close()
+    return dict(bench="long_context", shape=shape, requests=requests, prompt=prompt, generated=generated,
+                prefill_tokens_per_s=round(requests * prompt / (pre[-1] / 1e3), 1), prefill_ms=round(pre[-1], 1),
+                decode_ms_per_step=round(ms / generated, 4), decode_tokens_per_s=round(requests * generated / (ms / 1e3), 1),
+                decode_gb_per_step=round(nbytes / 1e9, 3), decode_gb_s=round(nbytes / (ms / generated / 1e3) / 1e9, 1))
+
+
 def _main():
     import argparse
     import json
 
-    ap = argparse.ArgumentParser(description="time single kernels of the bfloat16 path (cold L2, CUDA events)")
+    ap = argparse.ArgumentParser(description="single kernels of the bfloat16 path (cold L2, CUDA events), and two whole-engine runs")
     sub = ap.add_subparsers(dest="what", required=True)
     lin = sub.add_parser("linear", help="y = x . w^T with one of the epilogues")
     lin.add_argument("--m", type=int, nargs="+", default=[8])
@@ -287,7 +387,23 @@ def _main():
     att.add_argument("--kv-heads", type=int, default=8)
     att.add_argument("--head-dim", type=int, default=64)
     att.add_argument("--iters", type=int, default=20)
+    srv = sub.add_parser("serving", help="many requests through the engine, prompt portions mixed with decoding")
+    srv.add_argument("--shape", default="350m", choices=sorted(SHAPES))
+    srv.add_argument("--requests", type=int, default=256)
+    srv.add_argument("--generated", type=int, default=128)
+    srv.add_argument("--chunk", type=int, default=512)
+    lng = sub.add_parser("long-context", help="a few very long prompts, then decoding")
+    lng.add_argument("--shape", default="700m", choices=sorted(SHAPES))
+    lng.add_argument("--requests", type=int, default=8)
+    lng.add_argument("--prompt", type=int, default=30000)
+    lng.add_argument("--generated", type=int, default=256)
     args = ap.parse_args()
+    if args.what == "serving":
+        print(json.dumps(bench_serving(args.shape, args.requests, generated=args.generated, chunk=args.chunk)))
+        return
+    if args.what == "long-context":
+        print(json.dumps(bench_long_context(args.shape, args.requests, args.prompt, args.generated)))
+        return
     if args.what == "attention":
         for b in args.batch:
             print(json.dumps(bench_attention(args.kind, b, args.context, args.heads, args.kv_heads, args.head_dim,
