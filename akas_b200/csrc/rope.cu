@@ -227,10 +227,10 @@ AKAS_API int akas_qk_norm_rope_store(void* qkv, void* q_out, const float* q_w, c
                         max_blocks, seq_of_token, positions, page_size, H, KH, D);
 }
 
-// k, v: [N, KH * D] rows (row stride `stride` elements) into the pages; for position encodings that
+// k, v: [N, KH * D] rows (row strides `stride` and `v_stride` elements) into the pages; for position encodings that
 // rewrite k outside the fused kernel.
 template <typename T>
-__global__ void kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v, size_t stride,
+__global__ void kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v, size_t stride, size_t v_stride,
                                 T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ block_table,
                                 int max_blocks, const int* __restrict__ seq_of_token,
                                 const int* __restrict__ positions, int page_size, int KH, int D) {
@@ -243,21 +243,21 @@ __global__ void kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v
   const size_t row = (((size_t)page * KH + kvh) * page_size + pos % page_size) * D;
   for (int e = threadIdx.x; e < D; e += blockDim.x) {
     k_pool[row + e] = k[(size_t)t * stride + kvh * D + e];
-    v_pool[row + e] = v[(size_t)t * stride + kvh * D + e];
+    v_pool[row + e] = v[(size_t)t * v_stride + kvh * D + e];
   }
 }
 
-AKAS_API int akas_kv_store(const void* k, const void* v, long long stride, void* k_pool, void* v_pool,
+AKAS_API int akas_kv_store(const void* k, const void* v, long long stride, long long v_stride, void* k_pool, void* v_pool,
                            const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
                            int page_size, int N, int KH, int D, int dtype, cudaStream_t stream) {
   if (N <= 0) return 0;
   const dim3 grid(N, KH);
   if (dtype == AKAS_F32)
-    kv_store_kernel<float><<<grid, 64, 0, stream>>>((const float*)k, (const float*)v, (size_t)stride, (float*)k_pool,
+    kv_store_kernel<float><<<grid, 64, 0, stream>>>((const float*)k, (const float*)v, (size_t)stride, (size_t)v_stride, (float*)k_pool,
                                                     (float*)v_pool, block_table, max_blocks, seq_of_token, positions,
                                                     page_size, KH, D);
   else
-    kv_store_kernel<bf16><<<grid, 64, 0, stream>>>((const bf16*)k, (const bf16*)v, (size_t)stride, (bf16*)k_pool,
+    kv_store_kernel<bf16><<<grid, 64, 0, stream>>>((const bf16*)k, (const bf16*)v, (size_t)stride, (size_t)v_stride, (bf16*)k_pool,
                                                    (bf16*)v_pool, block_table, max_blocks, seq_of_token, positions,
                                                    page_size, KH, D);
   return launch_status();

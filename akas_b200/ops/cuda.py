@@ -43,7 +43,7 @@ _SIGNATURES = {
         "akas_qk_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int,
                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                     c_int, c_int, c_int, c_void_p],
-        "akas_kv_store": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+        "akas_kv_store": [c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_int, c_int, c_void_p],
     },
     "attention": {
@@ -455,9 +455,9 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_weight, k_weight, eps, 
 def kv_store(k, v, k_pool, v_pool, block_table, seq_of_token, positions, page_size):
     n = k.shape[0]
     kh, d = k_pool.shape[1], k_pool.shape[3]
-    if k.stride(1) != 1 or v.stride(1) != 1 or k.stride(0) != v.stride(0):
-        raise ValueError("kv_store: k and v must be rows of one buffer with unit inner stride")
-    _check(_fn("rope", "akas_kv_store")(_ptr(k), _ptr(v), k.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+    if k.stride(1) != 1 or v.stride(1) != 1:
+        raise ValueError("kv_store: k and v must have unit inner stride")
+    _check(_fn("rope", "akas_kv_store")(_ptr(k), _ptr(v), k.stride(0), v.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
                                        block_table.shape[1], _ptr(seq_of_token), _ptr(positions), page_size, n, kh, d,
                                        _code(k_pool), _stream()), "kv_store")
 

@@ -113,7 +113,7 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_weight, k_weight, eps, 
     n = qkv.shape[0]
     d = head_dim
     q = qkv[:, : heads * d].reshape(n, heads, d).to(torch.float32)
-    k = qkv[:, heads * d : (heads + kv_heads) * d].reshape(n, kv_heads, d).to(torch.float32)
+    k = qkv[:, heads * d : (heads + kv_heads) * d].reshape(n, kv_heads, d).to(torch.float32).clone()  # written back below
     if q_weight is not None:
         q = rmsnorm(q, q_weight, eps, zero_centered, torch.float32)
         k = rmsnorm(k, k_weight, eps, zero_centered, torch.float32)

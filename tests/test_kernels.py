@@ -200,6 +200,25 @@ def test_short_conv_decode_kernel_equals_the_general_one(ops):
         assert torch.equal(got, want) and torch.equal(s1, s2)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_kv_store_of_separate_rows(ops, dtype):
+    """Keys rewritten by a position encoding of its own (a fresh tensor) and values still inside the qkv buffer:
+    rows of different pitch go to the same pages."""
+    cuda, ref = ops
+    kh, d, page, n = 2, 32, 4, 9
+    qkv = _rand((n, (3 + 2 * kh) * d), dtype, 40)
+    k = _rand((n, kh * d), dtype, 41)
+    v = qkv[:, (3 + kh) * d:]
+    table = torch.tensor([[5, 2, 7], [1, -1, -1]], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([0] * 6 + [1, 1, -1], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([3, 4, 5, 6, 7, 8, 0, 1, 0], dtype=torch.int32, device=DEV)
+    pools = [_rand((8, kh, page, d), dtype, 42 + i) for i in range(4)]
+    pools[2].copy_(pools[0]), pools[3].copy_(pools[1])
+    cuda.kv_store(k, v, pools[0], pools[1], table, seq, pos, page)
+    ref.kv_store(k, v, pools[2], pools[3], table, seq, pos, page)
+    assert torch.equal(pools[0], pools[2]) and torch.equal(pools[1], pools[3])
+
+
 def _batch(lengths, pad=0):
     """cu_seqlens, seq_of_token, for requests of the given lengths, plus ``pad`` padding tokens."""
     cu = [0]

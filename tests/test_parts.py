@@ -3,7 +3,8 @@
 The toy architecture is defined here and registered through the public registries only; no file of the
 framework knows it. It holds a mixer with state of its own (an exponential moving average), an
 attention layer with a window (a page group of its own whose pages are given back as the window moves),
-a layer that runs twice, and a schedule entry that reads another entry's cache.
+a layer that runs twice, a schedule entry that reads another entry's cache, a feed-forward that routes every
+token to one of three experts, and a position encoding that is not rotary (a decay with distance).
 """
 
 from dataclasses import dataclass, field
@@ -21,7 +22,8 @@ from akas_b200.config import (AttentionSpec, EngineConfig, LayerSpec, ModelSpec,
 from akas_b200.engine.batch import BatchLayout, StepEntry, fill_batch
 from akas_b200.engine.runner import ModelRunner
 from akas_b200.ops import reference
-from akas_b200.parts import (Block, Mixer, Param, Runtime, StateSpec, build_part, register_mixer)
+from akas_b200.parts import (Block, FeedForward, Mixer, Param, Part, Runtime, StateSpec, build_part, register_ffn,
+                             register_mixer, register_position)
 from akas_b200.weights import write_random_model
 
 
@@ -183,6 +185,47 @@ class EmaMixer(Mixer):
         return residual.add_(out) if residual is not None else out.to(x.dtype)
 
 
+class RoutedFeedForward(FeedForward):
+    """Every token goes to the expert whose router logit is largest (lowest index among equals); the expert's
+    output, relu(x U^T) D^T, is weighted by the softmax probability of that logit. Router and softmax in float32."""
+
+    def params(self):
+        o = self.spec.options
+        p = {"router.weight": Param((o["experts"], o["width"]))}
+        for e in range(o["experts"]):
+            p[f"experts.{e}.up.weight"] = Param((o["hidden"], o["width"]))
+            p[f"experts.{e}.down.weight"] = Param((o["width"], o["hidden"]))
+        return p
+
+    def load(self, get):
+        n = self.spec.options["experts"]
+        self.router = get("router.weight")
+        self.up = [get(f"experts.{e}.up.weight") for e in range(n)]
+        self.down = [get(f"experts.{e}.down.weight") for e in range(n)]
+
+    def forward(self, x, ctx, residual=None):
+        ops = self.rt.ops
+        logits = ops.linear(x, self.router, out_dtype=torch.float32)
+        weight, expert = torch.softmax(logits, dim=-1).max(dim=-1)
+        out = torch.zeros((x.shape[0], self.spec.options["width"]), dtype=torch.float32, device=x.device)
+        for e in range(len(self.up)):
+            rows = (expert == e).nonzero().flatten()
+            if rows.numel():
+                hidden = torch.relu(ops.linear(x[rows].contiguous(), self.up[e], out_dtype=torch.float32)).to(x.dtype)
+                out[rows] = ops.linear(hidden, self.down[e], out_dtype=torch.float32) * weight[rows, None]
+        return residual.add_(out) if residual is not None else out.to(x.dtype)
+
+
+class DecayPosition(Part):
+    """q_t *= g^t, k_t *= g^-t per channel pair rate g: a score then carries g^(t - s), a decay with distance.
+    No tables for the fused rotary kernel, so the attention mixer calls ``apply`` and stores k and v after it."""
+
+    def apply(self, q, k, ctx):
+        rate = float(self.spec.options["rate"])
+        pos = ctx.positions.to(torch.float32)[:, None]
+        return (q.float() * rate ** pos).to(q.dtype), (k.float() * rate ** -pos).to(k.dtype)
+
+
 @dataclass(frozen=True)
 class ToyConfig:
     width: int = 32
@@ -201,19 +244,22 @@ class ToyConfig:
         c = self.width
         norm = RMSNormSpec(c, 1e-5)
 
-        def layer(i, mixer):
+        def layer(i, mixer, ffn=SwiGLUSpec(c, 48)):
             p = f"layers.{i}."
-            return LayerSpec(mixer, SwiGLUSpec(c, 48), norm, norm, p + "mixer.", p + "ffn.", p + "norm1", p + "norm2")
+            return LayerSpec(mixer, ffn, norm, norm, p + "mixer.", p + "ffn.", p + "norm1", p + "norm2")
 
         attn = dict(qk_norm=RMSNormSpec(16, 1e-5), position=RopeSpec(16, 1e4))
         return ModelSpec(
             architecture=self.architecture, hidden_size=c, vocab_size=self.vocab,
             layers=(layer(0, PartSpec("ema_for_tests", {"width": c})),
                     layer(1, AttentionSpec(c, 2, 1, 16, window=self.window, **attn)),
-                    layer(2, AttentionSpec(c, 2, 2, 16, **attn))),
+                    layer(2, AttentionSpec(c, 2, 2, 16, **attn)),
+                    layer(3, AttentionSpec(c, 2, 1, 16, qk_norm=None, position=PartSpec("decay_for_tests", {"rate": 0.97})),
+                          PartSpec("routed_for_tests", {"width": c, "hidden": 40, "experts": 3}))),
             final_norm=norm, embedding_name="embed", final_norm_name="final_norm", head_name=None,
             # layer 1 runs twice, each time with a cache of its own; the last entry reads entry 2's keys and values
-            schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(1), ScheduleEntry(2, cache=2)),
+            schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(1), ScheduleEntry(2, cache=2),
+                      ScheduleEntry(3)),
         )
 
 
@@ -223,18 +269,23 @@ def _toy_plain(cfg, w, tokens):
     h = w["embed"][torch.as_tensor(tokens)]
     kept = {}
 
-    def attn(i, x, window, heads, kv, shared=None):
+    def attn(i, x, window, heads, kv, shared=None, decay=None):
         p = f"layers.{i}.mixer."
         d = 16
-        q = plain.rms_norm((x @ w[p + "q_proj.weight"].T).reshape(T, heads, d), w[p + "q_norm.weight"], 1e-5)
-        cos, sin = plain.rope_tables(torch.arange(T), d, 1e4, torch.float64)
-        q = plain.apply_rope(q, cos, sin)
-        if shared is None:
-            k = plain.rms_norm((x @ w[p + "k_proj.weight"].T).reshape(T, kv, d), w[p + "k_norm.weight"], 1e-5)
-            k, v = plain.apply_rope(k, cos, sin), (x @ w[p + "v_proj.weight"].T).reshape(T, kv, d)
-        else:
-            k, v = shared
         pos = torch.arange(T)
+        if decay is not None:  # no QK-norm, decay position: q_t g^t, k_t g^-t
+            q = (x @ w[p + "q_proj.weight"].T).reshape(T, heads, d) * decay ** pos[:, None, None].double()
+            k = (x @ w[p + "k_proj.weight"].T).reshape(T, kv, d) * decay ** -pos[:, None, None].double()
+            v = (x @ w[p + "v_proj.weight"].T).reshape(T, kv, d)
+        else:
+            q = plain.rms_norm((x @ w[p + "q_proj.weight"].T).reshape(T, heads, d), w[p + "q_norm.weight"], 1e-5)
+            cos, sin = plain.rope_tables(torch.arange(T), d, 1e4, torch.float64)
+            q = plain.apply_rope(q, cos, sin)
+            if shared is None:
+                k = plain.rms_norm((x @ w[p + "k_proj.weight"].T).reshape(T, kv, d), w[p + "k_norm.weight"], 1e-5)
+                k, v = plain.apply_rope(k, cos, sin), (x @ w[p + "v_proj.weight"].T).reshape(T, kv, d)
+            else:
+                k, v = shared
         seen = pos[None, :] <= pos[:, None]
         if window:
             seen &= pos[None, :] > pos[:, None] - window
@@ -243,7 +294,7 @@ def _toy_plain(cfg, w, tokens):
         out = torch.einsum("hts,shd->thd", torch.softmax(score, -1), vv).reshape(T, heads * d)
         return out @ w[p + "out_proj.weight"].T, (k, v)
 
-    for n, (i, shared) in enumerate(((0, None), (1, None), (2, None), (1, None), (2, 2))):
+    for n, (i, shared) in enumerate(((0, None), (1, None), (2, None), (1, None), (2, 2), (3, None))):
         p = f"layers.{i}."
         x = plain.rms_norm(h, w[p + "norm1"], 1e-5)
         if i == 0:
@@ -253,18 +304,32 @@ def _toy_plain(cfg, w, tokens):
                 s = w[p + "mixer.decay"] * s + u[t]
                 rows.append(s)
             mixed = torch.stack(rows)
+        elif i == 3:
+            mixed, kept[n] = attn(i, x, None, 2, 1, decay=0.97)
         else:
             mixed, kept[n] = attn(i, x, cfg.window if i == 1 else None, 2, 1 if i == 1 else 2,
                                   kept[shared] if shared is not None else None)
         h = h + mixed
         f = p + "ffn."
-        h = h + plain.swiglu(plain.rms_norm(h, w[p + "norm2"], 1e-5), w[f + "w1.weight"], w[f + "w3.weight"], w[f + "w2.weight"])
+        y = plain.rms_norm(h, w[p + "norm2"], 1e-5)
+        if i == 3:  # routed: the expert with the largest router logit, weighted by its softmax probability
+            prob = torch.softmax(y @ w[f + "router.weight"].T, -1)
+            weight, expert = prob.max(-1)
+            routed = torch.zeros_like(h)
+            for t in range(T):
+                e = int(expert[t])
+                routed[t] = torch.relu(y[t] @ w[f + f"experts.{e}.up.weight"].T) @ w[f + f"experts.{e}.down.weight"].T * weight[t]
+            h = h + routed
+        else:
+            h = h + plain.swiglu(y, w[f + "w1.weight"], w[f + "w3.weight"], w[f + "w2.weight"])
     return plain.rms_norm(h, w["final_norm"], 1e-5) @ w["embed"].T
 
 
 @pytest.mark.parametrize("device", _devices())
 def test_toy_architecture_is_registered_built_and_stepped(device, tmp_path):
     register_mixer("ema_for_tests", EmaMixer)
+    register_ffn("routed_for_tests", RoutedFeedForward)
+    register_position("decay_for_tests", DecayPosition)
     register_architecture(ToyConfig.architecture, ToyConfig)
     cfg = ToyConfig()
     folder = write_random_model(tmp_path / "toy", cfg, seed=3, std=0.2, dtype="float32")
@@ -283,7 +348,7 @@ def test_toy_architecture_is_registered_built_and_stepped(device, tmp_path):
 
     r = runner(48)
     assert len(r.cache.groups) == 2 and [type(v).__name__ for v in r.cache.views] == [
-        "StateCache", "PagedCache", "PagedCache", "PagedCache", "NoneType"]
+        "StateCache", "PagedCache", "PagedCache", "PagedCache", "NoneType", "PagedCache"]
     steps, peak = traces.mixed(reqs, {rid: max(1, len(t) - 6) for rid, t in reqs.items()}, seed=2, live=3, page=page)
     for name, trace, pool in (("whole", traces.whole(reqs), 48), ("portions", traces.portions(reqs), 48),
                               ("tail", traces.tail_decoded(reqs, 8), 48), ("mixed", steps, peak)):
