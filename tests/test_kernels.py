@@ -83,6 +83,15 @@ def test_linear_float32_rows_do_not_depend_on_the_batch(ops):
     whole = cuda.linear(x, w)
     for rows in (slice(0, 1), slice(5, 22), slice(100, 164), slice(299, 300)):
         assert torch.equal(cuda.linear(x[rows].contiguous(), w), whole[rows])
+    # a wide w: up to 16 rows go through the kernel that streams w once; the same bits as the tiled kernel
+    for k, o in ((200, 400), (520, 257), (1028, 300)):
+        x, w = _rand((300, k), torch.float32, 8), _rand((o, k), torch.float32, 9)
+        whole = cuda.linear(x, w)
+        res = _rand((300, o), torch.float32, 10)
+        added = cuda.linear(x, w, residual=res.clone())
+        for rows in (slice(0, 1), slice(7, 10), slice(40, 48), slice(100, 109), slice(284, 300)):
+            assert torch.equal(cuda.linear(x[rows].contiguous(), w), whole[rows])
+            assert torch.equal(cuda.linear(x[rows].contiguous(), w, residual=res[rows].clone()), added[rows])
 
 
 @pytest.mark.parametrize("n,k,o", [(1, 64, 50), (17, 104, 37), (70, 56, 130), (300, 96, 192), (8, 2048, 321)])
