@@ -234,7 +234,9 @@ AKAS_API int akas_gemm_tcgen05(const void* x, const void* w, void* y, int M, int
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || (uintptr_t)x % 16 || (uintptr_t)w % 16 || (uintptr_t)y % 16) return (int)cudaErrorInvalidValue;
   if (epilogue == EPI_SWIGLU && (N % 2 || (N / 2) % 8)) return (int)cudaErrorInvalidValue;
-  const bool narrow = (epilogue == EPI_SWIGLU ? N / 2 : N) <= 2048 && M <= 4096;  // more, smaller tiles for few tiles
+  // 128 x 256 tiles, unless they would leave most SMs without one: then 128 x 128 (measured at 512 and 2,048 tokens:
+  // the wide tile wins from about a hundred tiles on)
+  const bool narrow = (long long)((M + BM - 1) / BM) * ((N + 255) / 256) <= 64;
   switch (epilogue) {
     case EPI_BF16: return narrow ? launch<128, EPI_BF16>(x, w, y, M, N, K, stream) : launch<256, EPI_BF16>(x, w, y, M, N, K, stream);
     case EPI_ACC: return narrow ? launch<128, EPI_ACC>(x, w, y, M, N, K, stream) : launch<256, EPI_ACC>(x, w, y, M, N, K, stream);
