@@ -30,6 +30,7 @@ from .batch import BatchLayout, StepContext, StepEntry, fill_batch
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 _GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+_SHAPE_REPEATS, _SHAPE_GRAPHS = 3, 4  # a step shape is captured when it comes the third time; at most four are kept
 
 
 def default_ops(device: torch.device, dtype: torch.dtype):
@@ -64,6 +65,8 @@ class ModelRunner:
         self._host = None  # pinned int32 staging
         self._dev = None
         self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._shape_graphs: Dict[tuple, "_DecodeGraph"] = {}
+        self._shape_counts: Dict[tuple, int] = {}
         self.steps = 0
         self.kernels_per_decode_step: Dict[int, int] = {}  # bucket -> kernels inside its captured graph
 
@@ -139,8 +142,12 @@ class ModelRunner:
 
         decode_only = all(len(e.tokens) == 1 for e in entries)
         all_wanted = all(list(e.want) == [0] for e in entries)
-        if decode_only and all_wanted and self.config.cuda_graphs and self.device.type == "cuda":
+        graphs = self.config.cuda_graphs and self.device.type == "cuda"
+        repeated = self._repeated_shape(entries) if graphs and not (decode_only and all_wanted) else None
+        if decode_only and all_wanted and graphs:
             logits = self._decode_graph_step(entries, arrays, previous)
+        elif repeated is not None:
+            logits = repeated.run(entries, arrays, previous)
         else:
             n = sum(len(e.tokens) for e in entries)
             m = sum(len(e.want) for e in entries)
@@ -160,7 +167,24 @@ class ModelRunner:
         self.steps += 1
         return logits
 
-    # ------------------------------------------------------------------ captured decode
+    # ------------------------------------------------------------------ captured steps
+
+    def _repeated_shape(self, entries):
+        """A captured graph for steps whose requests bring exactly these numbers of tokens, once that shape has come
+        _SHAPE_REPEATS times (the equal portions of a long prompt, a batch of prompts of one length); else None.
+        At most _SHAPE_GRAPHS shapes are kept: each holds the activations of its step."""
+        key = (tuple(len(e.tokens) for e in entries), sum(len(e.want) for e in entries))
+        graph = self._shape_graphs.get(key)
+        if graph is not None:
+            return graph
+        seen = self._shape_counts.get(key, 0) + 1
+        self._shape_counts[key] = seen
+        if len(self._shape_counts) > 4096:
+            self._shape_counts.clear()
+        if seen < _SHAPE_REPEATS or len(self._shape_graphs) >= _SHAPE_GRAPHS:
+            return None
+        graph = self._shape_graphs[key] = _DecodeGraph(self, 0, lengths=key[0], wanted=key[1])
+        return graph
 
     def _decode_graph_step(self, entries, arrays=None, previous=None):
         count = len(entries)
@@ -204,18 +228,23 @@ class _Pinned:
 
 
 class _DecodeGraph:
-    """One captured decode step for ``bucket`` requests of one token each.
+    """One captured step: a decode step for ``bucket`` requests of one token each, or (``lengths`` given) a step
+    of requests that bring exactly these numbers of tokens, ``wanted`` logits rows in all.
 
     The batch arrays live at fixed addresses; a replay copies the step's arrays in
     and launches the graph. Requests short of the bucket are padding (request -1).
-    Launch shapes inside depend on the bucket only; lengths are read on the device.
+    Launch shapes inside depend on the bucket (or the lengths) only; positions, pages and slots are read on the device.
     """
 
-    def __init__(self, runner: ModelRunner, bucket: int):
+    def __init__(self, runner: ModelRunner, bucket: int, lengths=None, wanted: int = 0):
         self.runner = runner
         self.bucket = bucket
+        self.lengths = lengths
         cache = runner.cache
-        self.layout = BatchLayout(bucket, bucket, bucket, len(cache.groups), cache.max_blocks)
+        if lengths is None:
+            self.layout = BatchLayout(bucket, bucket, bucket, len(cache.groups), cache.max_blocks)
+        else:
+            self.layout = BatchLayout(sum(lengths), len(lengths), wanted, len(cache.groups), cache.max_blocks)
         self.ring = _Pinned(self.layout.size, runner.device)
         self.dev = torch.zeros(self.layout.size, dtype=torch.int32, device=runner.device)
         self.graph = None
@@ -223,9 +252,15 @@ class _DecodeGraph:
 
     def _fill(self, entries, arrays=None):
         host = self.ring.take()
-        fill_batch(host.numpy(), self.layout, entries, self.runner.cache, pad_to=self.bucket, tokens=arrays)
-        rows = host.numpy()[self.layout.logit_rows : self.layout.logit_rows + self.bucket]
-        rows[:] = np.arange(self.bucket, dtype=np.int32)
+        lay = self.layout
+        if self.lengths is None:
+            fill_batch(host.numpy(), lay, entries, self.runner.cache, pad_to=self.bucket, tokens=arrays)
+            host.numpy()[lay.logit_rows : lay.logit_rows + self.bucket] = np.arange(self.bucket, dtype=np.int32)
+        elif entries:
+            fill_batch(host.numpy(), lay, entries, self.runner.cache, tokens=arrays)
+        else:  # all padding, for warm-up and capture
+            fill_batch(host.numpy(), lay, [], self.runner.cache, pad_to=lay.n)
+            host.numpy()[lay.logit_rows : lay.logit_rows + max(lay.m, 1)] = 0
         self.dev.copy_(host, non_blocking=True)
         self.ring.copied()
 
@@ -235,7 +270,12 @@ class _DecodeGraph:
             # Warm-up and capture run on a batch of padding only: they must leave pages and state alone.
             # The context's host-side sizes are upper bounds so that the captured launches fit every replay.
             self._fill([])
-            ctx = runner._context(self.dev, self.layout, 1, runner.config.context, True)
+            if self.lengths is None:
+                ctx = runner._context(self.dev, self.layout, 1, runner.config.context, True)
+            else:
+                ctx = runner._context(self.dev, self.layout, max(self.lengths), runner.config.context,
+                                      all(n == 1 for n in self.lengths))
+                ctx.query_tiles = sum(-(-n // 64) for n in self.lengths)
             ctx.memo["captured"] = True
             stream = torch.cuda.Stream(device=runner.device)
             stream.wait_stream(torch.cuda.current_stream(runner.device))
@@ -250,7 +290,8 @@ class _DecodeGraph:
             before = getattr(runner.ops, "launch_count", 0)
             with torch.cuda.graph(graph):
                 self.logits = runner.model.forward(ctx, runner.cache.views)
-            runner.kernels_per_decode_step[self.bucket] = getattr(runner.ops, "launch_count", 0) - before
+            if self.lengths is None:
+                runner.kernels_per_decode_step[self.bucket] = getattr(runner.ops, "launch_count", 0) - before
             self.graph = graph
 
     def run(self, entries, arrays=None, previous=None):
@@ -262,4 +303,4 @@ class _DecodeGraph:
             runner.ops.take_tokens(self.dev[lay.token_ids : lay.token_ids + lay.n],
                                    self.dev[lay.token_src : lay.token_src + lay.n], previous)
         self.graph.replay()
-        return self.logits[: len(entries)]
+        return self.logits[: len(entries)] if self.lengths is None else self.logits

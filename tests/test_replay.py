@@ -92,3 +92,39 @@ def test_ways_of_cutting_agree_with_each_other(dtype, tmp_path):
         got = traces.replay(_runner(folder, dtype, "cuda:0", page, longest), getattr(traces, mode)(reqs))
         for rid in reqs:
             assert traces.first_bad(got[rid], base[rid], tol) is None, (mode, rid, traces.worst(got[rid], base[rid]))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["a", "b"])
+def test_captured_steps_agree_with_the_plain_model(key, dtype, tmp_path):
+    """With graphs on: the same traces, so that single-token steps replay the captured decode graphs, and a trace of
+    equal portions (two requests side by side, ten tokens each per step), whose step shape repeats and is captured
+    after its second appearance. Captured or not, the logits are the plain model's."""
+    from akas_b200.config import EngineConfig
+    from akas_b200.engine.runner import ModelRunner
+
+    folder, reqs, want = _setup(key, dtype, tmp_path)
+    page = tiny.PAGE[key]
+    longest = -(-max(len(t) for t in reqs.values()) // page) * page
+
+    def runner(tokens):
+        return ModelRunner(folder, EngineConfig(dtype=dtype, device="cuda:0", page_size=page, max_tokens=tokens,
+                                                max_requests=4, context=longest, cuda_graphs=True))
+
+    r = runner(longest)
+    _check(traces.replay(r, traces.tail_decoded(reqs)), want, dtype, "tail decoded, captured")
+    assert r._graphs and all(g.graph is not None for g in r._graphs.values())
+
+    # the two longest requests side by side in portions of ten tokens, logits wanted at the last two places of each
+    a, b = sorted(reqs, key=lambda rid: -len(reqs[rid]))[:2]
+    n = min(len(reqs[a]), len(reqs[b])) // 10 * 10
+    steps = [{"step": i, "entries": [{"id": rid, "tokens": reqs[rid][at:at + 10], "want": [8, 9]} for rid in (a, b)],
+              "end": [a, b] if at + 10 >= n else []} for i, at in enumerate(range(0, n, 10))]
+    r = runner(2 * longest)
+    got = traces.replay(r, steps)
+    assert len(r._shape_graphs) == 1 and next(iter(r._shape_graphs.values())).graph is not None
+    for rid in (a, b):
+        places = [p for at in range(0, n, 10) for p in (at + 8, at + 9)]
+        bad = traces.first_bad(got[rid], want[rid][places], TOL[dtype])
+        assert bad is None, (rid, bad, traces.worst(got[rid], want[rid][places]))
