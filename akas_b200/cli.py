@@ -94,8 +94,9 @@ def _random(args):
     from .config import config_from_dict
     from .weights import write_random_model
 
-    source = args.config
-    data = json.loads(Path(source).read_text()) if Path(source).is_file() else json.loads(source)
+    source = args.config.strip()
+    # config.json content (a JSON object) or the path of a file that holds it
+    data = json.loads(source) if source.startswith("{") else json.loads(Path(source).read_text())
     folder = write_random_model(args.out, config_from_dict(data), seed=args.seed, std=args.std, dtype=args.dtype)
     print(folder)
 
