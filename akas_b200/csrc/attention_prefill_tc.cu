@@ -1,0 +1,355 @@
+// Paged GQA attention for prompt portions on Blackwell's tensor cores (tcgen05, accumulators in tensor memory),
+// bfloat16, head size 64, pages that hold whole 64-key half tiles (page size a multiple of 64).
+//
+// One block per (tile of 128 consecutive query tokens of one request, query head). It walks 128-key tiles
+// aligned to absolute position 0, from the first key any of its queries may see to its last query's own
+// position. Six warps, three roles:
+//   warp 0    producer: one thread issues TMA loads (128-byte swizzle): the Q tile once, then per key tile two
+//             boxes of 64 keys of K and two of V, found through the block table, into a two-stage ring; K and V
+//             have "full" and "empty" mbarriers of their own, so the scores can start before V has landed.
+//   warp 1    tensor cores: allocates tensor memory (128 columns of scores S, 64 of P.V) and, one thread,
+//             issues S = Q.K^T (four tcgen05.mma, M 128, N 128, K 16, both operands K-major) and, once the
+//             softmax warps have written P, PV = P.V (eight tcgen05.mma, M 128, N 64, K 16; V is read as it
+//             lies in the pages, rows of keys with the head's channels contiguous: an MN-major B operand).
+//             The scores of the next tile are issued right behind P.V of the current one.
+//   warps 2-5 softmax and read-out: thread = query row = tensor-memory lane. Per tile it reads its row of S
+//             (tcgen05.ld) twice: once for the row maximum (scale and causal / window mask applied), once to
+//             form P = exp2(s - max), which it rounds to bfloat16 and writes to shared memory in the swizzled
+//             K-major layout the second product reads; then it reads its row of PV and keeps the running
+//             output in registers: O = O * exp2(old max - new max) + PV. Softmax is float32 throughout.
+// A block's tiles follow one another strictly (scores, softmax, P.V): the tensor cores idle while the softmax warps
+// work and the other way round, and at 113 KB of shared memory a second block does not always fit beside it. As
+// it stands the kernel is correct and slower than the mma.sync kernel of attention_prefill.cu (measured 70-87
+// TFLOP/s against 180-220); it is selected with AKAS_B200_PROMPT_ATTENTION=tcgen05.
+//
+// Keys past a query's position are masked by position, not by content: pages past the end of a request are
+// not fetched (a valid page stands in), and rows of V past the block's last key are zeroed in shared memory so
+// that whatever a page held before cannot meet a zero probability as NaN.
+// Every wait on an mbarrier is bounded (akas_prefill_attention_tc_status; see gemm_tcgen05.cu).
+#include <math.h>
+
+#include "mma.cuh"
+#include "tcgen05.cuh"
+
+using namespace akas;
+using namespace akas::tc;
+
+namespace {
+
+constexpr int BQ = 128, BKEYS = 128, D = 64, THREADS = 192, STAGES = 2;
+constexpr int TILE_BYTES = 128 * 128;  // 128 rows of 64 bfloat16: Q, one stage of K, one of V
+constexpr int SMEM_BYTES = 1024 + TILE_BYTES * (1 + 2 * STAGES) + 2 * TILE_BYTES;  // + P: 128 rows x 128 keys
+constexpr int TMEM_COLS = 256;  // S: columns 0..127, PV: 128..191
+
+__device__ int g_attention_status = 0;
+
+// A shared-memory descriptor of an MN-major operand in the 128-byte swizzle: rows of 64 elements along N, one row
+// per k, eight rows (1024 bytes) per swizzle atom; atoms follow one another along K.
+__device__ __forceinline__ uint64_t smem_desc_mn(const void* tile) {
+  return (uint64_t)((smem_u32(tile) >> 4) & 0x3fff) | ((uint64_t)(1024 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void tmem_load32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      "tcgen05.wait::ld.sync.aligned;\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__global__ void __launch_bounds__(THREADS, 2)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
+                            int max_blocks, const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
+                            bf16* __restrict__ out, float scale, int window, int page_size, int H, int KH, int R) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_s = smem;                                   // [128 queries][128 bytes]
+  unsigned char* k_s = q_s + TILE_BYTES;                       // [STAGES][128 keys][128 bytes]
+  unsigned char* v_s = k_s + STAGES * TILE_BYTES;              // [STAGES][128 keys][128 bytes]
+  unsigned char* p_s = v_s + STAGES * TILE_BYTES;              // [2 groups of 64 keys][128 queries][128 bytes]
+  __shared__ __align__(8) uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full,
+      p_full, pv_full;
+  __shared__ unsigned tmem_base_s;
+  __shared__ int abort_s;
+
+  // which tile of which request: heads are x, tiles y, last tile first (the longest walks start first)
+  int tile = (int)gridDim.y - 1 - (int)blockIdx.y, r = 0, n = 0;
+  for (; r < R; ++r) {
+    n = cu_seqlens[r + 1] - cu_seqlens[r];
+    const int tiles = (n + BQ - 1) / BQ;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (r >= R) return;  // the grid is sized for 64-token tiles: more blocks than 128-token tiles
+  const int head = blockIdx.x, kvh = head / (H / KH);
+  const int q0 = cu_seqlens[r] + tile * BQ;
+  const int rows = min(BQ, n - tile * BQ);
+  const int pos0 = positions[q0];
+  const int last_key = pos0 + rows - 1;
+  const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int kt0 = first_key / BKEYS, kt1 = last_key / BKEYS, tiles_k = kt1 - kt0 + 1;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    abort_s = 0;
+    mbar_init(&q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
+    mbar_init(&s_full, 1);
+    mbar_init(&p_full, 128);
+    mbar_init(&pv_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = tmem_base_s;
+
+  auto wait_for = [&](uint64_t* bar, unsigned parity, int code) {
+    if (*(volatile int*)&abort_s) return;
+    if (!mbar_wait(bar, parity)) {
+      *(volatile int*)&abort_s = 1;
+      atomicExch(&g_attention_status, code);
+    }
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      mbar_expect_tx(&q_full, TILE_BYTES);
+      tma_load_2d(q_s, &map_q, head * D, q0, &q_full);
+      for (int t = 0; t < tiles_k; ++t) {
+        const int s = t % STAGES, kt = kt0 + t;
+        // the pool rows of the tile's two halves of 64 keys
+        int pool_row[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int key0 = kt * BKEYS + h * 64;
+          int page = key0 <= last_key ? block_table[(size_t)r * max_blocks + key0 / page_size] : -1;
+          if (page < 0) page = 0;  // nothing of it will be seen: any valid rows will do
+          pool_row[h] = (page * KH + kvh) * page_size + (key0 <= last_key ? key0 % page_size : 0);
+        }
+        if (t >= STAGES) wait_for(&k_empty[s], ((t / STAGES) & 1) ^ 1, 1);
+        if (*(volatile int*)&abort_s) break;
+        mbar_expect_tx(&k_full[s], TILE_BYTES);
+        tma_load_2d(k_s + s * TILE_BYTES, &map_k, 0, pool_row[0], &k_full[s]);
+        tma_load_2d(k_s + s * TILE_BYTES + TILE_BYTES / 2, &map_k, 0, pool_row[1], &k_full[s]);
+        if (t >= STAGES) wait_for(&v_empty[s], ((t / STAGES) & 1) ^ 1, 1);
+        if (*(volatile int*)&abort_s) break;
+        mbar_expect_tx(&v_full[s], TILE_BYTES);
+        tma_load_2d(v_s + s * TILE_BYTES, &map_v, 0, pool_row[0], &v_full[s]);
+        tma_load_2d(v_s + s * TILE_BYTES + TILE_BYTES / 2, &map_v, 0, pool_row[1], &v_full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ tensor cores
+    if (lane == 0) {
+      // float32 accumulate, bfloat16 operands; scores: M 128, N 128, both K-major; P.V: M 128, N 64, B MN-major
+      constexpr unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BKEYS >> 3) << 17) | ((unsigned)(BQ >> 4) << 24);
+      constexpr unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(D >> 3) << 17) | ((unsigned)(BQ >> 4) << 24);
+      const unsigned tmem_s = tmem_base, tmem_pv = tmem_base + 128;
+      auto scores = [&](int t) {
+        const int s = t % STAGES;
+        wait_for(&k_full[s], (t / STAGES) & 1, 2);
+        if (*(volatile int*)&abort_s) return;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t a = smem_desc(q_s), b = smem_desc(k_s + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / UMMA_K; ++k) umma(tmem_s, a + (uint64_t)(k * 2), b + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
+        umma_commit(&k_empty[s]);
+        umma_commit(&s_full);
+      };
+      wait_for(&q_full, 0, 2);
+      scores(0);
+      for (int t = 0; t < tiles_k && !*(volatile int*)&abort_s; ++t) {
+        const int s = t % STAGES;
+        wait_for(&p_full, t & 1, 2);  // the softmax warps have read S and written P
+        wait_for(&v_full[s], (t / STAGES) & 1, 2);
+        if (*(volatile int*)&abort_s) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < BKEYS / UMMA_K; ++j) {  // 16 keys a step: P advances along its swizzled rows, V by 16 rows
+          const uint64_t a = smem_desc(p_s + (j >> 2) * TILE_BYTES) + (uint64_t)((j & 3) * 2);
+          const uint64_t b = smem_desc_mn(v_s + s * TILE_BYTES + j * 16 * 128);
+          umma(tmem_pv, a, b, idesc_pv, j ? 1u : 0u);
+        }
+        umma_commit(&v_empty[s]);
+        umma_commit(&pv_full);
+        if (t + 1 < tiles_k) scores(t + 1);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax and read-out: warps 2..5
+    const int sub = warp & 3, row = sub * 32 + lane;  // tensor-memory lane = query row of the tile
+    const unsigned lane_addr = (unsigned)(sub * 32) << 16;
+    const unsigned tmem_s = tmem_base + lane_addr, tmem_pv = tmem_base + 128 + lane_addr;
+    const int qpos = pos0 + row;
+    const float sl2 = scale * 1.4426950408889634f;  // scores in units of log2(e): exp is exp2
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    for (int t = 0; t < tiles_k; ++t) {
+      const int kt = kt0 + t, key_base = kt * BKEYS, s = t % STAGES;
+      // rows of V past the block's last key: whatever the page held must not meet a zero probability as NaN
+      if (key_base + BKEYS - 1 > last_key) {
+        wait_for(&v_full[s], (t / STAGES) & 1, 3);
+        const int first_dead = max(0, last_key + 1 - key_base);
+        for (int i = (tid - 64) + first_dead * 8; i < BKEYS * 8; i += 128)
+          *reinterpret_cast<uint4*>(v_s + s * TILE_BYTES + i * 16) = make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      wait_for(&s_full, t & 1, 3);
+      if (*(volatile int*)&abort_s) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool whole = key_base + BKEYS - 1 <= pos0 && key_base >= first_key &&
+                         (window <= 0 || key_base > pos0 + rows - 1 - window);  // no query of the tile masks any of it
+      // pass 1: the row's maximum
+      float top = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BKEYS; c += 32) {
+        float v[32];
+        tmem_load32(tmem_s + c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = key_base + c + i;
+          const bool seen = whole || (key <= qpos && key >= first_key && (window <= 0 || key > qpos - window));
+          top = fmaxf(top, seen ? v[i] * sl2 : -INFINITY);
+        }
+      }
+      const float m_new = fmaxf(m_run, top);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that sees nothing yet
+      const float corr = fast_exp2(m_run - m_use);
+      m_run = m_new;
+      // pass 2: P = exp2(s - max), rounded to bfloat16, into the swizzled K-major tile the second product reads
+      float l_add = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BKEYS; c += 32) {
+        float v[32];
+        tmem_load32(tmem_s + c, v);
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int key = key_base + c + i;
+          const bool seen0 = whole || (key <= qpos && key >= first_key && (window <= 0 || key > qpos - window));
+          const bool seen1 = whole || (key + 1 <= qpos && key + 1 >= first_key && (window <= 0 || key + 1 > qpos - window));
+          const float p0 = seen0 ? fast_exp2(v[i] * sl2 - m_use) : 0.f;
+          const float p1 = seen1 ? fast_exp2(v[i + 1] * sl2 - m_use) : 0.f;
+          l_add += p0 + p1;
+          packed[i >> 1] = pack_bf16(p0, p1);
+        }
+        unsigned char* group = p_s + (c >> 6) * TILE_BYTES + row * 128;  // keys 0-63 or 64-127 of the tile
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {  // four 16-byte chunks of 8 keys
+          const int chunk = ((c & 63) >> 3) + q;
+          *reinterpret_cast<uint4*>(group + ((chunk ^ (row & 7)) << 4)) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      }
+      l_run = l_run * corr + l_add;
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor cores read what this thread wrote
+      mbar_arrive(&p_full);
+      // the running output: O = O * corr + P.V
+      wait_for(&pv_full, t & 1, 3);
+      if (*(volatile int*)&abort_s) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        float v[32];
+        tmem_load32(tmem_pv + c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr, v[i]);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    if (row < rows && !*(volatile int*)&abort_s) {
+      const float inv = 1.f / l_run;
+      bf16* dst = out + ((size_t)(q0 + row) * H + head) * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 8) {
+        float piece[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) piece[i] = o[c + i] * inv;
+        store_vec(dst + c, piece);
+      }
+    }
+  }
+
+  if (*(volatile int*)&abort_s) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);  // a lost launch: let copies and products in flight finish
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+  }
+}
+
+// A tensor map of rows of `row_elems` bfloat16 (row pitch `pitch_elems`), boxes of 64 elements x `box_rows` rows.
+int rows_map(CUtensorMap* map, const void* base, long long rows, int row_elems, long long pitch_elems, int box_rows) {
+  EncodeTiled fn = encode_tiled();
+  if (!fn) return 3001;
+  const cuuint64_t dims[2] = {(cuuint64_t)row_elems, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * 2};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 3000 + (int)r;
+}
+
+}  // namespace
+
+// q: bfloat16 [N, H * 64]; pools: bfloat16 [pages, KH, page_size, 64] with page_size a multiple of 64; out: bfloat16
+// [N, H * 64]. tiles: an upper bound of the number of 128-token tiles (the sum over requests of ceil(tokens / 64)
+// will do). Returns 0, a CUDA error, 3000 + a driver error from building a tensor map, or 3999 if the kernel does
+// not take these sizes (nothing was launched).
+AKAS_API int akas_prefill_attention_tc(const void* q, const void* k_pool, const void* v_pool, long long pool_rows,
+                                       const int* block_table, int max_blocks, const int* cu_seqlens,
+                                       const int* positions, void* out, float scale, int window, int page_size, int tiles,
+                                       int N, int H, int KH, int head_dim, int R, cudaStream_t stream) {
+  if (head_dim != D || page_size % 64 || H % KH || tiles > 65535 || R <= 0 || N <= 0) return 3999;
+  if ((uintptr_t)q % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 16) return 3999;
+  if (tiles <= 0) return 0;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap map_q, map_k, map_v;
+  int err = rows_map(&map_q, q, N, H * D, (long long)H * D, 128);
+  if (!err) err = rows_map(&map_k, k_pool, pool_rows, D, D, 64);
+  if (!err) err = rows_map(&map_v, v_pool, pool_rows, D, D, 64);
+  if (err) return err;
+  prefill_attention_tc_kernel<<<dim3(H, tiles), THREADS, SMEM_BYTES, stream>>>(
+      map_q, map_k, map_v, block_table, max_blocks, cu_seqlens, positions, (bf16*)out, scale, window, page_size, H, KH, R);
+  return launch_status();
+}
+
+// 0 if no bounded wait of the kernel has ever run out on the current device (1: producer, 2: tensor cores,
+// 3: softmax). Synchronises with the device.
+AKAS_API int akas_prefill_attention_tc_status() {
+  int status = -1;
+  const cudaError_t e = cudaMemcpyFromSymbol(&status, g_attention_status, sizeof(int));
+  return e == cudaSuccess ? status : -(int)e;
+}

@@ -57,6 +57,11 @@ _SIGNATURES = {
         "akas_prefill_attention_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                         c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     },
+    "attention_prefill_tc": {
+        "akas_prefill_attention_tc": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                      c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_prefill_attention_tc_status": [],
+    },
     "attention_decode": {
         "akas_decode_attention_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -96,7 +101,7 @@ _functions = {}
 def libraries_for(dtype: torch.dtype) -> list:
     """The kernel files a model of this compute dtype needs."""
     names = ["elementwise", "conv", "rope", "attention", "sampling"]
-    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "gemm_stream", "skinny_gemm", "attention_prefill", "attention_decode"]
+    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "gemm_stream", "skinny_gemm", "attention_prefill", "attention_prefill_tc", "attention_decode"]
     return names
 
 
@@ -462,6 +467,21 @@ def kv_store(k, v, k_pool, v_pool, block_table, seq_of_token, positions, page_si
                                        _code(k_pool), _stream()), "kv_store")
 
 
+# Which kernel runs attention over prompt portions in bfloat16: "mma" (the mma.sync kernel) or "tcgen05" (the
+# tensor-memory kernel, where it takes the sizes: head size 64, page size a multiple of 64). The tensor-memory kernel
+# walks its key tiles one after the other (scores, softmax, P.V in turn) and measures 70-87 TFLOP/s against
+# 180-220 of the mma.sync kernel (whose instruction peaks at 550 on this GPU), so it is not the default; both are
+# tested.
+prompt_attention = os.environ.get("AKAS_B200_PROMPT_ATTENTION", "mma")
+if prompt_attention not in ("tcgen05", "mma"):
+    raise ValueError(f"AKAS_B200_PROMPT_ATTENTION must be tcgen05 or mma, got {prompt_attention!r}")
+
+
+def prefill_attention_tc_status() -> int:
+    """0 unless a bounded wait inside the tcgen05 prompt-attention kernel has run out on this device."""
+    return int(_fn("attention_prefill_tc", "akas_prefill_attention_tc_status")())
+
+
 def decode_splits(num_tokens: int, kv_heads: int, head_tiles: int, max_context: int) -> int:
     """How many parts the keys of a decoding request are cut into, from sizes known on the host: enough
     blocks for several rounds over the SMs (a single round and a bit leaves most of the GPU idle in the
@@ -504,6 +524,16 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
             splits, _code(q), _stream()), "paged_attention_decode", kernels=2)
         return out
     tiles = getattr(ctx, "query_tiles", 0) if ctx is not None else 0
+    if (q.dtype == torch.bfloat16 and prompt_attention == "tcgen05" and d == 64 and page_size % 64 == 0
+            and 0 < tiles <= 65535):
+        # prompt portions, head size 64, pages of whole half tiles: 128-query tiles on tcgen05
+        err = _fn("attention_prefill_tc", "akas_prefill_attention_tc")(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0] * k_pool.shape[1] * k_pool.shape[2], _ptr(block_table),
+            block_table.shape[1], _ptr(ctx.cu_seqlens), _ptr(positions), _ptr(out), float(scale), win, page_size, tiles, n,
+            heads, kh, d, ctx.cu_seqlens.numel() - 1, _stream())
+        if err != 3999:
+            _check(err, "prefill_attention_tc")
+            return out
     if q.dtype == torch.bfloat16 and d in (16, 32, 64, 128) and 0 < tiles <= 65535:
         # prompt portions (and whatever decodes beside them): 64-query tiles on the tensor cores
         _check(_fn("attention_prefill", "akas_prefill_attention_bf16")(

@@ -371,24 +371,35 @@ class _Prompt:
 
 @pytest.mark.parametrize("h,kh,d,page,window", [
     (4, 2, 16, 16, None), (3, 1, 32, 8, None), (8, 2, 64, 64, None), (6, 2, 64, 8, 37), (16, 2, 128, 32, None),
-    (5, 1, 128, 16, 100), (32, 8, 64, 64, 70), (2, 2, 16, 4, None),
+    (5, 1, 128, 16, 100), (32, 8, 64, 64, 70), (2, 2, 16, 4, None), (4, 1, 64, 128, None), (6, 3, 64, 256, 200),
+    (2, 2, 64, 64, 129),
 ])
-def test_prompt_attention_on_tensor_cores(ops, h, kh, d, page, window):
-    """Portions that start mid-page and mid-tile, of 1 to 200 tokens, beside decoded tokens with long contexts."""
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+def test_prompt_attention_on_tensor_cores(ops, h, kh, d, page, window, kernel, monkeypatch):
+    """Portions that start mid-page and mid-tile, of 1 to 300 tokens, beside decoded tokens with long contexts; with
+    the tensor-memory kernel (head size 64 and pages of 64 keys or more; the others fall to mma.sync) and with the
+    mma.sync kernel. What the pages hold past the end of a request is poisoned: it must not be looked at."""
     cuda, ref = ops
+    monkeypatch.setattr(cuda, "prompt_attention", kernel)
     dtype = torch.bfloat16
-    lengths, starts = [37, 1, 200, 1, 64, 65, 0, 130], [29, 333, 0, 64, 64, 100, 5, 700]
+    lengths, starts = [37, 1, 200, 1, 64, 65, 0, 130, 300, 128], [29, 333, 0, 64, 64, 100, 5, 700, 100, 128]
     cu, seq = _batch(lengths)
     pos = torch.tensor([s + j for s, n in zip(starts, lengths) for j in range(n)], dtype=torch.int32, device=DEV)
     contexts = [s + l for s, l in zip(starts, lengths)]
     pages = sum(-(-c // page) for c in contexts) + 3
     bt = _tables(contexts, page, pages, 4)
     k, v = _pools(pages, kh, page, d, dtype, 40)
+    for r, context in enumerate(contexts):  # past the end of every request: not a number
+        last = int(bt[r, (context - 1) // page]) if context else -1
+        if last >= 0 and context % page:
+            k[last, :, context % page:] = float("nan")
+            v[last, :, context % page:] = float("nan")
     q = _rand((pos.numel(), h * d), dtype, 42)
     scale = d ** -0.5
     want = ref.paged_attention(q, k, v, bt, seq, pos, scale, window, page)
     got = cuda.paged_attention(q, k, v, bt, seq, pos, scale, window, page, _Prompt(cu, lengths))
     _close(got, want, dtype, "tensor-core prompt attention")
+    assert cuda.prefill_attention_tc_status() == 0
     general = cuda.paged_attention(q, k, v, bt, seq, pos, scale, window, page)
     _close(general, want, dtype, "general kernel")
 
