@@ -17,10 +17,11 @@
 //             form P = exp2(s - max), which it rounds to bfloat16 and writes to shared memory in the swizzled
 //             K-major layout the second product reads; then it reads its row of PV and keeps the running
 //             output in registers: O = O * exp2(old max - new max) + PV. Softmax is float32 throughout.
-// A block's tiles follow one another strictly (scores, softmax, P.V): the tensor cores idle while the softmax warps
-// work and the other way round, and at 113 KB of shared memory a second block does not always fit beside it. As
-// it stands the kernel is correct and slower than the mma.sync kernel of attention_prefill.cu (measured 70-87
-// TFLOP/s against 180-220); it is selected with AKAS_B200_PROMPT_ATTENTION=tcgen05.
+// A block's tiles follow one another (scores, softmax, P.V; only the next tile's scores run ahead), so its tensor
+// cores idle while its softmax warps work and the other way round; two blocks fit an SM (112 KB of shared memory and
+// 256 columns of tensor memory each, no static shared memory) and fill each other's gaps. The softmax warps are
+// bound by the exponentials (128 a row and tile on the special-function units). Measured on the 1.2B shape: 222
+// TFLOP/s at 2,048 tokens and 392 at 8,192, against 182 and 220 of the mma.sync kernel of attention_prefill.cu.
 //
 // Keys past a query's position are masked by position, not by content: pages past the end of a request are
 // not fetched (a valid page stands in), and rows of V past the block's last key are zeroed in shared memory so
@@ -38,7 +39,7 @@ namespace {
 
 constexpr int BQ = 128, BKEYS = 128, D = 64, THREADS = 192, STAGES = 2;
 constexpr int TILE_BYTES = 128 * 128;  // 128 rows of 64 bfloat16: Q, one stage of K, one of V
-constexpr int SMEM_BYTES = 1024 + TILE_BYTES * (1 + 2 * STAGES) + 2 * TILE_BYTES;  // + P: 128 rows x 128 keys
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 2 * TILE_BYTES + 256;  // tiles, P (128 x 128 keys), barriers
 constexpr int TMEM_COLS = 256;  // S: columns 0..127, PV: 128..191
 
 __device__ int g_attention_status = 0;
@@ -68,16 +69,18 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                             int max_blocks, const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
                             bf16* __restrict__ out, float scale, int window, int page_size, int H, int KH, int R) {
-  extern __shared__ unsigned char smem_dyn[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  // The block has no static shared memory, so the dynamic array starts the block's window, 1024-byte aligned (the
+  // swizzled tiles need that; it is checked below): with no bytes lost to alignment, two blocks fit an SM.
+  extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_s = smem;                                   // [128 queries][128 bytes]
   unsigned char* k_s = q_s + TILE_BYTES;                       // [STAGES][128 keys][128 bytes]
   unsigned char* v_s = k_s + STAGES * TILE_BYTES;              // [STAGES][128 keys][128 bytes]
   unsigned char* p_s = v_s + STAGES * TILE_BYTES;              // [2 groups of 64 keys][128 queries][128 bytes]
-  __shared__ __align__(8) uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full,
-      p_full, pv_full;
-  __shared__ unsigned tmem_base_s;
-  __shared__ int abort_s;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * TILE_BYTES);
+  uint64_t &q_full = bars[0], &s_full = bars[1], &p_full = bars[2], &pv_full = bars[3];
+  uint64_t *k_full = bars + 4, *k_empty = bars + 6, *v_full = bars + 8, *v_empty = bars + 10;  // STAGES of each
+  unsigned& tmem_base_s = *reinterpret_cast<unsigned*>(bars + 12);
+  int& abort_s = *reinterpret_cast<int*>(bars + 13);
 
   // which tile of which request: heads are x, tiles y, last tile first (the longest walks start first)
   int tile = (int)gridDim.y - 1 - (int)blockIdx.y, r = 0, n = 0;
@@ -88,6 +91,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tile -= tiles;
   }
   if (r >= R) return;  // the grid is sized for 64-token tiles: more blocks than 128-token tiles
+  if (smem_u32(smem) & 1023u) {  // never seen; the tiles' swizzle would be wrong
+    if (threadIdx.x == 0) atomicExch(&g_attention_status, 9);
+    return;
+  }
   const int head = blockIdx.x, kvh = head / (H / KH);
   const int q0 = cu_seqlens[r] + tile * BQ;
   const int rows = min(BQ, n - tile * BQ);
@@ -204,7 +211,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float o[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;  // the running maximum is kept in units of the raw scores
     for (int t = 0; t < tiles_k; ++t) {
       const int kt = kt0 + t, key_base = kt * BKEYS, s = t % STAGES;
       // rows of V past the block's last key: whatever the page held must not meet a zero probability as NaN
@@ -220,39 +227,60 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool whole = key_base + BKEYS - 1 <= pos0 && key_base >= first_key &&
                          (window <= 0 || key_base > pos0 + rows - 1 - window);  // no query of the tile masks any of it
-      // pass 1: the row's maximum
+      // Two passes over the row of S: its maximum (of the raw scores: the scale is positive), then
+      // P = exp2(s * scale - max * scale), rounded to bfloat16, into the swizzled K-major tile the second product
+      // reads. Tiles that no query of the block masks (all but the last one or two) take the short path.
       float top = -INFINITY;
+      if (whole) {
 #pragma unroll 1
-      for (int c = 0; c < BKEYS; c += 32) {
-        float v[32];
-        tmem_load32(tmem_s + c, v);
+        for (int c = 0; c < BKEYS; c += 32) {
+          float v[32];
+          tmem_load32(tmem_s + c, v);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key_base + c + i;
-          const bool seen = whole || (key <= qpos && key >= first_key && (window <= 0 || key > qpos - window));
-          top = fmaxf(top, seen ? v[i] * sl2 : -INFINITY);
+          for (int i = 0; i < 32; ++i) top = fmaxf(top, v[i]);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BKEYS; c += 32) {
+          float v[32];
+          tmem_load32(tmem_s + c, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key_base + c + i;
+            const bool seen = key <= qpos && key >= first_key && (window <= 0 || key > qpos - window);
+            top = fmaxf(top, seen ? v[i] : -INFINITY);
+          }
         }
       }
-      const float m_new = fmaxf(m_run, top);
+      const float m_new = fmaxf(m_run, top);                 // raw units
       const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that sees nothing yet
-      const float corr = fast_exp2(m_run - m_use);
+      const float corr = fast_exp2((m_run - m_use) * sl2);
+      const float bias = -m_use * sl2;
       m_run = m_new;
-      // pass 2: P = exp2(s - max), rounded to bfloat16, into the swizzled K-major tile the second product reads
       float l_add = 0.f;
 #pragma unroll 1
       for (int c = 0; c < BKEYS; c += 32) {
         float v[32];
         tmem_load32(tmem_s + c, v);
         uint32_t packed[16];
+        if (whole) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int key = key_base + c + i;
-          const bool seen0 = whole || (key <= qpos && key >= first_key && (window <= 0 || key > qpos - window));
-          const bool seen1 = whole || (key + 1 <= qpos && key + 1 >= first_key && (window <= 0 || key + 1 > qpos - window));
-          const float p0 = seen0 ? fast_exp2(v[i] * sl2 - m_use) : 0.f;
-          const float p1 = seen1 ? fast_exp2(v[i + 1] * sl2 - m_use) : 0.f;
-          l_add += p0 + p1;
-          packed[i >> 1] = pack_bf16(p0, p1);
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(v[i], sl2, bias)), p1 = fast_exp2(fmaf(v[i + 1], sl2, bias));
+            l_add += p0 + p1;
+            packed[i >> 1] = pack_bf16(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int key = key_base + c + i;
+            const bool seen0 = key <= qpos && key >= first_key && (window <= 0 || key > qpos - window);
+            const bool seen1 = key + 1 <= qpos && key + 1 >= first_key && (window <= 0 || key + 1 > qpos - window);
+            const float p0 = seen0 ? fast_exp2(fmaf(v[i], sl2, bias)) : 0.f;
+            const float p1 = seen1 ? fast_exp2(fmaf(v[i + 1], sl2, bias)) : 0.f;
+            l_add += p0 + p1;
+            packed[i >> 1] = pack_bf16(p0, p1);
+          }
         }
         unsigned char* group = p_s + (c >> 6) * TILE_BYTES + row * 128;  // keys 0-63 or 64-127 of the tile
 #pragma unroll

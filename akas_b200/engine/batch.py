@@ -50,6 +50,7 @@ class StepContext:
     max_context: int  # largest position + 1 in the batch
     decode_only: bool  # every request brings exactly one token
     query_tiles: int = 0  # sum over requests of ceil(tokens / 64): the grid of the prompt-attention kernel
+    query_tiles_wide: int = 0  # the same with 128-token tiles (the tensor-memory kernel's)
     memo: Dict = field(default_factory=dict)  # per-step results shared between layers (rotary tables)
 
     def block_table(self, group: int) -> torch.Tensor:

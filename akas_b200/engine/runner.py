@@ -161,6 +161,7 @@ class ModelRunner:
             if previous is not None:
                 self.ops.take_tokens(ctx.token_ids, dev[lay.token_src : lay.token_src + lay.n], previous)
             ctx.query_tiles = sum(-(-len(e.tokens) // 64) for e in entries)
+            ctx.query_tiles_wide = sum(-(-len(e.tokens) // 128) for e in entries)
             logits = self.model.forward(ctx, self.cache.views)
         for e in entries:
             self.cache.advance(e.request, len(e.tokens))
@@ -276,6 +277,7 @@ class _DecodeGraph:
                 ctx = runner._context(self.dev, self.layout, max(self.lengths), runner.config.context,
                                       all(n == 1 for n in self.lengths))
                 ctx.query_tiles = sum(-(-n // 64) for n in self.lengths)
+                ctx.query_tiles_wide = sum(-(-n // 128) for n in self.lengths)
             ctx.memo["captured"] = True
             stream = torch.cuda.Stream(device=runner.device)
             stream.wait_stream(torch.cuda.current_stream(runner.device))

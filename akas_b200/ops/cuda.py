@@ -467,14 +467,13 @@ def kv_store(k, v, k_pool, v_pool, block_table, seq_of_token, positions, page_si
                                        _code(k_pool), _stream()), "kv_store")
 
 
-# Which kernel runs attention over prompt portions in bfloat16: "mma" (the mma.sync kernel) or "tcgen05" (the
-# tensor-memory kernel, where it takes the sizes: head size 64, page size a multiple of 64). The tensor-memory kernel
-# walks its key tiles one after the other (scores, softmax, P.V in turn) and measures 70-87 TFLOP/s against
-# 180-220 of the mma.sync kernel (whose instruction peaks at 550 on this GPU), so it is not the default; both are
-# tested.
-prompt_attention = os.environ.get("AKAS_B200_PROMPT_ATTENTION", "mma")
-if prompt_attention not in ("tcgen05", "mma"):
-    raise ValueError(f"AKAS_B200_PROMPT_ATTENTION must be tcgen05 or mma, got {prompt_attention!r}")
+# Which kernel runs attention over prompt portions in bfloat16: "mma" (the mma.sync kernel, 64-query tiles),
+# "tcgen05" (the tensor-memory kernel, 128-query tiles, where it takes the sizes: head size 64, page size a multiple
+# of 64) or "auto": the tensor-memory kernel when the step's requests mostly bring more than 64 tokens. Measured on
+# the 1.2B shape: 222 against 182 TFLOP/s at 2,048 tokens, 392 against 220 at 8,192 (mma.sync peaks at 550 here).
+prompt_attention = os.environ.get("AKAS_B200_PROMPT_ATTENTION", "auto")
+if prompt_attention not in ("auto", "tcgen05", "mma"):
+    raise ValueError(f"AKAS_B200_PROMPT_ATTENTION must be auto, tcgen05 or mma, got {prompt_attention!r}")
 
 
 def prefill_attention_tc_status() -> int:
@@ -524,8 +523,11 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
             splits, _code(q), _stream()), "paged_attention_decode", kernels=2)
         return out
     tiles = getattr(ctx, "query_tiles", 0) if ctx is not None else 0
-    if (q.dtype == torch.bfloat16 and prompt_attention == "tcgen05" and d == 64 and page_size % 64 == 0
-            and 0 < tiles <= 65535):
+    wide = getattr(ctx, "query_tiles_wide", 0) if ctx is not None else 0
+    # A 128-query tile of the tensor-memory kernel costs about what a 64-query tile of the mma.sync kernel costs
+    # (measured: 1.8 times the throughput): it pays when requests bring more than 64 tokens, not for single tokens.
+    tensor_memory = prompt_attention == "tcgen05" or (prompt_attention == "auto" and 0 < wide and wide <= 0.9 * tiles)
+    if q.dtype == torch.bfloat16 and tensor_memory and d == 64 and page_size % 64 == 0 and 0 < tiles <= 65535:
         # prompt portions, head size 64, pages of whole half tiles: 128-query tiles on tcgen05
         err = _fn("attention_prefill_tc", "akas_prefill_attention_tc")(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0] * k_pool.shape[1] * k_pool.shape[2], _ptr(block_table),
