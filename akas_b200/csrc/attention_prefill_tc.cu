@@ -12,11 +12,13 @@
 //             softmax warps have written P, PV = P.V (eight tcgen05.mma, M 128, N 64, K 16; V is read as it
 //             lies in the pages, rows of keys with the head's channels contiguous: an MN-major B operand).
 //             The scores of the next tile are issued right behind P.V of the current one.
-//   warps 2-5 softmax and read-out: thread = query row = tensor-memory lane. Per tile it reads its row of S
-//             (tcgen05.ld) twice: once for the row maximum (scale and causal / window mask applied), once to
-//             form P = exp2(s - max), which it rounds to bfloat16 and writes to shared memory in the swizzled
-//             K-major layout the second product reads; then it reads its row of PV and keeps the running
-//             output in registers: O = O * exp2(old max - new max) + PV. Softmax is float32 throughout.
+//   warps 2-9 softmax and read-out: two threads per query row (= tensor-memory lane), warps 2-5 for the tile's
+//             keys 0-63 and output channels 0-31, warps 6-9 for keys 64-127 and channels 32-63. Per tile a
+//             thread reads its half of the row of S (tcgen05.ld) twice: once for the maximum (causal / window
+//             mask applied; the two halves meet through shared memory), once to form P = exp2(s - max), which
+//             it rounds to bfloat16 and writes to shared memory in the swizzled K-major layout the second
+//             product reads; then it reads its channels of PV and keeps the running output in registers:
+//             O = O * exp2(old max - new max) + PV. Softmax is float32 throughout.
 // A block's tiles follow one another (scores, softmax, P.V; only the next tile's scores run ahead), so its tensor
 // cores idle while its softmax warps work and the other way round; two blocks fit an SM (112 KB of shared memory and
 // 256 columns of tensor memory each, no static shared memory) and fill each other's gaps. The softmax warps are
@@ -37,9 +39,10 @@ using namespace akas::tc;
 
 namespace {
 
-constexpr int BQ = 128, BKEYS = 128, D = 64, THREADS = 192, STAGES = 2;
+constexpr int BQ = 128, BKEYS = 128, D = 64, THREADS = 320, STAGES = 2;
 constexpr int TILE_BYTES = 128 * 128;  // 128 rows of 64 bfloat16: Q, one stage of K, one of V
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 2 * TILE_BYTES + 256;  // tiles, P (128 x 128 keys), barriers
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 2 * TILE_BYTES + 128 + 512;  // tiles, P, barriers, exchange
+static_assert(2 * (SMEM_BYTES + 1024) <= 228 * 1024, "two blocks an SM");
 constexpr int TMEM_COLS = 256;  // S: columns 0..127, PV: 128..191
 
 __device__ int g_attention_status = 0;
@@ -81,6 +84,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint64_t *k_full = bars + 4, *k_empty = bars + 6, *v_full = bars + 8, *v_empty = bars + 10;  // STAGES of each
   unsigned& tmem_base_s = *reinterpret_cast<unsigned*>(bars + 12);
   int& abort_s = *reinterpret_cast<int*>(bars + 13);
+  bf16* exchange = reinterpret_cast<bf16*>(bars + 16);  // [2 halves of a row][128 rows]: the halves' maxima meet here
 
   // which tile of which request: heads are x, tiles y, last tile first (the longest walks start first)
   int tile = (int)gridDim.y - 1 - (int)blockIdx.y, r = 0, n = 0;
@@ -112,7 +116,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
     mbar_init(&s_full, 1);
-    mbar_init(&p_full, 128);
+    mbar_init(&p_full, 256);
     mbar_init(&pv_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -202,48 +206,45 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax and read-out: warps 2..5
+    // ------------------------------------------------------------------ softmax and read-out: warps 2..9
     const int sub = warp & 3, row = sub * 32 + lane;  // tensor-memory lane = query row of the tile
+    const int half = (warp - 2) >> 2;                 // which 64 keys of a tile, which 32 output channels
     const unsigned lane_addr = (unsigned)(sub * 32) << 16;
-    const unsigned tmem_s = tmem_base + lane_addr, tmem_pv = tmem_base + 128 + lane_addr;
+    const unsigned tmem_s = tmem_base + lane_addr + half * 64, tmem_pv = tmem_base + 128 + lane_addr + half * 32;
     const int qpos = pos0 + row;
     const float sl2 = scale * 1.4426950408889634f;  // scores in units of log2(e): exp is exp2
-    float o[D];
+    float o[32];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    for (int i = 0; i < 32; ++i) o[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;  // the running maximum is kept in units of the raw scores
+    auto meet = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(2 + sub) : "memory"); };  // the two warps of these rows
     for (int t = 0; t < tiles_k; ++t) {
-      const int kt = kt0 + t, key_base = kt * BKEYS, s = t % STAGES;
+      const int kt = kt0 + t, key_base = kt * BKEYS + half * 64, s = t % STAGES;
       // rows of V past the block's last key: whatever the page held must not meet a zero probability as NaN
-      if (key_base + BKEYS - 1 > last_key) {
+      if (kt * BKEYS + BKEYS - 1 > last_key) {
         wait_for(&v_full[s], (t / STAGES) & 1, 3);
-        const int first_dead = max(0, last_key + 1 - key_base);
-        for (int i = (tid - 64) + first_dead * 8; i < BKEYS * 8; i += 128)
+        const int first_dead = max(0, last_key + 1 - kt * BKEYS);
+        for (int i = (tid - 64) + first_dead * 8; i < BKEYS * 8; i += 256)
           *reinterpret_cast<uint4*>(v_s + s * TILE_BYTES + i * 16) = make_uint4(0u, 0u, 0u, 0u);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      wait_for(&s_full, t & 1, 3);
-      if (*(volatile int*)&abort_s) break;
+      wait_for(&s_full, t & 1, 3);  // after a wait has run out nobody waits any more, but every thread still walks
+                                    // all tiles: the two warps of a row meet at a barrier in each
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool whole = key_base + BKEYS - 1 <= pos0 && key_base >= first_key &&
-                         (window <= 0 || key_base > pos0 + rows - 1 - window);  // no query of the tile masks any of it
-      // Two passes over the row of S: its maximum (of the raw scores: the scale is positive), then
-      // P = exp2(s * scale - max * scale), rounded to bfloat16, into the swizzled K-major tile the second product
-      // reads. Tiles that no query of the block masks (all but the last one or two) take the short path.
+      const bool whole = kt * BKEYS + BKEYS - 1 <= pos0 && kt * BKEYS >= first_key &&
+                         (window <= 0 || kt * BKEYS > pos0 + rows - 1 - window);  // no query of the tile masks any of it
+      // Two passes over this thread's half of the row of S: its maximum (of the raw scores: the scale is positive),
+      // then P = exp2(s * scale - max * scale), rounded to bfloat16, into the swizzled K-major tile the second
+      // product reads. Tiles that no query of the block masks (all but the last one or two) take the short path.
       float top = -INFINITY;
-      if (whole) {
 #pragma unroll 1
-        for (int c = 0; c < BKEYS; c += 32) {
-          float v[32];
-          tmem_load32(tmem_s + c, v);
+      for (int c = 0; c < 64; c += 32) {
+        float v[32];
+        tmem_load32(tmem_s + c, v);
+        if (whole) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) top = fmaxf(top, v[i]);
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BKEYS; c += 32) {
-          float v[32];
-          tmem_load32(tmem_s + c, v);
+        } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int key = key_base + c + i;
@@ -252,6 +253,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           }
         }
       }
+      // The halves' maxima meet rounded up to bfloat16 (the exchange has 512 bytes): the shift of the softmax need
+      // not be the exact maximum, only the same for both halves and not below any score.
+      const bf16 rounded = __float2bfloat16_ru(top);
+      meet();  // the other half has read the last tile's value
+      exchange[half * 128 + row] = rounded;
+      meet();
+      top = fmaxf(__bfloat162float(rounded), __bfloat162float(exchange[(half ^ 1) * 128 + row]));
       const float m_new = fmaxf(m_run, top);                 // raw units
       const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that sees nothing yet
       const float corr = fast_exp2((m_run - m_use) * sl2);
@@ -259,7 +267,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       m_run = m_new;
       float l_add = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < BKEYS; c += 32) {
+      for (int c = 0; c < 64; c += 32) {
         float v[32];
         tmem_load32(tmem_s + c, v);
         uint32_t packed[16];
@@ -282,10 +290,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             packed[i >> 1] = pack_bf16(p0, p1);
           }
         }
-        unsigned char* group = p_s + (c >> 6) * TILE_BYTES + row * 128;  // keys 0-63 or 64-127 of the tile
+        unsigned char* group = p_s + half * TILE_BYTES + row * 128;  // keys 0-63 or 64-127 of the tile
 #pragma unroll
         for (int q = 0; q < 4; ++q) {  // four 16-byte chunks of 8 keys
-          const int chunk = ((c & 63) >> 3) + q;
+          const int chunk = (c >> 3) + q;
           *reinterpret_cast<uint4*>(group + ((chunk ^ (row & 7)) << 4)) =
               make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
         }
@@ -294,24 +302,27 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor cores read what this thread wrote
       mbar_arrive(&p_full);
-      // the running output: O = O * corr + P.V
+      // the running output: O = O * corr + P.V, this thread's 32 channels
       wait_for(&pv_full, t & 1, 3);
-      if (*(volatile int*)&abort_s) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c = 0; c < D; c += 32) {
+      {
         float v[32];
-        tmem_load32(tmem_pv + c, v);
+        tmem_load32(tmem_pv, v);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr, v[i]);
+        for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], corr, v[i]);
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
+    // the row's sum: both halves, through the Q tile's memory, which no product reads any more
+    float* sums = reinterpret_cast<float*>(q_s);
+    sums[half * 128 + row] = l_run;
+    meet();
+    l_run += sums[(half ^ 1) * 128 + row];
     if (row < rows && !*(volatile int*)&abort_s) {
       const float inv = 1.f / l_run;
-      bf16* dst = out + ((size_t)(q0 + row) * H + head) * D;
+      bf16* dst = out + ((size_t)(q0 + row) * H + head) * D + half * 32;
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
+      for (int c = 0; c < 32; c += 8) {
         float piece[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) piece[i] = o[c + i] * inv;
