@@ -16,7 +16,7 @@ import traces
 
 # largest |difference| over largest |reference logit|, per dtype
 TOL = {"float32": 2e-5, "bfloat16": 4e-2}
-LENGTHS = {"a": [1, 40, 33, 70, 17, 100, 64, 129], "b": [70, 1, 5, 96, 48, 130, 9]}
+LENGTHS = {"a": [1, 40, 33, 70, 17, 100, 64, 129], "b": [70, 1, 5, 96, 48, 130, 9], "c": [300, 65, 1, 129, 260, 40]}
 
 
 def _runner(folder, dtype, device, page, max_tokens, ops=None, max_requests=4, context=None):
@@ -29,7 +29,7 @@ def _runner(folder, dtype, device, page, max_tokens, ops=None, max_requests=4, c
 
 
 def _setup(key, dtype, tmp_path):
-    folder = tiny.make_folder(tiny.CONFIGS[key], seed=11 if key == "a" else 12, dtype=dtype, folder=tmp_path / key)
+    folder = tiny.make_folder(tiny.CONFIGS[key], seed={"a": 11, "b": 12, "c": 13}[key], dtype=dtype, folder=tmp_path / key)
     cfg, w = plain.load_folder(folder)
     reqs = {f"r{i}": p for i, p in enumerate(tiny.prompts(cfg["vocab_size"], LENGTHS[key], seed=5))}
     want = {rid: plain.forward(cfg, w, toks).numpy() for rid, toks in reqs.items()}
@@ -73,7 +73,7 @@ def test_replay_host_logic_on_cpu(key, tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["a", "b"])
+@pytest.mark.parametrize("key", ["a", "b", "c"])
 @pytest.mark.parametrize("mode", MODES)
 def test_replay_gpu(key, dtype, mode, tmp_path):
     _run_modes(key, dtype, "cuda:0", None, tmp_path, [mode])
@@ -96,7 +96,7 @@ def test_ways_of_cutting_agree_with_each_other(dtype, tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["a", "b"])
+@pytest.mark.parametrize("key", ["a", "b", "c"])
 def test_captured_steps_agree_with_the_plain_model(key, dtype, tmp_path):
     """With graphs on: the same traces, so that single-token steps replay the captured decode graphs, and a trace of
     equal portions (two requests side by side, ten tokens each per step), whose step shape repeats and is captured
