@@ -215,6 +215,8 @@ class CacheManager:
     def reserve(self, request, tokens: int) -> None:
         """Takes pages in every group for the next ``tokens`` positions; all groups or none."""
         req = self._requests[request]
+        if req.length + tokens <= req.reserved:
+            return  # already covered (the scheduler reserves when it plans, the step function when it runs)
         if req.length + tokens > self.context:
             raise ValueError(f"request {request!r}: {req.length + tokens} tokens exceed the context of {self.context}")
         need = self.pages_needed(request, tokens)

@@ -66,19 +66,47 @@ AKAS_API int akas_gemm_bf16(const void* x, const void* w, void* y, int N, int O,
       const cublasStatus_t st = cublasLtCreate(&g_handle);
       if (st != CUBLAS_STATUS_SUCCESS) return 1000 + (int)st;
     }
-    const auto key = std::make_tuple(N, O, K, out_f32, (size_t)workspace_bytes);
+    // The library's choice of algorithm is looked up once per shape. A serving step brings any number of tokens, so
+    // beyond 256 tokens the choice is made for the count rounded up to a multiple of 256 and reused for every count
+    // in that range (the look-up costs about as much as a short product runs).
+    const int planned = N <= 256 ? N : (N + 255) / 256 * 256;
+    const auto key = std::make_tuple(planned, O, K, out_f32, (size_t)workspace_bytes);
     auto it = g_plans.find(key);
     if (it == g_plans.end()) {
       Plan fresh;
-      const int err = make_plan(fresh, N, O, K, out_f32, (size_t)workspace_bytes);
+      const int err = make_plan(fresh, planned, O, K, out_f32, (size_t)workspace_bytes);
       if (err) return err;
       it = g_plans.emplace(key, fresh).first;
     }
     plan = &it->second;
   }
   const float alpha = 1.f, beta = accumulate ? 1.f : 0.f;
-  const cublasStatus_t st = cublasLtMatmul(g_handle, plan->op, &alpha, w, plan->a, x, plan->b, &beta, y, plan->c, y,
-                                           plan->c, &plan->algo, workspace, (size_t)workspace_bytes, stream);
+  cublasLtMatrixLayout_t b = plan->b, c = plan->c;
+  const bool other_count = N > 256 && N % 256 != 0;  // the plan's layouts are for the rounded count
+  if (other_count) {
+    if (cublasLtMatrixLayoutCreate(&b, CUDA_R_16BF, K, N, K) != CUBLAS_STATUS_SUCCESS) return 1000;
+    if (cublasLtMatrixLayoutCreate(&c, out_f32 ? CUDA_R_32F : CUDA_R_16BF, O, N, O) != CUBLAS_STATUS_SUCCESS) {
+      cublasLtMatrixLayoutDestroy(b);
+      return 1000;
+    }
+  }
+  cublasStatus_t st = cublasLtMatmul(g_handle, plan->op, &alpha, w, plan->a, x, b, &beta, y, c, y, c, &plan->algo, workspace,
+                                     (size_t)workspace_bytes, stream);
+  if (other_count) {
+    cublasLtMatrixLayoutDestroy(b);
+    cublasLtMatrixLayoutDestroy(c);
+    if (st != CUBLAS_STATUS_SUCCESS) {  // the algorithm does not take this count after all: look it up exactly
+      Plan exact;
+      const int err = make_plan(exact, N, O, K, out_f32, (size_t)workspace_bytes);
+      if (err) return err;
+      st = cublasLtMatmul(g_handle, exact.op, &alpha, w, exact.a, x, exact.b, &beta, y, exact.c, y, exact.c, &exact.algo,
+                          workspace, (size_t)workspace_bytes, stream);
+      cublasLtMatrixLayoutDestroy(exact.a);
+      cublasLtMatrixLayoutDestroy(exact.b);
+      cublasLtMatrixLayoutDestroy(exact.c);
+      cublasLtMatmulDescDestroy(exact.op);
+    }
+  }
   if (st != CUBLAS_STATUS_SUCCESS) return 1000 + (int)st;
   return 0;
 }

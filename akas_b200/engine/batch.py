@@ -97,42 +97,47 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntr
     slots = host[layout.slots : layout.slots + r]
     rows = host[layout.logit_rows : layout.logit_rows + max(layout.m, 1)]
     max_blocks = cache.max_blocks
-    at = 0
-    row_at = 0
-    max_q = max_ctx = 0
-    for i, e in enumerate(entries):
-        k = len(e.tokens)
-        start = cache.length(e.request)
-        tok[at : at + k] = e.tokens if tokens is None else tokens[i]
-        src[at : at + k] = -1
-        if e.source >= 0:
-            if k != 1:
-                raise ValueError("only a single token can come from the step before")
-            src[at] = e.source
-        pos[at : at + k] = np.arange(start, start + k, dtype=np.int32)
-        seq[at : at + k] = i
-        cu[i] = at
-        slots[i] = cache.slot(e.request)
-        for w in e.want:
-            rows[row_at] = at + w
-            row_at += 1
+    live = len(entries)
+    max_q = max_ctx = at = 0
+    if live:
+        # whole arrays at once: a step may hold hundreds of requests, and a statement per request adds up
+        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=live)
+        starts = np.fromiter((cache.length(e.request) for e in entries), dtype=np.int64, count=live)
+        first = np.zeros(live + 1, dtype=np.int64)
+        np.cumsum(counts, out=first[1:])
+        at = int(first[live])
+        if tokens is None:
+            tokens = [np.asarray(e.tokens, dtype=np.int64) for e in entries]
+        tok[:at] = np.concatenate(tokens) if live > 1 else tokens[0]
+        owner = np.repeat(np.arange(live, dtype=np.int64), counts)
+        seq[:at] = owner
+        pos[:at] = np.arange(at, dtype=np.int64) + (starts - first[:live])[owner]
+        cu[:live] = first[:live]
+        slots[:live] = np.fromiter((cache.slot(e.request) for e in entries), dtype=np.int64, count=live)
+        src[:at] = -1
+        for i, e in enumerate(entries):
+            if e.source >= 0:
+                if counts[i] != 1:
+                    raise ValueError("only a single token can come from the step before")
+                src[first[i]] = e.source
+        wanted = [int(first[i]) + w for i, e in enumerate(entries) for w in e.want]
+        rows[: len(wanted)] = wanted
         for g, offset in enumerate(layout.tables):
-            blocks = cache.blocks(e.request, g)
-            row = host[offset + i * max_blocks : offset + (i + 1) * max_blocks]
-            row[: len(blocks)] = blocks
-            row[len(blocks) :] = -1
-        at += k
-        max_q = max(max_q, k)
-        max_ctx = max(max_ctx, start + k)
+            table = host[offset : offset + live * max_blocks].reshape(live, max_blocks)
+            table[:] = -1
+            for i, e in enumerate(entries):
+                blocks = cache.blocks(e.request, g)
+                table[i, : len(blocks)] = blocks
+        max_q = int(counts.max())
+        max_ctx = int((starts + counts).max())
     cu[len(entries)] = at
     if pad_to:
         tok[at:n] = 0
         src[at:n] = -1
         pos[at:n] = 0
         seq[at:n] = -1
-        for i in range(len(entries), r):
-            cu[i + 1] = at
-            slots[i] = -1
-            for offset in layout.tables:
-                host[offset + i * max_blocks : offset + (i + 1) * max_blocks] = -1
+        cu[live + 1 : r + 1] = at
+        slots[live:r] = -1
+        for offset in layout.tables:
+            host[offset + live * max_blocks : offset + r * max_blocks] = -1
     return max_q, max_ctx

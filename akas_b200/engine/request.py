@@ -17,7 +17,7 @@ import numpy as np
 _ids = itertools.count()
 
 
-@dataclass
+@dataclass(eq=False)  # a request is itself, not its field values: lists of requests are searched by identity
 class Request:
     prompt: List[int]
     limit: int  # most tokens to generate

@@ -120,19 +120,21 @@ class ModelRunner:
         entries = [e for e in entries if len(e.tokens)]
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        seen = set()
         arrays = [np.asarray(e.tokens, dtype=np.int64) for e in entries]  # converted once, checked and copied as arrays
         if previous is None and any(e.source >= 0 for e in entries):
             raise ValueError("an entry takes its token from the step before, but no such tokens were given")
-        for e, ids in zip(entries, arrays):
-            if e.request in seen:
-                raise ValueError(f"request {e.request!r} appears twice in one step")
-            seen.add(e.request)
-            if ids.ndim != 1:
-                raise ValueError(f"request {e.request!r}: tokens must be a flat sequence of ids")
-            if int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size:
+        if len({e.request for e in entries}) != len(entries):
+            twice = [e.request for e in entries if sum(1 for o in entries if o.request == e.request) > 1]
+            raise ValueError(f"request {twice[0]!r} appears twice in one step")
+        flat = np.concatenate(arrays) if len(arrays) > 1 else arrays[0]
+        if flat.ndim != 1 or any(ids.ndim != 1 for ids in arrays):
+            raise ValueError("tokens must be flat sequences of ids")
+        if int(flat.min()) < 0 or int(flat.max()) >= self.vocab_size:  # one check for the step; the culprit only then
+            for e, ids in zip(entries, arrays):
                 bad = ids[(ids < 0) | (ids >= self.vocab_size)]
-                raise ValueError(f"request {e.request!r}: token ids {bad[:4].tolist()} outside [0, {self.vocab_size})")
+                if bad.size:
+                    raise ValueError(f"request {e.request!r}: token ids {bad[:4].tolist()} outside [0, {self.vocab_size})")
+        for e, ids in zip(entries, arrays):
             if any(not 0 <= w < len(e.tokens) for w in e.want):
                 raise ValueError(f"request {e.request!r}: wanted places {list(e.want)} outside its {len(e.tokens)} tokens")
             if e.request not in self.cache:
