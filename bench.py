@@ -190,17 +190,10 @@ def main():
         gc.freeze()
         before = sum(len(r.output) for r in requests)
         t1 = time.perf_counter()
-        turns = []
         for _ in range(e2e_steps):
-            t_turn = time.perf_counter()
             engine.step()
-            turns.append(time.perf_counter() - t_turn)
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t1
-        if os.environ.get("AKAS_BENCH_DEBUG"):
-            worst = sorted(range(len(turns)), key=lambda i: -turns[i])[:6]
-            print("e2e turns (index, ms):", [(i, round(turns[i] * 1e3, 2)) for i in sorted(worst)], "sync tail ms",
-                  round((e2e_s - sum(turns)) * 1e3, 2), engine.stats, file=sys.stderr)
         produced = sum(len(r.output) for r in requests) - before
         for r in requests:
             engine.cancel(r)
