@@ -16,6 +16,7 @@
 
 #include "common.cuh"
 #include "mma.cuh"
+#include "tcgen05.cuh"
 
 using namespace akas;
 
@@ -250,6 +251,222 @@ __global__ void decode_merge_bf16_kernel(const float* __restrict__ part_o, const
   }
 }
 
+// The same for head size 64 and pages that hold whole 64-key tiles, with the K and V tiles fetched by TMA: a fifth
+// warp's one thread issues two tensor loads per tile (128-byte swizzle) into a four-stage ring guarded by "full" and
+// "empty" mbarriers, instead of every thread computing addresses and issuing eight 16-byte copies per tile; the four
+// consumer warps read their fragments from the swizzled tiles. Rows of V past the request's position are zeroed in
+// shared memory (a page may hold anything there, and nothing may meet a zero probability as NaN). Waits are bounded
+// (akas_decode_attention_status).
+constexpr int TMA_STAGES = 4, TMA_TILE = BK * 128;  // a tile: 64 rows of 64 bfloat16
+
+__device__ int g_decode_status = 0;
+
+__global__ void __launch_bounds__((WARPS + 1) * 32)
+decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const bf16* __restrict__ q, const int* __restrict__ block_table, int max_blocks,
+                            const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                            bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, float scale,
+                            int window, int page_size, int H, int KH, int row_tiles, int splits) {
+  using namespace akas::tc;
+  constexpr int D = 64, STRIDE = D + 8, CHUNKS = D / 8, KS = D / 16, NB = D / 8;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  unsigned char* k_t = tiles;                              // [TMA_STAGES][64 keys][128 bytes], swizzled
+  unsigned char* v_t = k_t + TMA_STAGES * TMA_TILE;        // [TMA_STAGES][64 keys][128 bytes], swizzled
+  bf16* q_s = reinterpret_cast<bf16*>(v_t + TMA_STAGES * TMA_TILE);  // [ROWS][STRIDE]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(q_s + ROWS * STRIDE);
+  uint64_t* empty_bar = full_bar + TMA_STAGES;
+  int* abort_s = reinterpret_cast<int*>(empty_bar + TMA_STAGES);
+
+  chain_release();
+  chain_wait();
+  const int tok = blockIdx.x, split = blockIdx.z;
+  const int kvh = blockIdx.y / row_tiles, row_tile = blockIdx.y % row_tiles;
+  const int G = H / KH;
+  const int g0 = row_tile * ROWS, gn = min(ROWS, G - g0);
+  const int head0 = kvh * G + g0;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int r = seq_of_token[tok];
+  if (r < 0) {
+    if (split == 0)
+      for (int i = tid; i < gn * D; i += (WARPS + 1) * 32) out[((size_t)tok * H + head0) * D + i] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int pos = positions[tok];
+  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kt_first = first_key / BK, kt_last = pos / BK;
+  const int per_split = (kt_last - kt_first + 1 + splits - 1) / splits;
+  const int lo = kt_first + split * per_split, hi = min(lo + per_split, kt_last + 1);
+
+  if (tid == 0) {
+    *abort_s = 0;
+    for (int s = 0; s < TMA_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], WARPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  auto wait_for = [&](uint64_t* bar, unsigned parity, int code) {
+    if (*(volatile int*)abort_s) return;
+    if (!mbar_wait(bar, parity)) {
+      *(volatile int*)abort_s = 1;
+      atomicExch(&g_decode_status, code);
+    }
+  };
+
+  if (warp == WARPS) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      for (int kt = lo; kt < hi; ++kt) {
+        const int i = kt - lo, s = i % TMA_STAGES;
+        int page = block_table[(size_t)r * max_blocks + kt * BK / page_size];
+        if (page < 0) page = 0;  // cannot happen for keys up to the request's position
+        const int row = (page * KH + kvh) * page_size + (kt * BK) % page_size;
+        if (i >= TMA_STAGES) wait_for(&empty_bar[s], ((i / TMA_STAGES) & 1) ^ 1, 2);
+        if (*(volatile int*)abort_s) break;
+        mbar_expect_tx(&full_bar[s], 2 * TMA_TILE);
+        tma_load_2d(k_t + s * TMA_TILE, &map_k, 0, row, &full_bar[s]);
+        tma_load_2d(v_t + s * TMA_TILE, &map_v, 0, row, &full_bar[s]);
+      }
+    }
+    return;  // the consumers wait for every load before the block ends
+  }
+
+  // -------------------------------------------------------------------- consumers: warps 0..3
+  auto consumers_meet = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory"); };
+  for (int c = tid; c < ROWS * CHUNKS; c += WARPS * 32) {
+    const int row = c / CHUNKS, col = (c % CHUNKS) * 8;
+    const bf16* src = q + ((size_t)tok * H + head0 + min(row, gn - 1)) * D + col;
+    cp_async16(q_s + row * STRIDE + col, src, row < gn ? 16 : 0);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  consumers_meet();
+  uint32_t qf[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) ldmatrix_x4(qf[ks], q_s + (lane & 15) * STRIDE + ks * 16 + (lane >> 4) * 8);
+
+  float o[NB][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) { o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float sl2 = scale * 1.4426950408889634f;
+  // this lane's rows inside the warp's 16 keys of a tile, and the 16-byte units it reads there
+  const int k_row = warp * 16 + (lane & 7) + (lane >> 4) * 8, k_unit = (lane >> 3) & 1;
+  const int v_row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, v_unit = lane >> 4;
+
+  for (int kt = lo; kt < hi; ++kt) {
+    const int i = kt - lo, s = i % TMA_STAGES;
+    wait_for(&full_bar[s], (i / TMA_STAGES) & 1, 1);
+    const unsigned char* kt_ = k_t + s * TMA_TILE;
+    unsigned char* vt_ = v_t + s * TMA_TILE;
+    if (kt == kt_last && pos % BK != BK - 1) {  // rows of V past the position: zero
+      for (int c = tid + (pos % BK + 1) * 8; c < BK * 8; c += WARPS * 32)
+        *reinterpret_cast<uint4*>(vt_ + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+      consumers_meet();
+    }
+    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      uint32_t b[4];
+      ldmatrix_x4(b, kt_ + k_row * 128 + (((ks * 2 + k_unit) ^ (k_row & 7)) << 4));
+      mma_bf16(sc[0], qf[ks], b[0], b[1]);
+      mma_bf16(sc[1], qf[ks], b[2], b[3]);
+    }
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = kt * BK + warp * 16 + nb * 8 + 2 * t + (e & 1);
+        const bool seen = key <= pos && key >= first_key;
+        sc[nb][e] = seen ? sc[nb][e] * sl2 : -INFINITY;
+        m_new[e >> 1] = fmaxf(m_new[e >> 1], sc[nb][e]);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      m_new[h2] = fmaxf(m_new[h2], __shfl_xor_sync(0xffffffffu, m_new[h2], 1));
+      m_new[h2] = fmaxf(m_new[h2], __shfl_xor_sync(0xffffffffu, m_new[h2], 2));
+      m_use[h2] = m_new[h2] == -INFINITY ? 0.f : m_new[h2];
+      corr[h2] = exp2f(m_run[h2] - m_use[h2]);
+      m_run[h2] = m_new[h2];
+    }
+    uint32_t pf[4];
+    float l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      const float p0 = exp2f(sc[nb][0] - m_use[0]), p1 = exp2f(sc[nb][1] - m_use[0]);
+      const float p2 = exp2f(sc[nb][2] - m_use[1]), p3 = exp2f(sc[nb][3] - m_use[1]);
+      l_add[0] += p0 + p1;
+      l_add[1] += p2 + p3;
+      pf[nb * 2] = pack_bf16(p0, p1);
+      pf[nb * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) l_run[h2] = l_run[h2] * corr[h2] + l_add[h2];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      o[nb][0] *= corr[0]; o[nb][1] *= corr[0];
+      o[nb][2] *= corr[1]; o[nb][3] *= corr[1];
+    }
+#pragma unroll
+    for (int np = 0; np < NB / 2; ++np) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, vt_ + v_row * 128 + (((np * 2 + v_unit) ^ (v_row & 7)) << 4));
+      mma_bf16(o[2 * np], pf, b[0], b[1]);
+      mma_bf16(o[2 * np + 1], pf, b[2], b[3]);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);  // this warp has read the stage
+  }
+  consumers_meet();  // every warp is done with the tiles: their memory becomes the merge buffers
+
+  float* o_s = reinterpret_cast<float*>(k_t);            // [WARPS][ROWS][D]
+  float* ml_s = o_s + WARPS * ROWS * D;                  // [WARPS][ROWS][2]
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 1);
+    l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 2);
+    const int row = g + h2 * 8;
+    if (t == 0) {
+      ml_s[(warp * ROWS + row) * 2] = m_run[h2];
+      ml_s[(warp * ROWS + row) * 2 + 1] = l_run[h2];
+    }
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      float* dst = o_s + ((size_t)warp * ROWS + row) * D + nb * 8 + 2 * t;
+      dst[0] = o[nb][h2 * 2];
+      dst[1] = o[nb][h2 * 2 + 1];
+    }
+  }
+  consumers_meet();
+  for (int i = tid; i < gn * D; i += WARPS * 32) {
+    const int row = i / D, e = i % D;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) top = fmaxf(top, ml_s[(w * ROWS + row) * 2]);
+    float sum = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float mw = ml_s[(w * ROWS + row) * 2];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - top);
+      sum = fmaf(ml_s[(w * ROWS + row) * 2 + 1], f, sum);
+      acc = fmaf(o_s[((size_t)w * ROWS + row) * D + e], f, acc);
+    }
+    const size_t head = (size_t)tok * H + head0 + row;
+    if (splits == 1) {
+      out[head * D + e] = __float2bfloat16_rn(acc / sum);
+    } else {
+      part_o[(head * splits + split) * D + e] = acc;
+      if (e == 0) {
+        part_ml[(head * splits + split) * 2] = top;  // in units of log2(e)
+        part_ml[(head * splits + split) * 2 + 1] = sum;
+      }
+    }
+  }
+}
+
 template <int D>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* block_table, int max_blocks,
            const int* seq_of_token, const int* positions, void* out, float* part_o, float* part_ml, float scale,
@@ -274,7 +491,48 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* blo
                         (const float*)part_o, (const float*)part_ml, seq_of_token, (bf16*)out, H, D, splits);
 }
 
+// Head size 64, pages of whole tiles: the TMA-fed kernel. pool_rows: pages x kv heads x page size.
+int launch_tma(const void* q, const void* k_pool, const void* v_pool, long long pool_rows, const int* block_table,
+               int max_blocks, const int* seq_of_token, const int* positions, void* out, float* part_o, float* part_ml,
+               float scale, int window, int page_size, int N, int H, int KH, int splits, cudaStream_t stream) {
+  constexpr int D = 64;
+  constexpr int smem = 1024 + 2 * TMA_STAGES * TMA_TILE + ROWS * (D + 8) * (int)sizeof(bf16) + 2 * TMA_STAGES * 8 + 16;
+  static_assert(2 * TMA_STAGES * TMA_TILE >= WARPS * ROWS * (D + 2) * (int)sizeof(float), "the merge buffers fit the tiles");
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(decode_attention_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap map_k, map_v;
+  int err = akas::tc::cached_map(&map_k, k_pool, (int)pool_rows, D, BK, true);
+  if (!err) err = akas::tc::cached_map(&map_v, v_pool, (int)pool_rows, D, BK, true);
+  if (err) return err;
+  const int G = H / KH, row_tiles = (G + ROWS - 1) / ROWS;
+  err = launch_chained(decode_attention_tma_kernel, dim3(N, KH * row_tiles, splits), dim3((WARPS + 1) * 32), smem, stream,
+                       map_k, map_v, (const bf16*)q, block_table, max_blocks, seq_of_token, positions, (bf16*)out, part_o,
+                       part_ml, scale, window, page_size, H, KH, row_tiles, splits);
+  if (err || splits == 1) return err;
+  return launch_chained(decode_merge_bf16_kernel, dim3(N, H), dim3(64), 0, stream, (const float*)part_o,
+                        (const float*)part_ml, seq_of_token, (bf16*)out, H, D, splits);
+}
+
 }  // namespace
+
+// The same as akas_decode_attention_bf16 below for callers that know the size of the pools (pool_pages pages): with
+// head size 64 and a page size that is a multiple of 64 the K and V tiles are fetched by TMA.
+AKAS_API int akas_decode_attention_bf16_paged(const void* q, const void* k_pool, const void* v_pool, int pool_pages,
+                                              const int* block_table, int max_blocks, const int* seq_of_token,
+                                              const int* positions, void* out, float* part_o, float* part_ml, float scale,
+                                              int window, int page_size, int N, int H, int KH, int D, int splits,
+                                              cudaStream_t stream);
+
+// 0 if no bounded wait of the TMA-fed kernel has ever run out on the current device (1: consumers, 2: producer).
+AKAS_API int akas_decode_attention_status() {
+  int status = -1;
+  const cudaError_t e = cudaMemcpyFromSymbol(&status, g_decode_status, sizeof(int));
+  return e == cudaSuccess ? status : -(int)e;
+}
 
 // Scratch (untouched when splits == 1): part_o float32 [N, H, splits, D], part_ml float32 [N, H, splits, 2].
 AKAS_API int akas_decode_attention_bf16(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
@@ -297,6 +555,23 @@ AKAS_API int akas_decode_attention_bf16(const void* q, const void* k_pool, const
       return (int)cudaErrorInvalidValue;
   }
 #undef AKAS_DECODE
+}
+
+AKAS_API int akas_decode_attention_bf16_paged(const void* q, const void* k_pool, const void* v_pool, int pool_pages,
+                                              const int* block_table, int max_blocks, const int* seq_of_token,
+                                              const int* positions, void* out, float* part_o, float* part_ml, float scale,
+                                              int window, int page_size, int N, int H, int KH, int D, int splits,
+                                              cudaStream_t stream) {
+  const long long pool_rows = (long long)pool_pages * KH * page_size;
+  if (D == 64 && page_size % BK == 0 && H % KH == 0 && splits >= 1 && splits <= 65535 && pool_rows > 0 &&
+      pool_rows < (1ll << 31) && (long long)KH * ((H / KH + ROWS - 1) / ROWS) <= 65535 && (uintptr_t)k_pool % 16 == 0 &&
+      (uintptr_t)v_pool % 16 == 0) {
+    if (N <= 0) return 0;
+    return launch_tma(q, k_pool, v_pool, pool_rows, block_table, max_blocks, seq_of_token, positions, out, part_o, part_ml,
+                      scale, window, page_size, N, H, KH, splits, stream);
+  }
+  return akas_decode_attention_bf16(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, part_o,
+                                    part_ml, scale, window, page_size, N, H, KH, D, splits, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------

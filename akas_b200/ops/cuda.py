@@ -66,6 +66,10 @@ _SIGNATURES = {
         "akas_decode_attention_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_void_p],
+        "akas_decode_attention_bf16_paged": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int,
+                                             c_int, c_int, c_void_p],
+        "akas_decode_attention_status": [],
     },
     "gemm_tcgen05": {
         "akas_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -476,6 +480,11 @@ if prompt_attention not in ("auto", "tcgen05", "mma"):
     raise ValueError(f"AKAS_B200_PROMPT_ATTENTION must be auto, tcgen05 or mma, got {prompt_attention!r}")
 
 
+def decode_attention_status() -> int:
+    """0 unless a bounded wait inside the TMA-fed decode-attention kernel has run out on this device."""
+    return int(_fn("attention_decode", "akas_decode_attention_status")())
+
+
 def prefill_attention_tc_status() -> int:
     """0 unless a bounded wait inside the tcgen05 prompt-attention kernel has run out on this device."""
     return int(_fn("attention_prefill_tc", "akas_prefill_attention_tc_status")())
@@ -508,8 +517,8 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
             if splits > 1:
                 part_o = torch.empty((n, heads, splits, d), dtype=torch.float32, device=q.device)
                 part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
-            _check(_fn("attention_decode", "akas_decode_attention_bf16")(
-                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
+            _check(_fn("attention_decode", "akas_decode_attention_bf16_paged")(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
                 _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
                 splits, _stream()), "decode_attention", kernels=2 if splits > 1 else 1)
             return out

@@ -415,21 +415,29 @@ class _Decode:
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("h,kh,d,page,window", [
     (4, 2, 16, 16, None), (3, 1, 32, 8, None), (32, 8, 64, 64, None), (6, 1, 48, 8, 300), (16, 2, 128, 32, None),
-    (24, 1, 64, 16, None), (5, 5, 256, 64, None),
+    (24, 1, 64, 16, None), (5, 5, 256, 64, None), (8, 2, 64, 128, 300), (4, 4, 64, 256, None), (32, 8, 64, 64, 1000),
 ])
 def test_paged_attention_decode_split(ops, dtype, h, kh, d, page, window):
+    """Split-key decode attention; head size 64 with pages of 64 keys or more takes the TMA-fed kernel in bfloat16.
+    What the pages hold past the end of a request is poisoned: it must not be looked at."""
     cuda, ref = ops
-    contexts = [1, 2, 33, 700, 1500, 257]
+    contexts = [1, 2, 33, 700, 1500, 257, 64, 128]
     cu, seq = _batch([1] * len(contexts), pad=2)
     pos = torch.tensor([c - 1 for c in contexts] + [0, 0], dtype=torch.int32, device=DEV)
     pages = sum(-(-c // page) for c in contexts) + 3
     bt = _tables(contexts, page, pages, 6)
     k, v = _pools(pages, kh, page, d, dtype, 50)
+    for r, context in enumerate(contexts):
+        if context % page:
+            last = int(bt[r, (context - 1) // page])
+            k[last, :, context % page:] = float("nan")
+            v[last, :, context % page:] = float("nan")
     q = _rand((pos.numel(), h * d), dtype, 52)
     scale = d ** -0.5
     want = ref.paged_attention(q, k, v, bt, seq, pos, scale, window, page)
     got = cuda.paged_attention(q, k, v, bt, seq, pos, scale, window, page, _Decode(max(contexts)))
     _close(got, want, dtype, "split decode")
+    assert cuda.decode_attention_status() == 0
     assert torch.equal(got[-2:], torch.zeros_like(got[-2:]))
 
 
