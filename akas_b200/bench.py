@@ -311,7 +311,8 @@ def bench_serving(shape: str = "350m", requests: int = 256, shortest: int = 128,
     engine = _random_engine(shape, max_requests=requests, context=longest + generated + 64, max_tokens=pool + 64 * requests,
                             prefill_chunk=chunk, prefill_requests=32, prefill_token_budget=8192)
     with engine:
-        engine.generate(prompts[:4], max_tokens=8)  # warm up: kernels, library handles, the first graphs
+        engine.warm_up()  # the decode graphs of every batch size
+        engine.generate(prompts[:4], max_tokens=8)  # kernels and library handles of the prompt path
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         results = engine.generate(prompts, max_tokens=generated)

@@ -119,6 +119,12 @@ class Engine:
         self.scheduler.submit(request)
         return request
 
+    def warm_up(self, most: Optional[int] = None) -> None:
+        """Compiles, loads and captures what serving will need (the decode graphs of every batch size up to ``most``
+        requests, default ``max_requests``), so that the first requests do not pay for it."""
+        self._check_thread()
+        self.runner.capture_decode_graphs(most)
+
     def _execute(self, entries, requests) -> List[int]:
         logits = self.runner.step(entries)
         return self.sampler.sample(logits, requests)

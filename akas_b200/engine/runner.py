@@ -30,6 +30,7 @@ from .batch import BatchLayout, StepContext, StepEntry, fill_batch
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 _GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+_TOKEN_ROUNDING = 256
 _SHAPE_REPEATS, _SHAPE_GRAPHS = 3, 4  # a step shape is captured when it comes the third time; at most four are kept
 
 
@@ -153,10 +154,15 @@ class ModelRunner:
         else:
             n = sum(len(e.tokens) for e in entries)
             m = sum(len(e.want) for e in entries)
-            lay = BatchLayout(n, len(entries), m, len(self.cache.groups), self.cache.max_blocks)
+            # The library behind the larger bfloat16 products sets itself up anew for every number of rows it has
+            # not seen (about 45 us of host time a product), and a serving step brings any number of tokens: beyond
+            # 256 the step is padded to a multiple of 256 with tokens of no request, which every kernel skips.
+            padded = -(-n // _TOKEN_ROUNDING) * _TOKEN_ROUNDING if n > _TOKEN_ROUNDING and self.dtype == torch.bfloat16 else n
+            lay = BatchLayout(padded, len(entries), m, len(self.cache.groups), self.cache.max_blocks)
             ring, dev = self._staging(lay.size)
             host = ring.take()
-            max_q, max_ctx = fill_batch(host.numpy(), lay, entries, self.cache, tokens=arrays)
+            max_q, max_ctx = fill_batch(host.numpy(), lay, entries, self.cache, pad_to=padded if padded > n else 0,
+                                        tokens=arrays)
             dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
             ring.copied()
             ctx = self._context(dev, lay, max_q, max_ctx, decode_only)
@@ -171,6 +177,21 @@ class ModelRunner:
         return logits
 
     # ------------------------------------------------------------------ captured steps
+
+    def capture_decode_graphs(self, most: Optional[int] = None) -> List[int]:
+        """Captures the decode graphs for every batch-size bucket up to ``most`` requests (default: the engine's
+        ``max_requests``) now, rather than when a batch of that size first comes; returns the buckets."""
+        if not (self.config.cuda_graphs and self.device.type == "cuda"):
+            return []
+        most = self.config.max_requests if most is None else most
+        top = next((b for b in _GRAPH_BUCKETS if b >= most), -(-most // 64) * 64)
+        done = []
+        for bucket in [b for b in _GRAPH_BUCKETS if b < top] + [top]:
+            if bucket not in self._graphs:
+                self._graphs[bucket] = _DecodeGraph(self, bucket)
+            self._graphs[bucket].capture()
+            done.append(bucket)
+        return done
 
     def _repeated_shape(self, entries):
         """A captured graph for steps whose requests bring exactly these numbers of tokens, once that shape has come
