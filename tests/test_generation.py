@@ -121,6 +121,19 @@ def test_a_step_ahead_changes_nothing(tmp_path):
     assert runs[True, True] == runs[False, True] == runs[True, False] == runs[False, False]
 
 
+def test_warm_up_captures_every_bucket_and_changes_nothing(tmp_path):
+    folder = tiny.make_folder(tiny.TINY_A, seed=28, dtype="float32", folder=tmp_path / "m")
+    cfg, w = plain.load_folder(folder)
+    prompts = tiny.prompts(256, [12, 3, 25], seed=9)
+    with _engine(folder, "float32", 16, max_requests=6) as engine:
+        engine.warm_up()
+        graphs = engine.runner._graphs
+        assert sorted(graphs) == [1, 2, 4, 8] and all(g.graph is not None for g in graphs.values())
+        results = engine.generate(prompts, max_tokens=10)
+    for prompt, result in zip(prompts, results):
+        assert result["generated_tokens"] == plain.greedy(cfg, w, prompt, 10)
+
+
 def test_preemption_on_the_device_recomputes_exactly(tmp_path):
     """A pool too small for three growing requests: the youngest is preempted and recomputed; every output
     still equals the plain greedy continuation."""
