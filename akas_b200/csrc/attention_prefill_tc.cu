@@ -3,27 +3,31 @@
 //
 // One block per (tile of 128 consecutive query tokens of one request, query head). It walks 128-key tiles
 // aligned to absolute position 0, from the first key any of its queries may see to its last query's own
-// position. Six warps, three roles:
+// position. Ten warps, three roles:
 //   warp 0    producer: one thread issues TMA loads (128-byte swizzle): the Q tile once, then per key tile two
 //             boxes of 64 keys of K and two of V, found through the block table, into a two-stage ring; K and V
 //             have "full" and "empty" mbarriers of their own, so the scores can start before V has landed.
-//   warp 1    tensor cores: allocates tensor memory (128 columns of scores S, 64 of P.V) and, one thread,
+//   warp 1    tensor cores: allocates tensor memory (128 columns of scores S, 64 of the output O) and, one thread,
 //             issues S = Q.K^T (four tcgen05.mma, M 128, N 128, K 16, both operands K-major) and, once the
-//             softmax warps have written P, PV = P.V (eight tcgen05.mma, M 128, N 64, K 16; V is read as it
+//             softmax warps have written P, O += P.V (eight tcgen05.mma, M 128, N 64, K 16; V is read as it
 //             lies in the pages, rows of keys with the head's channels contiguous: an MN-major B operand).
-//             The scores of the next tile are issued right behind P.V of the current one.
+//             The scores of the next tile are issued as soon as the softmax warps hold this tile's in registers,
+//             so they run under the exponentials.
 //   warps 2-9 softmax and read-out: two threads per query row (= tensor-memory lane), warps 2-5 for the tile's
 //             keys 0-63 and output channels 0-31, warps 6-9 for keys 64-127 and channels 32-63. Per tile a
-//             thread reads its half of the row of S (tcgen05.ld) twice: once for the maximum (causal / window
-//             mask applied; the two halves meet through shared memory), once to form P = exp2(s - max), which
-//             it rounds to bfloat16 and writes to shared memory in the swizzled K-major layout the second
-//             product reads; then it reads its channels of PV and keeps the running output in registers:
-//             O = O * exp2(old max - new max) + PV. Softmax is float32 throughout.
-// A block's tiles follow one another (scores, softmax, P.V; only the next tile's scores run ahead), so its tensor
-// cores idle while its softmax warps work and the other way round; two blocks fit an SM (112 KB of shared memory and
-// 256 columns of tensor memory each, no static shared memory) and fill each other's gaps. The softmax warps are
-// bound by the exponentials (128 a row and tile on the special-function units). Measured on the 1.2B shape: 222
-// TFLOP/s at 2,048 tokens and 392 at 8,192, against 182 and 220 of the mma.sync kernel of attention_prefill.cu.
+//             thread reads its half of the row of S (tcgen05.ld) into registers, masks it (causal / window) where
+//             the tile needs that, takes the maximum (the two halves meet through shared memory), forms
+//             P = exp2(s - reference), rounds it to bfloat16 and writes it to shared memory in the swizzled
+//             K-major layout the second product reads. The output stays in tensor memory over all tiles and is
+//             divided by the row's sum at the end. The reference of a row follows its running maximum lazily:
+//             only when the maximum has grown by more than 2^8 since the reference was set does the thread
+//             rescale its channels of O (tcgen05.ld, multiply, tcgen05.st) and its sum; in between P may exceed 1,
+//             which float32 sums and bfloat16's exponent take. Softmax is float32 throughout.
+// A block's softmax warps and its tensor cores still take turns for the most part; two blocks fit an SM (112 KB of
+// shared memory and 256 columns of tensor memory each, no static shared memory) and fill each other's gaps. The
+// softmax warps are bound by the exponentials (128 a row and tile on the special-function units). Measured on the
+// 1.2B shape: 280 TFLOP/s at 2,048 tokens and 522 at 8,192, against 182 and 220 of the mma.sync kernel of
+// attention_prefill.cu.
 //
 // Keys past a query's position are masked by position, not by content: pages past the end of a request are
 // not fetched (a valid page stands in), and rows of V past the block's last key are zeroed in shared memory so
@@ -43,7 +47,7 @@ constexpr int BQ = 128, BKEYS = 128, D = 64, THREADS = 320, STAGES = 2;
 constexpr int TILE_BYTES = 128 * 128;  // 128 rows of 64 bfloat16: Q, one stage of K, one of V
 constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 2 * TILE_BYTES + 128 + 512;  // tiles, P, barriers, exchange
 static_assert(2 * (SMEM_BYTES + 1024) <= 228 * 1024, "two blocks an SM");
-constexpr int TMEM_COLS = 256;  // S: columns 0..127, PV: 128..191
+constexpr int TMEM_COLS = 256;  // S: columns 0..127, O: 128..191
 
 __device__ int g_attention_status = 0;
 
@@ -67,6 +71,21 @@ __device__ __forceinline__ void tmem_load32(unsigned taddr, float (&v)[32]) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_store16(unsigned taddr, const float (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
+      "tcgen05.wait::st.sync.aligned;\n" ::"r"(taddr),
+      "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+      "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+      "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+      "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+      : "memory");
+}
+// When the running maximum of a row grows by less than this (in powers of two) the output so far is not rescaled:
+// the row goes on with its old reference, and its probabilities may reach 2^8 instead of 1 (float32 sums and
+// bfloat16's exponent have room for that).
+constexpr float RESCALE_STEP = 8.f;
+
 __global__ void __launch_bounds__(THREADS, 2)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
@@ -80,7 +99,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   unsigned char* v_s = k_s + STAGES * TILE_BYTES;              // [STAGES][128 keys][128 bytes]
   unsigned char* p_s = v_s + STAGES * TILE_BYTES;              // [2 groups of 64 keys][128 queries][128 bytes]
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * TILE_BYTES);
-  uint64_t &q_full = bars[0], &s_full = bars[1], &p_full = bars[2], &pv_full = bars[3];
+  uint64_t &q_full = bars[0], &s_full = bars[1], &p_full = bars[2], &pv_full = bars[3], &s_empty = bars[14];
   uint64_t *k_full = bars + 4, *k_empty = bars + 6, *v_full = bars + 8, *v_empty = bars + 10;  // STAGES of each
   unsigned& tmem_base_s = *reinterpret_cast<unsigned*>(bars + 12);
   int& abort_s = *reinterpret_cast<int*>(bars + 13);
@@ -117,6 +136,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     mbar_init(&s_full, 1);
     mbar_init(&p_full, 256);
+    mbar_init(&s_empty, 256);
     mbar_init(&pv_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -190,7 +210,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       scores(0);
       for (int t = 0; t < tiles_k && !*(volatile int*)&abort_s; ++t) {
         const int s = t % STAGES;
-        wait_for(&p_full, t & 1, 2);  // the softmax warps have read S and written P
+        if (t + 1 < tiles_k) {
+          wait_for(&s_empty, t & 1, 2);  // the softmax warps hold S in registers: the next tile's scores may land
+          scores(t + 1);
+        }
+        wait_for(&p_full, t & 1, 2);  // P is written, and the output so far is rescaled where it had to be
         wait_for(&v_full[s], (t / STAGES) & 1, 2);
         if (*(volatile int*)&abort_s) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -198,11 +222,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int j = 0; j < BKEYS / UMMA_K; ++j) {  // 16 keys a step: P advances along its swizzled rows, V by 16 rows
           const uint64_t a = smem_desc(p_s + (j >> 2) * TILE_BYTES) + (uint64_t)((j & 3) * 2);
           const uint64_t b = smem_desc_mn(v_s + s * TILE_BYTES + j * 16 * 128);
-          umma(tmem_pv, a, b, idesc_pv, j ? 1u : 0u);
+          umma(tmem_pv, a, b, idesc_pv, (t | j) ? 1u : 0u);  // the output accumulates in tensor memory over the tiles
         }
         umma_commit(&v_empty[s]);
         umma_commit(&pv_full);
-        if (t + 1 < tiles_k) scores(t + 1);
       }
     }
   } else {
@@ -213,10 +236,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const unsigned tmem_s = tmem_base + lane_addr + half * 64, tmem_pv = tmem_base + 128 + lane_addr + half * 32;
     const int qpos = pos0 + row;
     const float sl2 = scale * 1.4426950408889634f;  // scores in units of log2(e): exp is exp2
-    float o[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;  // the running maximum is kept in units of the raw scores
+    float m_ref = -INFINITY, l_run = 0.f;  // the reference the row's probabilities are taken against, in raw units
     auto meet = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(2 + sub) : "memory"); };  // the two warps of these rows
     for (int t = 0; t < tiles_k; ++t) {
       const int kt = kt0 + t, key_base = kt * BKEYS + half * 64, s = t % STAGES;
@@ -231,28 +251,30 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       wait_for(&s_full, t & 1, 3);  // after a wait has run out nobody waits any more, but every thread still walks
                                     // all tiles: the two warps of a row meet at a barrier in each
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // This thread's half of the row of S, into registers; tensor memory is then free for the next tile's scores.
+      float v[64];
+      {
+        float a[32], b[32];
+        tmem_load32(tmem_s, a);
+        tmem_load32(tmem_s + 32, b);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { v[i] = a[i]; v[32 + i] = b[i]; }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(&s_empty);
       const bool whole = kt * BKEYS + BKEYS - 1 <= pos0 && kt * BKEYS >= first_key &&
                          (window <= 0 || kt * BKEYS > pos0 + rows - 1 - window);  // no query of the tile masks any of it
-      // Two passes over this thread's half of the row of S: its maximum (of the raw scores: the scale is positive),
-      // then P = exp2(s * scale - max * scale), rounded to bfloat16, into the swizzled K-major tile the second
-      // product reads. Tiles that no query of the block masks (all but the last one or two) take the short path.
-      float top = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 64; c += 32) {
-        float v[32];
-        tmem_load32(tmem_s + c, v);
-        if (whole) {
+      if (!whole) {  // all tiles but the last one or two (and the first, under a window) skip this
 #pragma unroll
-          for (int i = 0; i < 32; ++i) top = fmaxf(top, v[i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key_base + c + i;
-            const bool seen = key <= qpos && key >= first_key && (window <= 0 || key > qpos - window);
-            top = fmaxf(top, seen ? v[i] : -INFINITY);
-          }
+        for (int i = 0; i < 64; ++i) {
+          const int key = key_base + i;
+          const bool seen = key <= qpos && key >= first_key && (window <= 0 || key > qpos - window);
+          v[i] = seen ? v[i] : -INFINITY;
         }
       }
+      float top = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) top = fmaxf(top, v[i]);
       // The halves' maxima meet rounded up to bfloat16 (the exchange has 512 bytes): the shift of the softmax need
       // not be the exact maximum, only the same for both halves and not below any score.
       const bf16 rounded = __float2bfloat16_ru(top);
@@ -260,59 +282,55 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       exchange[half * 128 + row] = rounded;
       meet();
       top = fmaxf(__bfloat162float(rounded), __bfloat162float(exchange[(half ^ 1) * 128 + row]));
-      const float m_new = fmaxf(m_run, top);                 // raw units
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that sees nothing yet
-      const float corr = fast_exp2((m_run - m_use) * sl2);
-      const float bias = -m_use * sl2;
-      m_run = m_new;
-      float l_add = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 64; c += 32) {
-        float v[32];
-        tmem_load32(tmem_s + c, v);
-        uint32_t packed[16];
-        if (whole) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(v[i], sl2, bias)), p1 = fast_exp2(fmaf(v[i + 1], sl2, bias));
-            l_add += p0 + p1;
-            packed[i >> 1] = pack_bf16(p0, p1);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const int key = key_base + c + i;
-            const bool seen0 = key <= qpos && key >= first_key && (window <= 0 || key > qpos - window);
-            const bool seen1 = key + 1 <= qpos && key + 1 >= first_key && (window <= 0 || key + 1 > qpos - window);
-            const float p0 = seen0 ? fast_exp2(fmaf(v[i], sl2, bias)) : 0.f;
-            const float p1 = seen1 ? fast_exp2(fmaf(v[i + 1], sl2, bias)) : 0.f;
-            l_add += p0 + p1;
-            packed[i >> 1] = pack_bf16(p0, p1);
-          }
-        }
-        unsigned char* group = p_s + half * TILE_BYTES + row * 128;  // keys 0-63 or 64-127 of the tile
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {  // four 16-byte chunks of 8 keys
-          const int chunk = (c >> 3) + q;
-          *reinterpret_cast<uint4*>(group + ((chunk ^ (row & 7)) << 4)) =
-              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-        }
+      const float m_new = fmaxf(m_ref, top);
+      // P.V of the tile before has run: P's memory is free again and the output so far is complete
+      if (t > 0) {
+        wait_for(&pv_full, (t - 1) & 1, 3);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       }
-      l_run = l_run * corr + l_add;
+      // The output so far, O in tensor memory, refers to m_ref. It is brought to the new maximum only when that has
+      // grown by more than RESCALE_STEP for some row of this warp (the two warps of a row see the same maxima and
+      // decide alike); then every row of the warp moves to its new maximum. (-inf) - (-inf) is NaN: not greater.
+      const bool grown = (m_new - m_ref) * sl2 > RESCALE_STEP;
+      if (t == 0) {
+        m_ref = m_new;
+      } else if (__any_sync(0xffffffffu, grown)) {
+        const float corr = m_new == -INFINITY ? 1.f : fast_exp2((m_ref - m_new) * sl2);
+#pragma unroll 1
+        for (int c = 0; c < 32; c += 16) {  // in pieces: the scores of the tile are held in registers meanwhile
+          float o[16];
+          tmem_load16(tmem_pv + c, o);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] *= corr;
+          tmem_store16(tmem_pv + c, o);
+        }
+        l_run *= corr;
+        m_ref = m_new;
+      }
+      const float bias = m_ref == -INFINITY ? 0.f : -m_ref * sl2;  // a row that sees nothing yet: every P is 0
+      float l_add = 0.f;
+      unsigned char* group = p_s + half * TILE_BYTES + row * 128;  // keys 0-63 or 64-127 of the tile
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {  // eight 16-byte chunks of 8 keys: P, rounded to bfloat16, swizzled K-major
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float p0 = fast_exp2(fmaf(v[8 * q + 2 * i], sl2, bias)), p1 = fast_exp2(fmaf(v[8 * q + 2 * i + 1], sl2, bias));
+          l_add += p0 + p1;
+          packed[i] = pack_bf16(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(group + ((q ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+      l_run += l_add;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor cores read what this thread wrote
       mbar_arrive(&p_full);
-      // the running output: O = O * corr + P.V, this thread's 32 channels
-      wait_for(&pv_full, t & 1, 3);
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      {
-        float v[32];
-        tmem_load32(tmem_pv, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], corr, v[i]);
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
+    // the output: O of the last product, over the row's sum
+    wait_for(&pv_full, (tiles_k - 1) & 1, 3);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    float o[32];
+    tmem_load32(tmem_pv, o);
     // the row's sum: both halves, through the Q tile's memory, which no product reads any more
     float* sums = reinterpret_cast<float*>(q_s);
     sums[half * 128 + row] = l_run;

@@ -78,6 +78,7 @@ class Engine:
             admit=self.runner.admit,
             launch=self._launch if self.config.run_ahead else None,
             collect=self._collect if self.config.run_ahead else None,
+            capacity=self.runner.decode_capacity,
         )
 
     @classmethod

@@ -210,11 +210,15 @@ class ModelRunner:
         graph = self._shape_graphs[key] = _DecodeGraph(self, 0, lengths=key[0], wanted=key[1])
         return graph
 
+    def decode_capacity(self, count: int) -> int:
+        """The number of rows that a step of ``count`` decoded tokens runs at: the bucket of its captured graph."""
+        if not (self.config.cuda_graphs and self.device.type == "cuda"):
+            return count
+        return next((b for b in _GRAPH_BUCKETS if b >= count), -(-count // 64) * 64)
+
     def _decode_graph_step(self, entries, arrays=None, previous=None):
         count = len(entries)
-        bucket = next((b for b in _GRAPH_BUCKETS if b >= count), None)
-        if bucket is None:
-            bucket = -(-count // 64) * 64
+        bucket = next((b for b in _GRAPH_BUCKETS if b >= count), -(-count // 64) * 64)
         graph = self._graphs.get(bucket)
         if graph is None:
             graph = self._graphs[bucket] = _DecodeGraph(self, bucket)

@@ -56,7 +56,7 @@ class Scheduler:
     def __init__(self, cache: CacheManager, execute: Callable, publish: Callable, *, prefill_chunk=2048,
                  prefill_requests=32, prefill_token_budget=None, decode_prefill_token_budget=None,
                  admit: Optional[Callable] = None, launch: Optional[Callable] = None,
-                 collect: Optional[Callable] = None):
+                 collect: Optional[Callable] = None, capacity: Optional[Callable] = None):
         if prefill_chunk <= 0 or prefill_requests <= 0:
             raise ValueError("invalid prefill budget")
         for name, value in (("prefill token budget", prefill_token_budget),
@@ -69,6 +69,7 @@ class Scheduler:
             raise ValueError("launch and collect come as a pair")
         self.launch, self.collect = launch, collect
         self.flight: Optional[_Flight] = None
+        self.capacity = capacity  # rows that a step of only decoded tokens runs at, for the statistics
         self.publish = publish
         self.admit_request = admit or cache.admit
         self.prefill_chunk = prefill_chunk
@@ -82,7 +83,8 @@ class Scheduler:
         self.stats = dict(
             tokens=0, completed=0, cancelled=0, steps=0, decode_rounds=0, prefill_rounds=0, decode_rows=0,
             max_active=0, prefill_tokens=0, max_prefill_tokens_per_turn=0, max_prefill_tokens_with_decoding=0,
-            max_tokens_per_step=0, preemptions=0, pages_in_use_max=0, steps_ahead=0,
+            max_tokens_per_step=0, preemptions=0, pages_in_use_max=0, steps_ahead=0, padded_decode_rows=0,
+            capacity_counts={},
         )
 
     # ------------------------------------------------------------------ requests in and out
@@ -264,6 +266,10 @@ class Scheduler:
         if decode_rows:
             st["decode_rounds"] += 1
             st["decode_rows"] += decode_rows
+            if not prefill_tokens and self.capacity is not None:
+                capacity = self.capacity(decode_rows)
+                st["padded_decode_rows"] += capacity - decode_rows
+                st["capacity_counts"][str(capacity)] = st["capacity_counts"].get(str(capacity), 0) + 1
         if prefill_tokens:
             st["prefill_rounds"] += 1
             st["prefill_tokens"] += prefill_tokens

@@ -405,6 +405,36 @@ def test_prompt_attention_on_tensor_cores(ops, h, kh, d, page, window, kernel, m
     _close(general, want, dtype, "general kernel")
 
 
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+def test_prompt_attention_when_the_maximum_keeps_growing(ops, kernel, monkeypatch):
+    """Random scores find their maximum in the first tile of keys. Here one channel of the keys grows with the
+    position, so the row maximum of the queries that look along it rises a little with every tile (the output so far
+    is rescaled on some tiles and left on others), falls for the queries that look the other way, and two keys far
+    apart stand out by a wide margin."""
+    cuda, ref = ops
+    monkeypatch.setattr(cuda, "prompt_attention", kernel)
+    dtype, h, kh, d, page = torch.bfloat16, 4, 2, 64, 64
+    lengths, starts = [520, 300, 1], [200, 0, 900]
+    cu, seq = _batch(lengths)
+    pos = torch.tensor([s + j for s, n in zip(starts, lengths) for j in range(n)], dtype=torch.int32, device=DEV)
+    contexts = [s + l for s, l in zip(starts, lengths)]
+    pages = sum(-(-c // page) for c in contexts) + 2
+    bt = _tables(contexts, page, pages, 9)
+    k, v = _pools(pages, kh, page, d, dtype, 60)
+    q = _rand((pos.numel(), h * d), dtype, 62)
+    q.view(-1, h, d)[:, :, 0] = torch.where(torch.arange(pos.numel(), device=DEV) % 3 == 0, -6.0, 6.0)[:, None].to(dtype)
+    tables = bt.cpu()
+    for r, context in enumerate(contexts):
+        where = torch.arange(context)
+        value = where / 30.0 + 25.0 * ((where == 310) | (where == 650))
+        k[tables[r, where // page].long().to(DEV), :, (where % page).to(DEV), 0] = value.to(DEV, dtype)[:, None]
+    scale = d ** -0.5
+    want = ref.paged_attention(q, k, v, bt, seq, pos, scale, None, page)
+    got = cuda.paged_attention(q, k, v, bt, seq, pos, scale, None, page, _Prompt(cu, lengths))
+    _close(got, want, dtype, "prompt attention under a rising maximum")
+    assert cuda.prefill_attention_tc_status() == 0
+
+
 class _Decode:
     decode_only = True
 

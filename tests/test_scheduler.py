@@ -262,3 +262,19 @@ def test_a_late_arrival_is_admitted_between_steps_ahead(mode):
     drain(s)
     assert a.output == expected(a.prompt, 20) and b.output == expected(b.prompt, 4) and c.output == expected(c.prompt, 5)
     assert not model.cache.live()
+
+
+def test_the_rows_a_decode_step_is_padded_to_are_counted():
+    model = FakeModel(tokens=256, requests=4)
+    s, _ = make(model, capacity=lambda rows: 1 << (rows - 1).bit_length())
+    reqs = [Request([i + 1] * 3, n) for i, n in enumerate((6, 6, 6, 2))]
+    for r in reqs:
+        s.submit(r)
+    drain(s)
+    st = s.stats
+    decode_only = [b for b in model.batches if all(n == 1 for _, n in b)]
+    assert sum(st["capacity_counts"].values()) == len(decode_only)
+    assert st["capacity_counts"] == {"4": sum(1 for b in decode_only if len(b) in (3, 4)),
+                                     **({"2": n} if (n := sum(1 for b in decode_only if len(b) == 2)) else {}),
+                                     **({"1": n} if (n := sum(1 for b in decode_only if len(b) == 1)) else {})}
+    assert st["padded_decode_rows"] == sum(1 for b in decode_only if len(b) == 3)
