@@ -18,6 +18,10 @@ namespace tc {
 constexpr int BK = 64;       // elements of K per tile row: 128 bytes of bfloat16, one swizzle row
 constexpr int UMMA_K = 16;   // K of one tcgen05.mma of 16-bit operands
 constexpr unsigned kSpinLimit = 1u << 22;
+// A waiting thread may be suspended this long (nanoseconds) per try before it polls again: the hardware wakes it
+// when the phase completes, so the wait is as prompt as a spin but does not fill the issue slots of the warps
+// that work (a third of all instructions of the attention kernel were polls before this).
+constexpr unsigned kSuspendNs = 2000;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
@@ -34,8 +38,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
   for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
     unsigned done;
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity), "r"(kSuspendNs) : "memory");
     if (done) return true;
   }
   return false;
