@@ -25,6 +25,7 @@ class FakeModel:
         self.hash = {}
         self.batches = []
         self.ahead = 0  # steps launched before the tokens of the step before them were read
+        self.fail_at = None  # the number of the step that raises instead of running, once
 
     def admit(self, rid):
         self.hash[rid] = 7
@@ -40,6 +41,9 @@ class FakeModel:
         return list(handle)
 
     def execute(self, entries, requests, previous=None):
+        if self.fail_at is not None and len(self.batches) == self.fail_at:
+            self.fail_at = None
+            raise RuntimeError("launch failed")
         self.batches.append([(e.request, len(e.tokens)) for e in entries])
         out = []
         for e in entries:
@@ -278,3 +282,28 @@ def test_the_rows_a_decode_step_is_padded_to_are_counted():
                                      **({"2": n} if (n := sum(1 for b in decode_only if len(b) == 2)) else {}),
                                      **({"1": n} if (n := sum(1 for b in decode_only if len(b) == 1)) else {})}
     assert st["padded_decode_rows"] == sum(1 for b in decode_only if len(b) == 3)
+
+
+@pytest.mark.parametrize("fail_at", [0, 1, 3, 6])
+def test_a_failed_step_is_raised_and_leaves_the_requests_where_they_were(fail_at):
+    """The reference puts the selected requests back in order and re-raises (src/akas/scheduling/scheduler.py:170-173).
+    Here nothing was taken out: the step after the failure plans the same tokens again."""
+    model = FakeModel(tokens=256, requests=4)
+    model.fail_at = fail_at
+    s, _ = make(model, prefill_chunk=4, prefill_requests=2)
+    reqs = [Request([i + 1] * n, 5) for i, n in enumerate((3, 9, 6))]
+    for r in reqs:
+        s.submit(r)
+    raised = 0
+    for _ in range(1000):
+        try:
+            if not s.turn():
+                break
+        except RuntimeError as error:
+            assert "launch failed" in str(error)
+            raised += 1
+    assert raised == 1
+    for r in reqs:
+        assert r.output == expected(r.prompt, 5) and r.finish_reason == "length"
+    assert not model.cache.live() and model.cache.free_pages() == 64
+    model.cache.check()
