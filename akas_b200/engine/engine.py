@@ -120,11 +120,17 @@ class Engine:
         self.scheduler.submit(request)
         return request
 
-    def warm_up(self, most: Optional[int] = None) -> None:
-        """Compiles, loads and captures what serving will need (the decode graphs of every batch size up to ``most``
-        requests, default ``max_requests``), so that the first requests do not pay for it."""
+    def warm_up(self, most: Optional[int] = None, tokens: Optional[int] = None) -> None:
+        """Compiles, loads and captures what serving will need, so that the first requests do not pay for it: the
+        decode graphs of every batch size up to ``most`` requests (default ``max_requests``), and a step of padding
+        for every size a step of prompt portions can have, up to ``tokens`` (default: the prefill token budget plus
+        one decoded token per request)."""
         self._check_thread()
         self.runner.capture_decode_graphs(most)
+        if tokens is None:
+            budget = self.config.prefill_token_budget or self.config.prefill_chunk * self.config.prefill_requests
+            tokens = budget + self.config.max_requests
+        self.runner.prepare_steps(tokens)
 
     def _execute(self, entries, requests) -> List[int]:
         logits = self.runner.step(entries)

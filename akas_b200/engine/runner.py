@@ -193,6 +193,29 @@ class ModelRunner:
             done.append(bucket)
         return done
 
+    def prepare_steps(self, most_tokens: int) -> List[int]:
+        """Runs a step of padding only for every number of tokens that an eager bfloat16 step can be padded to, up
+        to ``most_tokens``: whatever the kernels and the library behind the larger products set up per size (plans,
+        heuristics, tensor maps, workspaces) is then in place before the first request. Pages and state are left
+        alone. Returns the sizes."""
+        if self.device.type != "cuda" or self.dtype != torch.bfloat16:
+            return []
+        sizes = list(range(2 * _TOKEN_ROUNDING, -(-most_tokens // _TOKEN_ROUNDING) * _TOKEN_ROUNDING + 1, _TOKEN_ROUNDING))
+        for n in sizes:
+            lay = BatchLayout(n, 1, 1, len(self.cache.groups), self.cache.max_blocks)
+            ring, dev = self._staging(lay.size)
+            host = ring.take()
+            fill_batch(host.numpy(), lay, [], self.cache, pad_to=n)
+            host.numpy()[lay.logit_rows] = 0
+            dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
+            ring.copied()
+            ctx = self._context(dev, lay, n, self.config.context, False)
+            ctx.query_tiles = -(-n // 64)
+            ctx.query_tiles_wide = -(-n // 128)
+            self.model.forward(ctx, self.cache.views)
+        torch.cuda.synchronize(self.device)
+        return sizes
+
     def _repeated_shape(self, entries):
         """A captured graph for steps whose requests bring exactly these numbers of tokens, once that shape has come
         _SHAPE_REPEATS times (the equal portions of a long prompt, a batch of prompts of one length); else None.
