@@ -79,8 +79,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
   for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
     unsigned done;
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity), "r"(2000u) : "memory");
     if (done) return true;
   }
   return false;
