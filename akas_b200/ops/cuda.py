@@ -75,6 +75,10 @@ _SIGNATURES = {
         "akas_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "akas_gemm_tcgen05_status": [],
     },
+    "gemm_pair": {
+        "akas_gemm_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_gemm_pair_status": [],
+    },
     "gemm_stream": {
         "akas_stream_gemm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_int, c_void_p],
@@ -105,7 +109,7 @@ _functions = {}
 def libraries_for(dtype: torch.dtype) -> list:
     """The kernel files a model of this compute dtype needs."""
     names = ["elementwise", "conv", "rope", "attention", "sampling"]
-    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "gemm_stream", "skinny_gemm", "attention_prefill", "attention_prefill_tc", "attention_decode"]
+    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "gemm_pair", "gemm_stream", "skinny_gemm", "attention_prefill", "attention_prefill_tc", "attention_decode"]
     return names
 
 
@@ -296,24 +300,36 @@ def _skinny_fits(m: int, k: int) -> bool:
 
 
 _SKINNY_ROWS = 16
-# Which kernel runs the products of prompt portions (more than 16 tokens). "auto": the tcgen05 kernel where its
-# fused read-out saves a pass over memory (SwiGLU), cuBLASLt for the plain and residual products, which the
-# library's two-SM tiles still run faster; "tcgen05": the hand-written kernel everywhere; "library": cuBLASLt
-# everywhere (SwiGLU then runs as a kernel of its own).
+# Which kernel runs the products of prompt portions (more than 16 tokens). "auto": the hand-written tcgen05 kernels for
+# the fused gate/up + SwiGLU product where they are as fast as the library or faster (see _swiglu_route), cuBLASLt for
+# the plain and residual products, which the library's multicast-fed two-SM tiles still run faster; "tcgen05": the
+# hand-written kernels everywhere; "library": cuBLASLt everywhere (SwiGLU then runs as a kernel of its own).
 products = os.environ.get("AKAS_B200_PRODUCTS", "auto")
 if products not in ("auto", "tcgen05", "library"):
     raise ValueError(f"AKAS_B200_PRODUCTS must be auto, tcgen05 or library, got {products!r}")
 
 
-def _tcgen05_takes(n: int, k: int, fused: bool = False, channels: int = 0) -> bool:
-    """More tokens than the decode kernels take, a 16-byte row pitch, and the policy above. Under "auto" the fused
-    product must also have a tile (128 tokens x 128 channels) for every SM: with fewer, reading the weights is the
-    cost, and the library's narrow tiles spread that over more SMs."""
-    if n <= _SKINNY_ROWS or k % 8:
-        return False
+def _tcgen05_takes(n: int, k: int) -> bool:
+    """Whether the one-block tcgen05 kernel runs a plain or residual product: only when the policy says everywhere."""
+    return products == "tcgen05" and n > _SKINNY_ROWS and k % 8 == 0
+
+
+def _swiglu_route(n: int, k: int, channels: int) -> str:
+    """Which kernel runs the fused gate/up product of a prompt portion: "paired" (gemm_pair.cu), "block"
+    (gemm_tcgen05.cu) or "library" (cuBLASLt, then the SwiGLU kernel). Under "auto" by what measured fastest on the
+    LFM2 shapes (K 1,024 / 1,536 / 2,048; 256 to 8,192 tokens): the library below 2,048 tokens and for small K, the
+    paired kernel from K = 2,048 on (within 3 % of the library everywhere there, ahead at 2,048 tokens, and without the
+    [N, 2F] intermediate), the one-block kernel in between (ahead of both at K = 1,536)."""
+    if n <= _SKINNY_ROWS or k % 8 or channels % 8 or products == "library":
+        return "library"
+    pair_ok = paired_sms == "1" and -(-n // 256) * -(-channels // 128) >= _sm_count() // 2
     if products == "tcgen05":
-        return True
-    return products == "auto" and fused and -(-n // 128) * -(-channels // 128) >= _sm_count()
+        return "paired" if pair_ok else "block"
+    if n < 2048 or k < 1536:
+        return "library"
+    if k >= 2048 and pair_ok:
+        return "paired"
+    return "block" if -(-n // 128) * -(-channels // 128) >= _sm_count() else "library"
 
 
 _sms = 0
@@ -324,6 +340,31 @@ def _sm_count() -> int:
     if not _sms:
         _sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     return _sms
+
+
+# Whether the fused SwiGLU product of prompt portions runs on pairs of SMs (tcgen05.mma.cta_group::2, gemm_pair.cu)
+# where it has a tile of 256 tokens x 128 channels for every pair; "0" keeps it on the one-block kernel.
+paired_sms = os.environ.get("AKAS_B200_PAIRED_SMS", "1")
+if paired_sms not in ("0", "1"):
+    raise ValueError(f"AKAS_B200_PAIRED_SMS must be 0 or 1, got {paired_sms!r}")
+
+
+def paired_product(x, w, swiglu_out: bool = False):
+    """x [N, K] times w [O, K] transposed on pairs of SMs, bfloat16 out; with ``swiglu_out`` w is the stacked
+    [2F, K] gate and up matrices and the result is swiglu of the product, [N, F]."""
+    n, k = x.shape
+    o = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k or k % 8 or (swiglu_out and o % 16):
+        raise ValueError("paired_product takes bfloat16 [N, K] and [O, K] with K a multiple of 8 (and O of 16 for SwiGLU)")
+    out = torch.empty((n, o // 2 if swiglu_out else o), dtype=torch.bfloat16, device=x.device)
+    _check(_fn("gemm_pair", "akas_gemm_pair")(_ptr(_dense(x, "x")), _ptr(_dense(w, "w")), _ptr(out), n, o, k,
+                                             2 if swiglu_out else 0, _stream()), f"paired tcgen05 product [{n}x{k}] x [{o}x{k}]^T")
+    return out
+
+
+def gemm_pair_status() -> int:
+    """0 unless a bounded wait inside the paired-SM product kernel has run out on this device. Synchronises."""
+    return int(_fn("gemm_pair", "akas_gemm_pair_status")())
 
 
 def gemm_tcgen05_status() -> int:
@@ -391,8 +432,12 @@ def linear_swiglu(x, w_gate_up):
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _skinny(_dense(x, "x"), None, None, 0.0, False, _dense(w_gate_up, "w"), out, n, f2, k, 0, _OUT_SWIGLU)
         return out
-    if x.dtype == torch.bfloat16 and _tcgen05_takes(n, k, fused=True, channels=f2 // 2) and f2 % 16 == 0:
-        # SwiGLU in the read-out of the product: the [N, 2F] intermediate is never written
+    route = _swiglu_route(n, k, f2 // 2) if x.dtype == torch.bfloat16 and f2 % 16 == 0 else "library"
+    if route == "paired":
+        # SwiGLU in the read-out of the product, on pairs of SMs: each stages half of a 256-channel tile
+        return paired_product(x, w_gate_up, swiglu_out=True)
+    if route == "block":
+        # the same on single SMs: the [N, 2F] intermediate is never written
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _check(_fn("gemm_tcgen05", "akas_gemm_tcgen05")(_ptr(_dense(x, "x")), _ptr(_dense(w_gate_up, "w")), _ptr(out), n,
                                                        f2, k, 2, _stream()), f"tcgen05 SwiGLU product [{n}x{k}]")

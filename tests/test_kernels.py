@@ -193,6 +193,19 @@ def test_tensor_memory_products_for_prompt_portions(ops, m, k, o):
     assert cuda.gemm_tcgen05_status() == 0
 
 
+@pytest.mark.parametrize("m,k,o", [(17, 64, 48), (256, 128, 256), (300, 264, 520), (2048, 256, 512), (333, 2048, 2056),
+                                   (1000, 1024, 1160), (130, 2048, 6144)])
+def test_products_on_pairs_of_sms(ops, m, k, o):
+    """The cta_group::2 kernel (each block of a pair stages half of a 256-channel tile), both read-outs, at sizes that
+    leave ragged tiles in every direction and more tiles than pairs."""
+    cuda, ref = ops
+    x, w = _rand((m, k), torch.bfloat16, 5), _rand((o, k), torch.bfloat16, 6, 0.05)
+    _close(cuda.paired_product(x, w), x.double() @ w.double().T, torch.bfloat16, "bf16 out")
+    w2 = _rand((2 * o, k), torch.bfloat16, 8, 0.05)
+    _close(cuda.paired_product(x, w2, swiglu_out=True), ref.linear_swiglu(x, w2), torch.bfloat16, "swiglu")
+    assert cuda.gemm_pair_status() == 0
+
+
 def test_short_conv_decode_kernel_equals_the_general_one(ops):
     cuda, ref = ops
     c, taps = 72, 4
