@@ -2,16 +2,17 @@
 // tcgen05.mma.cta_group::2, float32 accumulation in the tensor memory of both SMs, epilogues fused into the read-out.
 //
 // A thread-block cluster of two blocks (two SMs) walks output tiles of 256 tokens x 256 channels. Each block stages
-// its own 128 token rows of x and HALF of the tile's channels of W (128 rows), 32 KB a stage instead of the 48 KB a
+// its own 128 token rows of x and HALF of the tile's channels of W (128 rows), 32 KB a step of K instead of the 48 KB a
 // lone block needs for a 128 x 256 tile: a product of the pair reads the 256 channels from both blocks' shared
 // memory. That halves what a block writes into and reads out of its shared memory per multiply-add, which is what
 // bounds the one-block kernel of gemm_tcgen05.cu (its TMA writes and operand reads ask for 192 bytes a cycle of a
 // shared memory that gives 128).
-//   warp 0   producer, in both blocks: TMA loads of the block's slice of x and of W into a six-stage ring. Every load
+//   warp 0   producer, in both blocks: TMA loads of the block's slice of x and of W into a ring of three stages of two
+//            64-wide steps of K each. Every load
 //            of either block counts its bytes on the LEADER's "full" barrier of the stage (the block of cluster rank
 //            0), on which the leader has announced the bytes of both.
 //   warp 1   tensor cores: both blocks allocate tensor memory together (two accumulators of 256 columns); one thread
-//            of the leader issues, per stage, four tcgen05.mma.cta_group::2 (M 256, N 256, K 16) and commits them to
+//            of the leader issues, per stage, eight tcgen05.mma.cta_group::2 (M 256, N 256, K 16) and commits them to
 //            the stage's "empty" barrier of BOTH blocks (multicast commit); after a tile's last stage it commits to
 //            both blocks' "accumulator full" barrier.
 //   warps 2-5 epilogue, in both blocks: each warp reads the 32 accumulator lanes (token rows) of its sub-partition of
@@ -32,9 +33,11 @@ namespace {
 
 constexpr int BM = 128;    // token rows a block stages; a pair's tile has 256
 constexpr int BN = 256;    // channels of a pair's tile; a block stages half of them
-constexpr int STAGES = 6;
+constexpr int STEPS = 2;    // 64-wide steps of K in a stage
+constexpr int STAGES = 3;
 constexpr int THREADS = 192;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, HALF_BYTES = A_BYTES + B_BYTES;
+constexpr int STAGE_BYTES = STEPS * HALF_BYTES;  // [x, W] of one step of K, then of the next
 enum { EPI_BF16 = 0, EPI_SWIGLU = 2 };  // the numbers of gemm_tcgen05.cu's read-outs
 
 __device__ int g_pair_status = 0;  // 0, or which bounded wait ran out last (1 producer, 2 tensor cores, 3 epilogue)
@@ -125,15 +128,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const int m0 = (tile / tiles_n) * 2 * BM + (int)rank * BM, n0 = (tile % tiles_n) * TILE_N;
         // this block's half of the tile's channels: rows of W
         const int w_row = EPI == EPI_SWIGLU ? (rank == 0 ? n0 : F + n0) : n0 + (int)rank * (BN / 2);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = 0; kb < k_blocks; kb += STEPS, ++it) {
           const int s = it % STAGES;
           wait_for(&empty_bar[s], ((it / STAGES) & 1) ^ 1, 1);
           if (*(volatile int*)&abort_s) break;
           unsigned char* a = smem + (size_t)s * STAGE_BYTES;
           const unsigned leader_full = peer_address(&full_bar[s], 0);
           if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);  // the bytes of both blocks
-          tma_load_2d_for(a, &map_x, kb * BK, m0, leader_full);
-          tma_load_2d_for(a + A_BYTES, &map_w, kb * BK, w_row, leader_full);
+#pragma unroll
+          for (int h = 0; h < STEPS; ++h) {  // a step past the end of K is filled with zeros
+            tma_load_2d_for(a + h * HALF_BYTES, &map_x, (kb + h) * BK, m0, leader_full);
+            tma_load_2d_for(a + h * HALF_BYTES + A_BYTES, &map_w, (kb + h) * BK, w_row, leader_full);
+          }
         }
         if (*(volatile int*)&abort_s) break;
       }
@@ -149,17 +155,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         wait_for(&acc_empty[acc], ((t >> 1) & 1) ^ 1, 2);  // both blocks' epilogues have drained this accumulator
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned d = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = 0; kb < k_blocks; kb += STEPS, ++it) {
           const int s = it % STAGES;
           wait_for(&full_bar[s], (it / STAGES) & 1, 2);
           if (*(volatile int*)&abort_s) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const unsigned char* a = smem + (size_t)s * STAGE_BYTES;
-          const uint64_t a_desc = smem_desc(a), b_desc = smem_desc(a + A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further along the swizzled row per step
-            umma_pair(d, a_desc + (uint64_t)(k * UMMA_K * 2 >> 4), b_desc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc,
-                      (kb | k) != 0 ? 1u : 0u);
+          for (int h = 0; h < STEPS; ++h) {
+            if (kb + h >= k_blocks) break;  // zeros: nothing to add
+            const uint64_t a_desc = smem_desc(a + h * HALF_BYTES), b_desc = smem_desc(a + h * HALF_BYTES + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further along the swizzled row per step
+              umma_pair(d, a_desc + (uint64_t)(k * UMMA_K * 2 >> 4), b_desc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc,
+                        (kb | h | k) != 0 ? 1u : 0u);
+          }
+          // One commit for eight products: a commit to both blocks costs the issuing thread about as much as four
+          // products do, so a stage holds two steps of K.
           umma_commit_pair(&empty_bar[s]);  // the stage is free in both blocks once these products have read it
         }
         if (*(volatile int*)&abort_s) break;

@@ -317,19 +317,18 @@ def _tcgen05_takes(n: int, k: int) -> bool:
 def _swiglu_route(n: int, k: int, channels: int) -> str:
     """Which kernel runs the fused gate/up product of a prompt portion: "paired" (gemm_pair.cu), "block"
     (gemm_tcgen05.cu) or "library" (cuBLASLt, then the SwiGLU kernel). Under "auto" by what measured fastest on the
-    LFM2 shapes (K 1,024 / 1,536 / 2,048; 256 to 8,192 tokens): the library below 2,048 tokens and for small K, the
-    paired kernel from K = 2,048 on (within 3 % of the library everywhere there, ahead at 2,048 tokens, and without the
-    [N, 2F] intermediate), the one-block kernel in between (ahead of both at K = 1,536)."""
+    LFM2 shapes (K 1,024 / 1,536 / 2,048; 256 to 8,192 tokens): the paired kernel from 1,536 tokens on at K = 2,048
+    (9 to 12 % ahead of the library from 2,048 tokens on) and from 4,096 tokens on at K = 1,536; the library for fewer
+    tokens and for K = 1,024, where its narrower tiles spread few tiles over more SMs."""
     if n <= _SKINNY_ROWS or k % 8 or channels % 8 or products == "library":
         return "library"
     pair_ok = paired_sms == "1" and -(-n // 256) * -(-channels // 128) >= _sm_count() // 2
+    block_ok = -(-n // 128) * -(-channels // 128) >= _sm_count()
     if products == "tcgen05":
         return "paired" if pair_ok else "block"
-    if n < 2048 or k < 1536:
+    if n < 1536 or k < 1536 or (k < 2048 and n < 4096):
         return "library"
-    if k >= 2048 and pair_ok:
-        return "paired"
-    return "block" if -(-n // 128) * -(-channels // 128) >= _sm_count() else "library"
+    return "paired" if pair_ok else "block" if block_ok and n >= 2048 else "library"
 
 
 _sms = 0
