@@ -298,8 +298,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const uint64_t b = smem_desc(k_s + s * TILE_BYTES);
 #pragma unroll
       for (int k = 0; k < D / UMMA_K; ++k) umma_if(lead, tmem_s, desc_q + (uint64_t)(k * 2), b + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
+      umma_commit_if(lead, &s_full);      // first what the softmax warps wait for: a commit costs the issuing thread time
       umma_commit_if(lead, &k_empty[s]);
-      umma_commit_if(lead, &s_full);
     };
     wait_warp(&q_full, 0, 2);
     scores(0);
@@ -317,8 +317,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
       for (int j = 0; j < BKEYS / UMMA_K; ++j)  // 16 keys a step: P advances by 8 columns, V by 16 rows of 128 bytes
         umma_ts_if(lead, tmem_pv, tmem_p + j * 8, b + (uint64_t)(j * (16 * 128 >> 4)), idesc_pv, (t | j) ? 1u : 0u);
-      umma_commit_if(lead, &v_empty[s]);
       umma_commit_if(lead, &pv_full);
+      umma_commit_if(lead, &v_empty[s]);
     }
   } else {
     // ------------------------------------------------------------------ softmax and read-out: warps 2..9

@@ -273,6 +273,9 @@ def linear(x, w, out_dtype=None, residual=None):
         return out
     if k % 8:
         raise ValueError(f"bfloat16 matrix products need an inner size that is a multiple of 8, got {k}")
+    if _tcgen05_takes(n, k) and residual is None and target == torch.bfloat16 and paired_sms == "1" and \
+            -(-n // 256) * -(-o // 256) >= _sm_count() // 2:
+        return paired_product(x, w)  # a plain product with a tile for every pair of SMs
     if _tcgen05_takes(n, k) and (residual is not None or target == torch.bfloat16):
         # prompt portions: the hand-written tcgen05 kernel, residual add fused into its read-out
         out = residual if residual is not None else torch.empty((n, o), dtype=torch.bfloat16, device=x.device)
