@@ -128,3 +128,27 @@ def test_captured_steps_agree_with_the_plain_model(key, dtype, tmp_path):
         places = [p for at in range(0, n, 10) for p in (at + 8, at + 9)]
         bad = traces.first_bad(got[rid], want[rid][places], TOL[dtype])
         assert bad is None, (rid, bad, traces.worst(got[rid], want[rid][places]))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("key", ["a", "c"])
+def test_whole_prompts_through_the_tensor_memory_products(key, tmp_path, monkeypatch):
+    """The default policy gives prompt-sized products of models this small to the library. Here every such product
+    runs on the hand-written tcgen05 kernels: with the policy "tcgen05", and with a device that claims two SMs, so
+    that the kernel for pairs of SMs (a tile for every pair) takes the gate/up and the plain products, ragged tiles
+    included, and the one-block kernel the residual ones."""
+    from akas_b200.ops import cuda
+
+    monkeypatch.setattr(cuda, "products", "tcgen05")
+    monkeypatch.setattr(cuda, "_sms", 2)
+    calls = {"paired": 0}
+    paired = cuda.paired_product
+
+    def counted(*args, **kwargs):
+        calls["paired"] += 1
+        return paired(*args, **kwargs)
+
+    monkeypatch.setattr(cuda, "paired_product", counted)
+    _run_modes(key, "bfloat16", "cuda:0", None, tmp_path, ["whole", "portions"])
+    assert calls["paired"] > 0
+    assert cuda.gemm_pair_status() == 0 and cuda.gemm_tcgen05_status() == 0
