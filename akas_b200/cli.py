@@ -3,6 +3,8 @@
     python -m akas_b200 inspect  --model DIR
     python -m akas_b200 generate --model DIR --prompt "5 17 3" [--max-tokens 128] [--context N]
                                  [--raw] [--out FILE.json] [--device 0] [--config JSON]
+                                 [--temperature T --top-k K --top-p P --seed S --softcap C
+                                  --repetition-penalty Q --repetition-window W --ignore-eos]
     python -m akas_b200 random   --out DIR --config JSON|FILE [--seed 0] [--dtype bfloat16]
     python -m akas_b200 bench    --model DIR [--batches 1 8] [--prompts 2048] [--generated 128] ...
     python -m akas_b200 replay   --model DIR --dtype float32 --out DIR --max-tokens N   (bin/trace_run)
@@ -83,7 +85,8 @@ def _generate(args):
     config = replace(config, max_requests=min(config.max_requests, 8), max_tokens=None)
     with Engine(args.model, config=config) as engine:
         result = engine.generate(args.prompt, max_tokens=args.max_tokens, temperature=args.temperature,
-                                 top_k=args.top_k, top_p=args.top_p, seed=args.seed,
+                                 top_k=args.top_k, top_p=args.top_p, seed=args.seed, softcap=args.softcap,
+                                 repetition_penalty=args.repetition_penalty, repetition_window=args.repetition_window,
                                  eos_token_id=None if args.ignore_eos else engine.runner.model_config.eos_token_id)
     print(" ".join(str(t) for t in result["generated_tokens"]))
     if args.out:
@@ -146,6 +149,9 @@ def main(argv=None):
     generate.add_argument("--temperature", type=float, default=0.0)
     generate.add_argument("--top-k", type=int, default=0)
     generate.add_argument("--top-p", type=float, default=1.0)
+    generate.add_argument("--softcap", type=float, default=0.0, help="c > 0: logits become c tanh(logit / c)")
+    generate.add_argument("--repetition-penalty", type=float, default=1.0)
+    generate.add_argument("--repetition-window", type=int, default=96)
     generate.add_argument("--seed", type=int)
     generate.add_argument("--ignore-eos", action="store_true")
     generate.set_defaults(run=_generate)

@@ -13,6 +13,12 @@
 // no sort is needed: both cuts are thresholds on the logit, found by bisection over the ordered
 // bit patterns of float32 with one counting or summing pass over the row per step.
 // One block of 1024 threads per row. Softmax terms and sums are float32.
+//
+// adjust: the two stages that sampler applies before those, on the logits in place, per row:
+//   softcap c > 0:  x = c * tanh(x / c)                                   (kernel.py:559)
+//   penalty q != 1: a token found among the row's recent tokens (a window of the request's last generated
+//                   tokens, -1 where there are fewer) becomes x / q if x > 0, else x * q, once however often it
+//                   was generated                                          (kernel.py:560-575)
 #include <math.h>
 
 #include "common.cuh"
@@ -199,6 +205,36 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   if (my_last >= 0) atomicMax(&last_kept, my_last);
   __syncthreads();
   if (threadIdx.x == 0) out[row] = pick < V ? pick : last_kept;
+}
+
+// One block per (slice of 4,096 logits, row): the softcap over the slice, then one thread per entry of the history
+// whose token lies in the slice and did not occur earlier in the history applies the penalty.
+__global__ void adjust_logits_kernel(float* __restrict__ logits, const float* __restrict__ softcap,
+                                     const float* __restrict__ penalty, const int* __restrict__ history, int W, int V) {
+  const int row = blockIdx.y, v0 = blockIdx.x * 4096, v1 = min(V, v0 + 4096);
+  float* x = logits + (size_t)row * V;
+  const float cap = softcap[row], q = penalty[row];
+  if (cap > 0.f)
+    for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) x[i] = cap * tanhf(x[i] / cap);
+  if (q == 1.f) return;
+  __syncthreads();
+  const int* seen = history + (size_t)row * W;
+  for (int w = threadIdx.x; w < W; w += blockDim.x) {
+    const int token = seen[w];
+    if (token < v0 || token >= v1) continue;
+    bool first = true;
+    for (int e = 0; e < w; ++e) first = first && seen[e] != token;
+    if (first) x[token] = x[token] > 0.f ? x[token] / q : x[token] * q;
+  }
+}
+
+// logits: float32 [M, V], changed in place; softcap, penalty: float32 [M]; history: int32 [M, W], -1 where empty.
+AKAS_API int akas_adjust_logits(float* logits, const float* softcap, const float* penalty, const int* history, int W,
+                                int M, int V, cudaStream_t stream) {
+  if (M <= 0 || V <= 0) return 0;
+  if (W < 0 || M > 65535) return (int)cudaErrorInvalidValue;
+  adjust_logits_kernel<<<dim3((V + 4095) / 4096, M), 256, 0, stream>>>(logits, softcap, penalty, history, W, V);
+  return launch_status();
 }
 
 AKAS_API int akas_sample(const float* logits, const float* temperature, const int* top_k, const float* top_p,

@@ -104,7 +104,8 @@ class Engine:
     # ------------------------------------------------------------------ requests
 
     def submit(self, prompt, *, max_tokens, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
-               seed: Optional[int] = None, eos_token_id: Optional[int] = None) -> Request:
+               seed: Optional[int] = None, eos_token_id: Optional[int] = None, softcap: float = 0.0,
+               repetition_penalty: float = 1.0, repetition_window: int = 96) -> Request:
         prompt = list(prompt)
         vocab = self.runner.vocab_size
         if not prompt or any(type(t) is not int or t < 0 or t >= vocab for t in prompt):
@@ -115,8 +116,11 @@ class Engine:
             raise ValueError("generation exceeds context capacity")
         if not 0.0 < top_p <= 1.0 or top_k < 0 or temperature < 0:
             raise ValueError("need temperature >= 0, top_k >= 0 and 0 < top_p <= 1")
+        if softcap < 0 or repetition_penalty <= 0 or repetition_window < 0:
+            raise ValueError("need softcap >= 0, repetition_penalty > 0 and repetition_window >= 0")
         request = Request(prompt, max_tokens, temperature=float(temperature), top_k=int(top_k), top_p=float(top_p),
-                          seed=seed, eos_token_id=eos_token_id)
+                          seed=seed, eos_token_id=eos_token_id, softcap=float(softcap),
+                          repetition_penalty=float(repetition_penalty), repetition_window=int(repetition_window))
         self.scheduler.submit(request)
         return request
 
@@ -191,7 +195,8 @@ class Engine:
 
     def generate(self, prompts: Sequence[Sequence[int]], *, max_tokens: int = 128, temperature: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, seed: Optional[int] = None,
-                 eos_token_id: Optional[int] = None) -> List[dict]:
+                 eos_token_id: Optional[int] = None, softcap: float = 0.0, repetition_penalty: float = 1.0,
+                 repetition_window: int = 96) -> List[dict]:
         """Generates for every prompt (token ids) and returns, per prompt, what the reference's
         ``generate`` returns (src/akas/generation/greedy.py:110-114): ``prompt_tokens``,
         ``generated_tokens`` and ``text`` (``None``: this engine holds no tokenizer), plus ``finish_reason``.
@@ -200,7 +205,8 @@ class Engine:
         batch = [prompts] if single else list(prompts)
         requests = [
             self.submit(p, max_tokens=max_tokens, temperature=temperature, top_k=top_k, top_p=top_p,
-                        seed=None if seed is None else seed + i, eos_token_id=eos_token_id)
+                        seed=None if seed is None else seed + i, eos_token_id=eos_token_id, softcap=softcap,
+                        repetition_penalty=repetition_penalty, repetition_window=repetition_window)
             for i, p in enumerate(batch)
         ]
         while self.step():

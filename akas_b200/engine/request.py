@@ -30,6 +30,9 @@ class Request:
     temperature: float = 0.0
     top_k: int = 0
     top_p: float = 1.0
+    softcap: float = 0.0  # 0: none
+    repetition_penalty: float = 1.0  # 1: none
+    repetition_window: int = 96  # how many of the last generated tokens the penalty looks at
     seed: Optional[int] = None
     eos_token_id: Optional[int] = None
     finish_reason: Optional[str] = None  # "length", "stop" (end-of-sequence token) or "cancelled"
@@ -49,6 +52,14 @@ class Request:
     def pending_tokens(self) -> int:
         """Tokens the cache does not hold yet; a token that is still in flight counts as the last of them."""
         return len(self.prompt) + len(self.output) + self.inflight - self.offset
+
+    @property
+    def adjusts_logits(self) -> bool:
+        return self.softcap > 0 or self.repetition_penalty != 1.0
+
+    def recent(self) -> List[int]:
+        """The generated tokens that the repetition penalty looks at."""
+        return self.output[-self.repetition_window:] if self.repetition_window > 0 else []
 
     def uniform(self) -> float:
         """The uniform number for the next generated token: a function of (seed, index of that token) only,

@@ -314,7 +314,8 @@ class Scheduler:
     def _plan_ahead(self) -> Optional[List[Request]]:
         """The requests of the next decode step, if it can be launched before the step in flight has been read:
         the one in flight decodes only, nobody waits who could be admitted, every running request is in it with
-        nothing but its coming token outstanding, and pages are free for all without preempting. Requests that
+        nothing but its coming token outstanding and no repetition penalty, and pages are free for all without
+        preempting. Requests that
         reach their limit with the token in flight are left out. ``None``: plan in full after landing."""
         flight, cache = self.flight, self.cache
         if not flight.decode_only or (self.pending and cache.free_slots() > 0):
@@ -324,6 +325,8 @@ class Scheduler:
         for request in self.running:
             if id(request) not in members or request.inflight != 1 or request.pending_tokens() != 1:
                 return None
+            if getattr(request, "repetition_penalty", 1.0) != 1.0:
+                return None  # its penalty needs the token in flight on the host before the next one is sampled
             if len(request.output) + request.inflight < request.limit:
                 ahead.append(request)
         if not ahead:

@@ -100,6 +100,7 @@ _SIGNATURES = {
     "sampling": {
         "akas_argmax": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "akas_adjust_logits": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
 }
 
@@ -618,6 +619,18 @@ def argmax(logits):
     _check(_fn("sampling", "akas_argmax")(_ptr(_dense(logits, "logits")), _ptr(out), _ptr(part_val), _ptr(part_idx), m,
                                          v, parts, _stream()), "argmax", kernels=2)
     return out
+
+
+def adjust_logits(logits, softcap, penalty, history):
+    """In place on float32 logits [M, V]: softcap (float32 [M], 0 = none), then the repetition penalty (float32 [M],
+    1 = none) on the tokens of ``history`` (int32 [M, W], -1 where empty)."""
+    m, v = logits.shape
+    if logits.dtype != torch.float32 or history.dtype != torch.int32 or history.shape[0] != m:
+        raise ValueError("adjust_logits takes float32 logits [M, V] and an int32 history [M, W]")
+    _check(_fn("sampling", "akas_adjust_logits")(_ptr(_dense(logits, "logits")), _ptr(_dense(softcap, "softcap")),
+                                                 _ptr(_dense(penalty, "penalty")), _ptr(_dense(history, "history")),
+                                                 history.shape[1], m, v, _stream()), "adjust_logits")
+    return logits
 
 
 def sample(logits, temperature, top_k, top_p, uniform):

@@ -197,6 +197,21 @@ def sample(logits, temperature, top_k, top_p, uniform):
     return out
 
 
+def adjust_logits(logits, softcap, penalty, history):
+    """The stages before top-k of the reference's sampler (src/akas/ops/vocabulary/kernel.py:556-577), in place:
+    x = c tanh(x / c) where the row's softcap c > 0; then every token of the row's history (-1: none), once, becomes
+    x / q if x > 0 else x * q where the row's penalty q != 1."""
+    for r in range(logits.shape[0]):
+        c, q = float(softcap[r]), float(penalty[r])
+        if c > 0:
+            logits[r] = c * torch.tanh(logits[r] / c)
+        if q != 1.0:
+            tokens = torch.unique(history[r][history[r] >= 0]).long()
+            x = logits[r, tokens]
+            logits[r, tokens] = torch.where(x > 0, x / q, x * q)
+    return logits
+
+
 def take_tokens(token_ids, source, previous):
     live = source >= 0
     token_ids[live] = previous[source[live].long()]

@@ -1,9 +1,9 @@
 """From the logits of a step to one token per request: greedy, or temperature with top-k and top-p.
 
 kreasof-ai/akas samples LFM2 greedily on the device, ties to the lowest id
-(src/akas/ops/vocabulary/kernel.py:112-153). Temperature, top-k and top-p follow the stages of its one
-stochastic sampler (src/akas/ops/vocabulary/kernel.py:515-671): the uniform number comes from the host,
-one per (request, generated index), so results do not depend on batch composition.
+(src/akas/ops/vocabulary/kernel.py:112-153). Softcap, repetition penalty, top-k, temperature and top-p follow the
+stages of its one stochastic sampler, in its order (src/akas/ops/vocabulary/kernel.py:515-671): the uniform number
+comes from the host, one per (request, generated index), so results do not depend on batch composition.
 """
 
 from __future__ import annotations
@@ -27,6 +27,16 @@ class Sampler:
     def launch(self, logits: torch.Tensor, requests: Sequence) -> torch.Tensor:
         """The same without waiting for the device: the M token ids as an int32 device tensor. The uniform number
         of a request is the one of the token it is about to generate, counting tokens that are still in flight."""
+        if any(r.adjusts_logits for r in requests):
+            window = max(1, max(len(r.recent()) for r in requests))
+            history = torch.full((len(requests), window), -1, dtype=torch.int32)
+            for row, r in enumerate(requests):
+                recent = r.recent() if r.repetition_penalty != 1.0 else []
+                if recent:
+                    history[row, : len(recent)] = torch.tensor(recent, dtype=torch.int32)
+            knobs = torch.tensor([[r.softcap, r.repetition_penalty] for r in requests], dtype=torch.float32).t().contiguous()
+            knobs = knobs.to(self.device, non_blocking=True)
+            logits = self.ops.adjust_logits(logits, knobs[0], knobs[1], history.to(self.device, non_blocking=True))
         if all(r.temperature <= 0 for r in requests):
             return self.ops.argmax(logits)
         params = torch.tensor(

@@ -200,3 +200,31 @@ def test_trace_run_program(dtype, tmp_path):
                 assert np.abs(data[row] - ref).max() <= TOL[dtype] * np.abs(want[e["id"]]).max(), (s["step"], e["id"], k)
                 row += 1
             at[e["id"]] += len(e["tokens"])
+
+
+def test_softcap_and_repetition_penalty(tmp_path):
+    """Greedy generation under a repetition penalty: the same tokens alone and beside other requests, none of the
+    last `window` tokens chosen again while an unpenalised token is within reach, and the plain recomputation with the
+    same rule applied to its logits agrees."""
+    folder = tiny.make_folder(tiny.TINY_A, seed=21, dtype="float32", folder=tmp_path / "m")
+    cfg, w = plain.load_folder(folder)
+    prompts = tiny.prompts(cfg["vocab_size"], [9, 20, 5], seed=3)
+    knobs = dict(softcap=5.0, repetition_penalty=4.0, repetition_window=6)
+
+    def expected(prompt, n):
+        tokens, out = list(prompt), []
+        for _ in range(n):
+            x = plain.forward(cfg, w, tokens)[-1].double()
+            x = knobs["softcap"] * torch.tanh(x / knobs["softcap"])
+            for t in set(out[-knobs["repetition_window"]:]):
+                x[t] = x[t] / knobs["repetition_penalty"] if x[t] > 0 else x[t] * knobs["repetition_penalty"]
+            out.append(int(torch.argmax(x)))
+            tokens.append(out[-1])
+        return out
+
+    with _engine(folder, "float32", tiny.PAGE["a"]) as engine:
+        alone = engine.generate(prompts[0], max_tokens=12, **knobs)["generated_tokens"]
+        batch = engine.generate(prompts, max_tokens=12, **knobs)
+        plain_run = engine.generate(prompts[0], max_tokens=12)["generated_tokens"]
+    assert batch[0]["generated_tokens"] == alone == expected(prompts[0], 12)
+    assert alone != plain_run

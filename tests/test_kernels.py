@@ -545,3 +545,28 @@ def test_sample(ops):
     freq = torch.bincount(picks.long(), minlength=4).float() / 4096
     want = torch.softmax(small[0] / 0.8, dim=-1)
     assert (freq - want).abs().max() < 0.03
+
+
+@pytest.mark.parametrize("m,v,w", [(1, 300, 5), (5, 1000, 17), (3, 65536, 96), (2, 4099, 1)])
+def test_adjust_logits(ops, m, v, w):
+    """Softcap, then the repetition penalty once per token of the history (tokens repeated in the history, empty
+    places, rows without either)."""
+    cuda, ref = ops
+    logits = _rand((m, v), torch.float32, 31, 4.0)
+    g = torch.Generator().manual_seed(32)
+    history = torch.randint(0, v, (m, w), generator=g, dtype=torch.int32)
+    history[:, w // 2:] = history[:, : w - w // 2].clone()  # every token of the first half again
+    if w > 2:
+        history[0, -1] = -1
+    history = history.to(DEV)
+    softcap = torch.tensor([0.0, 15.0, 3.0, 0.0, 7.5][:m], dtype=torch.float32, device=DEV)
+    penalty = torch.tensor([2.4, 1.0, 1.3, 0.5, 2.4][:m], dtype=torch.float32, device=DEV)
+    want = ref.adjust_logits(logits.clone(), softcap, penalty, history)
+    got = cuda.adjust_logits(logits.clone(), softcap, penalty, history)
+    assert torch.allclose(got, want, rtol=1e-6, atol=1e-6), (got - want).abs().max()
+    # and what it is for: the argmax moves away from a penalised token
+    row = torch.zeros((1, v), dtype=torch.float32, device=DEV)
+    row[0, 7], row[0, 9] = 2.0, 1.5
+    seen = torch.tensor([[7]], dtype=torch.int32, device=DEV)
+    one, none = torch.tensor([2.0], device=DEV), torch.tensor([0.0], device=DEV)
+    assert int(cuda.argmax(cuda.adjust_logits(row.clone(), none, one, seen))) == 9

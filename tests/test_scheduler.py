@@ -307,3 +307,17 @@ def test_a_failed_step_is_raised_and_leaves_the_requests_where_they_were(fail_at
         assert r.output == expected(r.prompt, 5) and r.finish_reason == "length"
     assert not model.cache.live() and model.cache.free_pages() == 64
     model.cache.check()
+
+
+def test_a_repetition_penalty_keeps_the_host_in_step():
+    """The penalty of a request looks at the tokens it has generated: the step after cannot be launched before the
+    token in flight is on the host."""
+    model = FakeModel(tokens=256, requests=4)
+    s, _ = make(model)
+    reqs = [Request([i + 1] * 3, 6) for i in range(2)]
+    reqs[1].repetition_penalty = 1.3
+    for r in reqs:
+        s.submit(r)
+    drain(s)
+    assert model.ahead == 0 and s.stats["steps_ahead"] == 0
+    assert all(r.output == expected(r.prompt, 6) for r in reqs)
