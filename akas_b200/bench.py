@@ -139,15 +139,26 @@ def measure_decode(runner: ModelRunner, batch: int, prefix: int, steps: int, war
                 launches=runner.ops.launch_count - launches_before)
 
 
+def case_lengths(batch: int, prompt: int, mixed: bool) -> List[int]:
+    """Prompt length per slot: all ``prompt``, or staggered as the reference staggers them
+    (src/akas/benchmarking/cases.py:30-35)."""
+    return [max(1, prompt - i % min(prompt, 7)) if mixed else prompt for i in range(batch)]
+
+
 def run_matrix(model_dir, config, batches=(1, 8), prompts=(2048,), generated=128, repeats=5, warmup=1, seed=17,
-               prefill_chunk=None) -> dict:
-    """The reference's pp/tg matrix (src/akas/benchmarking/cases.py:8-42): for every (batch, prompt length)
-    the median prefill and decode tokens a second over ``repeats`` repetitions after ``warmup``."""
+               prefill_chunk=None, depths=(0,), mixed=False) -> dict:
+    """The reference's pp/tg matrix (src/akas/benchmarking/cases.py:8-61): for every (batch, prompt length, depth)
+    the median prefill and decode tokens a second over ``repeats`` repetitions after ``warmup``. ``depth``: tokens
+    already in the cache of every request before its measured prompt; ``mixed``: prompt lengths staggered over the
+    slots."""
     from dataclasses import replace
 
-    need = max(batches) * (max(prompts) + generated + 64)
+    if any(d < 0 for d in depths) or generated < 1 or min(batches) < 1 or min(prompts) < 1:
+        raise ValueError("positive batch/prompt/generation and nonnegative depth required")
+    longest = max(depths) + max(prompts) + generated
+    need = max(batches) * (longest + 64)
     config = replace(config, max_requests=max(config.max_requests, max(batches)),
-                     context=max(config.context, max(prompts) + generated + 1), max_tokens=None)
+                     context=max(config.context, longest + 1), max_tokens=None)
     if config.pool_tokens < need:
         config = replace(config, max_tokens=need)
     runner = ModelRunner(model_dir, config)
@@ -155,37 +166,65 @@ def run_matrix(model_dir, config, batches=(1, 8), prompts=(2048,), generated=128
     rows = []
     for batch in batches:
         for prefix in prompts:
-            pp, tg = [], []
-            for rep in range(warmup + repeats):
-                data = synthetic_prompts(batch, prefix, runner.vocab_size, seed)
-                ids = [f"m{j}" for j in range(batch)]
+            for depth in depths:
+                lengths = case_lengths(batch, prefix, mixed)
+                pp, tg = [], []
+                for rep in range(warmup + repeats):
+                    data = [p[:n] for p, n in zip(synthetic_prompts(batch, prefix, runner.vocab_size, seed), lengths)]
+                    ids = [f"m{j}" for j in range(batch)]
+                    if depth:
+                        fill_requests(runner, synthetic_prompts(batch, depth, runner.vocab_size, seed + 1), chunk, ids)
 
-                def prefill():
-                    fill_requests(runner, [p[:-1] for p in data], chunk, ids)
-                    logits = runner.step([StepEntry(rid, (p[-1],), (0,)) for rid, p in zip(ids, data)])
-                    return runner.ops.argmax(logits)
+                    def prefill():
+                        fill_requests(runner, [p[:-1] for p in data], chunk, ids)
+                        logits = runner.step([StepEntry(rid, (p[-1],), (0,)) for rid, p in zip(ids, data)])
+                        return runner.ops.argmax(logits)
 
-                holder = {}
-                pp_ms = _event_ms(lambda: holder.setdefault("t", prefill()))
-                tokens = holder["t"]
+                    holder = {}
+                    pp_ms = _event_ms(lambda: holder.setdefault("t", prefill()))
+                    tokens = holder["t"]
 
-                def decode():
-                    t = tokens
-                    for _ in range(generated - 1):
-                        host = t.tolist()
-                        logits = runner.step([StepEntry(rid, (host[j],), (0,)) for j, rid in enumerate(ids)])
-                        t = runner.ops.argmax(logits)
+                    def decode():
+                        t = tokens
+                        for _ in range(generated - 1):
+                            host = t.tolist()
+                            logits = runner.step([StepEntry(rid, (host[j],), (0,)) for j, rid in enumerate(ids)])
+                            t = runner.ops.argmax(logits)
 
-                tg_ms = _event_ms(decode)
-                for rid in ids:
-                    runner.release(rid)
-                if rep >= warmup:
-                    pp.append(batch * prefix / (pp_ms / 1e3))
-                    tg.append(batch * (generated - 1) / (tg_ms / 1e3))
-            rows.append(dict(batch=batch, prompt=prefix, generated=generated,
-                             prefill_tokens_per_s=statistics.median(pp), decode_tokens_per_s=statistics.median(tg)))
+                    tg_ms = _event_ms(decode)
+                    for rid in ids:
+                        runner.release(rid)
+                    if rep >= warmup:
+                        pp.append(sum(lengths) / (pp_ms / 1e3))
+                        if generated > 1:
+                            tg.append(batch * (generated - 1) / (tg_ms / 1e3))
+                rows.append(dict(batch=batch, prompt=prefix, generated=generated, depth=depth, mixed=mixed,
+                                 prefill_tokens_per_s=statistics.median(pp),
+                                 decode_tokens_per_s=statistics.median(tg) if tg else None))
     return dict(protocol="native-token-step-v2", dtype=config.dtype, seed=seed, repeats=repeats, warmup=warmup,
                 prefill_chunk=chunk, rows=rows)
+
+
+def compare_reports(report: dict, baseline: dict, max_regression: float = 0.1) -> List[dict]:
+    """Every measured case against the same case of an earlier report, as the reference's bench gate does
+    (src/akas/cli.py:527, 666-680): raises if the baseline lacks a case, returns the changes, and marks a case whose
+    prefill or decode rate fell by more than ``max_regression`` of the baseline's."""
+    if not 0 <= max_regression < 1:
+        raise ValueError("invalid regression setting")
+    key = lambda row: (row["batch"], row["prompt"], row.get("generated"), row.get("depth", 0), row.get("mixed", False))
+    before = {key(row): row for row in baseline.get("rows", [])}
+    changes = []
+    for row in report["rows"]:
+        old = before.get(key(row))
+        if old is None:
+            raise ValueError("baseline must cover every measured case")
+        change = dict(batch=row["batch"], prompt=row["prompt"], depth=row.get("depth", 0), mixed=row.get("mixed", False))
+        for name in ("prefill_tokens_per_s", "decode_tokens_per_s"):
+            if row.get(name) and old.get(name):
+                change[name + "_ratio"] = row[name] / old[name]
+        change["regressed"] = any(v < 1 - max_regression for k, v in change.items() if k.endswith("_ratio"))
+        changes.append(change)
+    return changes
 
 
 # --------------------------------------------------------------------------- single kernels

@@ -12,8 +12,9 @@
 Where the reference has an option, its name and meaning are kept: ``--model``, ``--prompt``,
 ``--max-tokens`` (default 128), ``--context``, ``--raw``, ``--out`` (the generated token ids as JSON),
 ``--device`` (ordinal), ``--config`` (a JSON object of engine options); for ``bench``: ``--batches``,
-``--prompts``, ``--generated`` (default 128), ``--prefill-chunk``, ``--repeats`` (default 5), ``--warmup``
-(default 1), ``--seed`` (default 17), ``--out``. ``--definition`` and ``--bundle`` have no meaning here
+``--prompts``, ``--depths`` (default 0), ``--generated`` (default 128), ``--mixed``, ``--prefill-chunk``,
+``--repeats`` (default 5), ``--warmup`` (default 1), ``--seed`` (default 17), ``--out``, ``--baseline`` and
+``--max-regression`` (default 0.1). ``--definition`` and ``--bundle`` have no meaning here
 (the model folder names its architecture; nothing is compiled ahead of time) and are accepted and ignored.
 This engine holds no tokenizer: ``--prompt`` is a list of token ids, and the output is token ids.
 """
@@ -107,13 +108,20 @@ def _random(args):
 def _bench(args):
     from .bench import run_matrix
 
+    from .bench import compare_reports
+
+    baseline = json.loads(args.baseline.read_text()) if args.baseline else None
     report = run_matrix(args.model, _engine_config(args), batches=args.batches, prompts=args.prompts,
                         generated=args.generated, repeats=args.repeats, warmup=args.warmup, seed=args.seed,
-                        prefill_chunk=args.prefill_chunk)
+                        prefill_chunk=args.prefill_chunk, depths=args.depths, mixed=args.mixed)
+    if baseline is not None:
+        report["changes"] = compare_reports(report, baseline, args.max_regression)
     text = json.dumps(report, indent=2)
     print(text)
     if args.out:
         args.out.write_text(text + "\n")
+    if baseline is not None and any(change["regressed"] for change in report["changes"]):
+        raise SystemExit(f"throughput fell by more than {args.max_regression:.0%} against {args.baseline}")
 
 
 def _replay(args):
@@ -170,7 +178,12 @@ def main(argv=None):
     bench.add_argument("--config", type=_settings, default={})
     bench.add_argument("--batches", type=int, nargs="+", default=[1, 8])
     bench.add_argument("--prompts", type=int, nargs="+", default=[2048])
+    bench.add_argument("--depths", type=int, nargs="+", default=[0], help="tokens already cached before the prompt")
     bench.add_argument("--generated", type=int, default=128)
+    bench.add_argument("--mixed", action="store_true", help="stagger prompt lengths across slots")
+    bench.add_argument("--baseline", type=Path, help="an earlier report to compare with")
+    bench.add_argument("--max-regression", type=float, default=0.1,
+                       help="fail on throughput loss beyond this fraction against the baseline")
     bench.add_argument("--prefill-chunk", type=int)
     bench.add_argument("--repeats", type=int, default=5)
     bench.add_argument("--warmup", type=int, default=1)

@@ -48,3 +48,13 @@ def test_generate_and_bench_run(tmp_path, capsys):
     main(["bench", "--model", str(tmp_path / "m"), "--batches", "1", "2", "--prompts", "32", "--generated", "4", "--repeats", "2"])
     report = json.loads(capsys.readouterr().out)
     assert all(row["decode_tokens_per_s"] > 0 and row["prefill_tokens_per_s"] > 0 for row in report["rows"])
+    # with tokens cached before the prompt, staggered lengths, and a comparison with an earlier report
+    earlier = tmp_path / "earlier.json"
+    main(["bench", "--model", str(tmp_path / "m"), "--batches", "3", "--prompts", "20", "--depths", "0", "24", "--mixed",
+          "--generated", "3", "--repeats", "1", "--out", str(earlier)])
+    report = json.loads(capsys.readouterr().out)
+    assert [(row["depth"], row["mixed"]) for row in report["rows"]] == [(0, True), (24, True)]
+    main(["bench", "--model", str(tmp_path / "m"), "--batches", "3", "--prompts", "20", "--depths", "0", "24", "--mixed",
+          "--generated", "3", "--repeats", "1", "--baseline", str(earlier), "--max-regression", "0.99"])
+    changes = json.loads(capsys.readouterr().out)["changes"]
+    assert len(changes) == 2 and not any(change["regressed"] for change in changes)

@@ -42,3 +42,20 @@ def test_plain_products_go_to_the_library_unless_told_otherwise(b200):
     assert not cuda._tcgen05_takes(2048, 2048)
     b200.setattr(cuda, "products", "tcgen05")
     assert cuda._tcgen05_takes(2048, 2048) and not cuda._tcgen05_takes(16, 2048) and not cuda._tcgen05_takes(2048, 2044)
+
+
+def test_reports_are_compared_case_by_case():
+    from akas_b200.bench import case_lengths, compare_reports
+
+    row = lambda prefill, decode, **kw: dict(batch=2, prompt=64, generated=8, depth=0, mixed=False,
+                                             prefill_tokens_per_s=prefill, decode_tokens_per_s=decode, **kw)
+    before, after = dict(rows=[row(1000.0, 100.0)]), dict(rows=[row(950.0, 80.0)])
+    change, = compare_reports(after, before, 0.1)
+    assert change["regressed"] and abs(change["decode_tokens_per_s_ratio"] - 0.8) < 1e-9
+    assert not compare_reports(after, before, 0.25)[0]["regressed"]
+    with pytest.raises(ValueError, match="cover every measured case"):
+        compare_reports(dict(rows=[dict(row(1.0, 1.0), depth=16)]), before)
+    with pytest.raises(ValueError):
+        compare_reports(after, before, 1.0)
+    assert case_lengths(9, 64, True) == [64, 63, 62, 61, 60, 59, 58, 64, 63] and case_lengths(3, 2, True) == [2, 1, 2]
+    assert case_lengths(3, 64, False) == [64, 64, 64]
