@@ -37,12 +37,16 @@ class EngineConfig:
     device: str = "cuda:0"
     cuda_graphs: bool = True  # replay captured graphs for steps that only decode
     run_ahead: bool = True  # launch the next decode step before the tokens of the one in flight are read
+    sampling: str = "device"  # "host": the logits are read back and NumPy picks the argmax, a check of the device's
+                              # choice as in the reference (src/akas/generation/greedy.py:82-93); greedy requests only
 
     def __post_init__(self):
         for name in ("prefill_chunk", "prefill_requests", "max_requests", "context", "page_size"):
             _positive(name, getattr(self, name))
         for name in ("prefill_token_budget", "decode_prefill_token_budget", "max_tokens"):
             _positive(name, getattr(self, name), optional=True)
+        if self.sampling not in ("device", "host"):
+            raise ValueError(f"sampling must be 'device' or 'host', got {self.sampling!r}")
         if self.dtype not in ("bfloat16", "float32"):
             raise ValueError(f"dtype must be 'bfloat16' or 'float32', got {self.dtype!r}")
 

@@ -59,7 +59,7 @@ class Engine:
         else:
             self.config = config or EngineConfig()
             self.runner = ModelRunner(model, self.config, ops=ops)
-        self.sampler = Sampler(self.runner.ops, self.runner.device)
+        self.sampler = Sampler(self.runner.ops, self.runner.device, self.config.sampling)
         on_gpu = self.runner.device.type == "cuda"
         self._copy_stream = torch.cuda.Stream(self.runner.device) if on_gpu else None
         self._token_buffers = [torch.empty(max(self.config.max_requests, 1), dtype=torch.int32, pin_memory=True)
@@ -116,6 +116,8 @@ class Engine:
             raise ValueError("generation exceeds context capacity")
         if not 0.0 < top_p <= 1.0 or top_k < 0 or temperature < 0:
             raise ValueError("need temperature >= 0, top_k >= 0 and 0 < top_p <= 1")
+        if self.config.sampling == "host" and temperature > 0:
+            raise ValueError("host sampling is greedy: a request asks for a temperature")
         if softcap < 0 or repetition_penalty <= 0 or repetition_window < 0:
             raise ValueError("need softcap >= 0, repetition_penalty > 0 and repetition_window >= 0")
         request = Request(prompt, max_tokens, temperature=float(temperature), top_k=int(top_k), top_p=float(top_p),

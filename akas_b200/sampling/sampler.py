@@ -14,9 +14,10 @@ import torch
 
 
 class Sampler:
-    def __init__(self, ops, device):
+    def __init__(self, ops, device, where: str = "device"):
         self.ops = ops
         self.device = device
+        self.where = where  # "host": greedy choices are made by NumPy on logits read back from the device
 
     def sample(self, logits: torch.Tensor, requests: Sequence) -> List[int]:
         """``logits``: float32 [M, vocab], one row per request in order. Returns M token ids (host ints)."""
@@ -37,6 +38,13 @@ class Sampler:
             knobs = torch.tensor([[r.softcap, r.repetition_penalty] for r in requests], dtype=torch.float32).t().contiguous()
             knobs = knobs.to(self.device, non_blocking=True)
             logits = self.ops.adjust_logits(logits, knobs[0], knobs[1], history.to(self.device, non_blocking=True))
+        if self.where == "host":
+            if any(r.temperature > 0 for r in requests):
+                raise ValueError("host sampling is greedy: a request asks for a temperature")
+            import numpy as np
+
+            picks = np.argmax(logits.detach().to("cpu", torch.float32).numpy(), axis=1).astype(np.int32)
+            return torch.from_numpy(picks).to(self.device)
         if all(r.temperature <= 0 for r in requests):
             return self.ops.argmax(logits)
         params = torch.tensor(

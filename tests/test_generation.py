@@ -228,3 +228,17 @@ def test_softcap_and_repetition_penalty(tmp_path):
         plain_run = engine.generate(prompts[0], max_tokens=12)["generated_tokens"]
     assert batch[0]["generated_tokens"] == alone == expected(prompts[0], 12)
     assert alone != plain_run
+
+
+def test_host_sampling_agrees_with_the_device(tmp_path):
+    """The reference's diagnostic: NumPy's argmax over logits read back, against the argmax kernel."""
+    folder = tiny.make_folder(tiny.TINY_B, seed=22, dtype="bfloat16", folder=tmp_path / "m")
+    cfg, _ = plain.load_folder(folder)
+    prompts = tiny.prompts(cfg["vocab_size"], [5, 33, 12], seed=4)
+    with _engine(folder, "bfloat16", tiny.PAGE["b"]) as engine:
+        device = [r["generated_tokens"] for r in engine.generate(prompts, max_tokens=10)]
+    with _engine(folder, "bfloat16", tiny.PAGE["b"], sampling="host") as engine:
+        host = [r["generated_tokens"] for r in engine.generate(prompts, max_tokens=10)]
+        with pytest.raises(ValueError, match="greedy"):
+            engine.generate(prompts[0], max_tokens=2, temperature=0.5)
+    assert host == device
