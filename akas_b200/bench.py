@@ -408,6 +408,42 @@ def bench_long_context(shape: str = "700m", requests: int = 8, prompt: int = 300
                 decode_gb_per_step=round(nbytes / 1e9, 3), decode_gb_s=round(nbytes / (ms / generated / 1e3) / 1e9, 1))
 
 
+def bench_ops(shape: str = "1.2b", prompt: int = 2048, batch: int = 8, steps: int = 16) -> dict:
+    """Where the device time of one prompt of ``prompt`` tokens and of ``steps`` decode steps of ``batch`` requests
+    goes, by operation (CUDA events around every call of the step function's operations; no captured graphs)."""
+    import tempfile
+
+    from .config import EngineConfig, config_from_dict
+    from .ops import cuda as cuda_ops
+    from .ops.timed import TimedOps
+    from .weights import write_random_model
+
+    cuda_ops.require(cuda_ops.libraries_for(torch.bfloat16))
+    timed = TimedOps(cuda_ops)
+    config = EngineConfig(dtype="bfloat16", max_requests=batch, context=prompt + steps + 64, cuda_graphs=False)
+    with tempfile.TemporaryDirectory(prefix="akas-bench-") as folder:
+        write_random_model(folder, config_from_dict(shape_config(shape)), seed=0, dtype="bfloat16")
+        runner = ModelRunner(folder, config, ops=timed)
+    prompts = synthetic_prompts(batch, prompt, runner.vocab_size)
+    ids = [f"o{j}" for j in range(batch)]
+    fill_requests(runner, [p[:-1] for p in prompts[1:]], config.prefill_chunk, ids[1:])  # the others, and a warm-up
+    timed.clear()
+    runner.step([StepEntry(ids[0], prompts[0][:-1], ())])
+    prefill = timed.table()
+    tokens = [p[-1] for p in prompts]
+    runner.step([StepEntry(rid, (t,), (0,)) for rid, t in zip(ids, tokens)])  # first decode step: set-up costs
+    timed.clear()
+    for _ in range(steps):
+        logits = runner.step([StepEntry(rid, (t,), (0,)) for rid, t in zip(ids, tokens)])
+        tokens = timed.argmax(logits).tolist()
+    decode = timed.table()
+    for row in decode:
+        row["ms"] /= steps
+    round_rows = lambda rows: [dict(op=r["op"], calls=r["calls"], ms=round(r["ms"], 4), share=round(r["share"], 3)) for r in rows]
+    return dict(bench="ops", shape=shape, prompt=prompt, batch=batch, prefill=round_rows(prefill),
+                decode_per_step=round_rows(decode))
+
+
 def _main():
     import argparse
     import json
@@ -438,7 +474,15 @@ def _main():
     lng.add_argument("--requests", type=int, default=8)
     lng.add_argument("--prompt", type=int, default=30000)
     lng.add_argument("--generated", type=int, default=256)
+    per = sub.add_parser("ops", help="device time of a prompt and of decode steps, by operation")
+    per.add_argument("--shape", default="1.2b", choices=sorted(SHAPES))
+    per.add_argument("--prompt", type=int, default=2048)
+    per.add_argument("--batch", type=int, default=8)
+    per.add_argument("--steps", type=int, default=16)
     args = ap.parse_args()
+    if args.what == "ops":
+        print(json.dumps(bench_ops(args.shape, args.prompt, args.batch, args.steps), indent=1))
+        return
     if args.what == "serving":
         print(json.dumps(bench_serving(args.shape, args.requests, generated=args.generated, chunk=args.chunk)))
         return

@@ -152,3 +152,25 @@ def test_whole_prompts_through_the_tensor_memory_products(key, tmp_path, monkeyp
     _run_modes(key, "bfloat16", "cuda:0", None, tmp_path, ["whole", "portions"])
     assert calls["paired"] > 0
     assert cuda.gemm_pair_status() == 0 and cuda.gemm_tcgen05_status() == 0
+
+
+@pytest.mark.gpu
+def test_timed_operations_change_nothing_and_account_for_the_step(tmp_path):
+    """The wrapper that brackets every operation with CUDA events runs the same kernels: same logits, and a table
+    that names the operations of a prompt and of a decoded token."""
+    from akas_b200.ops import cuda
+    from akas_b200.ops.timed import TimedOps
+
+    folder, reqs, want = _setup("c", "bfloat16", tmp_path)
+    page = tiny.PAGE["c"]
+    longest = -(-max(len(t) for t in reqs.values()) // page) * page
+    cuda.require(cuda.libraries_for(torch.bfloat16))
+    timed = TimedOps(cuda)
+    got = traces.replay(_runner(folder, "bfloat16", "cuda:0", page, longest, timed), traces.tail_decoded(reqs))
+    _check(got, want, "bfloat16", "timed operations")
+    rows = {row["op"]: row for row in timed.table()}
+    assert {"embedding", "paged_attention", "short_conv", "linear"} <= set(rows)
+    assert all(row["calls"] > 0 and row["ms"] > 0 for row in rows.values())
+    assert abs(sum(row["share"] for row in rows.values()) - 1.0) < 1e-6
+    timed.clear()
+    assert timed.table() == []
