@@ -321,3 +321,42 @@ def test_a_repetition_penalty_keeps_the_host_in_step():
     drain(s)
     assert model.ahead == 0 and s.stats["steps_ahead"] == 0
     assert all(r.output == expected(r.prompt, 6) for r in reqs)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_arrivals_cancellations_and_a_small_pool(seed):
+    """Requests of random lengths arrive at random turns into a pool that cannot hold them all, some are cancelled on
+    the way: whatever the order, every request that was not cancelled generates what it would have generated alone,
+    the cache's books balance after every turn, and everything is given back at the end."""
+    import random
+
+    rng = random.Random(seed)
+    model = FakeModel(page=4, tokens=96, requests=4, context=64)
+    s, events = make(model, prefill_chunk=rng.choice([3, 7, 16]), prefill_requests=rng.choice([1, 2, 4]),
+                     decode_prefill_token_budget=rng.choice([None, 5]))
+    waiting = [Request([rng.randrange(VOCAB) for _ in range(rng.randint(1, 30))], rng.randint(1, 12)) for _ in range(14)]
+    submitted, cancelled = [], set()
+    for turn in range(10000):
+        while waiting and rng.random() < 0.4:
+            submitted.append(waiting.pop())
+            s.submit(submitted[-1])
+        if submitted and rng.random() < 0.05:
+            victim = rng.choice(submitted)
+            if not victim.finished:
+                victim.cancelled.set()
+                cancelled.add(victim.id)
+        busy = s.turn()
+        model.cache.check()
+        if not busy and not waiting:
+            break
+    else:
+        raise AssertionError("the scheduler did not finish")
+    assert len(submitted) == 14
+    for r in submitted:
+        if r.finish_reason == "cancelled":
+            assert r.id in cancelled and r.output == expected(r.prompt, len(r.output))
+        else:
+            assert r.finish_reason == "length" and r.output == expected(r.prompt, r.limit)
+        assert r.slot is None
+    assert not model.cache.live() and model.cache.free_pages() == 24
+    assert s.stats["completed"] + s.stats["cancelled"] == 14
