@@ -467,6 +467,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
 }
 
+constexpr int kMaxDevices = 64;  // device ordinals that per-device set-up is remembered for
+
 template <int D>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* block_table, int max_blocks,
            const int* seq_of_token, const int* positions, void* out, float* part_o, float* part_ml, float scale,
@@ -475,11 +477,14 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* blo
   constexpr int tiles_bytes = (ROWS + 2 * STAGES * BK) * STRIDE * (int)sizeof(bf16);
   constexpr int merge_bytes = ROWS * STRIDE * (int)sizeof(bf16) + WARPS * ROWS * (D + 2) * (int)sizeof(float);
   constexpr int smem = tiles_bytes > merge_bytes ? tiles_bytes : merge_bytes;
-  static bool configured = false;
-  if (!configured) {
+  // The attribute belongs to a device, like the scratch address of the entry point that allocates nothing.
+  static bool configured[kMaxDevices] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+  if (!configured[device]) {
     const cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[device] = true;
   }
   const int G = H / KH, row_tiles = (G + ROWS - 1) / ROWS;
   int err = launch_chained(decode_attention_kernel<D>, dim3(N, KH * row_tiles, splits), dim3(WARPS * 32), smem, stream,
@@ -498,11 +503,13 @@ int launch_tma(const void* q, const void* k_pool, const void* v_pool, long long 
   constexpr int D = 64;
   constexpr int smem = 1024 + 2 * TMA_STAGES * TMA_TILE + ROWS * (D + 8) * (int)sizeof(bf16) + 2 * TMA_STAGES * 8 + 16;
   static_assert(2 * TMA_STAGES * TMA_TILE >= WARPS * ROWS * (D + 2) * (int)sizeof(float), "the merge buffers fit the tiles");
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+  if (!configured[device]) {
     const cudaError_t e = cudaFuncSetAttribute(decode_attention_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[device] = true;
   }
   CUtensorMap map_k, map_v;
   int err = akas::tc::cached_map(&map_k, k_pool, (int)pool_rows, D, BK, true);
@@ -586,7 +593,6 @@ namespace {
 // In host code this name is only a handle for cudaGetSymbolAddress, never a pointer a kernel may be given.
 static __device__ __align__(256) float g_decode_scratch[AKAS_DECODE_NOALLOC_FLOATS];
 
-constexpr int kMaxDevices = 64;
 float* g_decode_scratch_address[kMaxDevices] = {};  // device address of the array, per device ordinal
 std::mutex g_decode_scratch_mutex;
 
@@ -611,7 +617,14 @@ int decode_scratch(float** address) {
 
 long long akas_decode_attention_bf16_noalloc_needs(int tokens, int heads, int splits, int head_dim) {
   if (tokens <= 0 || heads <= 0 || splits <= 1 || head_dim <= 0) return 0;  // a single split writes the output directly
-  return (long long)tokens * heads * splits * (head_dim + 2);
+  // Four ints can overflow 64 bits: once a partial product is past the array, the answer is "too many" whatever follows.
+  const long long limit = (long long)AKAS_DECODE_NOALLOC_FLOATS + 1;
+  long long need = (long long)tokens * heads;          // < 2^62
+  if (need >= limit) return limit;
+  need *= splits;                                       // < 2^20 * 2^31
+  if (need >= limit) return limit;
+  need *= (long long)head_dim + 2;                      // < 2^20 * 2^32
+  return need >= limit ? limit : need;
 }
 
 const char* akas_noalloc_error_string(int code) {

@@ -7,7 +7,8 @@
 //                                             request's state (its last L-1 values of u, oldest first)
 //   out[t] = C[t] * (s[t] + bias[c])
 // and afterwards state[r] = the last L-1 values of u of (state ++ this step's u). Products, sums and
-// the state are float32. Two launches: the forward reads the old state, the update then rewrites it;
+// the state are float32. With write == 0 the state is read and left as it is (a layer that reads another
+// layer's state). Two launches: the forward reads the old state, the update then rewrites it;
 // both are per-token/per-request parallel, so a prompt portion is not walked serially.
 #include "common.cuh"
 
@@ -197,7 +198,7 @@ template <typename T>
 __global__ void short_conv_decode_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
                                          const float* __restrict__ bias, float* __restrict__ state,
                                          const int* __restrict__ seq_of_token, const int* __restrict__ slots,
-                                         T* __restrict__ out, int C, int L) {
+                                         T* __restrict__ out, int C, int L, int write) {
   chain_release();
   chain_wait();
   const int t = blockIdx.x;
@@ -216,31 +217,31 @@ __global__ void short_conv_decode_kernel(const T* __restrict__ bcx, const float*
   for (int i = 0; i < L - 1; ++i) {
     const float h = hist[(size_t)i * C];
     acc = fmaf(h, taps[(size_t)c * L + i], acc);
-    if (i > 0) hist[(size_t)(i - 1) * C] = h;
+    if (i > 0 && write) hist[(size_t)(i - 1) * C] = h;
   }
   acc = fmaf(u, taps[(size_t)c * L + L - 1], acc);
-  hist[(size_t)(L - 2) * C] = u;
+  if (write) hist[(size_t)(L - 2) * C] = u;
   if (bias) acc += bias[c];
   out[(size_t)t * C + c] = from_f32<T>(to_f32(row[C + c]) * acc);
 }
 
 AKAS_API int akas_short_conv_decode(const void* bcx, const float* taps, const float* bias, float* state,
                                     const int* seq_of_token, const int* slots, void* out, int N, int C, int L,
-                                    int dtype, cudaStream_t stream) {
+                                    int dtype, int write, cudaStream_t stream) {
   if (L < 2 || L > AKAS_CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
   if (N <= 0) return 0;
   const int threads = 128;
   const dim3 grid(N, (C + threads - 1) / threads);
   if (dtype == AKAS_F32)
     return launch_chained(short_conv_decode_kernel<float>, grid, dim3(threads), 0, stream, (const float*)bcx, taps, bias,
-                          state, seq_of_token, slots, (float*)out, C, L);
+                          state, seq_of_token, slots, (float*)out, C, L, write);
   return launch_chained(short_conv_decode_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)bcx, taps, bias,
-                        state, seq_of_token, slots, (bf16*)out, C, L);
+                        state, seq_of_token, slots, (bf16*)out, C, L, write);
 }
 
 AKAS_API int akas_short_conv(const void* bcx, const float* taps, const float* bias, float* state,
                              const int* cu_seqlens, const int* seq_of_token, const int* slots, void* out, int N,
-                             int R, int C, int L, int dtype, cudaStream_t stream) {
+                             int R, int C, int L, int dtype, int write, cudaStream_t stream) {
   if (L < 2 || L > AKAS_CONV_MAX_TAPS) return (int)cudaErrorInvalidValue;
   if (N <= 0 || R <= 0) return 0;
   const int threads = 128;
@@ -256,10 +257,10 @@ AKAS_API int akas_short_conv(const void* bcx, const float* taps, const float* bi
   if (runs) {
     if (dtype == AKAS_F32) {
       if (L == 2) AKAS_CONV_RUN(float, 2); else if (L == 3) AKAS_CONV_RUN(float, 3); else AKAS_CONV_RUN(float, 4);
-      short_conv_state_kernel<float><<<upd, threads, 0, stream>>>((const float*)bcx, state, cu_seqlens, slots, C, L);
+      if (write) short_conv_state_kernel<float><<<upd, threads, 0, stream>>>((const float*)bcx, state, cu_seqlens, slots, C, L);
     } else {
       if (L == 2) AKAS_CONV_RUN(bf16, 2); else if (L == 3) AKAS_CONV_RUN(bf16, 3); else AKAS_CONV_RUN(bf16, 4);
-      short_conv_state_kernel<bf16><<<upd, threads, 0, stream>>>((const bf16*)bcx, state, cu_seqlens, slots, C, L);
+      if (write) short_conv_state_kernel<bf16><<<upd, threads, 0, stream>>>((const bf16*)bcx, state, cu_seqlens, slots, C, L);
     }
     return launch_status();
   }
@@ -271,7 +272,7 @@ AKAS_API int akas_short_conv(const void* bcx, const float* taps, const float* bi
     else
       short_conv_forward_kernel<float><<<fwd, threads, 0, stream>>>((const float*)bcx, taps, bias, state, cu_seqlens,
                                                                     seq_of_token, slots, (float*)out, C, L);
-    short_conv_state_kernel<float><<<upd, threads, 0, stream>>>((const float*)bcx, state, cu_seqlens, slots, C, L);
+    if (write) short_conv_state_kernel<float><<<upd, threads, 0, stream>>>((const float*)bcx, state, cu_seqlens, slots, C, L);
   } else {
     if (wide)
       short_conv_forward8_kernel<bf16><<<fwd8, threads, 0, stream>>>((const bf16*)bcx, taps, bias, state, cu_seqlens,
@@ -279,7 +280,7 @@ AKAS_API int akas_short_conv(const void* bcx, const float* taps, const float* bi
     else
       short_conv_forward_kernel<bf16><<<fwd, threads, 0, stream>>>((const bf16*)bcx, taps, bias, state, cu_seqlens,
                                                                    seq_of_token, slots, (bf16*)out, C, L);
-    short_conv_state_kernel<bf16><<<upd, threads, 0, stream>>>((const bf16*)bcx, state, cu_seqlens, slots, C, L);
+    if (write) short_conv_state_kernel<bf16><<<upd, threads, 0, stream>>>((const bf16*)bcx, state, cu_seqlens, slots, C, L);
   }
   return launch_status();
 }

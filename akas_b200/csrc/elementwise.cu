@@ -196,3 +196,37 @@ AKAS_API int akas_take_tokens(int* token_ids, const int* source, const int* prev
   take_tokens_kernel<<<(N + 255) / 256, 256, 0, stream>>>(token_ids, source, previous, previous_count, N);
   return launch_status();
 }
+
+// out[n, c] = x[n, c] + bias[c], x float32, out float32 or bfloat16 (out may be x): the bias of a product whose
+// result was left in float32, added before the one rounding.
+template <typename TO>
+__global__ void add_bias_kernel(const float* __restrict__ x, const float* __restrict__ bias, TO* __restrict__ out, int C,
+                                size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) out[i] = from_f32<TO>(x[i] + bias[i % C]);
+}
+
+AKAS_API int akas_add_bias(const float* x, const float* bias, void* out, int N, int C, int out_dtype, cudaStream_t stream) {
+  const size_t total = (size_t)N * C;
+  if (total == 0) return 0;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (out_dtype == AKAS_F32) add_bias_kernel<float><<<blocks, 256, 0, stream>>>(x, bias, (float*)out, C, total);
+  else add_bias_kernel<bf16><<<blocks, 256, 0, stream>>>(x, bias, (bf16*)out, C, total);
+  return launch_status();
+}
+
+// In place on float32: x = x * scale, then x = cap * tanh(x / cap) where cap > 0 (an embedding multiplier, a
+// logit scale, a logit softcap).
+__global__ void scale_cap_kernel(float* __restrict__ x, float scale, float cap, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float v = x[i] * scale;
+  if (cap > 0.f) v = cap * tanhf(v / cap);
+  x[i] = v;
+}
+
+AKAS_API int akas_scale_cap(float* x, float scale, float cap, long long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  scale_cap_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, scale, cap, (size_t)total);
+  return launch_status();
+}

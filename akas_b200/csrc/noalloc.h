@@ -47,7 +47,8 @@ __attribute__((visibility("default"))) int akas_decode_attention_bf16_noalloc(
     const int* seq_of_token, const int* positions, void* out, float scale, int window, int page_size, int tokens,
     int heads, int kv_heads, int head_dim, int splits, cudaStream_t stream);
 
-/* How many float32 of scratch a call would need; compare with AKAS_DECODE_NOALLOC_FLOATS. */
+/* How many float32 of scratch a call would need; compare with AKAS_DECODE_NOALLOC_FLOATS. Sizes whose product
+ * is beyond the array (or beyond 64 bits) all give AKAS_DECODE_NOALLOC_FLOATS + 1. */
 __attribute__((visibility("default"))) long long akas_decode_attention_bf16_noalloc_needs(int tokens, int heads,
                                                                                           int splits, int head_dim);
 

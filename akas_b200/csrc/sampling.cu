@@ -3,15 +3,17 @@
 // argmax: ties go to the lowest index (kreasof-ai/akas, src/akas/ops/vocabulary/kernel.py:146-150).
 //
 // sample, per row with temperature T, top_k k, top_p p and a uniform u in [0, 1) from the caller:
-//   T <= 0: the argmax. Else w_i = exp((x_i - max x) / T) and token i is kept iff
-//     fewer than k tokens have a larger logit (k <= 0 or k >= V: no limit; ties stay together), and
-//     the kept tokens with a larger logit hold at most p of the kept mass (p >= 1: no limit);
+//   T <= 0: the argmax. Else w_i = exp((x_i - max x) / T); the tokens are ranked by logit, larger first, equal
+//   logits by id, lower first; token i is kept iff
+//     its rank is below k (k <= 0 or k >= V: no limit; exactly k are kept, whatever is equal), and
+//     the kept tokens ranked before it hold at most p of the kept mass (p >= 1: no limit);
 //   the result is the first kept i, in index order, whose running kept mass exceeds u * (kept mass).
 // The reference's only stochastic sampler (its audio model's `codebook_sample`,
 // src/akas/ops/vocabulary/kernel.py:515-671) has the same stages: top-k, exp((v - peak) / T), a
 // top-p cut on the mass before a token, inverse CDF with a supplied uniform, T <= 0 greedy. Here
-// no sort is needed: both cuts are thresholds on the logit, found by bisection over the ordered
-// bit patterns of float32 with one counting or summing pass over the row per step.
+// no sort is needed: both cuts are a threshold on the logit, found by bisection over the ordered
+// bit patterns of float32 with one counting or summing pass over the row per step, and, for the tokens
+// equal to the threshold, a largest id that is kept, found by a prefix count in index order.
 // One block of 1024 threads per row. Softmax terms and sums are float32.
 //
 // adjust: the two stages that sampler applies before those, on the logits in place, per row:
@@ -30,6 +32,10 @@ using namespace akas;
 __device__ __forceinline__ uint32_t ordered_key(float v) {
   const uint32_t b = __float_as_uint(v);
   return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+
+__device__ __forceinline__ float key_value(uint32_t key) {  // the float whose ordered key this is
+  return __uint_as_float(key ^ ((key >> 31) ? 0x80000000u : 0xffffffffu));
 }
 
 // (value, index) of the row maximum with the lowest index among equals; every thread gets it.
@@ -120,12 +126,48 @@ AKAS_API int akas_argmax(const float* logits, int* out, float* part_val, int* pa
                         out, parts);
 }
 
+// The index of the `want`-th (1-based) position i, in index order, whose key equals `tie` and for which i <= limit;
+// V - 1 if there are fewer (keep them all). Thread t owns the contiguous indices [t * chunk, (t + 1) * chunk).
+// `counts` holds one int per warp; every thread gets the result.
+__device__ int tie_cut(const float* __restrict__ x, int V, uint32_t tie, int limit, int want, int* counts, int* found) {
+  const int chunk = (V + blockDim.x - 1) / blockDim.x;
+  const int begin = min(V, (int)threadIdx.x * chunk), end = min(V, begin + chunk);
+  int local = 0;
+  for (int i = begin; i < end; ++i) local += (ordered_key(x[i]) == tie && i <= limit) ? 1 : 0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  __syncthreads();  // counts and found may still be read from an earlier call
+  if (threadIdx.x == 0) *found = V - 1;
+  if (lane == 31) counts[warp] = incl;
+  __syncthreads();
+  int before = 0;
+  for (int w = 0; w < warp; ++w) before += counts[w];
+  int run = before + incl - local;
+  if (run < want && run + local >= want) {  // the wanted one lies in this thread's chunk
+    for (int i = begin; i < end; ++i)
+      if (ordered_key(x[i]) == tie && i <= limit && ++run == want) { *found = i; break; }
+  }
+  __syncthreads();
+  return *found;
+}
+
+// The order of the tokens is (logit descending, id ascending), the order in which the reference's rank loop takes
+// them (src/akas/ops/vocabulary/kernel.py:586-622). top-k keeps the first k of that order exactly; top-p keeps a
+// token while the kept mass before it, in that order, is at most p of the kept mass. Both cuts are a threshold on
+// the logit plus, among the tokens equal to the threshold, an upper bound on the id.
 __global__ void __launch_bounds__(AKAS_SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
               int* __restrict__ out, int V) {
   __shared__ float scratch[32];
   __shared__ float warp_tot[32];
+  __shared__ int counts[32];
+  __shared__ int found;
   __shared__ int pick, last_kept;
   const int row = blockIdx.x;
   const float* x = logits + (size_t)row * V;
@@ -138,11 +180,12 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     return;
   }
   const float inv_t = 1.f / T;
-  uint32_t thr = 0u;  // keep tokens whose ordered key is >= thr
+  uint32_t thr = 0u;  // keep tokens whose ordered key is > thr, and those == thr whose id is <= cut
+  int cut = V - 1;
 
   const int k = top_k[row];
   if (k > 0 && k < V) {
-    uint32_t lo = 0u, hi = 0xffffffffu;  // smallest t with count(key > t) < k
+    uint32_t lo = 0u, hi = 0xffffffffu;  // smallest t with count(key > t) < k: the key of the k-th largest logit
     while (lo < hi) {
       const uint32_t mid = lo + (hi - lo) / 2u;
       float c = 0.f;
@@ -151,13 +194,19 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
       if (c < (float)k) hi = mid; else lo = mid + 1u;
     }
     thr = lo;
+    float above = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) above += ordered_key(x[i]) > thr ? 1.f : 0.f;
+    above = block_sum(above, scratch);
+    cut = tie_cut(x, V, thr, V - 1, k - (int)above, counts, &found);  // of the equals, the lowest ids fill up to k
   }
 
   const float p = top_p[row];
   if (p < 1.f) {
     float mass = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x)
-      if (ordered_key(x[i]) >= thr) mass += expf((x[i] - top) * inv_t);
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const uint32_t key = ordered_key(x[i]);
+      if (key > thr || (key == thr && i <= cut)) mass += expf((x[i] - top) * inv_t);
+    }
     mass = block_sum(mass, scratch);
     const float limit = p * mass;
     uint32_t lo = thr, hi = 0xffffffffu;  // smallest t >= thr with mass(key > t) <= limit
@@ -169,7 +218,17 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
       g = block_sum(g, scratch);
       if (g <= limit) hi = mid; else lo = mid + 1u;
     }
+    // Of the tokens equal to the new threshold, the j-th (from 0, by id) has above + j * w before it.
+    float above = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x)
+      if (ordered_key(x[i]) > lo) above += expf((x[i] - top) * inv_t);
+    above = block_sum(above, scratch);
+    const float tie_w = expf((key_value(lo) - top) * inv_t);  // the weight of every token at the threshold
+    int keep = 1;
+    while (keep < V && tie_w > 0.f && above + (float)keep * tie_w <= limit) ++keep;  // few: equals of one value
+    const int bound = lo == thr ? cut : V - 1;
     thr = lo;
+    cut = tie_cut(x, V, thr, bound, keep, counts, &found);
   }
 
   // inverse CDF in index order: thread t owns the contiguous indices [t * chunk, (t + 1) * chunk)
@@ -177,8 +236,10 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   const int begin = min(V, (int)threadIdx.x * chunk), end = min(V, begin + chunk);
   float local = 0.f;
   int my_last = -1;
-  for (int i = begin; i < end; ++i)
-    if (ordered_key(x[i]) >= thr) { local += expf((x[i] - top) * inv_t); my_last = i; }
+  for (int i = begin; i < end; ++i) {
+    const uint32_t key = ordered_key(x[i]);
+    if (key > thr || (key == thr && i <= cut)) { local += expf((x[i] - top) * inv_t); my_last = i; }
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float incl = local;
 #pragma unroll
@@ -197,7 +258,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   const float target = uniform[row] * total;
   float run = before + incl - local;
   for (int i = begin; i < end; ++i) {
-    if (ordered_key(x[i]) >= thr) {
+    const uint32_t key = ordered_key(x[i]);
+    if (key > thr || (key == thr && i <= cut)) {
       run += expf((x[i] - top) * inv_t);
       if (run > target) { atomicMin(&pick, i); break; }
     }

@@ -49,6 +49,27 @@ class _Sampled:
         return self.host.tolist()
 
 
+def _check_sampling(temperature, top_k, top_p, softcap, repetition_penalty, repetition_window, greedy_only=False):
+    """Refuses sampling options outside their ranges, naming each one that is."""
+    faults = []
+    if temperature < 0:
+        faults.append(f"temperature = {temperature} is negative (0 is greedy)")
+    if top_k < 0:
+        faults.append(f"top_k = {top_k} is negative (0 keeps every token)")
+    if not 0.0 < top_p <= 1.0:
+        faults.append(f"top_p = {top_p} is outside (0, 1]")
+    if softcap < 0:
+        faults.append(f"softcap = {softcap} is negative (0 is none)")
+    if repetition_penalty <= 0:
+        faults.append(f"repetition_penalty = {repetition_penalty} is not positive (1 is none)")
+    if repetition_window < 0:
+        faults.append(f"repetition_window = {repetition_window} is negative")
+    if greedy_only and temperature > 0:
+        faults.append("host sampling is greedy, and the request asks for a temperature")
+    if faults:
+        raise ValueError("; ".join(faults))
+
+
 class Engine:
     def __init__(self, model, *, config: Optional[EngineConfig] = None, publish=None, ops=None):
         """``model``: a model folder (config.json + model.safetensors), or a ready ``ModelRunner``."""
@@ -106,21 +127,24 @@ class Engine:
     def submit(self, prompt, *, max_tokens, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
                seed: Optional[int] = None, eos_token_id: Optional[int] = None, softcap: float = 0.0,
                repetition_penalty: float = 1.0, repetition_window: int = 96) -> Request:
-        prompt = list(prompt)
+        """Queues a request for the next turn (any thread may). Everything that could make a later step fail is refused here, with
+        the place of the fault in the message: the step function trusts what the scheduler hands it."""
+        tokens = list(prompt)
+        if not tokens:
+            raise ValueError("an empty prompt: a request needs at least one token id")
         vocab = self.runner.vocab_size
-        if not prompt or any(type(t) is not int or t < 0 or t >= vocab for t in prompt):
-            raise ValueError("prompt must contain valid integer token IDs")
-        if type(max_tokens) is not int or max_tokens < 1:
-            raise ValueError("max_tokens must be positive")
-        if len(prompt) + max_tokens > self.context:
-            raise ValueError("generation exceeds context capacity")
-        if not 0.0 < top_p <= 1.0 or top_k < 0 or temperature < 0:
-            raise ValueError("need temperature >= 0, top_k >= 0 and 0 < top_p <= 1")
-        if self.config.sampling == "host" and temperature > 0:
-            raise ValueError("host sampling is greedy: a request asks for a temperature")
-        if softcap < 0 or repetition_penalty <= 0 or repetition_window < 0:
-            raise ValueError("need softcap >= 0, repetition_penalty > 0 and repetition_window >= 0")
-        request = Request(prompt, max_tokens, temperature=float(temperature), top_k=int(top_k), top_p=float(top_p),
+        for place, token in enumerate(tokens):
+            if type(token) is not int or not 0 <= token < vocab:
+                raise ValueError(f"prompt[{place}] = {token!r} is not a token id (an int in [0, {vocab}))")
+        if type(max_tokens) is not int or max_tokens <= 0:
+            raise ValueError(f"max_tokens = {max_tokens!r}: a request generates a whole number of tokens, at least one")
+        room = self.context - len(tokens)
+        if max_tokens > room:
+            raise ValueError(f"{len(tokens)} prompt tokens and {max_tokens} to generate do not fit the context "
+                             f"of {self.context} tokens (room for {max(room, 0)})")
+        _check_sampling(temperature, top_k, top_p, softcap, repetition_penalty, repetition_window,
+                        greedy_only=self.config.sampling == "host")
+        request = Request(tokens, max_tokens, temperature=float(temperature), top_k=int(top_k), top_p=float(top_p),
                           seed=seed, eos_token_id=eos_token_id, softcap=float(softcap),
                           repetition_penalty=float(repetition_penalty), repetition_window=int(repetition_window))
         self.scheduler.submit(request)
@@ -131,7 +155,7 @@ class Engine:
         decode graphs of every batch size up to ``most`` requests (default ``max_requests``), and a step of padding
         for every size a step of prompt portions can have, up to ``tokens`` (default: the prefill token budget plus
         one decoded token per request)."""
-        self._check_thread()
+        self._owner_only("warm_up")
         self.runner.capture_decode_graphs(most)
         if tokens is None:
             budget = self.config.prefill_token_budget or self.config.prefill_chunk * self.config.prefill_requests
@@ -159,38 +183,40 @@ class Engine:
     def _collect(handle) -> List[int]:
         return [] if handle is None else handle.read()
 
-    def _check_thread(self):
+    def _owner_only(self, what: str) -> None:
+        """The cache manager, the staging ring and the captured graphs are not locked: one thread drives them."""
         if get_ident() != self.thread:
-            raise RuntimeError("engine must run on its owner thread")
+            raise RuntimeError(f"Engine.{what}() was called from another thread than the one that built the engine")
 
     def step(self) -> bool:
-        self._check_thread()
+        """One scheduler turn; whether anything is still waiting, running or in flight."""
+        self._owner_only("step")
         if self.closed:
-            raise RuntimeError("engine is closed")
+            raise RuntimeError("Engine.step() after close()")
         return self.scheduler.turn()
 
     def cancel(self, request: Request) -> None:
+        """Marks ``request`` (any thread may); the next turn gives back what it holds."""
         request.cancelled.set()
 
     def run(self) -> None:
-        self._check_thread()
-        try:
+        """Serves until ``scheduler.stopped`` is set (from any thread), then closes."""
+        self._owner_only("run")
+        with self:
             self.scheduler.run()
-        finally:
-            self.close()
 
     def close(self) -> None:
-        self._check_thread()
-        if self.closed:
-            return
-        self.scheduler.stopped.set()
-        self.scheduler.shutdown()
-        self.closed = True
+        """Stops the scheduler, waits for the step in flight and frees every request's pages and slot. Idempotent."""
+        self._owner_only("close")
+        if not self.closed:
+            self.closed = True
+            self.scheduler.stopped.set()
+            self.scheduler.shutdown()
 
     def __enter__(self):
         return self
 
-    def __exit__(self, *error):
+    def __exit__(self, kind, error, trace):
         self.close()
 
     # ------------------------------------------------------------------ whole batches

@@ -114,10 +114,13 @@ class ModelRunner:
 
     def step(self, entries: Sequence[StepEntry], previous: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs one batch. Returns float32 logits ``[sum(len(e.want)), vocab]`` on the device, in the
-        order of the entries and of their ``want``. Unknown requests are admitted; pages are taken
-        first (``OutOfPages`` leaves the cache as it was before the step, but for pages already
-        reserved, which stay with their requests). ``previous``: the int32 device tensor of tokens that the
-        step before sampled, for entries that name a ``source`` in it."""
+        order of the entries and of their ``want``. The result is valid until the next call of ``step``: a step that
+        replays a captured graph returns the graph's own output buffer, which the next replay overwrites (and which
+        the sampler may adjust in place); clone it to keep it longer. Unknown requests are admitted; pages are taken
+        first. When a request cannot be admitted or ``OutOfPages`` is raised, nothing has run, the requests that
+        this call admitted are released again, and pages already reserved for known requests stay with them.
+        ``previous``: the int32 device tensor of tokens that the step before sampled, for entries that name a
+        ``source`` in it."""
         entries = [e for e in entries if len(e.tokens)]
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
@@ -135,13 +138,21 @@ class ModelRunner:
                 bad = ids[(ids < 0) | (ids >= self.vocab_size)]
                 if bad.size:
                     raise ValueError(f"request {e.request!r}: token ids {bad[:4].tolist()} outside [0, {self.vocab_size})")
-        for e, ids in zip(entries, arrays):
+        for e in entries:  # every entry is checked before any request is admitted or any page is taken
             if any(not 0 <= w < len(e.tokens) for w in e.want):
                 raise ValueError(f"request {e.request!r}: wanted places {list(e.want)} outside its {len(e.tokens)} tokens")
-            if e.request not in self.cache:
-                self.admit(e.request)
-        for e in entries:
-            self.cache.reserve(e.request, len(e.tokens))
+        newcomers = []
+        try:
+            for e in entries:
+                if e.request not in self.cache:
+                    self.admit(e.request)
+                    newcomers.append(e.request)
+            for e in entries:
+                self.cache.reserve(e.request, len(e.tokens))
+        except Exception:
+            for request in newcomers:  # a step that cannot run leaves no request behind that it brought in itself
+                self.release(request)
+            raise
 
         decode_only = all(len(e.tokens) == 1 for e in entries)
         all_wanted = all(list(e.want) == [0] for e in entries)

@@ -35,11 +35,16 @@ from __future__ import annotations
 from collections import deque
 from queue import Empty, Queue
 from threading import Event
+from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence
 
 from ..cache.manager import CacheManager, OutOfPages
 from .batch import StepEntry
 from .request import Request
+
+
+# A request's first token and its last are published at once; in between, every fourth (the reference's rhythm).
+_PUBLISH_EVERY = 4
 
 
 class _Flight:
@@ -52,47 +57,83 @@ class _Flight:
         self.requests, self.handle, self.decode_only = requests, handle, decode_only
 
 
+@dataclass(frozen=True)
+class Budgets:
+    """How much prompt work a turn may hold, under kreasof-ai/akas's option names: at most ``prefill_requests``
+    requests get a portion, none longer than ``prefill_chunk``, ``prefill_token_budget`` tokens in all (default:
+    chunk x requests), and no more than ``decode_prefill_token_budget`` beside decoding requests."""
+
+    prefill_chunk: int = 2048
+    prefill_requests: int = 32
+    prefill_token_budget: Optional[int] = None
+    decode_prefill_token_budget: Optional[int] = None
+
+    def __post_init__(self):
+        for field in ("prefill_chunk", "prefill_requests"):
+            value = getattr(self, field)
+            if type(value) is not int or value < 1:
+                raise ValueError(f"{field} = {value!r}: a whole number of at least 1 is needed")
+        for field in ("prefill_token_budget", "decode_prefill_token_budget"):
+            value = getattr(self, field)
+            if value is not None and (type(value) is not int or value < 1):
+                raise ValueError(f"{field} = {value!r}: None (no limit of its own) or a whole number of at least 1")
+
+    def prompt_tokens(self, beside_decoding: bool) -> int:
+        """The prompt tokens one turn may run."""
+        most = self.prefill_token_budget if self.prefill_token_budget is not None else self.prefill_chunk * self.prefill_requests
+        if beside_decoding and self.decode_prefill_token_budget is not None:
+            most = min(most, self.decode_prefill_token_budget)
+        return most
+
+
+_COUNTERS = ("tokens", "completed", "cancelled", "steps", "decode_rounds", "prefill_rounds", "decode_rows",
+             "padded_decode_rows", "max_active", "prefill_tokens", "max_prefill_tokens_per_turn",
+             "max_prefill_tokens_with_decoding", "max_tokens_per_step", "preemptions", "pages_in_use_max", "steps_ahead")
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, execute: Callable, publish: Callable, *, prefill_chunk=2048,
                  prefill_requests=32, prefill_token_budget=None, decode_prefill_token_budget=None,
                  admit: Optional[Callable] = None, launch: Optional[Callable] = None,
                  collect: Optional[Callable] = None, capacity: Optional[Callable] = None):
-        if prefill_chunk <= 0 or prefill_requests <= 0:
-            raise ValueError("invalid prefill budget")
-        for name, value in (("prefill token budget", prefill_token_budget),
-                            ("decode prefill token budget", decode_prefill_token_budget)):
-            if value is not None and (type(value) is not int or value < 1):
-                raise ValueError(f"{name} must be a positive integer")
-        self.cache = cache
-        self.execute = execute
+        self.budgets = Budgets(prefill_chunk, prefill_requests, prefill_token_budget, decode_prefill_token_budget)
         if (launch is None) != (collect is None):
             raise ValueError("launch and collect come as a pair")
-        self.launch, self.collect = launch, collect
-        self.flight: Optional[_Flight] = None
-        self.capacity = capacity  # rows that a step of only decoded tokens runs at, for the statistics
+        self.cache = cache
+        self.execute, self.launch, self.collect = execute, launch, collect
         self.publish = publish
         self.admit_request = admit or cache.admit
-        self.prefill_chunk = prefill_chunk
-        self.prefill_requests = prefill_requests
-        self.prefill_token_budget = prefill_token_budget
-        self.decode_prefill_token_budget = decode_prefill_token_budget
-        self.incoming: Queue = Queue()
+        self.capacity = capacity  # rows that a step of only decoded tokens runs at, for the statistics
+        self.flight: Optional[_Flight] = None
+        self.incoming: Queue = Queue()  # filled by submit() from any thread, emptied at the start of a turn
         self.pending: deque = deque()  # waiting for a slot and pages
         self.running: List[Request] = []  # hold cache, in order of admission
         self.stopped = Event()
-        self.stats = dict(
-            tokens=0, completed=0, cancelled=0, steps=0, decode_rounds=0, prefill_rounds=0, decode_rows=0,
-            max_active=0, prefill_tokens=0, max_prefill_tokens_per_turn=0, max_prefill_tokens_with_decoding=0,
-            max_tokens_per_step=0, preemptions=0, pages_in_use_max=0, steps_ahead=0, padded_decode_rows=0,
-            capacity_counts={},
-        )
+        self.stats = {name: 0 for name in _COUNTERS}
+        self.stats["capacity_counts"] = {}
+
+    prefill_chunk = property(lambda self: self.budgets.prefill_chunk)
+    prefill_requests = property(lambda self: self.budgets.prefill_requests)
+    prefill_token_budget = property(lambda self: self.budgets.prefill_token_budget)
+    decode_prefill_token_budget = property(lambda self: self.budgets.decode_prefill_token_budget)
 
     # ------------------------------------------------------------------ requests in and out
 
     def submit(self, request: Request) -> None:
+        """Hands a request over (from any thread); the next turn sees it."""
         if self.stopped.is_set():
-            raise RuntimeError("scheduler stopped")
+            raise RuntimeError("the scheduler has been stopped and takes no more requests")
         self.incoming.put(request)
+
+    def _drain_inbox(self, wait: float = 0.0) -> None:
+        """Moves what ``submit`` queued to the waiting line; with ``wait``, blocks that long for a first arrival."""
+        try:
+            if wait:
+                self.pending.append(self.incoming.get(timeout=wait))
+            while True:
+                self.pending.append(self.incoming.get_nowait())
+        except Empty:
+            pass
 
     @property
     def prefilling(self) -> List[Request]:
@@ -121,16 +162,12 @@ class Scheduler:
         self.pending.appendleft(request)
         self.stats["preemptions"] += 1
 
-    def _event(self, request: Request) -> tuple:
-        finished = request.finished
-        return (request, dict(
-            output_ids=list(request.output),
-            meta_info=dict(
-                prompt_tokens=len(request.prompt),
-                completion_tokens=len(request.output),
-                finish_reason=dict(type=request.finish_reason, length=request.limit) if finished else None,
-            ),
-        ))
+    @staticmethod
+    def _event(request: Request) -> tuple:
+        """What ``publish`` gets for a request: the record layout of kreasof-ai/akas's stream events."""
+        end = {"type": request.finish_reason, "length": request.limit} if request.finished else None
+        counts = {"prompt_tokens": len(request.prompt), "completion_tokens": len(request.output), "finish_reason": end}
+        return request, {"output_ids": list(request.output), "meta_info": counts}
 
     # ------------------------------------------------------------------ one turn
 
@@ -162,10 +199,7 @@ class Scheduler:
                     batch = [(r, n) for r, n in batch if r is not victim]
                     self._preempt(victim)
         decoding_now = bool(batch)
-        budget = self.prefill_token_budget
-        remaining = budget if budget is not None else self.prefill_chunk * self.prefill_requests
-        if decoding_now and self.decode_prefill_token_budget is not None:
-            remaining = min(remaining, self.decode_prefill_token_budget)
+        remaining = self.budgets.prompt_tokens(beside_decoding=decoding_now)
         selected = 0
 
         def portion(request) -> None:
@@ -202,11 +236,7 @@ class Scheduler:
 
     def turn(self) -> bool:
         """One step of the engine. Returns whether anything is still waiting, running or in flight."""
-        while True:
-            try:
-                self.pending.append(self.incoming.get_nowait())
-            except Empty:
-                break
+        self._drain_inbox()
         for request in list(self.running):
             if request.cancelled.is_set():
                 self.running.remove(request)
@@ -296,8 +326,8 @@ class Scheduler:
             if reason:
                 self.running.remove(request)
                 self._finish(request, reason)
-            # the first token at once, later ones in groups of four, the last always (as the reference publishes)
-            if request.published == 0 or len(request.output) - request.published >= 4 or reason:
+            unpublished = len(request.output) - request.published
+            if reason or request.published == 0 or unpublished >= _PUBLISH_EVERY:
                 events.append(self._event(request))
                 request.published = len(request.output)
         if events:
@@ -357,10 +387,7 @@ class Scheduler:
         try:
             while not self.stopped.is_set():
                 if not self.turn() and self.flight is None:
-                    try:
-                        self.pending.append(self.incoming.get(timeout=0.01))
-                    except Empty:
-                        pass
+                    self._drain_inbox(wait=0.01)  # idle: sleep until something arrives
         finally:
             self.shutdown()
 

@@ -33,10 +33,12 @@ _SIGNATURES = {
         "akas_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_take_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "akas_zero_row": [c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p],
+        "akas_add_bias": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_scale_cap": [c_void_p, c_float, c_float, c_longlong, c_void_p],
     },
     "conv": {
-        "akas_short_conv": [c_void_p] * 8 + [c_int] * 5 + [c_void_p],
-        "akas_short_conv_decode": [c_void_p] * 7 + [c_int] * 4 + [c_void_p],
+        "akas_short_conv": [c_void_p] * 8 + [c_int] * 6 + [c_void_p],
+        "akas_short_conv_decode": [c_void_p] * 7 + [c_int] * 5 + [c_void_p],
     },
     "rope": {
         "akas_rope_tables": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -218,6 +220,27 @@ def swiglu(gate_up):
     _check(_fn("elementwise", "akas_swiglu")(_ptr(_dense(gate_up, "gate_up")), _ptr(out), n, f2 // 2, _code(gate_up),
                                             _stream()), "swiglu")
     return out
+
+
+def add_bias(x, bias, out_dtype=None):
+    """x [N, C] float32 plus bias [C] float32, rounded once to ``out_dtype``; in place when that is float32."""
+    n, c = x.shape
+    if x.dtype != torch.float32 or bias.dtype != torch.float32 or bias.numel() != c:
+        raise ValueError("add_bias takes float32 x [N, C] and a float32 bias [C]")
+    target = out_dtype or torch.float32
+    out = x if target == torch.float32 else torch.empty((n, c), dtype=target, device=x.device)
+    _check(_fn("elementwise", "akas_add_bias")(_ptr(_dense(x, "x")), _ptr(bias), _ptr(out), n, c, _CODE[target], _stream()),
+           "add_bias")
+    return out
+
+
+def scale_cap(x, scale=1.0, cap=0.0):
+    """In place on float32 x: times ``scale``, then ``cap * tanh(x / cap)`` where ``cap`` > 0."""
+    if x.dtype != torch.float32:
+        raise TypeError("scale_cap takes float32")
+    _check(_fn("elementwise", "akas_scale_cap")(_ptr(_dense(x, "x")), float(scale), float(cap), x.numel(), _stream()),
+           "scale_cap")
+    return x
 
 
 def zero_rows(state, slot):
@@ -470,18 +493,20 @@ def norm_linear(h, norm_weight, eps, zero_centered, w, out_dtype=None, rows=None
 # --------------------------------------------------------------------------- mixers
 
 
-def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots, decode_only=False):
+def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots, decode_only=False, write=True):
+    """The gated short convolution over the flat batch; ``write=False`` reads the state and leaves it as it is."""
     n, c3 = bcx.shape
     c, l = c3 // 3, taps.shape[1]
     out = torch.empty((n, c), dtype=bcx.dtype, device=bcx.device)
     if decode_only:
         _check(_fn("conv", "akas_short_conv_decode")(_ptr(_dense(bcx, "bcx")), _ptr(taps), _ptr(bias), _ptr(state),
                                                     _ptr(seq_of_token), _ptr(slots), _ptr(out), n, c, l, _code(bcx),
-                                                    _stream()), "short_conv_decode")
+                                                    int(bool(write)), _stream()), "short_conv_decode")
         return out
     _check(_fn("conv", "akas_short_conv")(_ptr(_dense(bcx, "bcx")), _ptr(taps), _ptr(bias), _ptr(state),
                                          _ptr(cu_seqlens), _ptr(seq_of_token), _ptr(slots), _ptr(out), n,
-                                         slots.numel(), c, l, _code(bcx), _stream()), "short_conv", kernels=2)
+                                         slots.numel(), c, l, _code(bcx), int(bool(write)), _stream()), "short_conv",
+           kernels=2 if write else 1)
     return out
 
 

@@ -62,7 +62,7 @@ def norm_linear(h, norm_weight, eps, zero_centered, w, out_dtype=None, rows=None
     return linear_swiglu(x, w) if swiglu_out else linear(x, w, out_dtype=out_dtype)
 
 
-def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots, decode_only=False):
+def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots, decode_only=False, write=True):
     n, c3 = bcx.shape
     c = c3 // 3
     l = taps.shape[1]
@@ -82,8 +82,24 @@ def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots, decode_o
         if bias is not None:
             acc = acc + bias
         out[a:b] = gate[a:b] * acc
-        state[slot] = hist[-(l - 1) :]
+        if write:
+            state[slot] = hist[-(l - 1) :]
     return out.to(bcx.dtype)
+
+
+def add_bias(x, bias, out_dtype=None):
+    """x float32 [N, C] plus bias [C], rounded once to ``out_dtype``; in place when that is float32."""
+    if out_dtype in (None, torch.float32):
+        return x.add_(bias)
+    return (x + bias).to(out_dtype)
+
+
+def scale_cap(x, scale=1.0, cap=0.0):
+    """In place on float32 x: times ``scale``, then ``cap * tanh(x / cap)`` where ``cap`` > 0."""
+    x.mul_(scale)
+    if cap > 0:
+        x.copy_(cap * torch.tanh(x / cap))
+    return x
 
 
 def rope_tables(positions, inv_freq):
@@ -166,10 +182,11 @@ def argmax(logits):
 
 
 def sample(logits, temperature, top_k, top_p, uniform):
-    """Per row with temperature T: T <= 0 is the argmax. Else w_i = exp((x_i - max x) / T); token i is kept
-    iff fewer than top_k tokens have a larger logit (top_k <= 0 or >= V: no limit; ties stay together) and
-    the kept tokens with a larger logit hold at most top_p of the kept mass (top_p >= 1: no limit); the
-    result is the first kept i, in index order, whose running kept mass exceeds uniform * (kept mass)."""
+    """Per row with temperature T: T <= 0 is the argmax. Else w_i = exp((x_i - max x) / T); tokens are ranked by
+    logit, larger first, equal logits by id, lower first (the order of the reference's rank loop,
+    src/akas/ops/vocabulary/kernel.py:586-622). Token i is kept iff its rank is below top_k (top_k <= 0 or >= V:
+    no limit) and the kept tokens ranked before it hold at most top_p of the kept mass (top_p >= 1: no limit);
+    the result is the first kept i, in index order, whose running kept mass exceeds uniform * (kept mass)."""
     out = argmax(logits).clone()
     m, v = logits.shape
     for r in range(m):
@@ -178,18 +195,18 @@ def sample(logits, temperature, top_k, top_p, uniform):
             continue
         x = logits[r].to(torch.float32)
         w = torch.exp((x - x.max()) * torch.tensor(1.0 / t, dtype=torch.float32, device=x.device)).double()
+        order = torch.sort(x, descending=True, stable=True).indices  # equal logits: the lower id first
+        rank = torch.empty(v, dtype=torch.long, device=x.device)
+        rank[order] = torch.arange(v, device=x.device)
         keep = torch.ones(v, dtype=torch.bool, device=x.device)
-        desc = torch.sort(x, descending=True).values
-        larger = torch.searchsorted(-desc, -x, right=False)  # how many logits are strictly larger
         k = int(top_k[r])
         if 0 < k < v:
-            keep &= larger < k
+            keep &= rank < k
         p = float(top_p[r])
         if p < 1.0:
             kept_w = torch.where(keep, w, torch.zeros_like(w))
-            order = torch.sort(x, descending=True, stable=True).indices
-            before = torch.cat((torch.zeros(1, dtype=torch.float64, device=x.device), torch.cumsum(kept_w[order], 0)))
-            keep &= before[larger] <= p * kept_w.sum()
+            before = torch.cumsum(kept_w[order], 0) - kept_w[order]  # kept mass ranked before each token
+            keep &= before[rank] <= p * kept_w.sum()
         kept_w = torch.where(keep, w, torch.zeros_like(w))
         run = torch.cumsum(kept_w, 0)
         hit = torch.nonzero(keep & (run > float(uniform[r]) * run[-1]))

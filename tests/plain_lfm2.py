@@ -10,7 +10,8 @@ formula it restates (paths are relative to that project's root).
 tiny random model; ``tests/test_plain_reference.py`` checks this file against
 them, so the formulas here do not rest on a reading of the sources alone. Two
 options have no counterpart that runs in the reference (``conv_L_cache != 3``
-and ``conv_bias``): those rest on the formulas cited at ``short_conv``.
+and ``conv_bias``): those rest on the formulas cited at ``short_conv``; ``conv_bias``
+is read as the architecture's three biases (projection in, taps, projection out).
 """
 
 from __future__ import annotations
@@ -85,11 +86,13 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return torch.cat((left * c - right * s, left * s + right * c), dim=-1)
 
 
-def short_conv(x, in_proj, conv_weight, conv_bias, out_proj):
+def short_conv(x, in_proj, conv_weight, conv_bias, out_proj, in_bias=None, out_bias=None):
     """Gated causal depthwise short convolution over one whole sequence.
 
     x: [T, C]; in_proj: [3C, C]; conv_weight: [C, L]; conv_bias: [C] or None;
-    out_proj: [C, C]. The projection's three parts are B, C-gate, x in that order;
+    out_proj: [C, C]; in_bias: [3C] or None; out_bias: [C] or None (LFM2's ``conv_bias`` option gives all three
+    biases or none; the reference refuses the option, src/akas/models/lfm2/config.py:87, so the two projection
+    biases are plain linear-layer biases: added to the product). The projection's three parts are B, C-gate, x in that order;
     u = B*x; tap L-1 multiplies the current token, earlier taps the earlier u (zero
     before the sequence starts); the C gate multiplies the tap sum.
     src/akas/ops/convolution/kernel.py:43-91 (general L), with the bias added to the
@@ -98,6 +101,8 @@ def short_conv(x, in_proj, conv_weight, conv_bias, out_proj):
     T, C = x.shape
     L = conv_weight.shape[1]
     bcx = x @ in_proj.T
+    if in_bias is not None:
+        bcx = bcx + in_bias
     b, gate, xv = bcx[:, :C], bcx[:, C : 2 * C], bcx[:, 2 * C :]
     u = b * xv
     padded = torch.cat((torch.zeros(L - 1, C, dtype=x.dtype), u), dim=0)
@@ -106,7 +111,8 @@ def short_conv(x, in_proj, conv_weight, conv_bias, out_proj):
         acc = acc + padded[j : j + T] * conv_weight[:, j]
     if conv_bias is not None:
         acc = acc + conv_bias
-    return (gate * acc) @ out_proj.T
+    out = (gate * acc) @ out_proj.T
+    return out if out_bias is None else out + out_bias
 
 
 def attention(x, wq, wk, wv, wo, q_norm, k_norm, eps, heads, kv_heads, dim, theta, window=None):
@@ -179,7 +185,8 @@ def forward(cfg: dict, w: dict, tokens, window=None) -> torch.Tensor:
             cw = w[p + "conv.conv.weight"]
             cw = cw.reshape(cw.shape[0], cw.shape[-1])
             mixed = short_conv(
-                x, w[p + "conv.in_proj.weight"], cw, w.get(p + "conv.conv.bias"), w[p + "conv.out_proj.weight"]
+                x, w[p + "conv.in_proj.weight"], cw, w.get(p + "conv.conv.bias"), w[p + "conv.out_proj.weight"],
+                w.get(p + "conv.in_proj.bias"), w.get(p + "conv.out_proj.bias"),
             )
         else:
             a = p + "self_attn."

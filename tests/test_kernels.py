@@ -537,6 +537,20 @@ def test_sample(ops):
         assert got.tolist() == want.tolist(), (seed, got.tolist(), want.tolist())
     assert cuda.sample(logits, temp, top_k, top_p, u)[0] == logits[0].argmax()
     assert cuda.sample(logits, temp, top_k, top_p, u)[4] == logits[4].argmax()
+    # equal logits at the cut: top-k keeps exactly k, the lower ids of the equals; top-p cuts inside a run of equals
+    tied = torch.full((4, 64), -3.0, device=DEV)
+    tied[:, [5, 9, 20, 33, 40, 41, 50]] = torch.tensor([2.0, 1.0, 1.0, 1.0, 1.0, 0.5, 1.0], device=DEV)
+    temp4, k4 = t([1.0, 1.0, 0.5, 1.0], torch.float32), t([3, 4, 0, 64], torch.int32)
+    p4 = t([1.0, 1.0, 0.7, 0.7], torch.float32)
+    seen = [set() for _ in range(4)]
+    for seed in range(200):
+        u = torch.rand(4, generator=torch.Generator().manual_seed(100 + seed)).to(DEV)
+        got, want = cuda.sample(tied, temp4, k4, p4, u), ref.sample(tied, temp4, k4, p4, u)
+        assert got.tolist() == want.tolist(), (seed, got.tolist(), want.tolist())
+        for r in range(4):
+            seen[r].add(int(got[r]))
+    assert seen[0] == {5, 9, 20} and seen[1] == {5, 9, 20, 33}, seen  # not every token equal to the k-th
+    assert seen[2] == {5, 9, 20} and seen[3] == {5, 9, 20, 33, 40}, seen  # top-p stops inside the run of equals
     # frequencies follow softmax(logits / T)
     small = torch.tensor([[0.0, 1.0, 2.0, -1.0]], device=DEV).repeat(4096, 1)
     u = torch.rand(4096, generator=torch.Generator().manual_seed(1)).to(DEV)

@@ -88,20 +88,34 @@ def test_short_conv_part(device, taps, bias):
     c = 40
     part = build_part("mixer", ShortConvSpec(c, taps, bias), rt)
     w = {"in_proj.weight": _rand((3 * c, c), 1, 0.3), "conv.weight": _rand((c, 1, taps), 2), "out_proj.weight": _rand((c, c), 3, 0.3),
-         "conv.bias": _rand((c,), 4)}
-    assert set(part.params()) == set(w) - (set() if bias else {"conv.bias"})
+         "conv.bias": _rand((c,), 4), "in_proj.bias": _rand((3 * c,), 8), "out_proj.bias": _rand((c,), 9)}
+    biases = {"conv.bias", "in_proj.bias", "out_proj.bias"}  # the option gives all three or none
+    assert set(part.params()) == set(w) - (set() if bias else biases)
     part.load(lambda name: w[name].float().to(rt.device))
     cache = CacheManager([part.cache()], 8, 64, 2, 32, device=rt.device)
     lengths = [11, 4]
     ctx = _context(rt, cache, lengths)
     x = _rand((sum(lengths), c), 5)
+    state_before = cache.views[0].state.clone()
+    peek = part.forward(x.float().to(rt.device), ctx, cache.views[0], write=False).double().cpu()
+    assert torch.equal(cache.views[0].state, state_before)  # a layer that reads another's state leaves it alone
+    h = _rand((sum(lengths), c), 6)
     got = part.forward(x.float().to(rt.device), ctx, cache.views[0]).double().cpu()
+    assert torch.equal(got, peek)
+    assert not torch.equal(cache.views[0].state, state_before)
     at = 0
     for n in lengths:
         want = plain.short_conv(x[at:at + n], w["in_proj.weight"], w["conv.weight"].reshape(c, taps),
-                                w["conv.bias"] if bias else None, w["out_proj.weight"])
+                                w["conv.bias"] if bias else None, w["out_proj.weight"],
+                                w["in_proj.bias"] if bias else None, w["out_proj.bias"] if bias else None)
         assert _rel(got[at:at + n], want) < 1e-5
         at += n
+    # with a residual the result is residual + mixer(x), the output bias included; the state moved on by then, so
+    # fresh requests run the same tokens again
+    cache2 = CacheManager([part.cache()], 8, 64, 2, 32, device=rt.device)
+    ctx2 = _context(rt, cache2, lengths)
+    summed = part.forward(x.float().to(rt.device), ctx2, cache2.views[0], residual=h.float().to(rt.device)).double().cpu()
+    assert _rel(summed, h.float().double() + got) < 1e-5
 
 
 @pytest.mark.parametrize("device", _devices())

@@ -31,6 +31,7 @@ def test_random_mode_is_seeded_and_complete(tmp_path):
     assert any(not torch.equal(a[k], c[k]) for k in a)
     assert set(a) == {n for n, p in _model(config).params().items() if not p.optional} | {"lm_head.weight"}
     assert a["model.layers.1.conv.conv.weight"].shape == (96, 1, 4) and "model.layers.1.conv.conv.bias" in a
+    assert a["model.layers.1.conv.in_proj.bias"].shape == (288,) and a["model.layers.1.conv.out_proj.bias"].shape == (96,)
     assert abs(a["model.layers.0.operator_norm.weight"].mean() - 1) < 0.05
     assert abs(a["model.layers.0.self_attn.q_proj.weight"].std() - 0.02) < 0.005
     folder = write_random_model(tmp_path / "m", config, seed=5)
@@ -71,6 +72,26 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
                  "unexpected tensors (1)", "model.layers.9.ghost.weight", "wrong shapes (1)",
                  "model.layers.1.conv.in_proj.weight: checkpoint [5, 96], model [288, 96]", "unusable dtypes (1)"):
         assert word in text, word
+
+
+def test_conv_bias_means_three_biases(tmp_path):
+    """``conv_bias: true`` puts a bias on the in projection, the taps and the out projection; a checkpoint that lacks
+    one of the three is refused, and one without the option that carries any is refused too."""
+    config = config_from_dict(tiny.TINY_B)
+    folder = write_random_model(tmp_path / "m", config, seed=1, dtype="float32")
+    tensors = load_file(str(folder / "model.safetensors"))
+    for lost in ("model.layers.1.conv.in_proj.bias", "model.layers.3.conv.out_proj.bias"):
+        kept = {k: v for k, v in tensors.items() if k != lost}
+        save_file(kept, str(folder / "model.safetensors"))
+        with pytest.raises(WeightError, match=lost.replace(".", r"\.")):
+            load_weights(_model(config), folder)
+    save_file(tensors, str(folder / "model.safetensors"))
+    model = _model(config)
+    load_weights(model, folder)
+    assert model.blocks[1].mixer.bias_in.shape == (288,) and model.blocks[1].mixer.bias_out.dtype == torch.float32
+    plain_config = config_from_dict({**tiny.TINY_B, "conv_bias": False})
+    with pytest.raises(WeightError, match="unexpected"):
+        load_weights(_model(plain_config), folder)
 
 
 def test_head_follows_the_checkpoint_as_the_reference_does(tmp_path):

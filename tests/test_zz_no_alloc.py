@@ -77,6 +77,8 @@ def test_entry_point_without_allocation_matches_the_allocating_one():
     lib = _library()
     first = _case(1, [700, 33, 1500, 1], heads=8, kv_heads=2, dim=64, page=16)
     second = _case(2, [64, 900, 257], heads=6, kv_heads=1, dim=128, page=64)
+    from akas_b200.ops import reference
+
     for case, splits in ((first, 6), (second, 3), (first, 1)):
         err, got = _run(lib, case, splits, noalloc=True)
         assert err == 0, lib.akas_noalloc_error_string(err).decode()
@@ -85,13 +87,10 @@ def test_entry_point_without_allocation_matches_the_allocating_one():
         assert torch.isfinite(got.float()).all()
         scale = want.float().abs().max().item()
         assert (got.float() - want.float()).abs().max().item() <= 1e-2 * scale  # the kernel tests' bfloat16 tolerance
-    # and against the plain statement of the kernel
-    from akas_b200.ops import reference
-
-    want = reference.paged_attention(second["q"], second["k"], second["v"], second["table"], second["seq"], second["pos"],
-                                     second["dim"] ** -0.5, None, second["page"])
-    _, got = _run(lib, second, 3, noalloc=True)
-    assert (got.float() - want.float()).abs().max().item() <= 1e-2 * want.float().abs().max().item()
+        # and against the plain statement of the operation, which shares no kernel with either entry point
+        plain = reference.paged_attention(case["q"], case["k"], case["v"], case["table"], case["seq"], case["pos"],
+                                          case["dim"] ** -0.5, None, case["page"])
+        assert (got.float() - plain.float()).abs().max().item() <= 1e-2 * plain.float().abs().max().item()
 
 
 def test_sizes_beyond_the_scratch_are_refused_with_a_clear_error():
@@ -101,6 +100,8 @@ def test_sizes_beyond_the_scratch_are_refused_with_a_clear_error():
     assert lib.akas_decode_attention_bf16_noalloc_needs(4, 8, 1, 64) == 0  # one split needs no scratch
     too_many = NOALLOC_FLOATS // (4 * 8 * 66) + 1
     assert lib.akas_decode_attention_bf16_noalloc_needs(4, 8, too_many, 64) > NOALLOC_FLOATS
+    big = 2 ** 31 - 1  # a product that does not fit 64 bits is still "too many", never a small number
+    assert lib.akas_decode_attention_bf16_noalloc_needs(big, big, big, big) > NOALLOC_FLOATS
     err, out = _run(lib, case, too_many, noalloc=True)
     assert err == TOO_LARGE
     assert torch.isnan(out.float()).all()  # nothing was launched
