@@ -290,15 +290,14 @@ def bench_attention(kind: str, batch: int, context: int, heads: int = 32, kv_hea
         n = batch
         seq = torch.arange(batch, dtype=torch.int32, device="cuda")
         pos = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
-        ctx = SimpleNamespace(decode_only=True, max_context=context, query_tiles=0, cu_seqlens=None)
+        ctx = SimpleNamespace(decode_only=True, max_context=context, query_lens=(1,) * batch, cu_seqlens=None, memo={})
         flops = 4.0 * batch * context * heads * dim
     else:
         n = batch * context
         seq = torch.arange(batch, dtype=torch.int32, device="cuda").repeat_interleave(context)
         pos = torch.arange(context, dtype=torch.int32, device="cuda").repeat(batch)
         cu = torch.arange(0, n + 1, context, dtype=torch.int32, device="cuda")
-        ctx = SimpleNamespace(decode_only=False, max_context=context, query_tiles=batch * -(-context // 64),
-                              query_tiles_wide=batch * -(-context // 128), cu_seqlens=cu)
+        ctx = SimpleNamespace(decode_only=False, max_context=context, query_lens=(context,) * batch, cu_seqlens=cu, memo={})
         flops = 4.0 * batch * context * (context + 1) / 2 * heads * dim
     q = torch.randn((n, heads * dim), device="cuda", generator=g).to(torch.bfloat16)
     ms = _time_kernel(lambda: ops.paged_attention(q, k, v, table, seq, pos, dim ** -0.5, None, page, ctx), iters)

@@ -26,7 +26,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
-from ..parts.base import PagedKVSpec, StateSpec
+from ..parts.base import PagedSpec, StateSpec
 
 
 class OutOfPages(RuntimeError):
@@ -63,15 +63,18 @@ class PageAllocator:
         self._free.append(page)
 
 
-@dataclass
 class PagedCache:
-    """What a paged mixer gets: its own pools and the group whose block table addresses them."""
+    """What a paged mixer gets: its own pools (attributes named as its spec named them, ``None`` without storage), the
+    group whose block table addresses them, and that group's page size."""
 
-    k: Optional[torch.Tensor]
-    v: Optional[torch.Tensor]
-    group: int
-    page_size: int
-    spec: PagedKVSpec = None
+    def __init__(self, pools: Dict[str, Optional[torch.Tensor]], group: int, page_size: int, spec: PagedSpec):
+        self.pools, self.group, self.page_size, self.spec = pools, group, page_size, spec
+
+    def __getattr__(self, name):
+        pools = self.__dict__.get("pools", {})
+        if name in pools:
+            return pools[name]
+        raise AttributeError(name)
 
 
 @dataclass
@@ -86,6 +89,8 @@ class StateCache:
 class _Group:
     window: Optional[int]
     allocator: PageAllocator
+    page_size: int = 0
+    max_blocks: int = 0  # columns of this group's block table: the pages a request of full context holds
     blocks: Dict[Hashable, List[int]] = field(default_factory=dict)  # request -> page per block, -1 once released
 
 
@@ -101,8 +106,9 @@ class CacheManager:
                  context: int, dtype=torch.float32, device="cpu", storage: bool = True):
         """``cache_specs``: for each schedule entry the spec its mixer asked for, or None.
 
-        Every group gets ``pool_tokens // page_size`` pages; a request may hold up to
-        ``context`` tokens, so a block table has ``ceil(context / page_size)`` columns.
+        Every group gets ``pool_tokens // its page size`` pages (the engine's ``page_size`` unless the group's
+        specs name their own); a request may hold up to ``context`` tokens, so a group's block table has
+        ``ceil(context / its page size)`` columns.
         """
         if page_size < 1 or pool_tokens < page_size:
             raise ValueError(f"pool of {pool_tokens} tokens holds no page of {page_size}")
@@ -114,7 +120,7 @@ class CacheManager:
         self.groups: List[_Group] = []
         self.views: List[Optional[object]] = []
         self.state_tensors: List[torch.Tensor] = []  # [layers of one state shape, slots, *shape]: zeroed per slot in one go
-        self._group_of_window: Dict[Optional[int], int] = {}
+        self._group_of: Dict[tuple, int] = {}  # a spec's paging() -> group
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
         self._requests: Dict[Hashable, _Request] = {}
         self.peak_pages = 0
@@ -134,18 +140,22 @@ class CacheManager:
         for spec in cache_specs:
             if spec is None:
                 self.views.append(None)
-            elif isinstance(spec, PagedKVSpec):
-                gid = self._group_of_window.get(spec.window)
+            elif isinstance(spec, PagedSpec):
+                size = spec.page_size or page_size
+                if size < 1 or pool_tokens < size:
+                    raise ValueError(f"pool of {pool_tokens} tokens holds no page of {size}")
+                gid = self._group_of.get(spec.paging())
                 if gid is None:
                     gid = len(self.groups)
-                    self._group_of_window[spec.window] = gid
-                    self.groups.append(_Group(spec.window, PageAllocator(self.num_pages)))
-                k = v = None
+                    self._group_of[spec.paging()] = gid
+                    self.groups.append(_Group(spec.window, PageAllocator(pool_tokens // size), page_size=size,
+                                              max_blocks=-(-context // size)))
+                pools = {name: None for name in spec.pools(size)}
                 if storage:
-                    shape = (self.num_pages, spec.num_kv_heads, page_size, spec.head_dim)
-                    k = torch.zeros(shape, dtype=dtype, device=device)
-                    v = torch.zeros(shape, dtype=dtype, device=device)
-                self.views.append(PagedCache(k, v, gid, page_size, spec))
+                    pages = self.groups[gid].allocator.num_pages
+                    pools = {name: torch.zeros((pages, *shape), dtype=spec.dtype or dtype, device=device)
+                             for name, shape in spec.pools(size).items()}
+                self.views.append(PagedCache(pools, gid, size, spec))
             elif isinstance(spec, StateSpec):
                 state = None
                 if storage:
@@ -169,6 +179,21 @@ class CacheManager:
 
     def length(self, request) -> int:
         return self._requests[request].length
+
+    @property
+    def table_widths(self) -> List[int]:
+        """Columns of each group's block table."""
+        return [g.max_blocks for g in self.groups]
+
+    def capacity_tokens(self) -> int:
+        """The most tokens one request can hold when it has the pool to itself (a windowed group gives pages back as
+        it goes, so only groups that keep everything bound it)."""
+        full = [g.allocator.num_pages * g.page_size for g in self.groups if g.window is None]
+        return min(full, default=self.context)
+
+    def fits(self, tokens: int) -> bool:
+        """Whether every group has free pages for the first ``tokens`` tokens of a request that holds none yet."""
+        return all(-(-tokens // g.page_size) <= g.allocator.free for g in self.groups)
 
     def free_slots(self) -> int:
         return len(self._free_slots)
@@ -201,7 +226,7 @@ class CacheManager:
         """Pages each group lacks before ``tokens`` more tokens of ``request`` can be written."""
         req = self._requests[request]
         end = req.length + tokens
-        return [max(0, -(-end // self.page_size) - len(group.blocks[request])) for group in self.groups]
+        return [max(0, -(-end // group.page_size) - len(group.blocks[request])) for group in self.groups]
 
     def room(self, request) -> int:
         """How many more tokens of ``request`` could be reserved now: the rest of its last page plus the
@@ -209,8 +234,9 @@ class CacheManager:
         req = self._requests[request]
         if not self.groups:
             return self.context - req.length
-        held = min(len(g.blocks[request]) for g in self.groups) * self.page_size
-        return min(max(0, held - req.length) + self.min_free_pages() * self.page_size, self.context - req.length)
+        room = min(max(0, len(g.blocks[request]) * g.page_size - req.length) + g.allocator.free * g.page_size
+                   for g in self.groups)
+        return min(room, self.context - req.length)
 
     def reserve(self, request, tokens: int) -> None:
         """Takes pages in every group for the next ``tokens`` positions; all groups or none."""
@@ -241,7 +267,7 @@ class CacheManager:
             # the next query sits at position `length` and sees keys >= length - window + 1
             first_needed = req.length - group.window + 1
             blocks = group.blocks[request]
-            for b in range(min(len(blocks), max(0, first_needed) // self.page_size)):
+            for b in range(min(len(blocks), max(0, first_needed) // group.page_size)):
                 if blocks[b] >= 0:
                     group.allocator.give(blocks[b])
                     blocks[b] = -1

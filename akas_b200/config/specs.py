@@ -134,6 +134,11 @@ class ModelSpec:
     head_optional: bool = False  # the head tensor may be absent; the embedding is the head then
     schedule: Tuple[ScheduleEntry, ...] = ()
     max_context: int = 128000
+    # What some architectures do at the decoder's two ends (LFM2 does none of it): the embedding's rows times a
+    # constant; the logits times a constant; then cap * tanh(logits / cap).
+    embedding_multiplier: Optional[float] = None
+    logit_scale: Optional[float] = None
+    logit_softcap: Optional[float] = None
 
     def run_order(self) -> Tuple[ScheduleEntry, ...]:
         if self.schedule:

@@ -10,7 +10,7 @@ single decoded tokens of others, cut anywhere.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -45,12 +45,11 @@ class StepContext:
     slots: torch.Tensor  # int32 [R] state slot of each request
     logit_rows: torch.Tensor  # int32 [M] flat token index of each wanted row
     num_logit_rows: int
-    block_tables: List[torch.Tensor]  # per group: int32 [R, max_blocks]
+    block_tables: List[torch.Tensor]  # per page group: int32 [R, that group's max_blocks]
     max_query_len: int
     max_context: int  # largest position + 1 in the batch
     decode_only: bool  # every request brings exactly one token
-    query_tiles: int = 0  # sum over requests of ceil(tokens / 64): the grid of the prompt-attention kernel
-    query_tiles_wide: int = 0  # the same with 128-token tiles (the tensor-memory kernel's)
+    query_lens: Tuple[int, ...] = ()  # how many tokens each request brings, known on the host (a kernel sizes its grid from it)
     memo: Dict = field(default_factory=dict)  # per-step results shared between layers (rotary tables)
 
     def block_table(self, group: int) -> torch.Tensor:
@@ -60,7 +59,8 @@ class StepContext:
 class BatchLayout:
     """Offsets (in int32 elements) of each array inside the staging buffer for a batch of N tokens, R requests."""
 
-    def __init__(self, n: int, r: int, m: int, groups: int, max_blocks: int):
+    def __init__(self, n: int, r: int, m: int, table_widths: Sequence[int]):
+        """``table_widths``: for each page group the columns of its block table (``CacheManager.table_widths``)."""
         self.n, self.r, self.m = n, r, m
         off = 0
 
@@ -77,7 +77,8 @@ class BatchLayout:
         self.cu_seqlens = take(r + 1)
         self.slots = take(r)
         self.logit_rows = take(max(m, 1))
-        self.tables = [take(r * max_blocks) for _ in range(groups)]
+        self.table_widths = tuple(table_widths)
+        self.tables = [take(r * width) for width in self.table_widths]
         self.size = off
 
 
@@ -96,7 +97,6 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntr
     cu = host[layout.cu_seqlens : layout.cu_seqlens + r + 1]
     slots = host[layout.slots : layout.slots + r]
     rows = host[layout.logit_rows : layout.logit_rows + max(layout.m, 1)]
-    max_blocks = cache.max_blocks
     live = len(entries)
     max_q = max_ctx = at = 0
     if live:
@@ -122,7 +122,7 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntr
                 src[first[i]] = e.source
         wanted = [int(first[i]) + w for i, e in enumerate(entries) for w in e.want]
         rows[: len(wanted)] = wanted
-        for g, offset in enumerate(layout.tables):
+        for g, (offset, max_blocks) in enumerate(zip(layout.tables, layout.table_widths)):
             table = host[offset : offset + live * max_blocks].reshape(live, max_blocks)
             table[:] = -1
             for i, e in enumerate(entries):
@@ -138,6 +138,6 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, entries: Sequence[StepEntr
         seq[at:n] = -1
         cu[live + 1 : r + 1] = at
         slots[live:r] = -1
-        for offset in layout.tables:
+        for offset, max_blocks in zip(layout.tables, layout.table_widths):
             host[offset + live * max_blocks : offset + r * max_blocks] = -1
     return max_q, max_ctx

@@ -112,7 +112,7 @@ class Engine:
 
     @property
     def context(self) -> int:
-        return min(self.config.context, self.runner.cache.num_pages * self.config.page_size)
+        return min(self.config.context, self.runner.cache.capacity_tokens())
 
     @property
     def capacity(self) -> int:

@@ -92,8 +92,7 @@ class ModelRunner:
             self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         return self._host, self._dev
 
-    def _context(self, dev: torch.Tensor, lay: BatchLayout, max_q: int, max_ctx: int, decode_only: bool):
-        mb = self.cache.max_blocks
+    def _context(self, dev: torch.Tensor, lay: BatchLayout, max_q: int, max_ctx: int, decode_only: bool, query_lens=()):
         return StepContext(
             num_tokens=lay.n,
             num_seqs=lay.r,
@@ -104,10 +103,11 @@ class ModelRunner:
             slots=dev[lay.slots : lay.slots + lay.r],
             logit_rows=dev[lay.logit_rows : lay.logit_rows + lay.m],
             num_logit_rows=lay.m,
-            block_tables=[dev[o : o + lay.r * mb].view(lay.r, mb) for o in lay.tables],
+            block_tables=[dev[o : o + lay.r * mb].view(lay.r, mb) for o, mb in zip(lay.tables, lay.table_widths)],
             max_query_len=max_q,
             max_context=max_ctx,
             decode_only=decode_only,
+            query_lens=tuple(query_lens),
         )
 
     # ------------------------------------------------------------------ the step
@@ -169,18 +169,16 @@ class ModelRunner:
             # not seen (about 45 us of host time a product), and a serving step brings any number of tokens: beyond
             # 256 the step is padded to a multiple of 256 with tokens of no request, which every kernel skips.
             padded = -(-n // _TOKEN_ROUNDING) * _TOKEN_ROUNDING if n > _TOKEN_ROUNDING and self.dtype == torch.bfloat16 else n
-            lay = BatchLayout(padded, len(entries), m, len(self.cache.groups), self.cache.max_blocks)
+            lay = BatchLayout(padded, len(entries), m, self.cache.table_widths)
             ring, dev = self._staging(lay.size)
             host = ring.take()
             max_q, max_ctx = fill_batch(host.numpy(), lay, entries, self.cache, pad_to=padded if padded > n else 0,
                                         tokens=arrays)
             dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
             ring.copied()
-            ctx = self._context(dev, lay, max_q, max_ctx, decode_only)
+            ctx = self._context(dev, lay, max_q, max_ctx, decode_only, [len(e.tokens) for e in entries])
             if previous is not None:
                 self.ops.take_tokens(ctx.token_ids, dev[lay.token_src : lay.token_src + lay.n], previous)
-            ctx.query_tiles = sum(-(-len(e.tokens) // 64) for e in entries)
-            ctx.query_tiles_wide = sum(-(-len(e.tokens) // 128) for e in entries)
             logits = self.model.forward(ctx, self.cache.views)
         for e in entries:
             self.cache.advance(e.request, len(e.tokens))
@@ -213,16 +211,14 @@ class ModelRunner:
             return []
         sizes = list(range(2 * _TOKEN_ROUNDING, -(-most_tokens // _TOKEN_ROUNDING) * _TOKEN_ROUNDING + 1, _TOKEN_ROUNDING))
         for n in sizes:
-            lay = BatchLayout(n, 1, 1, len(self.cache.groups), self.cache.max_blocks)
+            lay = BatchLayout(n, 1, 1, self.cache.table_widths)
             ring, dev = self._staging(lay.size)
             host = ring.take()
             fill_batch(host.numpy(), lay, [], self.cache, pad_to=n)
             host.numpy()[lay.logit_rows] = 0
             dev[: lay.size].copy_(host[: lay.size], non_blocking=True)
             ring.copied()
-            ctx = self._context(dev, lay, n, self.config.context, False)
-            ctx.query_tiles = -(-n // 64)
-            ctx.query_tiles_wide = -(-n // 128)
+            ctx = self._context(dev, lay, n, self.config.context, False, [n])
             self.model.forward(ctx, self.cache.views)
         torch.cuda.synchronize(self.device)
         return sizes
@@ -304,9 +300,9 @@ class _DecodeGraph:
         self.lengths = lengths
         cache = runner.cache
         if lengths is None:
-            self.layout = BatchLayout(bucket, bucket, bucket, len(cache.groups), cache.max_blocks)
+            self.layout = BatchLayout(bucket, bucket, bucket, cache.table_widths)
         else:
-            self.layout = BatchLayout(sum(lengths), len(lengths), wanted, len(cache.groups), cache.max_blocks)
+            self.layout = BatchLayout(sum(lengths), len(lengths), wanted, cache.table_widths)
         self.ring = _Pinned(self.layout.size, runner.device)
         self.dev = torch.zeros(self.layout.size, dtype=torch.int32, device=runner.device)
         self.graph = None
@@ -333,12 +329,10 @@ class _DecodeGraph:
             # The context's host-side sizes are upper bounds so that the captured launches fit every replay.
             self._fill([])
             if self.lengths is None:
-                ctx = runner._context(self.dev, self.layout, 1, runner.config.context, True)
+                ctx = runner._context(self.dev, self.layout, 1, runner.config.context, True, [1] * self.bucket)
             else:
                 ctx = runner._context(self.dev, self.layout, max(self.lengths), runner.config.context,
-                                      all(n == 1 for n in self.lengths))
-                ctx.query_tiles = sum(-(-n // 64) for n in self.lengths)
-                ctx.query_tiles_wide = sum(-(-n // 128) for n in self.lengths)
+                                      all(n == 1 for n in self.lengths), self.lengths)
             ctx.memo["captured"] = True
             stream = torch.cuda.Stream(device=runner.device)
             stream.wait_stream(torch.cuda.current_stream(runner.device))

@@ -226,7 +226,7 @@ class Scheduler:
                 self._finish(request, "cancelled")
                 continue
             first = min(self.prefill_chunk, request.pending_tokens())
-            if -(-first // cache.page_size) > cache.min_free_pages() and self.running:
+            if not cache.fits(first) and self.running:
                 break  # wait until running requests finish and give pages back
             self.pending.popleft()
             request.slot = self.admit_request(request.id)

@@ -1,8 +1,9 @@
 """The generic decoder that every registered architecture is built as.
 
-Embedding, the blocks of ``ModelSpec.layers`` in the order of ``ModelSpec.schedule``
-(a list that may name a layer twice or let an entry read another entry's cache),
-the final norm on the rows whose logits are wanted, and the head (the checkpoint's
+Embedding (times ``ModelSpec.embedding_multiplier`` if the architecture has one), the blocks of
+``ModelSpec.layers`` in the order of ``ModelSpec.schedule`` (a list that may name a layer twice or let an
+entry read another entry's cache), the final norm on the rows whose logits are wanted, the head, and the
+architecture's ``logit_scale`` and ``logit_softcap`` if it has them. The head is the checkpoint's
 head tensor when it has one, else the embedding:
 src/akas/models/lfm2/weights.py:399-402 and _composition.py:363-380 in kreasof-ai/akas).
 It holds weights and computes; caches belong to the cache manager and reach the
@@ -67,7 +68,10 @@ class Decoder:
     def forward(self, ctx, caches) -> torch.Tensor:
         """Runs the tokens of ``ctx`` and returns float32 logits ``[len(ctx.logit_rows), vocab]``."""
         ops = self.rt.ops
+        spec = self.spec
         h = ops.embedding(ctx.token_ids, self.embedding)
+        if spec.embedding_multiplier is not None:
+            h = ops.scale_cap(h, scale=spec.embedding_multiplier)
         for i, entry in enumerate(self.schedule):
             owner = i if entry.cache is None else entry.cache
             h = self.blocks[entry.layer].forward(h, ctx, caches[owner], write=entry.cache is None)
@@ -77,4 +81,8 @@ class Decoder:
             x = self.final_norm.lazy(h, rows=ctx.logit_rows)
         else:
             x = self.final_norm.forward(h, rows=ctx.logit_rows)
-        return project(self.rt, x, self.head, out_dtype=torch.float32)
+        logits = project(self.rt, x, self.head, out_dtype=torch.float32)
+        if spec.logit_scale is not None or spec.logit_softcap is not None:
+            logits = ops.scale_cap(logits, scale=1.0 if spec.logit_scale is None else spec.logit_scale,
+                                   cap=spec.logit_softcap or 0.0)
+        return logits

@@ -573,6 +573,18 @@ def decode_splits(num_tokens: int, kv_heads: int, head_tiles: int, max_context: 
     return max(1, min(want, most, 64))
 
 
+def _query_tiles(ctx):
+    """How many 64-query tiles (the mma.sync prompt kernel's) and 128-query tiles (the tensor-memory kernel's) the
+    requests of this step make, from the token counts the host knows; once per step."""
+    if ctx is None or not getattr(ctx, "query_lens", None):
+        return 0, 0
+    counts = ctx.memo.get("query_tiles")
+    if counts is None:
+        counts = ctx.memo["query_tiles"] = (sum(-(-n // 64) for n in ctx.query_lens),
+                                            sum(-(-n // 128) for n in ctx.query_lens))
+    return counts
+
+
 def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, page_size, ctx=None):
     n = q.shape[0]
     kh, d = k_pool.shape[1], k_pool.shape[3]
@@ -604,8 +616,7 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
             _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
             splits, _code(q), _stream()), "paged_attention_decode", kernels=2)
         return out
-    tiles = getattr(ctx, "query_tiles", 0) if ctx is not None else 0
-    wide = getattr(ctx, "query_tiles_wide", 0) if ctx is not None else 0
+    tiles, wide = _query_tiles(ctx)
     # A 128-query tile of the tensor-memory kernel costs about what a 64-query tile of the mma.sync kernel costs
     # (measured: 1.8 times the throughput): it pays when requests bring more than 64 tokens, not for single tokens.
     tensor_memory = prompt_attention == "tcgen05" or (prompt_attention == "auto" and 0 < wide and wide <= 0.9 * tiles)

@@ -5,6 +5,7 @@ from .base import (
     Mixer,
     Normed,
     PagedKVSpec,
+    PagedSpec,
     Param,
     Part,
     Runtime,
@@ -25,7 +26,7 @@ from .shortconv import ShortConv
 from .swiglu import SwiGLU
 
 __all__ = [
-    "ARRANGEMENTS", "Attention", "Block", "FeedForward", "Mixer", "Normed", "PagedKVSpec", "Param", "Part", "RMSNorm",
+    "ARRANGEMENTS", "Attention", "Block", "FeedForward", "Mixer", "Normed", "PagedKVSpec", "PagedSpec", "Param", "Part", "RMSNorm",
     "Rope", "Runtime", "ShortConv", "StateSpec", "SwiGLU", "build_part", "project", "project_swiglu", "register_ffn", "register_mixer",
     "register_norm", "register_position",
 ]

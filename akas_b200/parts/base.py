@@ -48,13 +48,40 @@ class Param:
     mean: float = 0.0
 
 
-@dataclass(frozen=True)
-class PagedKVSpec:
-    """Keys and values of every position (or of the last ``window``), in pages."""
+class PagedSpec:
+    """What a mixer with per-token storage asks of the cache manager; a mixer returns an instance from ``cache()``.
 
-    num_kv_heads: int
-    head_dim: int
+    ``pools(page_size)`` names its pools and gives the shape of ONE page of each (``{"k": (kv_heads, page, head_dim),
+    ...}``); the manager allocates ``[pages, *shape]`` per pool and hands them over as attributes of the view the
+    mixer gets (``cache.k``). ``window``: how many of the latest tokens are ever read (None: all); pages behind the
+    window are given back while the request runs. ``page_size``: tokens per page if the mixer needs a size of its own
+    (None: the engine's). ``dtype``: None for the compute dtype. Layers whose specs agree in ``paging()`` share page
+    numbers, a free list and a block table; everything else (what a page holds) is the layer's own."""
+
     window: Optional[int] = None
+    page_size: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
+
+    def pools(self, page_size: int) -> Dict[str, Tuple[int, ...]]:
+        raise NotImplementedError
+
+    def paging(self) -> tuple:
+        return (self.window, self.page_size)
+
+
+@dataclass(frozen=True)
+class PagedKVSpec(PagedSpec):
+    """Keys and values of every position (or of the last ``window``), in pages ``[kv_heads, page, head_dim]``."""
+
+    num_kv_heads: int = 1
+    head_dim: int = 16
+    window: Optional[int] = None
+    page_size: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
+
+    def pools(self, page_size: int) -> Dict[str, Tuple[int, ...]]:
+        shape = (self.num_kv_heads, page_size, self.head_dim)
+        return {"k": shape, "v": shape}
 
 
 @dataclass(frozen=True)

@@ -115,8 +115,14 @@ def short_conv(x, in_proj, conv_weight, conv_bias, out_proj, in_bias=None, out_b
     return out if out_bias is None else out + out_bias
 
 
-def attention(x, wq, wk, wv, wo, q_norm, k_norm, eps, heads, kv_heads, dim, theta, window=None):
+def attention(x, wq, wk, wv, wo, q_norm, k_norm, eps, heads, kv_heads, dim, theta, window=None, rotary=None, rows=None):
     """GQA attention over one whole sequence with per-head QK RMSNorm, then RoPE.
+
+    ``rotary`` (not an option of LFM2): only the first ``rotary`` channels of each head are rotated, with
+    frequencies base^(-2i/rotary) and pairs (i, i + rotary/2); the rest pass through
+    (src/akas/ops/attention/kernel.py:1301-1337).
+    ``rows``: compute the output for these query positions only (keys and values are still those of the whole
+    sequence); the result then has ``len(rows)`` rows.
 
     Query head H reads KV head H // (heads / kv_heads); scale d^-0.5; key j visible
     to query t iff j <= t (and j > t - window when a window is given).
@@ -124,25 +130,27 @@ def attention(x, wq, wk, wv, wo, q_norm, k_norm, eps, heads, kv_heads, dim, thet
     tests/support/numpy_reference.py:138-173.
     """
     T = x.shape[0]
-    q = (x @ wq.T).reshape(T, heads, dim)
+    at = torch.arange(T) if rows is None else torch.as_tensor(rows, dtype=torch.long)
+    q = (x[at] @ wq.T).reshape(len(at), heads, dim)
     k = (x @ wk.T).reshape(T, kv_heads, dim)
     v = (x @ wv.T).reshape(T, kv_heads, dim)
     q = rms_norm(q, q_norm, eps)
     k = rms_norm(k, k_norm, eps)
     pos = torch.arange(T)
-    cos, sin = rope_tables(pos, dim, theta, x.dtype)
-    q = apply_rope(q, cos, sin)
-    k = apply_rope(k, cos, sin)
+    rot = dim if rotary is None else rotary
+    cos, sin = rope_tables(pos, rot, theta, x.dtype)
+    q = torch.cat((apply_rope(q[..., :rot], cos[at], sin[at]), q[..., rot:]), dim=-1)
+    k = torch.cat((apply_rope(k[..., :rot], cos, sin), k[..., rot:]), dim=-1)
     group = heads // kv_heads
     k = k.repeat_interleave(group, dim=1)
     v = v.repeat_interleave(group, dim=1)
     scores = torch.einsum("thd,shd->hts", q, k) * (dim ** -0.5)
-    visible = pos[None, :] <= pos[:, None]
+    visible = pos[None, :] <= at[:, None]
     if window is not None:
-        visible &= pos[None, :] > pos[:, None] - window
+        visible &= pos[None, :] > at[:, None] - window
     scores = scores.masked_fill(~visible[None], float("-inf"))
     prob = torch.softmax(scores, dim=-1)
-    out = torch.einsum("hts,shd->thd", prob, v).reshape(T, heads * dim)
+    out = torch.einsum("hts,shd->thd", prob, v).reshape(len(at), heads * dim)
     return out @ wo.T
 
 
@@ -166,8 +174,9 @@ def load_folder(folder, dtype=torch.float64):
     return cfg, weights
 
 
-def forward(cfg: dict, w: dict, tokens, window=None) -> torch.Tensor:
-    """Logits at every position of one sequence: [T, vocab].
+def forward(cfg: dict, w: dict, tokens, window=None, rows=None) -> torch.Tensor:
+    """Logits at every position of one sequence: [T, vocab]; with ``rows``, at those positions only: [len(rows), vocab]
+    (every layer but the last still runs the whole sequence; the last one, the final norm and the head run the rows).
 
     src/akas/models/lfm2/_composition.py:108-380: embedding; per layer
     h += mixer(norm(h)); h += ffn(norm(h)); final norm; head (lm_head.weight when
@@ -178,8 +187,11 @@ def forward(cfg: dict, w: dict, tokens, window=None) -> torch.Tensor:
     heads, kv_heads, dim = cfg["num_attention_heads"], cfg["num_key_value_heads"], head_dim(cfg)
     theta = rope_theta(cfg)
     h = w["model.embed_tokens.weight"][tokens]
-    for i, kind in enumerate(layer_kinds(cfg)):
+    kinds = layer_kinds(cfg)
+    sel = None if rows is None else torch.as_tensor(rows, dtype=torch.long)
+    for i, kind in enumerate(kinds):
         p = f"model.layers.{i}."
+        last = sel is not None and i == len(kinds) - 1
         x = rms_norm(h, w[p + "operator_norm.weight"], eps)
         if kind == "conv":
             cw = w[p + "conv.conv.weight"]
@@ -188,17 +200,21 @@ def forward(cfg: dict, w: dict, tokens, window=None) -> torch.Tensor:
                 x, w[p + "conv.in_proj.weight"], cw, w.get(p + "conv.conv.bias"), w[p + "conv.out_proj.weight"],
                 w.get(p + "conv.in_proj.bias"), w.get(p + "conv.out_proj.bias"),
             )
+            if last:
+                mixed = mixed[sel]
         else:
             a = p + "self_attn."
             mixed = attention(
                 x, w[a + "q_proj.weight"], w[a + "k_proj.weight"], w[a + "v_proj.weight"],
                 w[a + "out_proj.weight"], w[a + "q_layernorm.weight"], w[a + "k_layernorm.weight"],
-                eps, heads, kv_heads, dim, theta, window,
+                eps, heads, kv_heads, dim, theta, window, rows=sel if last else None,
             )
-        h = h + mixed
+        h = (h[sel] if last else h) + mixed
         x = rms_norm(h, w[p + "ffn_norm.weight"], eps)
         f = p + "feed_forward."
         h = h + swiglu(x, w[f + "w1.weight"], w[f + "w3.weight"], w[f + "w2.weight"])
+    if sel is not None and not kinds:
+        h = h[sel]
     x = rms_norm(h, w["model.embedding_norm.weight"], eps)
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     return x @ head.T

@@ -378,8 +378,8 @@ class _Prompt:
 
     def __init__(self, cu, lengths):
         self.cu_seqlens = cu
-        self.query_tiles = sum(-(-n // 64) for n in lengths)
-        self.query_tiles_wide = sum(-(-n // 128) for n in lengths)
+        self.query_lens = tuple(lengths)
+        self.memo = {}
         self.max_context = 0
 
 

@@ -4,7 +4,9 @@ The toy architecture is defined here and registered through the public registrie
 framework knows it. It holds a mixer with state of its own (an exponential moving average), an
 attention layer with a window (a page group of its own whose pages are given back as the window moves),
 a layer that runs twice, a schedule entry that reads another entry's cache, a feed-forward that routes every
-token to one of three experts, and a position encoding that is not rotary (a decay with distance).
+token to one of three experts, a position encoding that is not rotary (a decay with distance), a mixer whose
+per-token storage is one pool of pages of a size of its own, and the decoder's optional ends (embedding multiplier,
+logit scale and softcap).
 """
 
 from dataclasses import dataclass, field
@@ -22,7 +24,7 @@ from akas_b200.config import (AttentionSpec, EngineConfig, LayerSpec, ModelSpec,
 from akas_b200.engine.batch import BatchLayout, StepEntry, fill_batch
 from akas_b200.engine.runner import ModelRunner
 from akas_b200.ops import reference
-from akas_b200.parts import (Block, FeedForward, Mixer, Param, Part, Runtime, StateSpec, build_part, register_ffn,
+from akas_b200.parts import (Block, FeedForward, Mixer, PagedSpec, Param, Part, Runtime, StateSpec, build_part, register_ffn,
                              register_mixer, register_position)
 from akas_b200.weights import write_random_model
 
@@ -51,7 +53,7 @@ def _context(rt, cache, lengths):
         cache.admit(i)
         cache.reserve(i, n)
         entries.append(StepEntry(i, [0] * n, ()))
-    lay = BatchLayout(sum(lengths), len(lengths), 0, len(cache.groups), cache.max_blocks)
+    lay = BatchLayout(sum(lengths), len(lengths), 0, cache.table_widths)
     host = torch.zeros(lay.size, dtype=torch.int32)
     mq, mc = fill_batch(host.numpy(), lay, entries, cache)
     dev = host.to(rt.device)
@@ -138,13 +140,11 @@ def test_attention_part(device, heads, kv, dim, window, rotary):
     got = part.forward(x.float().to(rt.device), ctx, cache.views[0], residual=h).double().cpu()
     at = 0
     for n in lengths:
-        if rotary is None:
-            want = plain.attention(x[at:at + n], w["q_proj.weight"], w["k_proj.weight"], w["v_proj.weight"],
-                                   w["out_proj.weight"], w["q_norm.weight"], w["k_norm.weight"], 1e-6, heads, kv, dim,
-                                   1e4, window)
-            assert _rel(got[at:at + n], want) < 1e-5
+        want = plain.attention(x[at:at + n], w["q_proj.weight"], w["k_proj.weight"], w["v_proj.weight"],
+                               w["out_proj.weight"], w["q_norm.weight"], w["k_norm.weight"], 1e-6, heads, kv, dim,
+                               1e4, window, rotary)
+        assert _rel(got[at:at + n], want) < 1e-5
         at += n
-    assert torch.isfinite(got).all()
 
 
 @pytest.mark.parametrize("device", _devices())
@@ -187,15 +187,54 @@ class EmaMixer(Mixer):
     def forward(self, x, ctx, cache=None, residual=None, write=True):
         u = self.rt.ops.linear(x, self.w, out_dtype=torch.float32)
         out = torch.zeros_like(u)
-        cu, slots = ctx.cu_seqlens.tolist(), ctx.slots.tolist()
-        for r, slot in enumerate(slots):
-            if slot < 0:
-                continue
-            s = cache.state[slot].clone()
-            for t in range(cu[r], cu[r + 1]):
+        slots, at = ctx.slots.tolist(), 0
+        for r, count in enumerate(ctx.query_lens):  # how many tokens each request brings is known on the host
+            s = cache.state[slots[r]].clone()
+            for t in range(at, at + count):
                 s = self.decay * s + u[t]
                 out[t] = s
-            cache.state[slot] = s
+            cache.state[slots[r]] = s
+            at += count
+        return residual.add_(out) if residual is not None else out.to(x.dtype)
+
+
+@dataclass(frozen=True)
+class LatentPages(PagedSpec):
+    """One pool, one vector per token, pages of two tokens whatever the engine's page size is."""
+
+    width: int = 0
+    page_size: int = 2
+    dtype: torch.dtype = torch.float32
+    window: int = None
+
+    def pools(self, page_size):
+        return {"latent": (page_size, self.width)}
+
+
+class PrefixMeanMixer(Mixer):
+    """z_t = x_t W^T goes into the request's pages; out_t is the mean of z_s over s <= t, read back from the pages."""
+
+    def params(self):
+        c = self.spec.options["width"]
+        return {"proj.weight": Param((c, c))}
+
+    def load(self, get):
+        self.w = get("proj.weight")
+
+    def cache(self):
+        return LatentPages(width=self.spec.options["width"])
+
+    def forward(self, x, ctx, cache=None, residual=None, write=True):
+        z = self.rt.ops.linear(x, self.w, out_dtype=torch.float32)
+        table, page = ctx.block_table(cache.group).long(), cache.page_size
+        seq, pos = ctx.seq_of_token.long(), ctx.positions.long()
+        live = (seq >= 0).nonzero().flatten()
+        if write:
+            cache.latent[table[seq[live], pos[live] // page], pos[live] % page] = z[live]
+        out = torch.zeros_like(z)
+        for t in live.tolist():
+            upto = torch.arange(int(pos[t]) + 1, device=x.device)
+            out[t] = cache.latent[table[seq[t], upto // page], upto % page].mean(dim=0)
         return residual.add_(out) if residual is not None else out.to(x.dtype)
 
 
@@ -269,18 +308,20 @@ class ToyConfig:
                     layer(1, AttentionSpec(c, 2, 1, 16, window=self.window, **attn)),
                     layer(2, AttentionSpec(c, 2, 2, 16, **attn)),
                     layer(3, AttentionSpec(c, 2, 1, 16, qk_norm=None, position=PartSpec("decay_for_tests", {"rate": 0.97})),
-                          PartSpec("routed_for_tests", {"width": c, "hidden": 40, "experts": 3}))),
+                          PartSpec("routed_for_tests", {"width": c, "hidden": 40, "experts": 3})),
+                    layer(4, PartSpec("prefix_mean_for_tests", {"width": c}))),
             final_norm=norm, embedding_name="embed", final_norm_name="final_norm", head_name=None,
             # layer 1 runs twice, each time with a cache of its own; the last entry reads entry 2's keys and values
             schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(1), ScheduleEntry(2, cache=2),
-                      ScheduleEntry(3)),
+                      ScheduleEntry(3), ScheduleEntry(4)),
+            embedding_multiplier=1.7, logit_scale=0.4, logit_softcap=2.5,
         )
 
 
 def _toy_plain(cfg, w, tokens):
     """The toy model, whole sequence, float64, from the plain part functions."""
     c, T = cfg.width, len(tokens)
-    h = w["embed"][torch.as_tensor(tokens)]
+    h = w["embed"][torch.as_tensor(tokens)] * 1.7
     kept = {}
 
     def attn(i, x, window, heads, kv, shared=None, decay=None):
@@ -308,7 +349,7 @@ def _toy_plain(cfg, w, tokens):
         out = torch.einsum("hts,shd->thd", torch.softmax(score, -1), vv).reshape(T, heads * d)
         return out @ w[p + "out_proj.weight"].T, (k, v)
 
-    for n, (i, shared) in enumerate(((0, None), (1, None), (2, None), (1, None), (2, 2), (3, None))):
+    for n, (i, shared) in enumerate(((0, None), (1, None), (2, None), (1, None), (2, 2), (3, None), (4, None))):
         p = f"layers.{i}."
         x = plain.rms_norm(h, w[p + "norm1"], 1e-5)
         if i == 0:
@@ -320,6 +361,9 @@ def _toy_plain(cfg, w, tokens):
             mixed = torch.stack(rows)
         elif i == 3:
             mixed, kept[n] = attn(i, x, None, 2, 1, decay=0.97)
+        elif i == 4:
+            z = x @ w[p + "mixer.proj.weight"].T
+            mixed = torch.cumsum(z, 0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
         else:
             mixed, kept[n] = attn(i, x, cfg.window if i == 1 else None, 2, 1 if i == 1 else 2,
                                   kept[shared] if shared is not None else None)
@@ -336,7 +380,8 @@ def _toy_plain(cfg, w, tokens):
             h = h + routed
         else:
             h = h + plain.swiglu(y, w[f + "w1.weight"], w[f + "w3.weight"], w[f + "w2.weight"])
-    return plain.rms_norm(h, w["final_norm"], 1e-5) @ w["embed"].T
+    logits = plain.rms_norm(h, w["final_norm"], 1e-5) @ w["embed"].T * 0.4
+    return 2.5 * torch.tanh(logits / 2.5)
 
 
 @pytest.mark.parametrize("device", _devices())
@@ -344,6 +389,7 @@ def test_toy_architecture_is_registered_built_and_stepped(device, tmp_path):
     register_mixer("ema_for_tests", EmaMixer)
     register_ffn("routed_for_tests", RoutedFeedForward)
     register_position("decay_for_tests", DecayPosition)
+    register_mixer("prefix_mean_for_tests", PrefixMeanMixer)
     register_architecture(ToyConfig.architecture, ToyConfig)
     cfg = ToyConfig()
     folder = write_random_model(tmp_path / "toy", cfg, seed=3, std=0.2, dtype="float32")
@@ -361,8 +407,10 @@ def test_toy_architecture_is_registered_built_and_stepped(device, tmp_path):
         return ModelRunner(folder, config, ops=ops)
 
     r = runner(48)
-    assert len(r.cache.groups) == 2 and [type(v).__name__ for v in r.cache.views] == [
-        "StateCache", "PagedCache", "PagedCache", "PagedCache", "NoneType", "PagedCache"]
+    assert len(r.cache.groups) == 3 and [type(v).__name__ for v in r.cache.views] == [
+        "StateCache", "PagedCache", "PagedCache", "PagedCache", "NoneType", "PagedCache", "PagedCache"]
+    latent = r.cache.views[6]
+    assert latent.page_size == 2 and latent.latent.shape == (24, 2, cfg.width) and r.cache.table_widths == [12, 12, 24]
     steps, peak = traces.mixed(reqs, {rid: max(1, len(t) - 6) for rid, t in reqs.items()}, seed=2, live=3, page=page)
     for name, trace, pool in (("whole", traces.whole(reqs), 48), ("portions", traces.portions(reqs), 48),
                               ("tail", traces.tail_decoded(reqs, 8), 48), ("mixed", steps, peak)):
