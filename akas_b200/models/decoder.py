@@ -68,13 +68,29 @@ class Decoder:
     def forward(self, ctx, caches) -> torch.Tensor:
         """Runs the tokens of ``ctx`` and returns float32 logits ``[len(ctx.logit_rows), vocab]``."""
         ops = self.rt.ops
+        # A decode step is a chain of small operations; kernels that can run such a chain as one launch are told
+        # where it begins and ends, and it is cut before any block that has not declared itself safe inside one.
+        chained = ctx.decode_only and hasattr(ops, "chain_begin") and ops.chain_begin(ctx.num_tokens)
+        try:
+            return self._forward(ctx, caches, chained)
+        finally:
+            if chained:
+                ops.chain_end()
+
+    def _forward(self, ctx, caches, chained: bool) -> torch.Tensor:
+        ops = self.rt.ops
         spec = self.spec
         h = ops.embedding(ctx.token_ids, self.embedding)
         if spec.embedding_multiplier is not None:
             h = ops.scale_cap(h, scale=spec.embedding_multiplier)
         for i, entry in enumerate(self.schedule):
             owner = i if entry.cache is None else entry.cache
-            h = self.blocks[entry.layer].forward(h, ctx, caches[owner], write=entry.cache is None)
+            block = self.blocks[entry.layer]
+            if chained and not block.chain_safe:
+                ops.chain_flush()
+            h = block.forward(h, ctx, caches[owner], write=entry.cache is None)
+        if chained and not getattr(self.final_norm, "chain_safe", False):
+            ops.chain_flush()
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
         if hasattr(self.final_norm, "lazy"):

@@ -10,6 +10,7 @@ is no other path.
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Iterable, Optional
@@ -92,6 +93,18 @@ _SIGNATURES = {
                              c_int, c_int, c_void_p],
         "akas_skinny_gemm_status": [],
     },
+    "decode_chain": {
+        "akas_chain_set_scratch": [c_void_p],
+        "akas_chain_scratch_words": [],
+        "akas_chain_begin": [],
+        "akas_chain_count": [],
+        "akas_chain_takes": [c_int] * 5,
+        "akas_chain_gemm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int],
+        "akas_chain_conv": [c_void_p] * 7 + [c_int] * 4,
+        "akas_chain_embed": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int],
+        "akas_chain_run": [c_void_p],
+        "akas_chain_status": [],
+    },
     "sgemm": {
         "akas_sgemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
@@ -112,7 +125,7 @@ _functions = {}
 def libraries_for(dtype: torch.dtype) -> list:
     """The kernel files a model of this compute dtype needs."""
     names = ["elementwise", "conv", "rope", "attention", "sampling"]
-    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "gemm_pair", "gemm_stream", "skinny_gemm", "attention_prefill", "attention_prefill_tc", "attention_decode"]
+    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "gemm_pair", "gemm_stream", "skinny_gemm", "decode_chain", "attention_prefill", "attention_prefill_tc", "attention_decode"]
     return names
 
 
@@ -124,6 +137,8 @@ def require(names: Optional[Iterable[str]] = None) -> None:
     build.ensure_built(names)
     for n in names:
         _bind(n)
+    if "decode_chain" in names:
+        _chain_barrier_word(torch.device("cuda", torch.cuda.current_device()))
 
 
 def _bind(lib_name: str) -> None:
@@ -184,23 +199,130 @@ def _dense(t: torch.Tensor, what: str) -> torch.Tensor:
     return t
 
 
+# --------------------------------------------------------------------------- chained decode steps
+#
+# A decode step is a chain of small operations: products for a handful of tokens, the short convolution, the
+# embedding look-up. Between ``chain_begin`` and ``chain_end`` (the decoder brackets a decode step with them) the
+# functions below that can join a chain do not launch: they allocate their output, add themselves to a program, and
+# return; the program runs as ONE persistent launch (csrc/decode_chain.cu) when an operation comes that cannot join
+# (every other function of this module flushes first), when it is full, or at ``chain_end``. A part that touches
+# tensors by other means than this module's functions must not run inside a chain: the decoder flushes before any
+# block whose parts do not declare ``chain_safe``. AKAS_B200_DECODE_CHAIN=0 turns chains off (every operation
+# launches by itself, as in steps that are not decode steps).
+decode_chain = os.environ.get("AKAS_B200_DECODE_CHAIN", "1")
+if decode_chain not in ("0", "1"):
+    raise ValueError(f"AKAS_B200_DECODE_CHAIN must be 0 or 1, got {decode_chain!r}")
+_CHAIN_ROWS = 16
+_chain_open = False
+_chain_keep = []  # tensors of the program under construction, kept alive until it has been launched
+_chain_words = {}
+_chain_answers = {}
+
+
+def _chain_barrier_word(device):
+    """The words of device memory that the blocks of a chain meet on and count tiles in (zeroed once; the kernel
+    leaves them as it found them)."""
+    word = _chain_words.get(device)
+    if word is None:
+        count = int(_fn("decode_chain", "akas_chain_scratch_words")())
+        word = _chain_words[device] = torch.zeros(count, dtype=torch.int32, device=device)
+        _check(_fn("decode_chain", "akas_chain_set_scratch")(_ptr(word)), "chain scratch", kernels=0)
+    return word
+
+
+def chain_begin(num_tokens: int) -> bool:
+    """Opens a chain for a decode step of ``num_tokens`` tokens; False if chains are off or the step is too large."""
+    global _chain_open
+    device = torch.device("cuda", torch.cuda.current_device())
+    if decode_chain != "1" or num_tokens > _CHAIN_ROWS or _chain_open or device not in _chain_words:
+        return False  # (no barrier word: the chain's library was not asked for, as for a float32 model)
+    _fn("decode_chain", "akas_chain_begin")()
+    _chain_open = True
+    return True
+
+
+def chain_flush() -> None:
+    """Launches what the chain holds so far; the chain stays open."""
+    if _chain_open and _fn("decode_chain", "akas_chain_count")():
+        err = _fn("decode_chain", "akas_chain_run")(_stream())
+        _chain_keep.clear()
+        _check(err, "decode chain")
+
+
+def chain_end() -> None:
+    global _chain_open
+    try:
+        chain_flush()
+    finally:
+        _chain_open = False
+        _chain_keep.clear()
+
+
+def chain_status() -> int:
+    """0 unless a bounded wait inside the chain kernel has run out on this device. Synchronises."""
+    return int(_fn("decode_chain", "akas_chain_status")())
+
+
+def _chain_takes(m: int, o: int, k: int, in_mode: int, mode: int) -> bool:
+    if not _chain_open or m > _CHAIN_ROWS:
+        return False
+    key = (m > 8, o % 2, k, in_mode, mode)
+    answer = _chain_answers.get(key)
+    if answer is None:
+        answer = _chain_answers[key] = bool(_fn("decode_chain", "akas_chain_takes")(m, o, k, in_mode, mode))
+    return answer
+
+
+_CHAIN_OPS = int(os.environ.get("AKAS_B200_CHAIN_OPS", "24"))  # the most operations of one launch
+
+
+def _chain_add(fn_name: str, keep, *args) -> None:
+    """Adds an operation to the open chain (launching the chain first when it is full)."""
+    fn = _fn("decode_chain", fn_name)
+    if _fn("decode_chain", "akas_chain_count")() >= _CHAIN_OPS:
+        chain_flush()
+    err = fn(*args)
+    if err == 1:  # the program is full
+        chain_flush()
+        err = fn(*args)
+    if err:
+        raise RuntimeError(f"{fn_name} failed: error {err}")
+    _chain_keep.extend(keep)
+
+
+def _flushes(fn):
+    """An operation that cannot join a chain: whatever the chain holds runs first."""
+    @functools.wraps(fn)
+    def flushed(*args, **kwargs):
+        if _chain_open:
+            chain_flush()
+        return fn(*args, **kwargs)
+    return flushed
+
+
 # --------------------------------------------------------------------------- elementwise
 
 
 def embedding(token_ids, table):
     n, c = token_ids.numel(), table.shape[1]
     out = torch.empty((n, c), dtype=torch.float32, device=table.device)
+    if _chain_open and n <= _CHAIN_ROWS:
+        _chain_add("akas_chain_embed", (token_ids, table, out), _ptr(token_ids), _ptr(_dense(table, "table")), _ptr(out), n, c,
+                   _code(table))
+        return out
     _check(_fn("elementwise", "akas_embedding")(_ptr(token_ids), _ptr(_dense(table, "table")), _ptr(out), n, c,
                                                _code(table), _stream()), "embedding")
     return out
 
 
+@_flushes
 def take_tokens(token_ids, source, previous):
     """token_ids[i] = previous[source[i]] where source[i] >= 0 (all int32, in place)."""
     _check(_fn("elementwise", "akas_take_tokens")(_ptr(token_ids), _ptr(source), _ptr(previous), previous.numel(),
                                                  token_ids.numel(), _stream()), "take_tokens")
 
 
+@_flushes
 def rmsnorm(x, weight, eps, zero_centered, out_dtype, rows=None):
     c = x.shape[-1]
     _dense(x, "x")
@@ -214,6 +336,7 @@ def rmsnorm(x, weight, eps, zero_centered, out_dtype, rows=None):
     return out
 
 
+@_flushes
 def swiglu(gate_up):
     n, f2 = gate_up.shape
     out = torch.empty((n, f2 // 2), dtype=gate_up.dtype, device=gate_up.device)
@@ -222,6 +345,7 @@ def swiglu(gate_up):
     return out
 
 
+@_flushes
 def add_bias(x, bias, out_dtype=None):
     """x [N, C] float32 plus bias [C] float32, rounded once to ``out_dtype``; in place when that is float32."""
     n, c = x.shape
@@ -234,6 +358,7 @@ def add_bias(x, bias, out_dtype=None):
     return out
 
 
+@_flushes
 def scale_cap(x, scale=1.0, cap=0.0):
     """In place on float32 x: times ``scale``, then ``cap * tanh(x / cap)`` where ``cap`` > 0."""
     if x.dtype != torch.float32:
@@ -243,6 +368,7 @@ def scale_cap(x, scale=1.0, cap=0.0):
     return x
 
 
+@_flushes
 def zero_rows(state, slot):
     """state[:, slot] = 0 for a contiguous tensor [layers, slots, ...]."""
     row = state[0, 0].numel()
@@ -277,6 +403,8 @@ def linear(x, w, out_dtype=None, residual=None):
         if residual.dtype != torch.float32 or residual.shape != (n, o) or not residual.is_contiguous():
             raise ValueError("linear: residual must be contiguous float32 [N, O]")
     if x.dtype == torch.float32:
+        if _chain_open:
+            chain_flush()
         out = residual if residual is not None else torch.empty((n, o), dtype=torch.float32, device=x.device)
         _check(_fn("sgemm", "akas_sgemm")(_ptr(x), _ptr(w), _ptr(out), _ptr(residual), n, o, k, _stream()), "sgemm")
         if residual is None and out_dtype not in (None, torch.float32):
@@ -286,6 +414,12 @@ def linear(x, w, out_dtype=None, residual=None):
         raise TypeError(f"linear takes float32 or bfloat16, got {x.dtype}")
     target = out_dtype or torch.bfloat16
     mode = _OUT_ACC if residual is not None else _OUT_F32 if target == torch.float32 else _OUT_BF16
+    if _chain_takes(n, o, k, 0, mode):
+        out = residual if residual is not None else torch.empty((n, o), dtype=target, device=x.device)
+        _chain_add("akas_chain_gemm", (x, w, out), _ptr(x), None, None, 0.0, 0, _ptr(w), _ptr(out), n, o, k, 0, mode)
+        return out
+    if _chain_open:
+        chain_flush()
     if _stream_takes(n, o, k, False, mode):
         # few tokens: the weights are streamed once through the tensor cores
         out = residual if residual is not None else torch.empty((n, o), dtype=target, device=x.device)
@@ -297,20 +431,14 @@ def linear(x, w, out_dtype=None, residual=None):
         return out
     if k % 8:
         raise ValueError(f"bfloat16 matrix products need an inner size that is a multiple of 8, got {k}")
-    if _tcgen05_takes(n, k) and residual is None and target == torch.bfloat16 and paired_sms == "1" and \
-            -(-n // 256) * -(-o // 256) >= _sm_count() // 2:
-        return paired_product(x, w)  # a plain product with a tile for every pair of SMs
-    if _tcgen05_takes(n, k) and (residual is not None or target == torch.bfloat16):
-        # prompt portions: the hand-written tcgen05 kernel, residual add fused into its read-out
-        out = residual if residual is not None else torch.empty((n, o), dtype=torch.bfloat16, device=x.device)
-        _check(_fn("gemm_tcgen05", "akas_gemm_tcgen05")(_ptr(x), _ptr(w), _ptr(out), n, o, k,
-                                                       1 if residual is not None else 0, _stream()),
-               f"tcgen05 product [{n}x{k}] x [{o}x{k}]^T")
-        return out
+    route = _product_route(k, o, mode)
+    if route == "paired":
+        return paired_product(x, w, out_dtype=target, residual=residual)
+    if route == "block":
+        return block_product(x, w, out_dtype=target, residual=residual)
     if residual is not None:
         out, out_f32, acc = residual, 1, 1
     else:
-        target = out_dtype or torch.bfloat16
         out = torch.empty((n, o), dtype=target, device=x.device)
         out_f32, acc = int(target == torch.float32), 0
     ws = _workspace(x.device)
@@ -327,35 +455,25 @@ def _skinny_fits(m: int, k: int) -> bool:
 
 
 _SKINNY_ROWS = 16
-# Which kernel runs the products of prompt portions (more than 16 tokens). "auto": the hand-written tcgen05 kernels for
-# the fused gate/up + SwiGLU product where they are as fast as the library or faster (see _swiglu_route), cuBLASLt for
-# the plain and residual products, which the library's multicast-fed two-SM tiles still run faster; "tcgen05": the
-# hand-written kernels everywhere; "library": cuBLASLt everywhere (SwiGLU then runs as a kernel of its own).
-products = os.environ.get("AKAS_B200_PRODUCTS", "auto")
-if products not in ("auto", "tcgen05", "library"):
-    raise ValueError(f"AKAS_B200_PRODUCTS must be auto, tcgen05 or library, got {products!r}")
+# Which kernels run the products of more than 16 tokens (prompt portions, mixed steps, large decode batches). "own"
+# (default; "auto" and "tcgen05" mean the same): the hand-written tcgen05 kernels everywhere: the kernel for pairs of
+# SMs (gemm_pair.cu, TMA-written read-outs) for every product whose output rows TMA can write, the one-block kernel
+# (gemm_tcgen05.cu, masked read-outs) for the rest. "library": cuBLASLt everywhere, with SwiGLU as a kernel of its
+# own: the arm that the hand-written kernels are measured against.
+products = os.environ.get("AKAS_B200_PRODUCTS", "own")
+if products not in ("own", "auto", "tcgen05", "library"):
+    raise ValueError(f"AKAS_B200_PRODUCTS must be own or library, got {products!r}")
 
 
-def _tcgen05_takes(n: int, k: int) -> bool:
-    """Whether the one-block tcgen05 kernel runs a plain or residual product: only when the policy says everywhere."""
-    return products == "tcgen05" and n > _SKINNY_ROWS and k % 8 == 0
-
-
-def _swiglu_route(n: int, k: int, channels: int) -> str:
-    """Which kernel runs the fused gate/up product of a prompt portion: "paired" (gemm_pair.cu), "block"
-    (gemm_tcgen05.cu) or "library" (cuBLASLt, then the SwiGLU kernel). Under "auto" by what measured fastest on the
-    LFM2 shapes (K 1,024 / 1,536 / 2,048; 256 to 8,192 tokens): the paired kernel from 1,536 tokens on at K = 2,048
-    (9 to 12 % ahead of the library from 2,048 tokens on) and from 4,096 tokens on at K = 1,536; the library for fewer
-    tokens and for K = 1,024, where its narrower tiles spread few tiles over more SMs."""
-    if n <= _SKINNY_ROWS or k % 8 or channels % 8 or products == "library":
+def _product_route(k: int, o: int, mode: int) -> str:
+    """Which kernel runs a product of more than 16 tokens with inner size k and o output channels (for SwiGLU the
+    stacked 2F): "paired", "block", "library", or (SwiGLU only) "unfused"."""
+    if products == "library":
         return "library"
-    pair_ok = paired_sms == "1" and -(-n // 256) * -(-channels // 128) >= _sm_count() // 2
-    block_ok = -(-n // 128) * -(-channels // 128) >= _sm_count()
-    if products == "tcgen05":
-        return "paired" if pair_ok else "block"
-    if n < 1536 or k < 1536 or (k < 2048 and n < 4096):
-        return "library"
-    return "paired" if pair_ok else "block" if block_ok and n >= 2048 else "library"
+    if mode == _OUT_SWIGLU:
+        return "paired" if o % 16 == 0 else "unfused"  # unfused: the plain product, then the SwiGLU kernel
+    pitch_ok = o % 8 == 0 if mode == _OUT_BF16 else o % 4 == 0
+    return "paired" if pitch_ok else "block"
 
 
 _sms = 0
@@ -368,23 +486,58 @@ def _sm_count() -> int:
     return _sms
 
 
-# Whether the fused SwiGLU product of prompt portions runs on pairs of SMs (tcgen05.mma.cta_group::2, gemm_pair.cu)
-# where it has a tile of 256 tokens x 128 channels for every pair; "0" keeps it on the one-block kernel.
-paired_sms = os.environ.get("AKAS_B200_PAIRED_SMS", "1")
-if paired_sms not in ("0", "1"):
-    raise ValueError(f"AKAS_B200_PAIRED_SMS must be 0 or 1, got {paired_sms!r}")
-
-
-def paired_product(x, w, swiglu_out: bool = False):
-    """x [N, K] times w [O, K] transposed on pairs of SMs, bfloat16 out; with ``swiglu_out`` w is the stacked
-    [2F, K] gate and up matrices and the result is swiglu of the product, [N, F]."""
+@_flushes
+def block_product(x, w, swiglu_out: bool = False, out_dtype=None, residual=None):
+    """The same products on the one-block tcgen05 kernel (gemm_tcgen05.cu), whose masked read-outs take any width:
+    the route of sizes whose rows TMA cannot write (a pitch that is no multiple of 16 bytes). A float32 result is
+    summed into zeros."""
     n, k = x.shape
     o = w.shape[0]
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k or k % 8 or (swiglu_out and o % 16):
-        raise ValueError("paired_product takes bfloat16 [N, K] and [O, K] with K a multiple of 8 (and O of 16 for SwiGLU)")
-    out = torch.empty((n, o // 2 if swiglu_out else o), dtype=torch.bfloat16, device=x.device)
-    _check(_fn("gemm_pair", "akas_gemm_pair")(_ptr(_dense(x, "x")), _ptr(_dense(w, "w")), _ptr(out), n, o, k,
-                                             2 if swiglu_out else 0, _stream()), f"paired tcgen05 product [{n}x{k}] x [{o}x{k}]^T")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k or k % 8:
+        raise ValueError("block_product takes bfloat16 [N, K] and [O, K] with K a multiple of 8")
+    kernels = 1
+    if swiglu_out:
+        if o % 16:
+            raise ValueError("block_product: the stacked gate and up matrices need a height that is a multiple of 16")
+        out, epilogue = torch.empty((n, o // 2), dtype=torch.bfloat16, device=x.device), 2
+    elif residual is not None:
+        out, epilogue = residual, 1
+    elif out_dtype == torch.float32:
+        out, epilogue, kernels = torch.zeros((n, o), dtype=torch.float32, device=x.device), 1, 2
+    else:
+        out, epilogue = torch.empty((n, o), dtype=torch.bfloat16, device=x.device), 0
+    _check(_fn("gemm_tcgen05", "akas_gemm_tcgen05")(_ptr(_dense(x, "x")), _ptr(_dense(w, "w")), _ptr(out), n, o, k, epilogue,
+                                                   _stream()), f"tcgen05 product [{n}x{k}] x [{o}x{k}]^T", kernels=kernels)
+    return out
+
+
+@_flushes
+def paired_product(x, w, swiglu_out: bool = False, out_dtype=None, residual=None):
+    """x [N, K] times w [O, K] transposed on pairs of SMs. bfloat16 out by default; float32 out with ``out_dtype``;
+    added into ``residual`` (float32 [N, O]) when that is given; with ``swiglu_out`` w is the stacked [2F, K] gate and
+    up matrices and the result is swiglu of the product, bfloat16 [N, F]."""
+    n, k = x.shape
+    o = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k or k % 8:
+        raise ValueError("paired_product takes bfloat16 [N, K] and [O, K] with K a multiple of 8")
+    if swiglu_out:
+        if o % 16:
+            raise ValueError("paired_product: the stacked gate and up matrices need a height that is a multiple of 16")
+        out, epilogue = torch.empty((n, o // 2), dtype=torch.bfloat16, device=x.device), 2
+    elif residual is not None:
+        if residual.dtype != torch.float32 or residual.shape != (n, o) or not residual.is_contiguous() or o % 4:
+            raise ValueError("paired_product: residual must be contiguous float32 [N, O] with O a multiple of 4")
+        out, epilogue = residual, 1
+    elif out_dtype == torch.float32:
+        if o % 4:
+            raise ValueError("paired_product: a float32 result needs a width that is a multiple of 4")
+        out, epilogue = torch.empty((n, o), dtype=torch.float32, device=x.device), 3
+    else:
+        if o % 8:
+            raise ValueError("paired_product: a bfloat16 result needs a width that is a multiple of 8")
+        out, epilogue = torch.empty((n, o), dtype=torch.bfloat16, device=x.device), 0
+    _check(_fn("gemm_pair", "akas_gemm_pair")(_ptr(_dense(x, "x")), _ptr(_dense(w, "w")), _ptr(out), n, o, k, epilogue,
+                                             _stream()), f"paired tcgen05 product [{n}x{k}] x [{o}x{k}]^T")
     return out
 
 
@@ -450,6 +603,13 @@ def linear_swiglu(x, w_gate_up):
     """swiglu(x . w^T) with w the stacked [2F, K] gate and up matrices: [N, F] in x's dtype."""
     n, k = x.shape
     f2 = w_gate_up.shape[0]
+    if x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and f2 % 2 == 0 and _chain_takes(n, f2, k, 0, _OUT_SWIGLU):
+        out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
+        _chain_add("akas_chain_gemm", (x, w_gate_up, out), _ptr(_dense(x, "x")), None, None, 0.0, 0,
+                   _ptr(_dense(w_gate_up, "w")), _ptr(out), n, f2, k, 0, _OUT_SWIGLU)
+        return out
+    if _chain_open:
+        chain_flush()
     if x.dtype == torch.bfloat16 and f2 % 2 == 0 and _stream_takes(n, f2, k, False, _OUT_SWIGLU):
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _stream_product(_dense(x, "x"), None, None, 0.0, False, False, _dense(w_gate_up, "w"), out, n, f2, k, _OUT_SWIGLU)
@@ -458,16 +618,10 @@ def linear_swiglu(x, w_gate_up):
         out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
         _skinny(_dense(x, "x"), None, None, 0.0, False, _dense(w_gate_up, "w"), out, n, f2, k, 0, _OUT_SWIGLU)
         return out
-    route = _swiglu_route(n, k, f2 // 2) if x.dtype == torch.bfloat16 and f2 % 16 == 0 else "library"
-    if route == "paired":
-        # SwiGLU in the read-out of the product, on pairs of SMs: each stages half of a 256-channel tile
+    if x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and k % 8 == 0 and \
+            _product_route(k, f2, _OUT_SWIGLU) == "paired":
+        # SwiGLU in the read-out of the product: the [N, 2F] intermediate is never written
         return paired_product(x, w_gate_up, swiglu_out=True)
-    if route == "block":
-        # the same on single SMs: the [N, 2F] intermediate is never written
-        out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
-        _check(_fn("gemm_tcgen05", "akas_gemm_tcgen05")(_ptr(_dense(x, "x")), _ptr(_dense(w_gate_up, "w")), _ptr(out), n,
-                                                       f2, k, 2, _stream()), f"tcgen05 SwiGLU product [{n}x{k}]")
-        return out
     return swiglu(linear(x, w_gate_up))
 
 
@@ -478,6 +632,13 @@ def norm_linear(h, norm_weight, eps, zero_centered, w, out_dtype=None, rows=None
     target = torch.bfloat16 if swiglu_out else (out_dtype or torch.bfloat16)
     mode = _OUT_SWIGLU if swiglu_out else _OUT_F32 if target == torch.float32 else _OUT_BF16
     fusable = w.dtype == torch.bfloat16 and h.dtype == torch.float32 and h.is_contiguous() and (not swiglu_out or o % 2 == 0)
+    if fusable and _chain_takes(m, o, k, 1, mode):
+        out = torch.empty((m, o // 2 if swiglu_out else o), dtype=target, device=h.device)
+        _chain_add("akas_chain_gemm", (h, rows, norm_weight, w, out), _ptr(h), _ptr(rows), _ptr(norm_weight), float(eps),
+                   int(bool(zero_centered)), _ptr(_dense(w, "w")), _ptr(out), m, o, k, 1, mode)
+        return out
+    if _chain_open:
+        chain_flush()
     if fusable and _stream_takes(m, o, k, True, mode):
         out = torch.empty((m, o // 2 if swiglu_out else o), dtype=target, device=h.device)
         _stream_product(h, rows, norm_weight, eps, zero_centered, True, _dense(w, "w"), out, m, o, k, mode)
@@ -498,6 +659,12 @@ def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots, decode_o
     n, c3 = bcx.shape
     c, l = c3 // 3, taps.shape[1]
     out = torch.empty((n, c), dtype=bcx.dtype, device=bcx.device)
+    if decode_only and _chain_open and n <= _CHAIN_ROWS and bcx.dtype == torch.bfloat16:
+        _chain_add("akas_chain_conv", (bcx, taps, bias, state, seq_of_token, slots, out), _ptr(_dense(bcx, "bcx")), _ptr(taps),
+                   _ptr(bias), _ptr(state), _ptr(seq_of_token), _ptr(slots), _ptr(out), n, c, l, int(bool(write)))
+        return out
+    if _chain_open:
+        chain_flush()
     if decode_only:
         _check(_fn("conv", "akas_short_conv_decode")(_ptr(_dense(bcx, "bcx")), _ptr(taps), _ptr(bias), _ptr(state),
                                                     _ptr(seq_of_token), _ptr(slots), _ptr(out), n, c, l, _code(bcx),
@@ -519,6 +686,7 @@ def rope_tables(positions, inv_freq):
     return cos, sin
 
 
+@_flushes
 def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_weight, k_weight, eps, zero_centered, cos, sin,
                        k_pool, v_pool, block_table, seq_of_token, positions, page_size):
     n = qkv.shape[0]
@@ -534,6 +702,7 @@ def qk_norm_rope_store(qkv, heads, kv_heads, head_dim, q_weight, k_weight, eps, 
     return q
 
 
+@_flushes
 def kv_store(k, v, k_pool, v_pool, block_table, seq_of_token, positions, page_size):
     n = k.shape[0]
     kh, d = k_pool.shape[1], k_pool.shape[3]
@@ -551,6 +720,13 @@ def kv_store(k, v, k_pool, v_pool, block_table, seq_of_token, positions, page_si
 prompt_attention = os.environ.get("AKAS_B200_PROMPT_ATTENTION", "auto")
 if prompt_attention not in ("auto", "tcgen05", "mma"):
     raise ValueError(f"AKAS_B200_PROMPT_ATTENTION must be auto, tcgen05 or mma, got {prompt_attention!r}")
+
+
+# How the decoded tokens of a step that also holds prompt portions are attended: "split" (default), by the split-key
+# decode kernel, or "tiles", inside the prompt kernels as query tiles with one live row each.
+mixed_attention = os.environ.get("AKAS_B200_MIXED_ATTENTION", "split")
+if mixed_attention not in ("split", "tiles"):
+    raise ValueError(f"AKAS_B200_MIXED_ATTENTION must be split or tiles, got {mixed_attention!r}")
 
 
 def decode_attention_status() -> int:
@@ -573,18 +749,43 @@ def decode_splits(num_tokens: int, kv_heads: int, head_tiles: int, max_context: 
     return max(1, min(want, most, 64))
 
 
-def _query_tiles(ctx):
-    """How many 64-query tiles (the mma.sync prompt kernel's) and 128-query tiles (the tensor-memory kernel's) the
-    requests of this step make, from the token counts the host knows; once per step."""
-    if ctx is None or not getattr(ctx, "query_lens", None):
-        return 0, 0
-    counts = ctx.memo.get("query_tiles")
-    if counts is None:
-        counts = ctx.memo["query_tiles"] = (sum(-(-n // 64) for n in ctx.query_lens),
-                                            sum(-(-n // 128) for n in ctx.query_lens))
-    return counts
+def _decode_attention(q, n, out, k_pool, v_pool, block_table, seq_of_token, positions, scale, win, page_size, keys):
+    """Split-key attention of the first ``n`` tokens of q, each the single token of its request, into out[:n]."""
+    kh, d = k_pool.shape[1], k_pool.shape[3]
+    heads = q.shape[1] // d
+    group = heads // kh
+    if q.dtype == torch.bfloat16 and d in (16, 32, 64, 128):
+        # tensor-core kernel: the query heads of a group are the rows of one tile
+        splits = decode_splits(n, kh, -(-group // 16), keys)
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty((n, heads, splits, d), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
+        _check(_fn("attention_decode", "akas_decode_attention_bf16_paged")(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
+            _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
+            splits, _stream()), "decode_attention", kernels=2 if splits > 1 else 1)
+        return
+    gt = 8 if group >= 8 else 4 if group > 2 else group
+    splits = decode_splits(n, kh, -(-group // gt), keys)
+    part_o = torch.empty((n, heads, splits, d), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
+    _check(_fn("attention", "akas_paged_attention_decode")(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
+        _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
+        splits, _code(q), _stream()), "paged_attention_decode", kernels=2)
 
 
+def _leading_single_tokens(ctx) -> int:
+    """How many requests at the front of the step bring exactly one token (the scheduler puts decoding requests first)."""
+    lens = getattr(ctx, "query_lens", ()) if ctx is not None else ()
+    count = 0
+    while count < len(lens) and lens[count] == 1:
+        count += 1
+    return count
+
+
+@_flushes
 def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, page_size, ctx=None):
     n = q.shape[0]
     kh, d = k_pool.shape[1], k_pool.shape[3]
@@ -593,47 +794,42 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
     out = torch.empty_like(q)
     win = int(window) if window else 0
     if ctx is not None and ctx.decode_only:
-        group = heads // kh
-        keys = win if win else ctx.max_context
-        if q.dtype == torch.bfloat16 and d in (16, 32, 64, 128):
-            # tensor-core kernel: the query heads of a group are the rows of one tile
-            splits = decode_splits(n, kh, -(-group // 16), keys)
-            part_o = part_ml = None
-            if splits > 1:
-                part_o = torch.empty((n, heads, splits, d), dtype=torch.float32, device=q.device)
-                part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
-            _check(_fn("attention_decode", "akas_decode_attention_bf16_paged")(
-                _ptr(q), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
-                _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
-                splits, _stream()), "decode_attention", kernels=2 if splits > 1 else 1)
-            return out
-        gt = 8 if group >= 8 else 4 if group > 2 else group
-        splits = decode_splits(n, kh, -(-group // gt), keys)
-        part_o = torch.empty((n, heads, splits, d), dtype=torch.float32, device=q.device)
-        part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
-        _check(_fn("attention", "akas_paged_attention_decode")(
-            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
-            _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
-            splits, _code(q), _stream()), "paged_attention_decode", kernels=2)
+        _decode_attention(q, n, out, k_pool, v_pool, block_table, seq_of_token, positions, scale, win, page_size,
+                          win if win else ctx.max_context)
         return out
-    tiles, wide = _query_tiles(ctx)
+    tensor_cores = q.dtype == torch.bfloat16 and d in (16, 32, 64, 128)
+    # A step that mixes portions of prompts with decoded tokens: the single tokens at its front go to the split-key
+    # kernel (one block per request, key/value head and part of the keys) instead of a 64-query tile each of which one
+    # row is alive; the prompt kernels then start at the first request that brings more. Two launches, one output.
+    first = _leading_single_tokens(ctx) if tensor_cores and mixed_attention == "split" else 0
+    lens = ctx.query_lens[first:] if first else (getattr(ctx, "query_lens", ()) if ctx is not None else ())
+    if first:
+        _decode_attention(q, first, out, k_pool, v_pool, block_table, seq_of_token, positions, scale, win, page_size,
+                          win if win else ctx.max_context)
+        if not lens:
+            return out
+    tiles, wide = sum(-(-c // 64) for c in lens), sum(-(-c // 128) for c in lens)
+    requests = len(lens) if first else (ctx.cu_seqlens.numel() - 1 if tiles else 0)
+    # the prompt kernels find their tiles from cu_seqlens and address block tables by request: both start at `first`
+    cu = ctx.cu_seqlens[first:] if tiles else None
+    table = block_table[first:] if first else block_table
     # A 128-query tile of the tensor-memory kernel costs about what a 64-query tile of the mma.sync kernel costs
     # (measured: 1.8 times the throughput): it pays when requests bring more than 64 tokens, not for single tokens.
     tensor_memory = prompt_attention == "tcgen05" or (prompt_attention == "auto" and 0 < wide and wide <= 0.9 * tiles)
     if q.dtype == torch.bfloat16 and tensor_memory and d == 64 and page_size % 64 == 0 and 0 < tiles <= 65535:
         # prompt portions, head size 64, pages of whole half tiles: 128-query tiles on tcgen05
         err = _fn("attention_prefill_tc", "akas_prefill_attention_tc")(
-            _ptr(q), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0] * k_pool.shape[1] * k_pool.shape[2], _ptr(block_table),
-            block_table.shape[1], _ptr(ctx.cu_seqlens), _ptr(positions), _ptr(out), float(scale), win, page_size, tiles, n,
-            heads, kh, d, ctx.cu_seqlens.numel() - 1, _stream())
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0] * k_pool.shape[1] * k_pool.shape[2], _ptr(table),
+            block_table.shape[1], _ptr(cu), _ptr(positions), _ptr(out), float(scale), win, page_size, tiles, n,
+            heads, kh, d, requests, _stream())
         if err != 3999:
             _check(err, "prefill_attention_tc")
             return out
-    if q.dtype == torch.bfloat16 and d in (16, 32, 64, 128) and 0 < tiles <= 65535:
+    if tensor_cores and 0 < tiles <= 65535:
         # prompt portions (and whatever decodes beside them): 64-query tiles on the tensor cores
         _check(_fn("attention_prefill", "akas_prefill_attention_bf16")(
-            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_seqlens),
-            _ptr(positions), _ptr(out), float(scale), win, page_size, tiles, heads, kh, d, ctx.cu_seqlens.numel() - 1,
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), block_table.shape[1], _ptr(cu),
+            _ptr(positions), _ptr(out), float(scale), win, page_size, tiles, heads, kh, d, requests,
             _stream()), "prefill_attention")
         return out
     _check(_fn("attention", "akas_paged_attention")(
@@ -646,6 +842,7 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
 # --------------------------------------------------------------------------- sampling
 
 
+@_flushes
 def argmax(logits):
     m, v = logits.shape
     out = torch.empty((m,), dtype=torch.int32, device=logits.device)
@@ -657,6 +854,7 @@ def argmax(logits):
     return out
 
 
+@_flushes
 def adjust_logits(logits, softcap, penalty, history):
     """In place on float32 logits [M, V]: softcap (float32 [M], 0 = none), then the repetition penalty (float32 [M],
     1 = none) on the tokens of ``history`` (int32 [M, W], -1 where empty)."""
@@ -669,6 +867,7 @@ def adjust_logits(logits, softcap, penalty, history):
     return logits
 
 
+@_flushes
 def sample(logits, temperature, top_k, top_p, uniform):
     m, v = logits.shape
     out = torch.empty((m,), dtype=torch.int32, device=logits.device)

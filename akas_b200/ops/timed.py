@@ -36,6 +36,10 @@ class TimedOps:
 
         return timed
 
+    def chain_begin(self, num_tokens: int) -> bool:
+        """Operations that join a chain launch together, later: there would be nothing to time per call."""
+        return False
+
     def clear(self) -> None:
         torch.cuda.synchronize()
         self._events.clear()

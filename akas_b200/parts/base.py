@@ -143,6 +143,10 @@ def project_swiglu(rt: "Runtime", x, w_gate_up):
 
 class Part:
     takes_normed = False  # True: forward accepts a ``Normed`` in place of the normed tensor
+    # True: the part reads and writes device tensors through ``runtime.ops`` functions only, so an operations module
+    # that defers launches (a decode step run as one chain) may keep deferring across it. A part that computes with
+    # torch directly leaves this False, and the decoder makes everything pending run before the part does.
+    chain_safe = False
 
     def __init__(self, spec, runtime: Runtime):
         self.spec = spec

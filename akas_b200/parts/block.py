@@ -35,6 +35,8 @@ class Block:
         self.mixer_norm = build_part("norm", spec.mixer_norm, runtime)
         self.ffn_norm = build_part("norm", spec.ffn_norm, runtime)
         self._run = ARRANGEMENTS[spec.arrangement]
+        # Whether every part of the block reaches its tensors through the runtime's operations only (see Part.chain_safe)
+        self.chain_safe = all(getattr(part, "chain_safe", False) for part in (self.mixer, self.ffn, self.mixer_norm, self.ffn_norm))
 
     def params(self):
         """Checkpoint name -> Param for everything this block holds."""

@@ -13,6 +13,8 @@ from .base import Normed, Param, Part, register_norm
 
 
 class RMSNorm(Part):
+    chain_safe = True
+
     def __init__(self, spec, runtime, name: str = "weight"):
         super().__init__(spec, runtime)
         self.name = name

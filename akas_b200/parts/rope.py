@@ -16,6 +16,8 @@ from .base import Part, register_position
 
 
 class Rope(Part):
+    chain_safe = True
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         rotary = spec.rotary

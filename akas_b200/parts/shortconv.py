@@ -24,6 +24,7 @@ from .base import Mixer, Param, StateSpec, project, register_mixer, renamed
 
 class ShortConv(Mixer):
     takes_normed = True
+    chain_safe = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)

@@ -15,6 +15,7 @@ from .base import FeedForward, Param, project, project_swiglu, register_ffn, ren
 
 class SwiGLU(FeedForward):
     takes_normed = True
+    chain_safe = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)

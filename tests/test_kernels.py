@@ -46,6 +46,17 @@ def test_embedding(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_add_bias_and_scale_cap(ops, dtype):
+    cuda, ref = ops
+    x, bias = _rand((9, 70), torch.float32, 4, 3.0), _rand((70,), torch.float32, 5)
+    got, want = cuda.add_bias(x.clone(), bias, dtype), ref.add_bias(x.clone(), bias, dtype)
+    assert got.dtype == dtype and torch.equal(got, want)  # one add, one rounding
+    for scale, cap in ((1.7, 0.0), (0.4, 2.5), (1.0, 30.0)):
+        got, want = cuda.scale_cap(x.clone(), scale, cap), ref.scale_cap(x.clone(), scale, cap)
+        assert torch.allclose(got, want, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("c", [16, 48, 100, 2048, 3000])
 def test_rmsnorm(ops, dtype, c):
     cuda, ref = ops
@@ -174,36 +185,98 @@ def test_streamed_products_for_few_tokens(ops, m, k, o, monkeypatch):
 
 
 @pytest.mark.parametrize("m,k,o", [(17, 64, 48), (64, 128, 256), (100, 96, 200), (128, 2048, 320), (300, 192, 1000),
-                                   (2048, 256, 512), (333, 2048, 2056)])
+                                   (2048, 256, 512), (333, 2048, 2056), (40, 128, 333), (70, 64, 1001)])
 def test_tensor_memory_products_for_prompt_portions(ops, m, k, o):
-    """The tcgen05 kernel (TMA in, accumulators in tensor memory) with its three read-outs, at sizes that leave
-    ragged tiles in every direction."""
+    """The one-block tcgen05 kernel (TMA in, accumulators in tensor memory, masked read-outs: the route of widths
+    whose rows TMA cannot write) with its three read-outs, at sizes that leave ragged tiles in every direction."""
     cuda, ref = ops
     x, w = _rand((m, k), torch.bfloat16, 5), _rand((o, k), torch.bfloat16, 6, 0.05)
     want = x.double() @ w.double().T
-    policy, cuda.products = cuda.products, "tcgen05"  # every read-out of the kernel, whatever the default policy
-    try:
-        _close(cuda.linear(x, w), want, torch.bfloat16, "bf16 out")
-        res = _rand((m, o), torch.float32, 7)
-        _close(cuda.linear(x, w, residual=res.clone()), res.double() + want, torch.float32, "accumulate", k)
+    _close(cuda.block_product(x, w), want, torch.bfloat16, "bf16 out")
+    _close(cuda.block_product(x, w, out_dtype=torch.float32), want, torch.float32, "f32 out", k)
+    res = _rand((m, o), torch.float32, 7)
+    _close(cuda.block_product(x, w, residual=res.clone()), res.double() + want, torch.float32, "accumulate", k)
+    if o % 8 == 0:  # gate and up rows come by TMA in boxes of 8
         w2 = _rand((2 * o, k), torch.bfloat16, 8, 0.05)
-        _close(cuda.linear_swiglu(x, w2), ref.linear_swiglu(x, w2), torch.bfloat16, "swiglu")
-    finally:
-        cuda.products = policy
+        _close(cuda.block_product(x, w2, swiglu_out=True), ref.linear_swiglu(x, w2), torch.bfloat16, "swiglu")
     assert cuda.gemm_tcgen05_status() == 0
 
 
 @pytest.mark.parametrize("m,k,o", [(17, 64, 48), (256, 128, 256), (300, 264, 520), (2048, 256, 512), (333, 2048, 2056),
-                                   (1000, 1024, 1160), (130, 2048, 6144)])
+                                   (1000, 1024, 1160), (130, 2048, 6144), (2048, 512, 16384), (4100, 320, 8200)])
 def test_products_on_pairs_of_sms(ops, m, k, o):
-    """The cta_group::2 kernel (each block of a pair stages half of a 256-channel tile), both read-outs, at sizes that
-    leave ragged tiles in every direction and more tiles than pairs."""
+    """The cta_group::2 kernel (each block of a pair stages half of a tile's channels; read-outs staged in shared memory
+    and written by TMA), all four read-outs, at sizes that leave ragged tiles in every direction, more tiles than
+    pairs, and tiles of every width."""
     cuda, ref = ops
     x, w = _rand((m, k), torch.bfloat16, 5), _rand((o, k), torch.bfloat16, 6, 0.05)
-    _close(cuda.paired_product(x, w), x.double() @ w.double().T, torch.bfloat16, "bf16 out")
+    want = x.double() @ w.double().T
+    _close(cuda.paired_product(x, w), want, torch.bfloat16, "bf16 out")
+    got = cuda.paired_product(x, w, out_dtype=torch.float32)
+    assert got.dtype == torch.float32
+    _close(got, want, torch.bfloat16, "f32 out")
+    h = _rand((m, o), torch.float32, 7, 2.0)
+    h0 = h.clone()
+    assert cuda.paired_product(x, w, residual=h) is h
+    _close(h, h0.double() + want, torch.bfloat16, "added into the residual stream")
     w2 = _rand((2 * o, k), torch.bfloat16, 8, 0.05)
     _close(cuda.paired_product(x, w2, swiglu_out=True), ref.linear_swiglu(x, w2), torch.bfloat16, "swiglu")
     assert cuda.gemm_pair_status() == 0
+
+
+@pytest.mark.parametrize("m,c,f,v,taps", [(1, 128, 320, 500, 3), (8, 256, 9216, 1000, 3), (5, 192, 448, 777, 4),
+                                         (13, 128, 6912, 300, 2), (16, 2048, 8192, 4096, 3), (3, 64, 64, 40, 5)])
+def test_decode_chain_runs_a_layer_as_one_launch(ops, m, c, f, v, taps):
+    """Embedding, norm + in projection, short convolution with its state, out projection into the residual stream,
+    norm + gate/up + SwiGLU, down projection (inner sizes up to 9,216: more than the two activation segments that
+    shared memory holds, so they roll), norm of gathered rows + head: recorded into one chain and run as one launch,
+    against the same functions of the plain module, with padding tokens, and twice in a row (the barrier word
+    resets itself)."""
+    cuda, ref = ops
+    bf = torch.bfloat16
+    table = _rand((v, c), bf, 1, 0.5)
+    w_in, w_out = _rand((3 * c, c), bf, 2, c ** -0.5), _rand((c, c), bf, 3, c ** -0.5)
+    w_gu, w_down = _rand((2 * f, c), bf, 4, c ** -0.5), _rand((c, f), bf, 5, f ** -0.5)
+    n1, n2, n3 = (_rand((c,), torch.float32, 6 + i) * 0.2 + 1 for i in range(3))
+    conv_w, conv_b = _rand((c, taps), torch.float32, 9), _rand((c,), torch.float32, 10)
+    ids = torch.randint(0, v, (m,), generator=torch.Generator().manual_seed(11), dtype=torch.int32).to(DEV)
+    live = max(1, m - 2) if m > 2 else m  # the last tokens are padding
+    seq = torch.tensor(list(range(live)) + [-1] * (m - live), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([(3 * r + 1) % 20 for r in range(live)] + [-1] * (m - live), dtype=torch.int32, device=DEV)
+    rows = torch.tensor(list(range(live))[::-1], dtype=torch.int32, device=DEV)
+    state0 = _rand((20, taps - 1, c), torch.float32, 12)
+
+    def layer(o, state):
+        h = o.embedding(ids, table)
+        bcx = o.norm_linear(h, n1, 1e-5, False, w_in)
+        y = o.short_conv(bcx, conv_w, conv_b, state, None, seq, slots, decode_only=True) if o is cuda else \
+            ref.short_conv(bcx, conv_w, conv_b, state, torch.arange(live + 1, dtype=torch.int32, device=DEV), seq, slots[:live])
+        h = o.linear(y, w_out, residual=h)
+        act = o.norm_linear(h, n2, 1e-5, False, w_gu, swiglu_out=True)
+        h = o.linear(act, w_down, residual=h)
+        return h, o.norm_linear(h, n3, 1e-6, True, table, out_dtype=torch.float32, rows=rows)
+
+    s_ref = state0.clone()
+    h_want, logits_want = layer(ref, s_ref)
+    for _ in range(2):
+        s_got = state0.clone()
+        before = cuda.launch_count
+        assert cuda.chain_begin(m)
+        h_got, logits_got = layer(cuda, s_got)
+        assert cuda.launch_count == before  # nothing has run yet
+        cuda.chain_end()
+        assert cuda.launch_count == before + 1
+        _close(h_got[:live], h_want[:live], bf, "residual stream")
+        _close(logits_got, logits_want, bf, "logits of gathered rows")
+        _close(s_got, s_ref, bf, "conv state")  # built from activations that were rounded to bfloat16
+    assert cuda.chain_status() == 0
+    # an operation that cannot join (a float32 product) makes the pending ones run first
+    assert cuda.chain_begin(m)
+    h = cuda.embedding(ids, table)
+    before = cuda.launch_count
+    cuda.rmsnorm(h, n1, 1e-5, False, torch.float32)
+    assert cuda.launch_count == before + 2
+    cuda.chain_end()
 
 
 def test_short_conv_decode_kernel_equals_the_general_one(ops):
@@ -416,6 +489,32 @@ def test_prompt_attention_on_tensor_cores(ops, h, kh, d, page, window, kernel, m
     assert cuda.prefill_attention_tc_status() == 0
     general = cuda.paged_attention(q, k, v, bt, seq, pos, scale, window, page)
     _close(general, want, dtype, "general kernel")
+
+
+@pytest.mark.parametrize("h,kh,d,page,window", [(8, 2, 64, 64, None), (4, 2, 16, 16, 300), (6, 1, 128, 32, None), (32, 8, 64, 64, None)])
+@pytest.mark.parametrize("mode", ["split", "tiles"])
+def test_decoded_tokens_at_the_front_of_a_mixed_step(ops, h, kh, d, page, window, mode, monkeypatch):
+    """Five decoded tokens with contexts of 1 to 2,000 keys, then portions of 130, 1 and 70 tokens: with "split" the
+    five go to the split-key kernel and the prompt kernels start at the sixth request; with "tiles"
+    everything runs as query tiles. Both write every row of the one output, and both are the plain attention."""
+    cuda, ref = ops
+    monkeypatch.setattr(cuda, "mixed_attention", mode)
+    dtype = torch.bfloat16
+    lengths, starts = [1, 1, 1, 1, 1, 130, 1, 70], [1999, 0, 63, 64, 700, 50, 300, 0]
+    cu, seq = _batch(lengths)
+    pos = torch.tensor([s + j for s, n in zip(starts, lengths) for j in range(n)], dtype=torch.int32, device=DEV)
+    contexts = [s + l for s, l in zip(starts, lengths)]
+    pages = sum(-(-c // page) for c in contexts) + 3
+    bt = _tables(contexts, page, pages, 14)
+    k, v = _pools(pages, kh, page, d, dtype, 70)
+    q = _rand((pos.numel(), h * d), dtype, 72)
+    ctx = _Prompt(cu, lengths)
+    ctx.max_context = max(contexts)
+    before = cuda.launch_count
+    got = cuda.paged_attention(q, k, v, bt, seq, pos, d ** -0.5, window, page, ctx)
+    assert cuda.launch_count - before == (3 if mode == "split" else 1)  # split keys, their merge, the prompt tiles
+    _close(got, ref.paged_attention(q, k, v, bt, seq, pos, d ** -0.5, window, page), dtype, mode)
+    assert cuda.decode_attention_status() == 0 and cuda.prefill_attention_tc_status() == 0
 
 
 @pytest.mark.parametrize("kernel", ["tcgen05", "mma"])

@@ -5,43 +5,19 @@ import pytest
 from akas_b200.ops import cuda
 
 
-@pytest.fixture
-def b200(monkeypatch):
-    monkeypatch.setattr(cuda, "_sms", 148)
-    monkeypatch.setattr(cuda, "products", "auto")
-    monkeypatch.setattr(cuda, "paired_sms", "1")
-    return monkeypatch
-
-
-def test_gate_up_route_on_the_lfm2_shapes(b200):
-    route = cuda._swiglu_route
-    # 1.2B shape: K 2,048, F 8,192
-    assert route(512, 2048, 8192) == "library" and route(1024, 2048, 8192) == "library"
-    assert route(1536, 2048, 8192) == "paired" and route(2048, 2048, 8192) == "paired" and route(8448, 2048, 8192) == "paired"
-    # 700M shape: K 1,536, F 6,912
-    assert route(2048, 1536, 6912) == "library" and route(8192, 1536, 6912) == "paired"
-    # 350M shape: K 1,024, F 4,608
-    assert route(2048, 1024, 4608) == "library" and route(8192, 1024, 4608) == "library"
-    # decode steps never come here, and an inner size that is no multiple of 8 cannot be fed by TMA
-    assert route(16, 2048, 8192) == "library" and route(2048, 2044, 8192) == "library"
-
-
-def test_gate_up_route_under_the_switches(b200):
-    route = cuda._swiglu_route
-    b200.setattr(cuda, "products", "library")
-    assert route(2048, 2048, 8192) == "library"
-    b200.setattr(cuda, "products", "tcgen05")
-    assert route(2048, 2048, 8192) == "paired" and route(64, 2048, 8192) == "block"  # too few tiles for 74 pairs
-    b200.setattr(cuda, "paired_sms", "0")
-    assert route(2048, 2048, 8192) == "block"
-    b200.setattr(cuda, "products", "auto")
-    assert route(2048, 2048, 8192) == "block" and route(1536, 2048, 8192) == "library"
-
-
-def test_plain_products_go_to_the_library_unless_told_otherwise(b200):
-    assert not cuda._tcgen05_takes(2048, 2048)
-    b200.setattr(cuda, "products", "tcgen05")
-    assert cuda._tcgen05_takes(2048, 2048) and not cuda._tcgen05_takes(16, 2048) and not cuda._tcgen05_takes(2048, 2044)
+def test_products_above_sixteen_tokens_run_on_the_hand_written_kernels(monkeypatch):
+    monkeypatch.setattr(cuda, "products", "own")
+    route = cuda._product_route
+    bf16, f32, acc, swiglu = cuda._OUT_BF16, cuda._OUT_F32, cuda._OUT_ACC, cuda._OUT_SWIGLU
+    # the LFM2 shapes: every product goes to the kernel for pairs of SMs
+    assert route(2048, 6144, bf16) == "paired" and route(2048, 2048, acc) == "paired" and route(8192, 2048, acc) == "paired"
+    assert route(2048, 16384, swiglu) == "paired" and route(2048, 65536, f32) == "paired"
+    # rows that TMA cannot write (a pitch that is no multiple of 16 bytes) go to the one-block kernel's masked read-outs
+    assert route(64, 500, f32) == "paired" and route(64, 502, f32) == "block" and route(64, 500, bf16) == "block"
+    assert route(64, 504, bf16) == "paired" and route(64, 1001, acc) == "block"
+    assert route(64, 2 * 24, swiglu) == "paired" and route(64, 2 * 20, swiglu) == "unfused"  # the product, then SwiGLU by itself
+    monkeypatch.setattr(cuda, "products", "library")
+    assert {route(2048, 2048, m) for m in (bf16, f32, acc, swiglu)} == {"library"}
 
 
 def test_reports_are_compared_case_by_case():

@@ -131,16 +131,13 @@ def test_captured_steps_agree_with_the_plain_model(key, dtype, tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("key", ["a", "c"])
-def test_whole_prompts_through_the_tensor_memory_products(key, tmp_path, monkeypatch):
-    """The default policy gives prompt-sized products of models this small to the library. Here every such product
-    runs on the hand-written tcgen05 kernels: with the policy "tcgen05", and with a device that claims two SMs, so
-    that the kernel for pairs of SMs (a tile for every pair) takes the gate/up and the plain products, ragged tiles
-    included, and the one-block kernel the residual ones."""
+@pytest.mark.parametrize("key", ["a", "b", "c"])
+def test_prompts_run_on_the_hand_written_products_and_agree_with_the_library(key, tmp_path, monkeypatch):
+    """By default every product of more than 16 tokens runs on the tcgen05 kernels (for pairs of SMs where TMA can write
+    the rows, the one-block kernel where it cannot: configuration b has a vocabulary whose rows it cannot); nothing
+    reaches the library. With the library in their place the logits are the plain model's too."""
     from akas_b200.ops import cuda
 
-    monkeypatch.setattr(cuda, "products", "tcgen05")
-    monkeypatch.setattr(cuda, "_sms", 2)
     calls = {"paired": 0}
     paired = cuda.paired_product
 
@@ -148,10 +145,21 @@ def test_whole_prompts_through_the_tensor_memory_products(key, tmp_path, monkeyp
         calls["paired"] += 1
         return paired(*args, **kwargs)
 
+    def refused(*args, **kwargs):
+        raise AssertionError("a product reached the library")
+
     monkeypatch.setattr(cuda, "paired_product", counted)
+    library = cuda._functions.get("akas_gemm_bf16")
+    monkeypatch.setitem(cuda._functions, "akas_gemm_bf16", refused)
     _run_modes(key, "bfloat16", "cuda:0", None, tmp_path, ["whole", "portions"])
     assert calls["paired"] > 0
     assert cuda.gemm_pair_status() == 0 and cuda.gemm_tcgen05_status() == 0
+    if library is not None:
+        monkeypatch.setitem(cuda._functions, "akas_gemm_bf16", library)
+    else:
+        monkeypatch.delitem(cuda._functions, "akas_gemm_bf16")
+    monkeypatch.setattr(cuda, "products", "library")
+    _run_modes(key, "bfloat16", "cuda:0", None, tmp_path / "library", ["whole"])
 
 
 @pytest.mark.gpu
