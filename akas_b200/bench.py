@@ -113,30 +113,42 @@ def measure_prefill(runner: ModelRunner, prompt: Sequence[int], repeats: int = 3
 
 
 def measure_decode(runner: ModelRunner, batch: int, prefix: int, steps: int, warmup: int, seed: int = 17,
-                   chunk: int = 2048) -> Dict[str, float]:
+                   chunk: int = 2048, repeats: int = 5) -> Dict[str, float]:
     """Milliseconds per decode step at ``batch`` requests whose prompts of ``prefix`` tokens are cached.
 
     Each timed step feeds one given (synthetic) token per request and includes the head and the argmax;
-    nothing is read back inside the timed region.
+    nothing is read back inside the timed region. A region is exactly ``steps`` steps between two synchronisations,
+    timed with CUDA events; it is run up to ``repeats`` times, one after the other (the requests keep decoding, as far
+    as the context allows), and the median region is reported: a single short region right after a synchronisation
+    also holds the host's preparation of its first step and whatever the clocks do on their way up. The entries of
+    every step are built beforehand.
     """
     vocab = runner.vocab_size
     prompts = synthetic_prompts(batch, prefix, vocab, seed)
     ids = fill_requests(runner, prompts, chunk)
-    feed = np.random.default_rng(seed + 1).integers(0, vocab, (warmup + steps, batch)).tolist()
+    room = runner.config.context - prefix - warmup - 1
+    repeats = max(1, min(repeats, room // max(steps, 1)))
+    total = warmup + repeats * steps
+    feed = np.random.default_rng(seed + 1).integers(0, vocab, (total, batch)).tolist()
+    entries = [[StepEntry(rid, (feed[i][j],), (0,)) for j, rid in enumerate(ids)] for i in range(total)]
 
-    def step(i):
-        logits = runner.step([StepEntry(rid, (feed[i][j],), (0,)) for j, rid in enumerate(ids)])
-        return runner.ops.argmax(logits)
+    def run(first, count):
+        for i in range(first, first + count):
+            runner.ops.argmax(runner.step(entries[i]))
 
-    for i in range(warmup):
-        step(i)
-    launches_before = runner.ops.launch_count
-    ms = _event_ms(lambda: [step(warmup + i) for i in range(steps)])
-    contexts = [prefix + warmup + steps // 2] * batch
+    run(0, warmup)
+    regions, launches = [], 0
+    for r in range(repeats):
+        before = runner.ops.launch_count
+        regions.append(_event_ms(lambda: run(warmup + r * steps, steps)))
+        launches = runner.ops.launch_count - before
+    ms = statistics.median(regions)
+    at = sorted(range(repeats), key=lambda r: regions[r])[repeats // 2]  # the region whose time is reported
+    contexts = [prefix + warmup + at * steps + steps // 2] * batch
     for rid in ids:
         runner.release(rid)
     return dict(ms_per_step=ms / steps, tokens_per_s=batch * steps / (ms / 1e3), bytes=decode_bytes(runner, contexts),
-                launches=runner.ops.launch_count - launches_before)
+                launches=launches, regions_ms=[round(x, 4) for x in regions])
 
 
 def case_lengths(batch: int, prompt: int, mixed: bool) -> List[int]:

@@ -148,6 +148,13 @@ __device__ __forceinline__ void named_sync(int id, int count) { asm volatile("ba
 __device__ __forceinline__ void named_arrive(int id, int count) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
+// The same once `value` has been computed: the arrival's count is made to depend on it, so the instruction cannot issue
+// while a load that feeds the value is still in flight. For a thread that hands back a buffer it has only read.
+__device__ __forceinline__ void named_arrive_after(int id, int count, float value) {
+  unsigned zero;
+  asm volatile("and.b32 %0, %1, 0;" : "=r"(zero) : "r"(__float_as_uint(value)));
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count + (int)zero) : "memory");
+}
 
 template <int NT, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -412,6 +419,7 @@ decode_chain_kernel(const __grid_constant__ Program prog) {
             const int buf = (int)(deposits & 1);
             named_sync(BAR_FULL + buf, WORKERS);  // the consumers' sums of this run are in the buffer
             const float* sums = red + (size_t)buf * CONSUMERS * NT * 128;
+            float all = 0.f;
 #pragma unroll
             for (int q = 0; q < NT * 4; ++q) {
               const int e = lane + 32 * q, j = e >> 7, row = (e & 127) >> 3, tok = e & 7;
@@ -420,8 +428,11 @@ decode_chain_kernel(const __grid_constant__ Program prog) {
               for (int w = 0; w < CONSUMERS; ++w)  // always in this order: results do not depend on timing
                 sum += sums[(((size_t)w * NT + j) * 16 + row) * 8 + tok];
               if (run == 0) v[q] = sum; else u[q] = sum;
+              all += sum;
             }
-            named_arrive(BAR_FREE + buf, WORKERS);  // the buffer may take the sums of the run after next
+            // The buffer may take the sums of the run after next - once every load from it has come back: an arrival
+            // that went out while loads were in flight let the consumers overwrite what was still being read.
+            named_arrive_after(BAR_FREE + buf, WORKERS, all);
           }
           // A product that is cut along K: the parts of a tile are added in the order of their numbers.
           int* counter = op.parts > 1 ? prog.counters + tile : nullptr;

@@ -9,7 +9,10 @@
 // into and reads out of its shared memory per multiply-add, which is what bounds a one-block kernel (its TMA writes
 // and operand reads ask for 192 bytes a cycle of a shared memory that gives 128).
 //   warp 0   producer, in both blocks: TMA loads of the block's slice of x and of W into a ring of stages of two
-//            64-wide steps of K each. Every load of either block counts its bytes on the LEADER's "full" barrier of
+//            64-wide steps of K each: ONE copy per operand and stage (a box of two groups of 64 k from a view
+//            [K / 64][rows][64] of the matrix; starting a copy costs the issuing thread some 300 cycles whatever it
+//            moves, and with a copy per step the producer fell behind the tensor cores; K that is no multiple of 64
+//            takes a copy per step). Every load of either block counts its bytes on the LEADER's "full" barrier of
 //            the stage (the block of cluster rank 0), on which the leader has announced the bytes of both.
 //   warp 1   tensor cores: both blocks allocate tensor memory together (two accumulators of BN columns); one thread
 //            of the leader issues, per stage, eight tcgen05.mma.cta_group::2 (M 256, N BN, K 16) and commits them to
@@ -49,7 +52,7 @@ enum { EPI_BF16 = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3 };
 
 template <int BN> struct Shape {
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, HALF_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGE_BYTES = STEPS * HALF_BYTES;  // [x, W] of one step of K, then of the next
+  static constexpr int STAGE_BYTES = STEPS * HALF_BYTES;  // x of both steps of K, then W of both steps
   static constexpr int STAGES = BN == 256 ? 3 : 4;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 8 * STAGING + 1024;
 };
@@ -79,6 +82,14 @@ __device__ __forceinline__ void tma_load_2d_for(void* smem_dst, const CUtensorMa
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(bar_address) : "memory");
+}
+// The same with a box of a three-dimensional view [K / 64][rows][64] of the matrix: rows x 64 k x `STEPS` groups of k
+// in ONE copy (an instruction that starts a TMA copy costs the issuing thread some 300 cycles whatever it moves; with
+// a copy per step of K the producer could not keep up with the tensor cores).
+__device__ __forceinline__ void tma_load_3d_for(void* smem_dst, const CUtensorMap* map, int row, int group, unsigned bar_address) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(0), "r"(row), "r"(group), "r"(bar_address) : "memory");
 }
 __device__ __forceinline__ void umma_pair(unsigned tmem_d, uint64_t a_desc, uint64_t b_desc, unsigned idesc, unsigned accumulate) {
   asm volatile(
@@ -126,14 +137,14 @@ template <int N> __device__ __forceinline__ void bulk_wait_read() {
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool WIDE>
 __global__ void __launch_bounds__(THREADS)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_y, int M, int N, int K, int F) {
   // N: channels of the product (for SWIGLU the stacked height 2F); a tile covers BN of them (SWIGLU: BN/2 gate
   // rows f0.. and BN/2 up rows F + f0..).
   using S = Shape<BN>;
-  constexpr int STAGES = S::STAGES, A_BYTES = S::A_BYTES, HALF_BYTES = S::HALF_BYTES, STAGE_BYTES = S::STAGE_BYTES;
+  constexpr int STAGES = S::STAGES, A_BYTES = S::A_BYTES, STAGE_BYTES = S::STAGE_BYTES;
   constexpr int TILE_N = EPI == EPI_SWIGLU ? BN / 2 : BN;  // output columns a tile yields
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -187,10 +198,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           unsigned char* a = smem + (size_t)s * STAGE_BYTES;
           const unsigned leader_full = peer_address(&full_bar[s], 0);
           if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);  // the bytes of both blocks
+          if (WIDE) {  // K is a multiple of 64: both steps of K in one copy per operand (groups past K: zeros)
+            tma_load_3d_for(a, &map_x, m0, kb, leader_full);
+            tma_load_3d_for(a + STEPS * A_BYTES, &map_w, w_row, kb, leader_full);
+          } else {
 #pragma unroll
-          for (int h = 0; h < STEPS; ++h) {  // a step past the end of K is filled with zeros
-            tma_load_2d_for(a + h * HALF_BYTES, &map_x, (kb + h) * BK, m0, leader_full);
-            tma_load_2d_for(a + h * HALF_BYTES + A_BYTES, &map_w, (kb + h) * BK, w_row, leader_full);
+            for (int h = 0; h < STEPS; ++h) {  // a step past the end of K is filled with zeros
+              tma_load_2d_for(a + h * A_BYTES, &map_x, (kb + h) * BK, m0, leader_full);
+              tma_load_2d_for(a + STEPS * A_BYTES + h * S::B_BYTES, &map_w, (kb + h) * BK, w_row, leader_full);
+            }
           }
         }
         if (*(volatile int*)&abort_s) break;
@@ -216,7 +232,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
           for (int h = 0; h < STEPS; ++h) {
             if (kb + h >= k_blocks) break;  // zeros: nothing to add
-            const uint64_t a_desc = smem_desc(a + h * HALF_BYTES), b_desc = smem_desc(a + h * HALF_BYTES + A_BYTES);
+            const uint64_t a_desc = smem_desc(a + h * A_BYTES), b_desc = smem_desc(a + STEPS * A_BYTES + h * S::B_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further along the swizzled row per step
               umma_pair(d, a_desc + (uint64_t)(k * UMMA_K * 2 >> 4), b_desc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc,
@@ -340,14 +356,47 @@ int make_out_map(CUtensorMap* map, void* base, int rows, int cols, int elem_byte
   return r == CUDA_SUCCESS ? 0 : 3000 + (int)r;
 }
 
-template <int BN, int EPI>
+// A tensor map of a row-major bfloat16 matrix [rows, K], K a multiple of 64, seen as [K / 64][rows][64]: boxes of 64 k x
+// box_rows x `STEPS` groups of k, 128-byte swizzle, zeros outside.
+int make_wide_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiled fn = encode_tiled();
+  if (!fn) return 3001;
+  const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(K / 64)};
+  const cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, STEPS};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 3000 + (int)r;
+}
+
+std::mutex g_wide_mutex;
+std::map<std::tuple<const void*, int, int, int>, CUtensorMap> g_wide_maps;  // weights keep their maps
+
+int cached_wide_map(CUtensorMap* out, const void* base, int rows, int K, int box_rows, bool cache) {
+  if (!cache) return make_wide_map(out, base, rows, K, box_rows);
+  std::lock_guard<std::mutex> lock(g_wide_mutex);
+  const auto key = std::make_tuple(base, rows, K, box_rows);
+  auto it = g_wide_maps.find(key);
+  if (it == g_wide_maps.end()) {
+    CUtensorMap map;
+    const int err = make_wide_map(&map, base, rows, K, box_rows);
+    if (err) return err;
+    it = g_wide_maps.emplace(key, map).first;
+  }
+  *out = it->second;
+  return 0;
+}
+
+template <int BN, int EPI, bool WIDE>
 int launch(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
   constexpr int smem = Shape<BN>::SMEM;
   static int pairs_room[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
   if (pairs_room[device] == 0) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     int sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
@@ -363,7 +412,7 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, cudaStrea
     probe.attrs = attribute;
     probe.numAttrs = 1;
     int room = 0;
-    e = cudaOccupancyMaxActiveClusters(&room, gemm_pair_kernel<BN, EPI>, &probe);
+    e = cudaOccupancyMaxActiveClusters(&room, gemm_pair_kernel<BN, EPI, WIDE>, &probe);
     if (e != cudaSuccess) return (int)e;
     if (room < 1) return (int)cudaErrorInvalidConfiguration;
     pairs_room[device] = room < sms / 2 ? room : sms / 2;
@@ -371,9 +420,9 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, cudaStrea
   const int F = N / 2;
   const int out_cols = EPI == EPI_SWIGLU ? F : N, tile_n = EPI == EPI_SWIGLU ? BN / 2 : BN;
   CUtensorMap map_x, map_w, map_y;
-  int err = cached_map(&map_x, x, M, K, BM, false);
+  int err = WIDE ? cached_wide_map(&map_x, x, M, K, BM, false) : cached_map(&map_x, x, M, K, BM, false);
   if (err) return err;
-  err = cached_map(&map_w, w, N, K, BN / 2, true);
+  err = WIDE ? cached_wide_map(&map_w, w, N, K, BN / 2, true) : cached_map(&map_w, w, N, K, BN / 2, true);
   if (err) return err;
   err = EPI == EPI_ACC || EPI == EPI_F32 ? make_out_map(&map_y, y, M, out_cols, 4, 32)
                                          : make_out_map(&map_y, y, M, out_cols, 2, EPI == EPI_BF16 ? 64 : 32);
@@ -392,7 +441,7 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, cudaStrea
   attribute[0].val.clusterDim.z = 1;
   config.attrs = attribute;
   config.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&config, gemm_pair_kernel<BN, EPI>, map_x, map_w, map_y, M, N, K, F);
+  const cudaError_t e = cudaLaunchKernelEx(&config, gemm_pair_kernel<BN, EPI, WIDE>, map_x, map_w, map_y, M, N, K, F);
   return e != cudaSuccess ? (int)e : launch_status();
 }
 
@@ -403,9 +452,14 @@ int launch_width(const void* x, const void* w, void* y, int M, int N, int K, cud
   const long long rows = (M + 2 * BM - 1) / (2 * BM);
   const int out_cols = EPI == EPI_SWIGLU ? N / 2 : N;
   const int unit = EPI == EPI_SWIGLU ? 2 : 1;  // a SwiGLU tile of BN stacked rows yields BN / 2 channels
-  if (rows * ((out_cols * unit + 255) / 256) >= 56) return launch<256, EPI>(x, w, y, M, N, K, stream);
-  if (rows * ((out_cols * unit + 127) / 128) >= 56) return launch<128, EPI>(x, w, y, M, N, K, stream);
-  return launch<64, EPI>(x, w, y, M, N, K, stream);
+  if (K % 64 == 0) {
+    if (rows * ((out_cols * unit + 255) / 256) >= 56) return launch<256, EPI, true>(x, w, y, M, N, K, stream);
+    if (rows * ((out_cols * unit + 127) / 128) >= 56) return launch<128, EPI, true>(x, w, y, M, N, K, stream);
+    return launch<64, EPI, true>(x, w, y, M, N, K, stream);
+  }
+  if (rows * ((out_cols * unit + 255) / 256) >= 56) return launch<256, EPI, false>(x, w, y, M, N, K, stream);
+  if (rows * ((out_cols * unit + 127) / 128) >= 56) return launch<128, EPI, false>(x, w, y, M, N, K, stream);
+  return launch<64, EPI, false>(x, w, y, M, N, K, stream);
 }
 
 }  // namespace

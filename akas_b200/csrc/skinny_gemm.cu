@@ -6,13 +6,15 @@
 // two per SM, each taking row tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 //
 // A block has one producer warp and 8 consumer warps. The producer streams the block's weight rows, in
-// 256-wide chunks, into an eight-stage ring in shared memory: two TMA tensor loads per stage (rows 0-7 and
-// rows 8-15 of the tile, each a box of 64 k x 8 rows x 4 groups of k from a three-dimensional view
-// [K/64][O][64] of the matrix, 128-byte swizzle), completion counted in bytes on the stage's "full" mbarrier.
+// 512-wide chunks, into a four-stage ring in shared memory: one TMA tensor load per stage (a box of 64 k x 16
+// rows x 8 groups of k from a three-dimensional view [K/64][O][64] of the matrix, 128-byte swizzle; for SwiGLU
+// two boxes of 8 rows), completion counted in bytes on the stage's "full" mbarrier. An instruction that starts a
+// TMA copy costs the issuing thread some 300 cycles whatever the copy holds, so a box is as large as it can be:
+// with 4 KB boxes one thread could not feed an SM's share of the memory bandwidth.
 // It runs ahead across row tiles, held back only by the stages' "empty" mbarriers, on which the consumer
 // warps arrive when they have read a stage. So up to 64 KB of loads are in flight per block with one thread
-// issuing them, and the consumers' loop is: wait for the stage, three 16-byte reads from shared memory, two
-// products, arrive. The 8 consumer warps split a chunk 32 k each; in its 32 k, thread (g, t) reads 16
+// issuing them, and the consumers' loop is: wait for the stage, 16-byte reads from shared memory, four
+// products, arrive. The 8 consumer warps split a chunk 64 k each; in each 32 k of it, thread (g, t) reads 16
 // contiguous bytes of W rows g and g + 8 and of token g at k = 8t. These 8 values feed two k-steps: the
 // product does not care which physical k sits in which k-slot as long as A and B agree, which is what makes
 // 16-byte reads possible. The tokens' activations are put into shared memory once per block (converted and
@@ -53,9 +55,9 @@ using namespace akas;
 
 namespace {
 
-constexpr int CONSUMERS = 8, KC = 256, STAGES = 8;
+constexpr int CONSUMERS = 8, KC = 512, STAGES = 4;
 constexpr int MAX_KSPLIT = 8, SPLIT_TILES = 4;  // parts of K; row tiles a cluster may take when K is cut
-constexpr int STAGE_BYTES = 16 * KC * 2;  // two boxes of [4 groups of k][8 rows][128 bytes]
+constexpr int STAGE_BYTES = 16 * KC * 2;  // one box of [8 groups of k][16 rows][128 bytes], or (SwiGLU) two of 8 rows
 constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr unsigned kSpinLimit = 1u << 22;  // try_wait calls before a wait gives up (each may block for a while)
 enum { IN_BF16 = 0, IN_NORM = 1 };
@@ -171,7 +173,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
   };
 
   if (warp == CONSUMERS) {
-    // ---------------------------------------------------------------- producer: one thread, two boxes per stage
+    // ---------------------------------------------------------------- producer: one thread, one box per stage (SwiGLU: two)
     if (lane == 0) {
       int tile = first_tile, chunk = 0;
       for (int n = 0; n < items; ++n) {
@@ -183,8 +185,16 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
         const int row_hi = OUT == OUT_SWIGLU ? F + tile * 8 : tile * 16 + 8;
         unsigned char* dst = ring + (size_t)s * STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);  // rows or k past the matrix arrive as zeros and count too
-        tma_load_box(dst, &map_w, row_lo, (chunk0 + chunk) * (KC / 64), &full_bar[s]);
-        tma_load_box(dst + STAGE_BYTES / 2, &map_w, row_hi, (chunk0 + chunk) * (KC / 64), &full_bar[s]);
+        // An instruction that starts a TMA copy costs the issuing thread some 300 cycles whatever the copy holds, so
+        // the boxes are as large as they can be: 16 rows x 512 k (16 KB), or two of 8 rows for SwiGLU's two halves.
+        // (SwiGLU as a run of stages over 16 gate rows and then one over 16 up rows, one box a stage, measured
+        // slower here: 0.926 against 0.898 ms a decode step of the 1.2B shape.)
+        if (OUT == OUT_SWIGLU) {
+          tma_load_box(dst, &map_w, row_lo, (chunk0 + chunk) * (KC / 64), &full_bar[s]);
+          tma_load_box(dst + STAGE_BYTES / 2, &map_w, row_hi, (chunk0 + chunk) * (KC / 64), &full_bar[s]);
+        } else {
+          tma_load_box(dst, &map_w, row_lo, (chunk0 + chunk) * (KC / 64), &full_bar[s]);
+        }
         if (++chunk == chunks) { chunk = 0; tile += tile_step; }
       }
     }
@@ -230,9 +240,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
     }
     consumer_barrier();  // the activations are in shared memory for every consumer warp
 
-    // Where this thread's 16 bytes of weight rows g and g + 8 lie inside a stage: box (rows 0-7 or 8-15), group of
-    // 64 k (warp / 2), row g, and the 16-byte unit ((warp & 1) * 4 + t) XOR g of the 128-byte swizzle.
-    const int a_off = ((warp >> 1) * 8 + g) * 128 + ((((warp & 1) * 4 + t) ^ g) << 4);
+    // Where this thread's 16 bytes of weight rows g and g + 8 lie inside a stage: group of 64 k, row, and the 16-byte
+    // unit (slice & 1) * 4 + t XOR g of the 128-byte swizzle. One box holds 16 rows to a group of k, SwiGLU's two boxes
+    // 8 rows each. A warp multiplies 64 of a chunk's 512 k: slices 2 * warp and 2 * warp + 1 of 32 k.
+    constexpr int kg_stride = OUT == OUT_SWIGLU ? 1024 : 2048, hi_off = OUT == OUT_SWIGLU ? STAGE_BYTES / 2 : 1024;
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
@@ -240,18 +251,21 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
     for (int n = 0; n < items; ++n) {
       const int s = n % STAGES;
       wait_for(&full_bar[s], (n / STAGES) & 1, 1);
-      const int k = c * KC + warp * 32 + 8 * t;  // this thread's 8 consecutive k of the chunk, counted from k0
-      if (k < k_len) {
-        const unsigned char* st = ring + (size_t)s * STAGE_BYTES + a_off;
-        const uint4 a_lo = *reinterpret_cast<const uint4*>(st);
-        const uint4 a_hi = *reinterpret_cast<const uint4*>(st + STAGE_BYTES / 2);
-        const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};  // first k-step: this thread's k 0..3
-        const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};  // second k-step: its k 4..7
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-          const uint4 b = *reinterpret_cast<const uint4*>(xs + (size_t)(8 * j + g) * XS + k);
-          mma_bf16(acc[j], a1, b.x, b.y);
-          mma_bf16(acc[j], a2, b.z, b.w);
+      for (int i2 = 0; i2 < 2; ++i2) {
+        const int k = c * KC + warp * 64 + i2 * 32 + 8 * t;  // this thread's 8 consecutive k, counted from k0
+        if (k < k_len) {
+          const unsigned char* st = ring + (size_t)s * STAGE_BYTES + warp * kg_stride + g * 128 + (((i2 * 4 + t) ^ g) << 4);
+          const uint4 a_lo = *reinterpret_cast<const uint4*>(st);
+          const uint4 a_hi = *reinterpret_cast<const uint4*>(st + hi_off);
+          const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};  // first k-step: this thread's k 0..3
+          const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};  // second k-step: its k 4..7
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            const uint4 b = *reinterpret_cast<const uint4*>(xs + (size_t)(8 * j + g) * XS + k);
+            mma_bf16(acc[j], a1, b.x, b.y);
+            mma_bf16(acc[j], a2, b.z, b.w);
+          }
         }
       }
       __syncwarp();
@@ -372,19 +386,19 @@ EncodeTiled encode_tiled() {
 }
 
 std::mutex g_map_mutex;
-std::map<std::tuple<const void*, int, int>, CUtensorMap> g_maps;  // one map per weight matrix
+std::map<std::tuple<const void*, int, int, int>, CUtensorMap> g_maps;  // one map per weight matrix and box height
 
-// The matrix [O, K] seen as [K / 64][O][64]: boxes of 64 k x 8 rows x 4 groups of k, 128-byte swizzle, zeros outside.
-int weight_map(CUtensorMap* out, const void* w, int O, int K) {
+// The matrix [O, K] seen as [K / 64][O][64]: boxes of 64 k x 16 (SwiGLU: 8) rows x 8 groups of k, 128-byte swizzle, zeros outside.
+int weight_map(CUtensorMap* out, const void* w, int O, int K, int box_rows) {
   std::lock_guard<std::mutex> lock(g_map_mutex);
-  const auto key = std::make_tuple(w, O, K);
+  const auto key = std::make_tuple(w, O, K, box_rows);
   auto it = g_maps.find(key);
   if (it == g_maps.end()) {
     EncodeTiled fn = encode_tiled();
     if (!fn) return 3001;
     const cuuint64_t dims[3] = {64, (cuuint64_t)O, (cuuint64_t)(K / 64)};
     const cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
-    const cuuint32_t box[3] = {64, 8, KC / 64};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, KC / 64};
     const cuuint32_t elem[3] = {1, 1, 1};
     CUtensorMap map;
     const CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(w), dims, strides, box, elem,
@@ -448,7 +462,8 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
         if (ksplit > 1 && (OUTM == OUT_SWIGLU || ksplit > chunks)) break;
         const int smem = block_smem<NT>(K, ksplit);
         if (smem > kMaxSmemBytes) continue;
-        const int per_sm = max(1, min(3, kMaxSmemBytes / (smem + 1024)));
+        static const int per_sm_cap = [] { const char* v = getenv("AKAS_B200_SKINNY_PER_SM"); return v ? atoi(v) : 3; }();
+        const int per_sm = max(1, min(per_sm_cap, kMaxSmemBytes / (smem + 1024)));
         int clusters = sms * per_sm / ksplit;
         if (ksplit > 1) {
           const auto room_key = std::make_tuple(ksplit, smem);
@@ -493,7 +508,7 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
     }
   }
   CUtensorMap map;
-  const int err = weight_map(&map, W, O, K);
+  const int err = weight_map(&map, W, O, K, OUTM == OUT_SWIGLU ? 8 : 16);
   if (err) return err;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(plan.grid);

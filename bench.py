@@ -5,7 +5,8 @@
 
 A step is one decode step of a batch of 8 requests whose 2,048-token prompts are in the cache
 (context 4,096). ``value`` is decoded tokens a second, timed on the device with CUDA events around
-exactly ``--steps`` steps after ``--warmup`` untimed ones; ``e2e`` is the same through ``Engine``
+exactly ``--steps`` steps after ``--warmup`` untimed ones (the region is repeated up to five times and the median
+is reported); ``e2e`` is the same through ``Engine``
 (host token ids in, sampled ids read back every step). The one JSON line also carries the prefill of
 2,048 tokens, the decode roofline (bytes a step must read / its time, against the measured copy
 bandwidth) and decode at batches 1 and 64. Inputs (2.3 GB of weights read every step) are larger
@@ -28,7 +29,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# BASELINE.json configs[2]: the LFM2-1.2B shape
+# the LFM2-1.2B shape: layer sizes of the published model, random weights
 LFM2_1_2B = dict(
     architectures=["Lfm2ForCausalLM"], model_type="lfm2", hidden_size=2048, num_attention_heads=32,
     num_key_value_heads=8, intermediate_size=12288, block_auto_adjust_ff_dim=True, block_ffn_dim_multiplier=1.0,
@@ -223,6 +224,7 @@ def main():
             "ff": model_config.feed_forward_size, "vocab": 65536, "conv_L_cache": 3, "tied": True,
             "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT, "page_size": 64,
             "parallelism": "single GPU", "cuda_graphs": True, "l2": "inputs (weights) larger than L2",
+            "timed_regions": len(main_run["regions_ms"]),
         },
         "clocks": clocks,
         "e2e": {"value": round(produced / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,

@@ -226,13 +226,14 @@ def test_products_on_pairs_of_sms(ops, m, k, o):
 
 @pytest.mark.parametrize("m,c,f,v,taps", [(1, 128, 320, 500, 3), (8, 256, 9216, 1000, 3), (5, 192, 448, 777, 4),
                                          (13, 128, 6912, 300, 2), (16, 2048, 8192, 4096, 3), (3, 64, 64, 40, 5)])
-def test_decode_chain_runs_a_layer_as_one_launch(ops, m, c, f, v, taps):
+def test_decode_chain_runs_a_layer_as_one_launch(ops, m, c, f, v, taps, monkeypatch):
     """Embedding, norm + in projection, short convolution with its state, out projection into the residual stream,
     norm + gate/up + SwiGLU, down projection (inner sizes up to 9,216: more than the two activation segments that
     shared memory holds, so they roll), norm of gathered rows + head: recorded into one chain and run as one launch,
     against the same functions of the plain module, with padding tokens, and twice in a row (the barrier word
     resets itself)."""
     cuda, ref = ops
+    monkeypatch.setattr(cuda, "decode_chain", "1")
     bf = torch.bfloat16
     table = _rand((v, c), bf, 1, 0.5)
     w_in, w_out = _rand((3 * c, c), bf, 2, c ** -0.5), _rand((c, c), bf, 3, c ** -0.5)

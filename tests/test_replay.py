@@ -163,6 +163,31 @@ def test_prompts_run_on_the_hand_written_products_and_agree_with_the_library(key
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("key", ["a", "b", "c"])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_decode_steps_as_chains_agree_with_the_plain_model(key, graphs, tmp_path, monkeypatch):
+    """With AKAS_B200_DECODE_CHAIN=1 the products, convolutions and embedding of a decode step run as persistent
+    launches with grid-wide barriers between operations (csrc/decode_chain.cu), cut where an attention layer needs its
+    own kernels; eagerly and inside captured graphs the logits are the plain model's, and no bounded wait runs out."""
+    from akas_b200.config import EngineConfig
+    from akas_b200.engine.runner import ModelRunner
+    from akas_b200.ops import cuda
+
+    monkeypatch.setattr(cuda, "decode_chain", "1")
+    folder, reqs, want = _setup(key, "bfloat16", tmp_path)
+    page = tiny.PAGE[key]
+    longest = -(-max(len(t) for t in reqs.values()) // page) * page
+    runner = ModelRunner(folder, EngineConfig(dtype="bfloat16", device="cuda:0", page_size=page, max_tokens=4 * longest,
+                                              max_requests=4, context=longest, cuda_graphs=graphs))
+    before = cuda.launch_count
+    _check(traces.replay(runner, traces.tail_decoded(reqs)), want, "bfloat16", "tail decoded, chained")
+    prompt_lens = {rid: max(1, len(t) - 9) for rid, t in reqs.items()}
+    steps, _ = traces.mixed(reqs, prompt_lens, seed=3, live=4, page=page)
+    _check(traces.replay(runner, steps), want, "bfloat16", "mixed, chained")
+    assert cuda.chain_status() == 0 and cuda.launch_count > before
+
+
+@pytest.mark.gpu
 def test_timed_operations_change_nothing_and_account_for_the_step(tmp_path):
     """The wrapper that brackets every operation with CUDA events runs the same kernels: same logits, and a table
     that names the operations of a prompt and of a decoded token."""
