@@ -300,7 +300,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           tmem_load32(taddr + c, v);
           tmem_load32(taddr + BN / 2 + c, u);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * u[i];
+          for (int i = 0; i < 32; ++i) v[i] = __fdividef(v[i], 1.f + __expf(-v[i])) * u[i];  // the fast division: IEEE division cost more than the tile's loads
           // row `lane` of 64 bytes, its 16-byte units XORed with bits 7-8 of the address (the 64-byte swizzle)
 #pragma unroll
           for (int j = 0; j < 4; ++j) {

@@ -334,7 +334,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
               if (tk < M && f < out_cols) {
                 const float scale = IN_NORM ? inv_s[tk] : 1.f;
                 const float g = v[i] * scale, u = gather[i * 64 + rho] * scale;
-                ((bf16*)y_)[(size_t)tk * out_cols + f] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
+                ((bf16*)y_)[(size_t)tk * out_cols + f] = __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
               }
             }
           }

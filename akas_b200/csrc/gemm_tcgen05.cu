@@ -150,7 +150,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           float u[16];
           tmem_load16(taddr + BN / 2 + c, u);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * u[i];
+          for (int i = 0; i < 16; ++i) v[i] = __fdividef(v[i], 1.f + __expf(-v[i])) * u[i];  // the fast division: IEEE division cost more than the tile's loads
         }
         const int col = n0 + c;
         if (row < M && col < out_cols) {

@@ -28,7 +28,7 @@ CSRC = Path(__file__).resolve().parent.parent / "csrc"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 LINK_FLAGS: Dict[str, List[str]] = {"gemm_bf16": ["-lcublasLt"]}
-SOURCES = ("elementwise", "conv", "rope", "attention", "attention_prefill", "attention_prefill_tc", "attention_decode", "sgemm", "gemm_bf16", "gemm_tcgen05", "gemm_pair", "gemm_stream", "skinny_gemm", "decode_chain", "sampling")
+SOURCES = ("elementwise", "conv", "rope", "attention", "attention_prefill", "attention_prefill_tc", "attention_decode", "sgemm", "gemm_bf16", "gemm_tcgen05", "gemm_pair", "gemm_rows", "gemm_stream", "skinny_gemm", "decode_chain", "sampling")
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -82,6 +82,11 @@ _SIGNATURES = {
         "akas_gemm_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "akas_gemm_pair_status": [],
     },
+    "gemm_rows": {
+        "akas_gemm_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_gemm_rows_takes": [c_int, c_int, c_int, c_int],
+        "akas_gemm_rows_status": [],
+    },
     "gemm_stream": {
         "akas_stream_gemm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_int, c_void_p],
@@ -125,7 +130,7 @@ _functions = {}
 def libraries_for(dtype: torch.dtype) -> list:
     """The kernel files a model of this compute dtype needs."""
     names = ["elementwise", "conv", "rope", "attention", "sampling"]
-    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "gemm_pair", "gemm_stream", "skinny_gemm", "decode_chain", "attention_prefill", "attention_prefill_tc", "attention_decode"]
+    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "gemm_pair", "gemm_rows", "gemm_stream", "skinny_gemm", "decode_chain", "attention_prefill", "attention_prefill_tc", "attention_decode"]
     return names
 
 
@@ -513,31 +518,78 @@ def block_product(x, w, swiglu_out: bool = False, out_dtype=None, residual=None)
     return out
 
 
-@_flushes
-def paired_product(x, w, swiglu_out: bool = False, out_dtype=None, residual=None):
-    """x [N, K] times w [O, K] transposed on pairs of SMs. bfloat16 out by default; float32 out with ``out_dtype``;
-    added into ``residual`` (float32 [N, O]) when that is given; with ``swiglu_out`` w is the stacked [2F, K] gate and
-    up matrices and the result is swiglu of the product, bfloat16 [N, F]."""
+def _tma_product(name, x, w, swiglu_out, out_dtype, residual):
+    """The checks and the output of a product whose read-out TMA writes: (out, epilogue code)."""
     n, k = x.shape
     o = w.shape[0]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k or k % 8:
-        raise ValueError("paired_product takes bfloat16 [N, K] and [O, K] with K a multiple of 8")
+        raise ValueError(f"{name} takes bfloat16 [N, K] and [O, K] with K a multiple of 8")
     if swiglu_out:
         if o % 16:
-            raise ValueError("paired_product: the stacked gate and up matrices need a height that is a multiple of 16")
-        out, epilogue = torch.empty((n, o // 2), dtype=torch.bfloat16, device=x.device), 2
-    elif residual is not None:
+            raise ValueError(f"{name}: the stacked gate and up matrices need a height that is a multiple of 16")
+        return torch.empty((n, o // 2), dtype=torch.bfloat16, device=x.device), 2
+    if residual is not None:
         if residual.dtype != torch.float32 or residual.shape != (n, o) or not residual.is_contiguous() or o % 4:
-            raise ValueError("paired_product: residual must be contiguous float32 [N, O] with O a multiple of 4")
-        out, epilogue = residual, 1
-    elif out_dtype == torch.float32:
+            raise ValueError(f"{name}: residual must be contiguous float32 [N, O] with O a multiple of 4")
+        return residual, 1
+    if out_dtype == torch.float32:
         if o % 4:
-            raise ValueError("paired_product: a float32 result needs a width that is a multiple of 4")
-        out, epilogue = torch.empty((n, o), dtype=torch.float32, device=x.device), 3
-    else:
-        if o % 8:
-            raise ValueError("paired_product: a bfloat16 result needs a width that is a multiple of 8")
-        out, epilogue = torch.empty((n, o), dtype=torch.bfloat16, device=x.device), 0
+            raise ValueError(f"{name}: a float32 result needs a width that is a multiple of 4")
+        return torch.empty((n, o), dtype=torch.float32, device=x.device), 3
+    if o % 8:
+        raise ValueError(f"{name}: a bfloat16 result needs a width that is a multiple of 8")
+    return torch.empty((n, o), dtype=torch.bfloat16, device=x.device), 0
+
+
+# Products of 17 to 128 tokens (decode steps of many requests, short portions) stream the weights through every SM
+# (gemm_rows.cu); AKAS_B200_ROWS_PRODUCTS=0 gives them to the kernel for pairs of SMs like longer portions.
+_ROWS_MAX = 128
+rows_products = os.environ.get("AKAS_B200_ROWS_PRODUCTS", "1") != "0"
+_rows_answers = {}
+
+
+def _rows_takes(n: int, o: int, k: int, epilogue: int) -> bool:
+    if not rows_products or n > _ROWS_MAX:
+        return False
+    key = (torch.cuda.current_device(), n, o, k, epilogue)
+    answer = _rows_answers.get(key)
+    if answer is None:
+        answer = _rows_answers[key] = bool(_fn("gemm_rows", "akas_gemm_rows_takes")(n, o, k, epilogue))
+    return answer
+
+
+@_flushes
+def rows_product(x, w, swiglu_out: bool = False, out_dtype=None, residual=None):
+    """x [N, K] times w [O, K] transposed for at most 128 tokens: the weights streamed once through all SMs, the
+    read-outs of ``paired_product``."""
+    n, k = x.shape
+    o = w.shape[0]
+    out, epilogue = _tma_product("rows_product", x, w, swiglu_out, out_dtype, residual)
+    if not _rows_takes(n, o, k, epilogue):
+        raise ValueError(f"rows_product does not take [{n}x{k}] x [{o}x{k}]^T (at most {_ROWS_MAX} tokens)")
+    _check(_fn("gemm_rows", "akas_gemm_rows")(_ptr(_dense(x, "x")), _ptr(_dense(w, "w")), _ptr(out), n, o, k, epilogue,
+                                             _stream()), f"streamed tcgen05 product [{n}x{k}] x [{o}x{k}]^T")
+    return out
+
+
+def gemm_rows_status() -> int:
+    """0 unless a bounded wait inside the kernel of ``rows_product`` has run out on this device. Synchronises."""
+    return int(_fn("gemm_rows", "akas_gemm_rows_status")())
+
+
+@_flushes
+def paired_product(x, w, swiglu_out: bool = False, out_dtype=None, residual=None, few_rows=True):
+    """x [N, K] times w [O, K] transposed on pairs of SMs. bfloat16 out by default; float32 out with ``out_dtype``;
+    added into ``residual`` (float32 [N, O]) when that is given; with ``swiglu_out`` w is the stacked [2F, K] gate and
+    up matrices and the result is swiglu of the product, bfloat16 [N, F]. Up to 128 tokens go to ``rows_product``
+    unless ``few_rows`` is False."""
+    n, k = x.shape
+    o = w.shape[0]
+    out, epilogue = _tma_product("paired_product", x, w, swiglu_out, out_dtype, residual)
+    if few_rows and _rows_takes(n, o, k, epilogue):
+        _check(_fn("gemm_rows", "akas_gemm_rows")(_ptr(_dense(x, "x")), _ptr(_dense(w, "w")), _ptr(out), n, o, k, epilogue,
+                                                 _stream()), f"streamed tcgen05 product [{n}x{k}] x [{o}x{k}]^T")
+        return out
     _check(_fn("gemm_pair", "akas_gemm_pair")(_ptr(_dense(x, "x")), _ptr(_dense(w, "w")), _ptr(out), n, o, k, epilogue,
                                              _stream()), f"paired tcgen05 product [{n}x{k}] x [{o}x{k}]^T")
     return out

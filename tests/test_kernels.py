@@ -224,6 +224,31 @@ def test_products_on_pairs_of_sms(ops, m, k, o):
     assert cuda.gemm_pair_status() == 0
 
 
+@pytest.mark.parametrize("m,k,o", [(17, 64, 48), (64, 2048, 6144), (33, 264, 520), (128, 8192, 2048), (100, 200, 2056),
+                                   (64, 2048, 65536), (20, 1024, 40), (96, 704, 1160), (48, 128, 40000)])
+def test_products_of_few_rows_stream_the_weights(ops, m, k, o):
+    """The one-block tcgen05 kernel for 17 to 128 tokens (tiles as wide as gives every SM one; token rows past the batch
+    are never loaded), all four read-outs, at inner sizes that are and are not multiples of 64 (one copy per stage, a
+    copy per step), widths that leave ragged tiles, more tiles than SMs, and one narrow tile."""
+    cuda, ref = ops
+    x, w = _rand((m, k), torch.bfloat16, 5), _rand((o, k), torch.bfloat16, 6, 0.05)
+    want = x.double() @ w.double().T
+    _close(cuda.rows_product(x, w), want, torch.bfloat16, "bf16 out")
+    got = cuda.rows_product(x, w, out_dtype=torch.float32)
+    assert got.dtype == torch.float32
+    _close(got, want, torch.bfloat16, "f32 out")
+    h = _rand((m, o), torch.float32, 7, 2.0)
+    h0 = h.clone()
+    assert cuda.rows_product(x, w, residual=h) is h
+    _close(h, h0.double() + want, torch.bfloat16, "added into the residual stream")
+    if o <= 20000:
+        w2 = _rand((2 * o, k), torch.bfloat16, 8, 0.05)
+        _close(cuda.rows_product(x, w2, swiglu_out=True), ref.linear_swiglu(x, w2), torch.bfloat16, "swiglu")
+    assert cuda.gemm_rows_status() == 0
+    with pytest.raises(ValueError, match="at most 128"):
+        cuda.rows_product(_rand((129, k), torch.bfloat16, 9), w)
+
+
 @pytest.mark.parametrize("m,c,f,v,taps", [(1, 128, 320, 500, 3), (8, 256, 9216, 1000, 3), (5, 192, 448, 777, 4),
                                          (13, 128, 6912, 300, 2), (16, 2048, 8192, 4096, 3), (3, 64, 64, 40, 5)])
 def test_decode_chain_runs_a_layer_as_one_launch(ops, m, c, f, v, taps, monkeypatch):
