@@ -290,9 +290,14 @@ decode_chain_kernel(const __grid_constant__ Program prog) {
         for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int j = 0; j < NT; ++j) { acc[h][j][0] = acc[h][j][1] = acc[h][j][2] = acc[h][j][3] = 0.f; }
+        // Chunk number `at` of the whole program goes to pair at % PAIRS and lies in stage at % STAGES; STAGES is a
+        // multiple of PAIRS, so a stage is always the same pair's and the pair sees every filling of it in turn. (A
+        // pair that skipped stages could ask for a stage's second filling before the first had landed, and the
+        // barrier would answer that the phase of that parity was complete: the one before the first.)
+        static_assert(STAGES % PAIRS == 0, "a stage of the ring belongs to one pair of warps");
         const int pair = warp / WPS, half = warp % WPS;
         for (int run = 0; run < sh.count * sh.runs; ++run, n += sh.chunks) {
-          for (int c = pair; c < sh.chunks; c += PAIRS) {
+          for (int c = (pair + PAIRS - (int)(n % PAIRS)) % PAIRS; c < sh.chunks; c += PAIRS) {
             const unsigned at = n + (unsigned)c, s = at % STAGES;
             wait_for(&full_bar[s], (at / STAGES) & 1, 1);
             // a stage: [group of 64 k][row][128 bytes]; row g's 16-byte unit u lies at unit u XOR g (the 128-byte swizzle)
@@ -541,7 +546,7 @@ constexpr int smem_bytes() {
   return 1024 + STAGES * STAGE_BYTES + 2 * CONSUMERS * NT * 128 * (int)sizeof(float) + NT * 8 * XSTRIDE * (int)sizeof(bf16) +
          (NT == 1 ? NW_MAX * (int)sizeof(float) : 0);
 }
-constexpr int STAGES_1 = 9, STAGES_2 = 5;
+constexpr int STAGES_1 = 8, STAGES_2 = 4;  // multiples of the number of warp pairs
 static_assert(smem_bytes<1, STAGES_1>() <= 226 * 1024 && smem_bytes<2, STAGES_2>() <= 226 * 1024, "the block fits an SM");
 
 template <int NT, int STAGES>

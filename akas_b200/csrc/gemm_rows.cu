@@ -131,7 +131,7 @@ struct Shape {
 };
 
 template <int EPI>
-__global__ void __launch_bounds__(THREADS, 2)  // two blocks to an SM: this kernel's and its successor's
+__global__ void __launch_bounds__(THREADS, 2)  // registers for two blocks to an SM, should their shared memory allow it
 gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_y, const Shape sh) {
   constexpr bool SWIGLU = EPI == EPI_SWIGLU;
@@ -455,10 +455,11 @@ bool plan(Shape* sh, int M, int O, int K, int epilogue, int sms, int budget) {
   sh->wide = K % 64 == 0 ? 1 : 0;
   const int k_blocks = (K + BK - 1) / BK;
   const int step_bytes = (sh->RT + halves * tile_n) * 128;
-  // Half of an SM's shared memory and tensor memory, so that a block of the next kernel on the stream can set itself
-  // up and fetch its first weights beside a block of this one that is still summing or reading out; all of it where
-  // half leaves fewer than three stages (AKAS_B200_ROWS_SMEM_KB overrides the share).
-  const int share = env_int("AKAS_B200_ROWS_SMEM_KB", 113) * 1024;
+  // All of an SM's shared memory by default. AKAS_B200_ROWS_SMEM_KB gives a block less (and at most half of tensor
+  // memory), so that a block of the next kernel on the stream can set itself up and fetch its first weights beside a
+  // block of this one that is still summing or reading out: measured on a B200 at 64 tokens that loses more (thinner
+  // rings, two blocks sharing an SM's 64 bytes a cycle from the L2) than the overlap wins, 1.72 ms a step against 1.40.
+  const int share = env_int("AKAS_B200_ROWS_SMEM_KB", 227) * 1024;
   int g = 1, stages = 0, tmem_cap = 256;
   for (int attempt = 0; attempt < 2; ++attempt) {
     const int have = attempt == 0 && share < budget ? share : budget;
