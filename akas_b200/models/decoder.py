@@ -35,6 +35,12 @@ class Decoder:
                 owner = self.schedule[entry.cache] if 0 <= entry.cache < i else None
                 if owner is None or owner.cache is not None:
                     raise ValueError(f"schedule entry {i} reads cache {entry.cache}, which is no earlier owning entry")
+                for which in (owner.layer, entry.layer):
+                    mixer = self.blocks[which].mixer
+                    if not mixer.shares_cache:
+                        raise ValueError(f"schedule entry {i} reads the cache of entry {entry.cache}, but the mixer of layer "
+                                         f"{which} ({type(mixer).__name__}) keeps a summary of the past that has moved on "
+                                         "when a reader runs: give the entry a cache of its own")
         self.embedding = None
         self.head = None
 

@@ -19,6 +19,7 @@ from .base import Mixer, PagedKVSpec, Param, build_part, project, register_mixer
 class Attention(Mixer):
     takes_normed = True
     chain_safe = True
+    shares_cache = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)

@@ -160,6 +160,13 @@ class Part:
 
 
 class Mixer(Part):
+    # True: another entry of the run order may read this mixer's cache (``write=False``) after the owner has run in
+    # the same step, and sees the same past however the tokens were cut into steps: attention does, since every
+    # earlier token's keys and values lie in the cache by then. A mixer whose cache is a summary of the past leaves
+    # this False: once the owner has run, the summary has moved past the step's tokens, so a reader would see another
+    # past in a step of one token than in a step of many. The decoder refuses a run order that shares such a cache.
+    shares_cache = False
+
     def cache(self):
         return None
 

@@ -17,7 +17,7 @@ import traces
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}  # of the largest logit; bfloat16 measures 1.3e-2 at most
 
 
 def _engine(folder, dtype, page, **kw):
@@ -242,3 +242,106 @@ def test_host_sampling_agrees_with_the_device(tmp_path):
         with pytest.raises(ValueError, match="greedy"):
             engine.generate(prompts[0], max_tokens=2, temperature=0.5)
     assert host == device
+
+
+def _every_token_is_a_plain_argmax(cfg, w, prompt, tokens, slack):
+    """Whether every generated token is the plain model's greedy choice given the tokens before it, or lies within
+    ``slack`` (a share of the largest logit) of it: what greedy decoding in reduced precision can be held to, since
+    two logits closer than the rounding may swap. Returns (ok, first bad place, share of exact choices)."""
+    if not len(tokens):  # cancelled before its first token
+        return True, None, 1.0
+    logits = plain.forward(cfg, w, list(prompt) + list(tokens)).numpy()[len(prompt) - 1:-1]
+    best = logits.max(axis=-1)
+    chosen = logits[np.arange(len(tokens)), tokens]
+    within = chosen >= best - slack * np.abs(logits).max()
+    exact = float((logits.argmax(axis=-1) == np.asarray(tokens)).mean()) if len(tokens) else 1.0
+    bad = np.nonzero(~within)[0]
+    return not len(bad), (int(bad[0]) if len(bad) else None), exact
+
+
+def test_greedy_tokens_in_bfloat16_agree_with_the_float32_engine(tmp_path):
+    """One folder of bfloat16 weights (the 32-bit path reads them exactly), two engines, 64 greedy tokens for each of
+    five prompts. The float32 engine generates the plain model's tokens. Given those tokens as its past, the bfloat16
+    engine would pick the same next token at 95 of 100 places or more (measured: 0.98; with random weights two logits
+    lie closer than the rounding now and then, and from there on two free-running continuations part ways, so the
+    shared prefix is only printed); and every token of its own free-running continuation is a greedy choice of the
+    plain model to within the rounding."""
+    from akas_b200 import StepEntry
+
+    folder = tiny.make_folder(tiny.TINY_C, seed=31, dtype="bfloat16", std=0.3, folder=tmp_path / "m")
+    cfg, w = plain.load_folder(folder)
+    prompts = tiny.prompts(cfg["vocab_size"], [40, 3, 129, 70, 11], seed=12)
+    with _engine(folder, "float32", tiny.PAGE["c"]) as engine:
+        want = [r["generated_tokens"] for r in engine.generate(prompts, max_tokens=64)]
+    with _engine(folder, "bfloat16", tiny.PAGE["c"]) as engine:
+        got = [r["generated_tokens"] for r in engine.generate(prompts, max_tokens=64)]
+        forced = []
+        for i, (prompt, tokens) in enumerate(zip(prompts, want)):  # the float32 engine's tokens as the past
+            engine.runner.step([StepEntry(("forced", i), prompt[:-1], ())])
+            picks = [int(engine.runner.step([StepEntry(("forced", i), (t,), (0,))]).argmax()) for t in [prompt[-1]] + tokens[:-1]]
+            engine.runner.release(("forced", i))
+            forced.append(picks)
+    shared = agree = 0
+    for prompt, a, b, f in zip(prompts, want, got, forced):
+        assert a == plain.greedy(cfg, w, prompt, 64)
+        shared += next((i for i, (x, y) in enumerate(zip(a, b)) if x != y), 64)
+        agree += sum(x == y for x, y in zip(a, f))
+        ok, bad, exact = _every_token_is_a_plain_argmax(cfg, w, prompt, b, 2 * TOL["bfloat16"])
+        assert ok, f"token {bad} of the bfloat16 continuation is not a greedy choice (exact choices: {exact:.3f})"
+        assert exact >= 0.95
+    total = 64 * len(prompts)
+    print(f"bfloat16 picks the float32 engine's token at {agree} of {total} places; free-running, the continuations "
+          f"share {shared} leading tokens")
+    assert agree >= 0.95 * total
+
+
+def test_preemption_and_arrivals_on_the_device_in_bfloat16(tmp_path):
+    """Configuration c in bfloat16 with captured graphs and steps launched ahead. First a pool too small for three
+    growing requests (the youngest is preempted and recomputed); then requests that arrive at random turns, some
+    cancelled on the way, into the same small pool. Every token that was generated is a greedy choice of the plain
+    model to within the rounding, nothing is held at the end, and the cache's books balance after every turn."""
+    import random
+
+    folder = tiny.make_folder(tiny.TINY_C, seed=32, dtype="bfloat16", std=0.3, folder=tmp_path / "m")
+    cfg, w = plain.load_folder(folder)
+    page = tiny.PAGE["c"]
+    options = dict(max_tokens=6 * page, context=4 * page, max_requests=4, run_ahead=True, cuda_graphs=True,
+                   prefill_chunk=48, prefill_requests=2)
+    prompts = tiny.prompts(cfg["vocab_size"], [70, 70, 70], seed=13)
+    with _engine(folder, "bfloat16", page, **options) as engine:
+        results = engine.generate(prompts, max_tokens=100)
+        assert engine.stats["preemptions"] > 0 and engine.stats["steps_ahead"] > 0
+        for prompt, result in zip(prompts, results):
+            assert len(result["generated_tokens"]) == 100
+            ok, bad, exact = _every_token_is_a_plain_argmax(cfg, w, prompt, result["generated_tokens"], 2 * TOL["bfloat16"])
+            assert ok and exact >= 0.95, (bad, exact)
+        assert not engine.runner.cache.live()
+
+        rng = random.Random(5)
+        waiting = [(tiny.prompts(cfg["vocab_size"], [rng.randint(1, 90)], seed=40 + i)[0], rng.randint(1, 40)) for i in range(12)]
+        submitted, cancelled = [], set()
+        for turn in range(20000):
+            while waiting and rng.random() < 0.3:
+                prompt, limit = waiting.pop()
+                submitted.append(engine.submit(prompt, max_tokens=limit))
+            if submitted and rng.random() < 0.03:
+                victim = rng.choice(submitted)
+                if not victim.finished:
+                    engine.cancel(victim)
+                    cancelled.add(victim.id)
+            busy = engine.step()
+            engine.runner.cache.check()
+            if not busy and not waiting:
+                break
+        else:
+            raise AssertionError("the engine did not finish")
+        assert len(submitted) == 12 and engine.stats["preemptions"] > 0
+        for r in submitted:
+            if r.finish_reason == "cancelled":
+                assert r.id in cancelled
+            else:
+                assert r.finish_reason == "length" and len(r.output) == r.limit
+            ok, bad, exact = _every_token_is_a_plain_argmax(cfg, w, r.prompt, r.output, 2 * TOL["bfloat16"])
+            assert ok, (r.id, bad, exact)
+        assert not engine.runner.cache.live()
+        assert engine.runner.cache.min_free_pages() >= 0 and engine.runner.cache.free_pages() == engine.runner.cache.num_pages

@@ -309,11 +309,13 @@ class ToyConfig:
                     layer(2, AttentionSpec(c, 2, 2, 16, **attn)),
                     layer(3, AttentionSpec(c, 2, 1, 16, qk_norm=None, position=PartSpec("decay_for_tests", {"rate": 0.97})),
                           PartSpec("routed_for_tests", {"width": c, "hidden": 40, "experts": 3})),
-                    layer(4, PartSpec("prefix_mean_for_tests", {"width": c}))),
+                    layer(4, PartSpec("prefix_mean_for_tests", {"width": c})),
+                    layer(5, ShortConvSpec(c, 3, bias=True))),
             final_norm=norm, embedding_name="embed", final_norm_name="final_norm", head_name=None,
-            # layer 1 runs twice, each time with a cache of its own; the last entry reads entry 2's keys and values
+            # layer 1 runs twice, each time with a cache of its own; the fifth entry reads entry 2's keys and values; the
+            # convolution layer runs twice in a row, each time with a state of its own
             schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(1), ScheduleEntry(2, cache=2),
-                      ScheduleEntry(3), ScheduleEntry(4)),
+                      ScheduleEntry(3), ScheduleEntry(4), ScheduleEntry(5), ScheduleEntry(5)),
             embedding_multiplier=1.7, logit_scale=0.4, logit_softcap=2.5,
         )
 
@@ -349,7 +351,8 @@ def _toy_plain(cfg, w, tokens):
         out = torch.einsum("hts,shd->thd", torch.softmax(score, -1), vv).reshape(T, heads * d)
         return out @ w[p + "out_proj.weight"].T, (k, v)
 
-    for n, (i, shared) in enumerate(((0, None), (1, None), (2, None), (1, None), (2, 2), (3, None), (4, None))):
+    for n, (i, shared) in enumerate(((0, None), (1, None), (2, None), (1, None), (2, 2), (3, None), (4, None), (5, None),
+                                     (5, None))):
         p = f"layers.{i}."
         x = plain.rms_norm(h, w[p + "norm1"], 1e-5)
         if i == 0:
@@ -364,6 +367,10 @@ def _toy_plain(cfg, w, tokens):
         elif i == 4:
             z = x @ w[p + "mixer.proj.weight"].T
             mixed = torch.cumsum(z, 0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+        elif i == 5:
+            m = p + "mixer."
+            mixed = plain.short_conv(x, w[m + "in_proj.weight"], w[m + "conv.weight"].reshape(c, 3), w[m + "conv.bias"],
+                                     w[m + "out_proj.weight"], w[m + "in_proj.bias"], w[m + "out_proj.bias"])
         else:
             mixed, kept[n] = attn(i, x, cfg.window if i == 1 else None, 2, 1 if i == 1 else 2,
                                   kept[shared] if shared is not None else None)
@@ -408,7 +415,9 @@ def test_toy_architecture_is_registered_built_and_stepped(device, tmp_path):
 
     r = runner(48)
     assert len(r.cache.groups) == 3 and [type(v).__name__ for v in r.cache.views] == [
-        "StateCache", "PagedCache", "PagedCache", "PagedCache", "NoneType", "PagedCache", "PagedCache"]
+        "StateCache", "PagedCache", "PagedCache", "PagedCache", "NoneType", "PagedCache", "PagedCache", "StateCache",
+        "StateCache"]
+    assert r.cache.views[7].state.data_ptr() != r.cache.views[8].state.data_ptr()  # the layer named twice: two states
     latent = r.cache.views[6]
     assert latent.page_size == 2 and latent.latent.shape == (24, 2, cfg.width) and r.cache.table_widths == [12, 12, 24]
     steps, peak = traces.mixed(reqs, {rid: max(1, len(t) - 6) for rid, t in reqs.items()}, seed=2, live=3, page=page)
@@ -420,6 +429,14 @@ def test_toy_architecture_is_registered_built_and_stepped(device, tmp_path):
             bad = traces.first_bad(got[rid], want[rid], 2e-5)
             assert bad is None, f"{name}: {rid} first differs at {bad}: {traces.worst(got[rid], want[rid])}"
         assert r.cache.min_free_pages() == r.cache.num_pages
+    # a summary of the past cannot be read by a second entry: after the owner has run it has moved past the step's tokens
+    from dataclasses import replace
+    from akas_b200.models.decoder import Decoder
+
+    spec = cfg.model_spec()
+    shared = replace(spec, schedule=spec.schedule[:8] + (ScheduleEntry(5, cache=7),))
+    with pytest.raises(ValueError, match="cache of its own"):
+        Decoder(shared, r.model.rt)
     # the windowed group gave pages back while the request was still running
     r = runner(48)
     r.step([StepEntry("w", reqs["t0"], ())])

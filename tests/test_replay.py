@@ -14,8 +14,14 @@ import plain_lfm2 as plain
 import tiny
 import traces
 
-# largest |difference| over largest |reference logit|, per dtype
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+# largest |difference| over largest |reference logit|, per dtype. bfloat16: the bound of a single position; whole
+# requests are held to BF16 below.
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+# bfloat16 against the float64 plain model, per tiny configuration: (largest |difference| over largest |reference|,
+# relative L2 error of a request's logits, share of positions whose argmax is the plain model's). The first is 1.5 times
+# what the kernels measure on a B200 (a and b 1.00e-2, c 1.27e-2, in every way of cutting); the L2 bound is the same for
+# all (measured 7.7e-3, 7.2e-3, 9.3e-3); the argmax agreement is measured at 0.988 to 0.993.
+BF16 = {"a": (1.5e-2, 1e-2, 0.97), "b": (1.5e-2, 1e-2, 0.97), "c": (1.9e-2, 1e-2, 0.97)}
 LENGTHS = {"a": [1, 40, 33, 70, 17, 100, 64, 129], "b": [70, 1, 5, 96, 48, 130, 9], "c": [300, 65, 1, 129, 260, 40]}
 
 
@@ -36,11 +42,18 @@ def _setup(key, dtype, tmp_path):
     return folder, reqs, want
 
 
-def _check(got, want, dtype, what):
+def _check(got, want, dtype, what, key="c"):
+    most, l2_most, agree_least = (TOL[dtype], TOL[dtype], 1.0) if dtype == "float32" else BF16[key]
+    same = total = 0
     for rid in want:
         err, l2 = traces.worst(got[rid], want[rid])
-        bad = traces.first_bad(got[rid], want[rid], TOL[dtype])
+        bad = traces.first_bad(got[rid], want[rid], most)
         assert bad is None, f"{what}: request {rid} first differs at position {bad} (max {err:.3g}, L2 {l2:.3g})"
+        assert l2 <= l2_most, f"{what}: request {rid} has relative L2 error {l2:.3g} > {l2_most}"
+        same += int((np.argmax(got[rid], -1) == np.argmax(want[rid], -1)).sum())
+        total += len(want[rid])
+    if dtype != "float32":  # in float32 an argmax may differ where two logits are equal to rounding
+        assert same >= agree_least * total, f"{what}: argmax agrees at {same} of {total} positions"
 
 
 def _run_modes(key, dtype, device, ops, tmp_path, modes):
@@ -58,7 +71,7 @@ def _run_modes(key, dtype, device, ops, tmp_path, modes):
         got = traces.replay(runner, steps)
         assert not runner.cache.live()
         assert runner.cache.min_free_pages() == runner.cache.num_pages
-        _check(got, want, dtype, f"{key}/{dtype}/{mode}")
+        _check(got, want, dtype, f"{key}/{dtype}/{mode}", key)
 
 
 MODES = ["whole", "tail_decoded", "portions", "mixed"]
@@ -69,6 +82,61 @@ def test_replay_host_logic_on_cpu(key, tmp_path):
     from akas_b200.ops import reference
 
     _run_modes(key, "float32", "cpu", reference, tmp_path, MODES)
+
+
+def test_a_step_that_cannot_run_leaves_no_request_behind(tmp_path):
+    """Every entry is checked before anybody is admitted; when the pages run out while the step's requests are being
+    given theirs, the requests that this very step brought in are released again, and the others keep what they had."""
+    from akas_b200.cache.manager import OutOfPages
+    from akas_b200.engine.batch import StepEntry
+    from akas_b200.ops import reference
+
+    folder = tiny.make_folder(tiny.CONFIGS["a"], seed=11, dtype="float32", folder=tmp_path / "a")
+    page = tiny.PAGE["a"]
+    runner = _runner(folder, "float32", "cpu", page, 3 * page, reference, context=3 * page)
+    free = runner.cache.free_pages()
+    with pytest.raises(ValueError, match="wanted places"):
+        runner.step([StepEntry("a", [1, 2, 3], (0,)), StepEntry("b", [4, 5], (7,))])
+    assert not runner.cache.live() and runner.cache.free_pages() == free
+    with pytest.raises(OutOfPages):  # "a" takes two pages, "b" would need two more
+        runner.step([StepEntry("a", list(range(2 * page)), ()), StepEntry("b", list(range(page + 1)), ())])
+    assert not runner.cache.live() and runner.cache.free_pages() == free
+    runner.step([StepEntry("c", [1, 2], ())])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry("c", [3], ()), StepEntry("d", list(range(3 * page)), ())])
+    assert runner.cache.live() == ["c"] and runner.cache.length("c") == 2
+    logits = runner.step([StepEntry("c", [3], (0,))])  # and "c" goes on where it was
+    want = plain.forward(*plain.load_folder(folder), [1, 2, 3]).numpy()[-1:]
+    assert traces.first_bad(logits.numpy(), want, TOL["float32"]) is None
+    runner.release("c")
+    assert runner.cache.free_pages() == free
+
+
+@pytest.mark.gpu
+def test_logits_of_a_captured_step_last_until_the_next_step(tmp_path):
+    """A step that replays a captured graph returns the graph's own output buffer: the next step of that shape
+    overwrites it. Whoever wants the logits longer clones them; without graphs every step returns a tensor of its own."""
+    from akas_b200.config import EngineConfig
+    from akas_b200.engine.batch import StepEntry
+    from akas_b200.engine.runner import ModelRunner
+
+    folder = tiny.make_folder(tiny.CONFIGS["a"], seed=11, dtype="float32", folder=tmp_path / "a")
+    cfg, w = plain.load_folder(folder)
+    page = tiny.PAGE["a"]
+    want = plain.forward(cfg, w, [5, 6, 7, 8, 9]).numpy()
+    for graphs in (True, False):
+        runner = ModelRunner(folder, EngineConfig(dtype="float32", device="cuda:0", page_size=page, max_tokens=4 * page,
+                                                  max_requests=2, context=4 * page, cuda_graphs=graphs))
+        runner.step([StepEntry("r", [5, 6, 7], ())])
+        first = runner.step([StepEntry("r", [8], (0,))])
+        kept = first.clone()
+        second = runner.step([StepEntry("r", [9], (0,))])
+        assert traces.first_bad(kept.cpu().numpy(), want[3:4], TOL["float32"]) is None
+        assert traces.first_bad(second.cpu().numpy(), want[4:5], TOL["float32"]) is None
+        if graphs:
+            assert first.data_ptr() == second.data_ptr() and torch.equal(first, second) and not torch.equal(first, kept)
+        else:
+            assert first.data_ptr() != second.data_ptr() and torch.equal(first, kept)
 
 
 @pytest.mark.gpu
@@ -113,7 +181,7 @@ def test_captured_steps_agree_with_the_plain_model(key, dtype, tmp_path):
                                                 max_requests=4, context=longest, cuda_graphs=True))
 
     r = runner(longest)
-    _check(traces.replay(r, traces.tail_decoded(reqs)), want, dtype, "tail decoded, captured")
+    _check(traces.replay(r, traces.tail_decoded(reqs)), want, dtype, "tail decoded, captured", key)
     assert r._graphs and all(g.graph is not None for g in r._graphs.values())
 
     # the two longest requests side by side in portions of ten tokens, logits wanted at the last two places of each
@@ -180,10 +248,10 @@ def test_decode_steps_as_chains_agree_with_the_plain_model(key, graphs, tmp_path
     runner = ModelRunner(folder, EngineConfig(dtype="bfloat16", device="cuda:0", page_size=page, max_tokens=4 * longest,
                                               max_requests=4, context=longest, cuda_graphs=graphs))
     before = cuda.launch_count
-    _check(traces.replay(runner, traces.tail_decoded(reqs)), want, "bfloat16", "tail decoded, chained")
+    _check(traces.replay(runner, traces.tail_decoded(reqs)), want, "bfloat16", "tail decoded, chained", key)
     prompt_lens = {rid: max(1, len(t) - 9) for rid, t in reqs.items()}
     steps, _ = traces.mixed(reqs, prompt_lens, seed=3, live=4, page=page)
-    _check(traces.replay(runner, steps), want, "bfloat16", "mixed, chained")
+    _check(traces.replay(runner, steps), want, "bfloat16", "mixed, chained", key)
     assert cuda.chain_status() == 0 and cuda.launch_count > before
 
 
