@@ -455,6 +455,57 @@ def bench_ops(shape: str = "1.2b", prompt: int = 2048, batch: int = 8, steps: in
                 decode_per_step=round_rows(decode))
 
 
+def bench_ops_mixed(shape: str = "350m", portion: int = 512, decoding: int = 255, shortest: int = 128,
+                    longest: int = 2176, steps: int = 4) -> dict:
+    """Where the device time of a MIXED step goes, by operation: a prompt portion of ``portion`` tokens (of a request
+    that already holds as many) beside ``decoding`` requests with contexts spread evenly from ``shortest`` to
+    ``longest``, one decoded token each. Measured for both ways of running the decoded tokens' attention: "split"
+    (they go to the split-key decode kernel, the portion to the prompt kernel) and "tiles" (every token is a query
+    tile of the prompt kernel). CUDA events around every call of the step function's operations; no captured graphs."""
+    import tempfile
+
+    from .config import EngineConfig, config_from_dict
+    from .ops import cuda as cuda_ops
+    from .ops.timed import TimedOps
+    from .weights import write_random_model
+
+    cuda_ops.require(cuda_ops.libraries_for(torch.bfloat16))
+    timed = TimedOps(cuda_ops)
+    lengths = [shortest + (longest - shortest) * j // max(decoding - 1, 1) for j in range(decoding)]
+    context = max(longest, 2 * portion) + steps * (portion + 1) + 64
+    pool = sum(-(-(n + steps + 64) // 64) * 64 for n in lengths) + context + 64
+    config = EngineConfig(dtype="bfloat16", max_requests=decoding + 1, context=context, max_tokens=pool, cuda_graphs=False)
+    with tempfile.TemporaryDirectory(prefix="akas-bench-") as folder:
+        write_random_model(folder, config_from_dict(shape_config(shape)), seed=0, dtype="bfloat16")
+        runner = ModelRunner(folder, config, ops=timed)
+    rng = np.random.default_rng(7)
+    ids = [f"d{j}" for j in range(decoding)]
+    fill_requests(runner, [rng.integers(0, runner.vocab_size, n).tolist() for n in lengths], config.prefill_chunk, ids)
+    runner.step([StepEntry("p", rng.integers(0, runner.vocab_size, portion).tolist(), ())])
+    report = dict(bench="ops-mixed", shape=shape, portion=portion, decoding=decoding, contexts=[shortest, longest])
+    before = cuda_ops.mixed_attention
+    try:
+        for policy in ("split", "tiles"):
+            cuda_ops.mixed_attention = policy
+            for step in range(steps + 1):
+                if step == 1:
+                    timed.clear()  # the first step of a policy pays for set-up
+                entries = [StepEntry(rid, (int(rng.integers(0, runner.vocab_size)),), (0,)) for rid in ids]
+                entries.append(StepEntry("p", rng.integers(0, runner.vocab_size, portion).tolist(), ()))
+                runner.step(entries)
+            rows = timed.table()
+            total = sum(r["ms"] for r in rows) / steps
+            report[policy] = dict(ms_per_step=round(total, 4), tokens_per_step=decoding + portion,
+                                  ops=[dict(op=r["op"], calls=r["calls"] // steps, ms=round(r["ms"] / steps, 4),
+                                            share=round(r["share"], 3)) for r in rows])
+            for rid in ["p"]:  # the portioned request starts over, so that both policies see the same lengths
+                runner.release(rid)
+            runner.step([StepEntry("p", rng.integers(0, runner.vocab_size, portion).tolist(), ())])
+    finally:
+        cuda_ops.mixed_attention = before
+    return report
+
+
 def _main():
     import argparse
     import json
@@ -490,7 +541,12 @@ def _main():
     per.add_argument("--prompt", type=int, default=2048)
     per.add_argument("--batch", type=int, default=8)
     per.add_argument("--steps", type=int, default=16)
+    per.add_argument("--mixed", type=int, nargs=2, metavar=("PORTION", "DECODING"), default=None,
+                     help="a mixed step instead: a prompt portion of PORTION tokens beside DECODING decoding requests")
     args = ap.parse_args()
+    if args.what == "ops" and args.mixed:
+        print(json.dumps(bench_ops_mixed(args.shape, args.mixed[0], args.mixed[1], steps=min(args.steps, 8)), indent=1))
+        return
     if args.what == "ops":
         print(json.dumps(bench_ops(args.shape, args.prompt, args.batch, args.steps), indent=1))
         return
