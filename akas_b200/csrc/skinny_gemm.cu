@@ -82,7 +82,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
     unsigned done;
     asm volatile(
         "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(addr), "r"(parity), "r"(2000u) : "memory");
+        : "=r"(done) : "r"(addr), "r"(parity), "r"(200u) : "memory");
     if (done) return true;
   }
   return false;

@@ -18,10 +18,11 @@ namespace tc {
 constexpr int BK = 64;       // elements of K per tile row: 128 bytes of bfloat16, one swizzle row
 constexpr int UMMA_K = 16;   // K of one tcgen05.mma of 16-bit operands
 constexpr unsigned kSpinLimit = 1u << 22;
-// A waiting thread may be suspended this long (nanoseconds) per try before it polls again: the hardware wakes it
-// when the phase completes, so the wait is as prompt as a spin but does not fill the issue slots of the warps
-// that work (a third of all instructions of the attention kernel were polls before this).
-constexpr unsigned kSuspendNs = 2000;
+// A waiting thread may be suspended this long (nanoseconds) per try before it polls again, so that waiting does not
+// fill the issue slots of the warps that work (a third of all instructions of the attention kernel were polls
+// before this). The limit also bounds how late a waiter notices: measured on a B200, a read-out warp that waited
+// with a limit of 2,000 ns woke some 0.8 us after its barrier's phase had completed, with 200 ns some 0.2 us.
+constexpr unsigned kSuspendNs = 200;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
