@@ -165,9 +165,10 @@ class ModelRunner:
         else:
             n = sum(len(e.tokens) for e in entries)
             m = sum(len(e.want) for e in entries)
-            # The library behind the larger bfloat16 products sets itself up anew for every number of rows it has
-            # not seen (about 45 us of host time a product), and a serving step brings any number of tokens: beyond
-            # 256 the step is padded to a multiple of 256 with tokens of no request, which every kernel skips.
+            # A serving step brings any number of tokens. Beyond 256 the step is padded to a multiple of 256 with
+            # tokens of no request, which every kernel skips: the products' tiles hold 256 token rows (a pair of SMs),
+            # so the rounding costs them nothing, and what is set up per number of rows (the library's plans, when
+            # the library is selected for the products: about 45 us of host time each) is set up for a few sizes only.
             padded = -(-n // _TOKEN_ROUNDING) * _TOKEN_ROUNDING if n > _TOKEN_ROUNDING and self.dtype == torch.bfloat16 else n
             lay = BatchLayout(padded, len(entries), m, self.cache.table_widths)
             ring, dev = self._staging(lay.size)
