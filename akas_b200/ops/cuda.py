@@ -128,9 +128,19 @@ _functions = {}
 
 
 def libraries_for(dtype: torch.dtype) -> list:
-    """The kernel files a model of this compute dtype needs."""
+    """The kernel files a model of this compute dtype needs under the switches as they stand: what a first call
+    compiles. A file that only a switch's other value needs (the library arm of the products, the tcgen05 decode
+    products, the decode chain) is built when that value is first used."""
     names = ["elementwise", "conv", "rope", "attention", "sampling"]
-    names += ["sgemm"] if dtype == torch.float32 else ["gemm_bf16", "gemm_tcgen05", "gemm_pair", "gemm_rows", "gemm_stream", "skinny_gemm", "decode_chain", "attention_prefill", "attention_prefill_tc", "attention_decode"]
+    if dtype == torch.float32:
+        return names + ["sgemm"]
+    names += ["gemm_tcgen05", "gemm_pair", "gemm_rows", "skinny_gemm", "attention_prefill", "attention_prefill_tc", "attention_decode"]
+    if products == "library":
+        names.append("gemm_bf16")
+    if decode_products == "stream":
+        names.append("gemm_stream")
+    if decode_chain == "1":
+        names.append("decode_chain")
     return names
 
 
@@ -793,12 +803,17 @@ def prefill_attention_tc_status() -> int:
     return int(_fn("attention_prefill_tc", "akas_prefill_attention_tc_status")())
 
 
+_DECODE_BLOCKS = int(os.environ.get("AKAS_B200_DECODE_BLOCKS", "300"))
+
+
 def decode_splits(num_tokens: int, kv_heads: int, head_tiles: int, max_context: int) -> int:
-    """How many parts the keys of a decoding request are cut into, from sizes known on the host: enough
-    blocks for several rounds over the SMs (a single round and a bit leaves most of the GPU idle in the
-    second), but at least four 64-key tiles per part."""
+    """How many parts the keys of a decoding request are cut into, from sizes known on the host: enough blocks for
+    two per SM (measured on a B200 at 2,048 to 4,096 keys: a block's fixed cost, its query load, barriers and the
+    partial result it writes for the merge, outweighs a fuller GPU beyond that; 8 requests of 8 KV heads run fastest
+    in 4 to 5 parts, 0.861 ms a step against 0.888 ms in 16), two parts even where the requests alone give that many
+    (64 requests: 44.8k tokens/s in 2 parts, 43.4k in 1, 44.4k in 4), and at least four 64-key tiles per part."""
     blocks = max(1, num_tokens * kv_heads * head_tiles)
-    want = -(-1800 // blocks)
+    want = max(-(-_DECODE_BLOCKS // blocks), 2)
     most = max(1, -(-max_context // 256))
     return max(1, min(want, most, 64))
 
