@@ -506,6 +506,54 @@ def bench_ops_mixed(shape: str = "350m", portion: int = 512, decoding: int = 255
     return report
 
 
+def bench_timeline(shape: str = "1.2b", batch: int = 8, prompt: int = 2048, context: int = 4096) -> dict:
+    """The kernels of ONE captured decode step of ``batch`` requests as the GPU ran them (torch's profiler around a
+    graph replay): per kernel name the number of launches, the summed duration, and the time the step advanced while
+    it ran, i.e. from the end of the kernels before it to its own end: kernels of the decode path are launched ahead
+    of their predecessor's end and wait inside, so durations overlap and their sum exceeds the step."""
+    import tempfile
+
+    from torch.profiler import ProfilerActivity, profile
+
+    from .config import EngineConfig, config_from_dict
+    from .weights import write_random_model
+
+    config = EngineConfig(dtype="bfloat16", max_requests=max(batch, 1), context=context, max_tokens=batch * context,
+                          cuda_graphs=True)
+    with tempfile.TemporaryDirectory(prefix="akas-bench-") as folder:
+        write_random_model(folder, config_from_dict(shape_config(shape)), seed=0, dtype="bfloat16")
+        runner = ModelRunner(folder, config)
+    ids = fill_requests(runner, synthetic_prompts(batch, prompt, runner.vocab_size))
+
+    def decode(steps):
+        for i in range(steps):
+            runner.ops.argmax(runner.step([StepEntry(rid, (5 + i,), (0,)) for rid in ids]))
+
+    decode(5)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        decode(2)
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_type.name == "CUDA" and "Memcpy" not in e.name and "Memset" not in e.name),
+                    key=lambda e: e.time_range.start)
+    first = max(i for i, e in enumerate(events) if "embedding" in e.name)  # the second step
+    events = events[first:]
+    start = done = events[0].time_range.start
+    table: Dict[str, list] = {}
+    for e in events:
+        name = e.name.replace("(anonymous namespace)::", "")
+        name = (name[5:] if name.startswith("void ") else name).split("(")[0].strip()
+        row = table.setdefault(name, [0, 0.0, 0.0])
+        row[0] += 1
+        row[1] += e.time_range.end - e.time_range.start
+        row[2] += max(0.0, e.time_range.end - max(done, e.time_range.start))
+        done = max(done, e.time_range.end)
+    rows = [dict(kernel=k, launches=v[0], duration_us=round(v[1], 1), advanced_us=round(v[2], 1))
+            for k, v in sorted(table.items(), key=lambda kv: -kv[1][2])]
+    return dict(bench="timeline", shape=shape, batch=batch, prompt=prompt, step_us=round(done - start, 1),
+                kernels_per_step=len(events), kernels=rows)
+
+
 def _main():
     import argparse
     import json
@@ -536,6 +584,10 @@ def _main():
     lng.add_argument("--requests", type=int, default=8)
     lng.add_argument("--prompt", type=int, default=30000)
     lng.add_argument("--generated", type=int, default=256)
+    tml = sub.add_parser("timeline", help="the kernels of one captured decode step as the GPU ran them")
+    tml.add_argument("--shape", default="1.2b", choices=sorted(SHAPES))
+    tml.add_argument("--batch", type=int, default=8)
+    tml.add_argument("--prompt", type=int, default=2048)
     per = sub.add_parser("ops", help="device time of a prompt and of decode steps, by operation")
     per.add_argument("--shape", default="1.2b", choices=sorted(SHAPES))
     per.add_argument("--prompt", type=int, default=2048)
@@ -544,6 +596,9 @@ def _main():
     per.add_argument("--mixed", type=int, nargs=2, metavar=("PORTION", "DECODING"), default=None,
                      help="a mixed step instead: a prompt portion of PORTION tokens beside DECODING decoding requests")
     args = ap.parse_args()
+    if args.what == "timeline":
+        print(json.dumps(bench_timeline(args.shape, args.batch, args.prompt), indent=1))
+        return
     if args.what == "ops" and args.mixed:
         print(json.dumps(bench_ops_mixed(args.shape, args.mixed[0], args.mixed[1], steps=min(args.steps, 8)), indent=1))
         return
