@@ -33,6 +33,12 @@
 // Output modes:  bf16 store | float32 store | float32 accumulate (y += ..., the residual stream) |
 //                swiglu: the block's 16 rows are gate rows f0..f0+7 and up rows F+f0..F+f0+7 of the
 //                stacked [2F, K] matrix, so silu(gate) * up is formed per thread and stored as bf16 [M, F].
+//                conv: W is the in projection [3C, K] of a gated short convolution and every token is the single
+//                token of its request (a decode step). A tile is 8 channels: 8 rows each of the projection's B, C
+//                and x parts (three boxes a stage, three stages), a second product per k-step for the x rows; the
+//                read-out rounds the three values to bfloat16 as the product by itself would, then does what the
+//                convolution's decode kernel does (u = B x; the taps over the request's state rows and u; the
+//                state shifted; bias; times C) and stores bf16 [M, C]: one launch and no [M, 3C] round trip.
 // Parts of K. A block must hold its tokens' activations for all the k it multiplies, and fetching them costs the
 // SM as much as fetching weights does; with a long K and few rows (the down projection of a feed-forward) they
 // are a third of what a block fetches, and they leave room for one block per SM only. Such a product is cut
@@ -61,7 +67,23 @@ constexpr int STAGE_BYTES = 16 * KC * 2;  // one box of [8 groups of k][16 rows]
 constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr unsigned kSpinLimit = 1u << 22;  // try_wait calls before a wait gives up (each may block for a while)
 enum { IN_BF16 = 0, IN_NORM = 1 };
-enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_ACC = 2, OUT_SWIGLU = 3 };
+enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_ACC = 2, OUT_SWIGLU = 3, OUT_CONV = 4 };
+// Bytes of a stage, stages of the ring and weight rows of a tile, by read-out: the convolution's three boxes of 8 rows
+// make a stage of 24 KB, and three of them leave room for two blocks on an SM.
+template <int OUT> struct Ring {
+  static constexpr int BYTES = OUT == OUT_CONV ? 24 * KC * 2 : STAGE_BYTES;
+  static constexpr int DEPTH = OUT == OUT_CONV ? 3 : STAGES;
+  static constexpr int ROWS = OUT == OUT_CONV ? 24 : 16;
+};
+// What the convolution's read-out needs beside the product's operands (all null or zero for the other read-outs).
+struct ConvTail {
+  const float* taps;        // [C, L]
+  const float* bias;        // [C] or null
+  float* state;             // [slots, L - 1, C]
+  const int* seq_of_token;  // [M]: the request of a token, or -1 for padding
+  const int* slots;         // [requests]: the state row of a request
+  int L, write;
+};
 
 __device__ int g_skinny_status = 0;  // 0, or the code of a wait that ran out (1: a full stage, 2: an empty stage)
 
@@ -126,12 +148,13 @@ template <int NT, int IN, int OUT>
 __global__ void __launch_bounds__(THREADS)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __restrict__ x_, const int* __restrict__ rows,
                    const float* __restrict__ norm_w, float eps, int zero_centered, void* __restrict__ y_, int M, int O,
-                   int K, int num_tiles, int ksplit) {
+                   int K, int num_tiles, int ksplit, const ConvTail tail) {
+  constexpr int STAGES = Ring<OUT>::DEPTH, STAGE_BYTES = Ring<OUT>::BYTES, RT = Ring<OUT>::ROWS;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);  // [STAGES][STAGE_BYTES]
-  float* red = reinterpret_cast<float*>(ring + STAGES * STAGE_BYTES);   // [CONSUMERS][NT][16][8]: partial sums
+  float* red = reinterpret_cast<float*>(ring + STAGES * STAGE_BYTES);   // [CONSUMERS][NT][RT][8]: partial sums
   // ksplit > 1: this block's sums of its row tiles, then (first block only) the other blocks' sums and sums of x^2
-  float* part = red + CONSUMERS * NT * 128;                              // [SPLIT_TILES][NT * 128]
+  float* part = red + CONSUMERS * NT * RT * 8;                           // [SPLIT_TILES][NT * 128]
   float* peer = part + (ksplit > 1 ? SPLIT_TILES * NT * 128 : 0);        // [ksplit - 1][SPLIT_TILES][NT * 128]
   float* peer_ss = peer + (ksplit > 1 ? (ksplit - 1) * SPLIT_TILES * NT * 128 : 0);  // [ksplit - 1][NT * 8]
   bf16* xs = reinterpret_cast<bf16*>(peer_ss + (ksplit > 1 ? (ksplit - 1) * NT * 8 : 0));  // [NT * 8][XS]: activations
@@ -189,7 +212,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
         // the boxes are as large as they can be: 16 rows x 512 k (16 KB), or two of 8 rows for SwiGLU's two halves.
         // (SwiGLU as a run of stages over 16 gate rows and then one over 16 up rows, one box a stage, measured
         // slower here: 0.926 against 0.898 ms a decode step of the 1.2B shape.)
-        if (OUT == OUT_SWIGLU) {
+        if (OUT == OUT_CONV) {  // 8 rows each of the projection's B, C and x parts, C = O / 3 rows apart
+          for (int h = 0; h < 3; ++h)
+            tma_load_box(dst + h * (STAGE_BYTES / 3), &map_w, h * (O / 3) + tile * 8, (chunk0 + chunk) * (KC / 64), &full_bar[s]);
+        } else if (OUT == OUT_SWIGLU) {
           tma_load_box(dst, &map_w, row_lo, (chunk0 + chunk) * (KC / 64), &full_bar[s]);
           tma_load_box(dst + STAGE_BYTES / 2, &map_w, row_hi, (chunk0 + chunk) * (KC / 64), &full_bar[s]);
         } else {
@@ -243,10 +269,14 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
     // Where this thread's 16 bytes of weight rows g and g + 8 lie inside a stage: group of 64 k, row, and the 16-byte
     // unit (slice & 1) * 4 + t XOR g of the 128-byte swizzle. One box holds 16 rows to a group of k, SwiGLU's two boxes
     // 8 rows each. A warp multiplies 64 of a chunk's 512 k: slices 2 * warp and 2 * warp + 1 of 32 k.
-    constexpr int kg_stride = OUT == OUT_SWIGLU ? 1024 : 2048, hi_off = OUT == OUT_SWIGLU ? STAGE_BYTES / 2 : 1024;
-    float acc[NT][4];
+    constexpr bool BOXES8 = OUT == OUT_SWIGLU || OUT == OUT_CONV;  // boxes of 8 rows: a group of 64 k is 1 KB
+    constexpr int kg_stride = BOXES8 ? 1024 : 2048;
+    constexpr int hi_off = OUT == OUT_CONV ? STAGE_BYTES / 3 : OUT == OUT_SWIGLU ? STAGE_BYTES / 2 : 1024;
+    float acc[NT][4], acc_x[OUT == OUT_CONV ? NT : 1][4];  // acc_x: the convolution's x rows (rows g; rows g + 8 unused)
 #pragma unroll
     for (int j = 0; j < NT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+#pragma unroll
+    for (int j = 0; j < (OUT == OUT_CONV ? NT : 1); ++j) { acc_x[j][0] = acc_x[j][1] = acc_x[j][2] = acc_x[j][3] = 0.f; }
     int tile = first_tile, c = 0, tiles_done = 0;
     for (int n = 0; n < items; ++n) {
       const int s = n % STAGES;
@@ -260,11 +290,18 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           const uint4 a_hi = *reinterpret_cast<const uint4*>(st + hi_off);
           const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};  // first k-step: this thread's k 0..3
           const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};  // second k-step: its k 4..7
+          uint4 a_x = make_uint4(0u, 0u, 0u, 0u);
+          if (OUT == OUT_CONV) a_x = *reinterpret_cast<const uint4*>(st + 2 * hi_off);
+          const uint32_t x1[4] = {a_x.x, 0u, a_x.y, 0u}, x2[4] = {a_x.z, 0u, a_x.w, 0u};
 #pragma unroll
           for (int j = 0; j < NT; ++j) {
             const uint4 b = *reinterpret_cast<const uint4*>(xs + (size_t)(8 * j + g) * XS + k);
             mma_bf16(acc[j], a1, b.x, b.y);
             mma_bf16(acc[j], a2, b.z, b.w);
+            if (OUT == OUT_CONV) {
+              mma_bf16(acc_x[j], x1, b.x, b.y);
+              mma_bf16(acc_x[j], x2, b.z, b.w);
+            }
           }
         }
       }
@@ -275,25 +312,31 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
       // the row tile is complete: the consumer warps' partial sums meet in shared memory, then the epilogue
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        float* r0 = red + (((size_t)warp * NT + j) * 16 + g) * 8 + 2 * t;
+        float* r0 = red + (((size_t)warp * NT + j) * RT + g) * 8 + 2 * t;
         r0[0] = acc[j][0];
         r0[1] = acc[j][1];
         r0[64] = acc[j][2];  // row g + 8
         r0[65] = acc[j][3];
         acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        if (OUT == OUT_CONV) {
+          r0[128] = acc_x[j][0];  // row g + 16: the x part
+          r0[129] = acc_x[j][1];
+          acc_x[j][0] = acc_x[j][1] = acc_x[j][2] = acc_x[j][3] = 0.f;
+        }
       }
       consumer_barrier();
-      constexpr int per_tile = OUT == OUT_SWIGLU ? 64 : 128;  // (row, token) pairs per n-block
+      constexpr int per_tile = BOXES8 ? 64 : 128;  // (row, token) pairs per n-block
       for (int i = tid; i < NT * per_tile; i += CONSUMERS * 32) {
         const int j = i / per_tile, row = (i % per_tile) / 8, tok = i % 8;
         const int m = 8 * j + tok;
         if (m >= M) continue;
-        float v = 0.f, u = 0.f;
+        float v = 0.f, u = 0.f, xv = 0.f;
 #pragma unroll
         for (int w = 0; w < CONSUMERS; ++w) {
-          const float* r0 = red + (((size_t)w * NT + j) * 16 + row) * 8 + tok;
+          const float* r0 = red + (((size_t)w * NT + j) * RT + row) * 8 + tok;
           v += r0[0];
-          if (OUT == OUT_SWIGLU) u += r0[64];
+          if (BOXES8) u += r0[64];
+          if (OUT == OUT_CONV) xv += r0[128];
         }
         if (ksplit > 1) {  // a part of K: kept until the parts meet
           part[tiles_done * NT * 128 + i] = v;
@@ -303,8 +346,33 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           const float inv = 1.f / sqrtf(ss_s[m] / (float)K + eps);
           v *= inv;
           u *= inv;
+          xv *= inv;
         }
-        if (OUT == OUT_SWIGLU) {
+        if (OUT == OUT_CONV) {
+          // v, u, xv: the B, C and x parts of channel c for token m, rounded as the projection's own read-out would
+          const int C = O / 3, c = tile * 8 + row, L = tail.L;
+          if (c >= C) continue;
+          const int r = tail.seq_of_token[m];
+          const int slot = r >= 0 ? tail.slots[r] : -1;
+          bf16* out = (bf16*)y_ + (size_t)m * C + c;
+          if (slot < 0) {
+            *out = __float2bfloat16_rn(0.f);
+            continue;
+          }
+          const float bq = to_f32(__float2bfloat16_rn(v)), cq = to_f32(__float2bfloat16_rn(u)), xq = to_f32(__float2bfloat16_rn(xv));
+          const float uu = bq * xq;
+          float* hist = tail.state + (size_t)slot * (L - 1) * C + c;
+          float sum = 0.f;
+          for (int l = 0; l < L - 1; ++l) {
+            const float h = hist[(size_t)l * C];
+            sum = fmaf(h, tail.taps[(size_t)c * L + l], sum);
+            if (l > 0 && tail.write) hist[(size_t)(l - 1) * C] = h;
+          }
+          sum = fmaf(uu, tail.taps[(size_t)c * L + L - 1], sum);
+          if (tail.write) hist[(size_t)(L - 2) * C] = uu;
+          if (tail.bias) sum += tail.bias[c];
+          *out = __float2bfloat16_rn(cq * sum);
+        } else if (OUT == OUT_SWIGLU) {
           const int f = tile * 8 + row;
           if (f < F) ((bf16*)y_)[(size_t)m * F + f] = __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
         } else {
@@ -322,7 +390,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
       ++tiles_done;
     }
 
-    if (ksplit > 1 && OUT != OUT_SWIGLU) {
+    if (ksplit > 1 && !BOXES8) {
       // ---------------------------------------------------------------- the parts of K meet in the first block
       const int count = my_tiles * NT * 128;
       if (rank > 0) {
@@ -415,10 +483,11 @@ constexpr int kMaxSmemBytes = 226 * 1024;  // the block also has a few hundred b
 
 // Shared memory of a block with `ksplit` parts of K: alignment slack, the ring, the consumers' partial sums, the
 // parts' meeting place, and the activations of this block's part of K.
-template <int NT>
+template <int NT, int OUTM>
 int block_smem(int K, int ksplit) {
   const int chunks = (K + KC - 1) / KC, part_k = (chunks + ksplit - 1) / ksplit * KC;
-  int bytes = 1024 + STAGES * STAGE_BYTES + CONSUMERS * NT * 128 * (int)sizeof(float) + NT * 8 * (part_k + 32) * (int)sizeof(bf16);
+  int bytes = 1024 + Ring<OUTM>::DEPTH * Ring<OUTM>::BYTES + CONSUMERS * NT * Ring<OUTM>::ROWS * 8 * (int)sizeof(float) +
+              NT * 8 * (part_k + 32) * (int)sizeof(bf16);
   if (ksplit > 1) bytes += (ksplit * SPLIT_TILES * NT * 128 + (ksplit - 1) * NT * 8) * (int)sizeof(float);
   return bytes;
 }
@@ -429,9 +498,10 @@ struct SplitPlan {
 
 template <int NT, int IN, int OUTM>
 int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
-               const void* W, void* y, int M, int O, int K, cudaStream_t stream) {
+               const void* W, void* y, int M, int O, int K, const ConvTail& tail, cudaStream_t stream) {
   auto kernel = skinny_gemm_kernel<NT, IN, OUTM>;
-  if (block_smem<NT>(K, 1) > kMaxSmemBytes && (OUTM == OUT_SWIGLU || block_smem<NT>(K, MAX_KSPLIT) > kMaxSmemBytes))
+  constexpr bool UNCUT = OUTM == OUT_SWIGLU || OUTM == OUT_CONV;  // read-outs that need a tile's whole K in one block
+  if (block_smem<NT, OUTM>(K, 1) > kMaxSmemBytes && (UNCUT || block_smem<NT, OUTM>(K, MAX_KSPLIT) > kMaxSmemBytes))
     return (int)cudaErrorInvalidValue;
   static int sms = 0;
   static std::mutex mutex;
@@ -459,8 +529,8 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
       long long best = -1;
       plan = SplitPlan{1, 0, 0};
       for (int ksplit = 1; ksplit <= MAX_KSPLIT; ksplit *= 2) {
-        if (ksplit > 1 && (OUTM == OUT_SWIGLU || ksplit > chunks)) break;
-        const int smem = block_smem<NT>(K, ksplit);
+        if (ksplit > 1 && (UNCUT || ksplit > chunks)) break;
+        const int smem = block_smem<NT, OUTM>(K, ksplit);
         if (smem > kMaxSmemBytes) continue;
         static const int per_sm_cap = [] { const char* v = getenv("AKAS_B200_SKINNY_PER_SM"); return v ? atoi(v) : 3; }();
         const int per_sm = max(1, min(per_sm_cap, kMaxSmemBytes / (smem + 1024)));
@@ -508,7 +578,7 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
     }
   }
   CUtensorMap map;
-  const int err = weight_map(&map, W, O, K, OUTM == OUT_SWIGLU ? 8 : 16);
+  const int err = weight_map(&map, W, O, K, UNCUT ? 8 : 16);
   if (err) return err;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(plan.grid);
@@ -531,19 +601,21 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
   }
   config.attrs = attribute;
   config.numAttrs = n;
-  return (int)cudaLaunchKernelEx(&config, kernel, map, x, rows, norm_w, eps, zero_centered, y, M, O, K, num_tiles, plan.ksplit);
+  return (int)cudaLaunchKernelEx(&config, kernel, map, x, rows, norm_w, eps, zero_centered, y, M, O, K, num_tiles, plan.ksplit, tail);
 }
 
 template <int NT, int IN>
 int launch_out(int out_mode, const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
-               const void* W, void* y, int M, int O, int K, cudaStream_t stream) {
+               const void* W, void* y, int M, int O, int K, const ConvTail& tail, cudaStream_t stream) {
   const int tiles = (O + 15) / 16;
   switch (out_mode) {
-    case OUT_BF16: return launch_one<NT, IN, OUT_BF16>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
-    case OUT_F32: return launch_one<NT, IN, OUT_F32>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
-    case OUT_ACC: return launch_one<NT, IN, OUT_ACC>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
+    case OUT_BF16: return launch_one<NT, IN, OUT_BF16>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+    case OUT_F32: return launch_one<NT, IN, OUT_F32>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+    case OUT_ACC: return launch_one<NT, IN, OUT_ACC>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
     case OUT_SWIGLU:
-      return launch_one<NT, IN, OUT_SWIGLU>((O / 2 + 7) / 8, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
+      return launch_one<NT, IN, OUT_SWIGLU>((O / 2 + 7) / 8, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+    case OUT_CONV:
+      return launch_one<NT, IN, OUT_CONV>((O / 3 + 7) / 8, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
     default: return (int)cudaErrorInvalidValue;
   }
 }
@@ -553,19 +625,39 @@ int launch_out(int out_mode, const void* x, const int* rows, const float* norm_w
 // x: bfloat16 [M, K] (in_mode 0) or float32 [*, K] rows gathered by `rows` (or 0..M-1) with RMSNorm fused (in_mode 1).
 // W: bfloat16 [O, K]. y: [M, O] in the output mode's type, or bfloat16 [M, O / 2] for swiglu (out_mode 3).
 // Returns 0, a CUDA error code, or 3000 + a driver error from building the weights' tensor map.
-AKAS_API int akas_skinny_gemm(const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
-                              const void* W, void* y, int M, int O, int K, int in_mode, int out_mode,
-                              cudaStream_t stream) {
+static int skinny_dispatch(const void* x, const int* rows, const float* norm_w, float eps, int zero_centered, const void* W,
+                           void* y, int M, int O, int K, int in_mode, int out_mode, const ConvTail& tail, cudaStream_t stream) {
   if (M <= 0 || O <= 0) return 0;
-  if (M > 16 || K <= 0 || K % 64 || (out_mode == OUT_SWIGLU && O % 2)) return (int)cudaErrorInvalidValue;
+  if (M > 16 || K <= 0 || K % 64 || (out_mode == OUT_SWIGLU && O % 2) || (out_mode == OUT_CONV && O % 3)) return (int)cudaErrorInvalidValue;
   if (in_mode == IN_NORM && norm_w == nullptr) return (int)cudaErrorInvalidValue;
   if ((uintptr_t)W % 16 || (uintptr_t)x % 16) return (int)cudaErrorInvalidValue;  // TMA and 16-byte loads
   if (M <= 8) {
-    if (in_mode == IN_BF16) return launch_out<1, IN_BF16>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
-    return launch_out<1, IN_NORM>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
+    if (in_mode == IN_BF16) return launch_out<1, IN_BF16>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+    return launch_out<1, IN_NORM>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
   }
-  if (in_mode == IN_BF16) return launch_out<2, IN_BF16>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
-  return launch_out<2, IN_NORM>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, stream);
+  if (in_mode == IN_BF16) return launch_out<2, IN_BF16>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+  return launch_out<2, IN_NORM>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+}
+
+AKAS_API int akas_skinny_gemm(const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
+                              const void* W, void* y, int M, int O, int K, int in_mode, int out_mode,
+                              cudaStream_t stream) {
+  if (out_mode < OUT_BF16 || out_mode > OUT_SWIGLU) return (int)cudaErrorInvalidValue;
+  return skinny_dispatch(x, rows, norm_w, eps, zero_centered, W, y, M, O, K, in_mode, out_mode, ConvTail{}, stream);
+}
+
+// The in projection of a gated short convolution and the convolution itself, for a decode step: W bfloat16 [3C, K]
+// (the B, C and x parts), x as for akas_skinny_gemm, every token the single token of request seq_of_token[t] (or -1:
+// padding, its output is zero) whose state row is slots[request]; taps float32 [C, L], bias float32 [C] or null,
+// state float32 [slots, L - 1, C] (read, and shifted by the token unless write is 0); y bfloat16 [M, C].
+AKAS_API int akas_skinny_gemm_conv(const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
+                                   const void* W, void* y, int M, int C, int K, int in_mode, const float* taps,
+                                   const float* bias, float* state, const int* seq_of_token, const int* slots, int L,
+                                   int write, cudaStream_t stream) {
+  if (L < 2 || L > 16 || C <= 0 || taps == nullptr || state == nullptr || seq_of_token == nullptr || slots == nullptr)
+    return (int)cudaErrorInvalidValue;
+  const ConvTail tail{taps, bias, state, seq_of_token, slots, L, write};
+  return skinny_dispatch(x, rows, norm_w, eps, zero_centered, W, y, M, 3 * C, K, in_mode, OUT_CONV, tail, stream);
 }
 
 // 0 if no bounded wait of the kernel has ever run out on the current device, else the code of the last one

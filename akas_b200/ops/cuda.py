@@ -96,6 +96,8 @@ _SIGNATURES = {
     "skinny_gemm": {
         "akas_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_int, c_int, c_void_p],
+        "akas_skinny_gemm_conv": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "akas_skinny_gemm_status": [],
     },
     "decode_chain": {
@@ -713,6 +715,28 @@ def norm_linear(h, norm_weight, eps, zero_centered, w, out_dtype=None, rows=None
         return out
     x = rmsnorm(h, norm_weight, eps, zero_centered, w.dtype, rows)
     return linear_swiglu(x, w) if swiglu_out else linear(x, w, out_dtype=out_dtype)
+
+
+# A decode step's in projection and gated short convolution as one kernel (csrc/skinny_gemm.cu, read-out "conv"):
+# AKAS_B200_FUSED_CONV=0 runs them as the product and the convolution kernel.
+fused_conv = os.environ.get("AKAS_B200_FUSED_CONV", "1") != "0"
+
+
+def norm_linear_short_conv(h, norm_weight, eps, zero_centered, w_in, taps, bias, state, seq_of_token, slots, write=True):
+    """``short_conv(norm_linear(h, ...), ...)`` for a decode step (every token the single token of its request) in one
+    launch, or None where the fused kernel does not take the sizes (the caller then runs the two by themselves)."""
+    m, k = h.shape
+    c3 = w_in.shape[0]
+    c, l = c3 // 3, taps.shape[1]
+    if not fused_conv or _chain_open or w_in.dtype != torch.bfloat16 or h.dtype != torch.float32 or not h.is_contiguous() \
+            or c3 % 3 or c % 8 or not 2 <= l <= 16 or not _skinny_fits(m, k) or state.dtype != torch.float32:
+        return None
+    out = torch.empty((m, c), dtype=torch.bfloat16, device=h.device)
+    _check(_fn("skinny_gemm", "akas_skinny_gemm_conv")(
+        _ptr(h), None, _ptr(norm_weight), float(eps), int(bool(zero_centered)), _ptr(_dense(w_in, "w")), _ptr(out), m, c, k, 1,
+        _ptr(taps), _ptr(bias), _ptr(state), _ptr(seq_of_token), _ptr(slots), l, int(bool(write)), _stream()),
+        f"fused in projection and short convolution [{m}x{k}] x [{c3}x{k}]^T")
+    return out
 
 
 # --------------------------------------------------------------------------- mixers

@@ -19,7 +19,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Mixer, Param, StateSpec, project, register_mixer, renamed
+from .base import Mixer, Normed, Param, StateSpec, project, register_mixer, renamed
 
 
 class ShortConv(Mixer):
@@ -63,12 +63,19 @@ class ShortConv(Mixer):
 
     def forward(self, x, ctx, cache=None, residual=None, write=True):
         ops = self.rt.ops
-        if self.bias_in is None:
-            bcx = project(self.rt, x, self.w_in)
-        else:  # the product stays float32 until its bias is in, then rounds once
-            bcx = ops.add_bias(project(self.rt, x, self.w_in, out_dtype=torch.float32), self.bias_in, self.rt.dtype)
-        y = ops.short_conv(bcx, self.taps, self.bias, cache.state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots,
-                           decode_only=ctx.decode_only, write=write)
+        y = None
+        if (self.bias_in is None and ctx.decode_only and isinstance(x, Normed) and x.rows is None
+                and getattr(x.norm.spec, "kind", None) == "rmsnorm" and hasattr(ops, "norm_linear_short_conv")):
+            # a decode step: norm, in projection and convolution as one kernel, where the kernels have one
+            y = ops.norm_linear_short_conv(x.h, x.norm.weight, x.norm.spec.eps, x.norm.spec.zero_centered, self.w_in,
+                                           self.taps, self.bias, cache.state, ctx.seq_of_token, ctx.slots, write=write)
+        if y is None:
+            if self.bias_in is None:
+                bcx = project(self.rt, x, self.w_in)
+            else:  # the product stays float32 until its bias is in, then rounds once
+                bcx = ops.add_bias(project(self.rt, x, self.w_in, out_dtype=torch.float32), self.bias_in, self.rt.dtype)
+            y = ops.short_conv(bcx, self.taps, self.bias, cache.state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots,
+                               decode_only=ctx.decode_only, write=write)
         if self.bias_out is None:
             return project(self.rt, y, self.w_out, residual=residual)
         if residual is None:

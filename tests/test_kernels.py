@@ -305,6 +305,41 @@ def test_decode_chain_runs_a_layer_as_one_launch(ops, m, c, f, v, taps, monkeypa
     cuda.chain_end()
 
 
+@pytest.mark.parametrize("m,c,k,taps,bias", [(8, 2048, 2048, 3, False), (5, 72, 128, 4, True), (13, 1024, 512, 2, False),
+                                             (1, 64, 64, 3, True), (16, 200, 320, 5, False)])
+def test_in_projection_and_short_conv_as_one_kernel(ops, m, c, k, taps, bias):
+    """A decode step's RMSNorm, in projection and gated short convolution in one launch, against the product and the
+    convolution kernel one after the other: the read-out rounds the projection to bfloat16 as the product would and
+    then does the convolution's arithmetic in its order, so the two differ only where the product by itself cut K into
+    parts (another order of the float32 sum) and a value lay on a rounding boundary: fewer than one element in a hundred,
+    by one step of bfloat16. State included; padding tokens give zeros and touch no state; ``write=False`` leaves the
+    state as it was."""
+    cuda, ref = ops
+    h = _rand((m, k), torch.float32, 1, 2.0)
+    norm_w = _rand((k,), torch.float32, 2) * 0.2 + 1
+    w_in = _rand((3 * c, k), torch.bfloat16, 3, k ** -0.5)
+    conv_w, conv_b = _rand((c, taps), torch.float32, 4), (_rand((c,), torch.float32, 5) if bias else None)
+    live = max(1, m - 2) if m > 2 else m
+    seq = torch.tensor(list(range(live)) + [-1] * (m - live), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([(5 * r + 2) % 24 for r in range(live)], dtype=torch.int32, device=DEV)
+    state0 = _rand((24, taps - 1, c), torch.float32, 6)
+    for write in (True, False):
+        s_two, s_one = state0.clone(), state0.clone()
+        bcx = cuda.norm_linear(h, norm_w, 1e-5, False, w_in)
+        want = cuda.short_conv(bcx, conv_w, conv_b, s_two, None, seq, slots, decode_only=True, write=write)
+        before = cuda.launch_count
+        got = cuda.norm_linear_short_conv(h, norm_w, 1e-5, False, w_in, conv_w, conv_b, s_one, seq, slots, write=write)
+        assert got is not None and cuda.launch_count == before + 1
+        _close(got, want, torch.bfloat16, "output")
+        _close(s_one, s_two, torch.bfloat16, "state")
+        assert (got != want).float().mean() < 0.01 and (s_one != s_two).float().mean() < 0.01
+        assert torch.equal(s_one, state0) != write
+        assert not got[live:].any()
+    assert cuda.skinny_status() == 0
+    assert cuda.norm_linear_short_conv(_rand((17, k), torch.float32, 7), norm_w, 1e-5, False, w_in, conv_w, conv_b, state0, seq,
+                                       slots) is None  # more tokens than the decode kernels take: the caller runs the two
+
+
 def test_short_conv_decode_kernel_equals_the_general_one(ops):
     cuda, ref = ops
     c, taps = 72, 4
