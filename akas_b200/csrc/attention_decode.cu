@@ -261,12 +261,24 @@ constexpr int TMA_STAGES = 4, TMA_TILE = BK * 128;  // a tile: 64 rows of 64 bfl
 
 __device__ int g_decode_status = 0;
 
+// The address of a shared-memory location of block `rank` of this cluster, and a store there.
+__device__ __forceinline__ unsigned peer_address(const void* local, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(akas::tc::smem_u32(local)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void peer_store(unsigned address, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(v) : "memory");
+}
+
 __global__ void __launch_bounds__((WARPS + 1) * 32)
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const bf16* __restrict__ q, const int* __restrict__ block_table, int max_blocks,
                             const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                             bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, float scale,
-                            int window, int page_size, int H, int KH, int row_tiles, int splits) {
+                            int window, int page_size, int H, int KH, int row_tiles, int splits, int in_cluster) {
+  // in_cluster: the blocks of a (token, KV head)'s key parts form a thread-block cluster; their partial results meet in
+  // the first block's shared memory and that block writes the output, instead of a second kernel over global scratch.
   using namespace akas::tc;
   constexpr int D = 64, STRIDE = D + 8, CHUNKS = D / 8, KS = D / 16, NB = D / 8;
   extern __shared__ unsigned char smem_dyn[];
@@ -276,7 +288,9 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   bf16* q_s = reinterpret_cast<bf16*>(v_t + TMA_STAGES * TMA_TILE);  // [ROWS][STRIDE]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(q_s + ROWS * STRIDE);
   uint64_t* empty_bar = full_bar + TMA_STAGES;
-  int* abort_s = reinterpret_cast<int*>(empty_bar + TMA_STAGES);
+  uint64_t* gathered = empty_bar + TMA_STAGES;  // first block of a cluster: the other parts have arrived
+  int* abort_s = reinterpret_cast<int*>(gathered + 1);
+  float* gather = reinterpret_cast<float*>(abort_s + 2);  // [splits - 1][rows of this tile][D + 2], in_cluster only
 
   chain_release();
   chain_wait();
@@ -302,9 +316,13 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   if (tid == 0) {
     *abort_s = 0;
     for (int s = 0; s < TMA_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], WARPS); }
+    mbar_init(gathered, in_cluster ? (unsigned)(splits - 1) : 1u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // Every block of the cluster says that its barriers exist; whoever writes into a peer waits for that first (at the
+  // end, when it has long happened). A padding token's blocks have all left above, before any of this.
+  if (in_cluster) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   auto wait_for = [&](uint64_t* bar, unsigned parity, int code) {
     if (*(volatile int*)abort_s) return;
     if (!mbar_wait(bar, parity)) {
@@ -457,13 +475,66 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const size_t head = (size_t)tok * H + head0 + row;
     if (splits == 1) {
       out[head * D + e] = __float2bfloat16_rn(acc / sum);
-    } else {
+    } else if (!in_cluster) {
       part_o[(head * splits + split) * D + e] = acc;
       if (e == 0) {
         part_ml[(head * splits + split) * 2] = top;  // in units of log2(e)
         part_ml[(head * splits + split) * 2 + 1] = sum;
       }
+    } else if (split == 0) {  // the first block keeps its own part where the merge below finds it: the tiles are done with
+      o_s[(size_t)WARPS * ROWS * (D + 2) + row * (D + 2) + e] = acc;
+      if (e == 0) {
+        o_s[(size_t)WARPS * ROWS * (D + 2) + row * (D + 2) + D] = top;
+        o_s[(size_t)WARPS * ROWS * (D + 2) + row * (D + 2) + D + 1] = sum;
+      }
+    } else {  // into the first block's shared memory
+      const unsigned to = peer_address(gather, 0) + (unsigned)((((split - 1) * gn + row) * (D + 2) + e) * 4);
+      peer_store(to, acc);
+      if (e == 0) {
+        peer_store(to + (unsigned)(D * 4), top);
+        peer_store(to + (unsigned)((D + 1) * 4), sum);
+      }
     }
+  }
+  if (!in_cluster) return;
+  __syncwarp();
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // (arrived long ago) the first block's barrier exists
+  consumers_meet();  // all of this block's part is written or on its way
+  if (split > 0) {
+    if (tid == 0) {
+      asm volatile("fence.acq_rel.cluster;" ::: "memory");
+      asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_address(gathered, 0)) : "memory");
+    }
+    return;
+  }
+  // the first block: the parts in the order of their numbers, as the merge kernel adds them
+  bool ok = !*(volatile int*)abort_s;
+  if (ok) {
+    const unsigned addr = smem_u32(gathered);
+    ok = false;
+    for (unsigned spin = 0; spin < kSpinLimit && !ok; ++spin) {
+      unsigned done;
+      asm volatile(
+          "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+          : "=r"(done) : "r"(addr), "r"(0u) : "memory");
+      ok = done != 0;
+    }
+    if (!ok) atomicExch(&g_decode_status, 3);
+  }
+  if (!ok) return;
+  const float* own = o_s + (size_t)WARPS * ROWS * (D + 2);
+  for (int i = tid; i < gn * D; i += WARPS * 32) {
+    const int row = i / D, e = i % D;
+    float top = own[row * (D + 2) + D];
+    for (int p = 1; p < splits; ++p) top = fmaxf(top, gather[((p - 1) * gn + row) * (D + 2) + D]);
+    float sum = 0.f, acc = 0.f;
+    for (int p = 0; p < splits; ++p) {
+      const float* part = p == 0 ? own + row * (D + 2) : gather + ((p - 1) * gn + row) * (D + 2);
+      const float f = part[D] == -INFINITY ? 0.f : exp2f(part[D] - top);
+      sum = fmaf(part[D + 1], f, sum);
+      acc = fmaf(part[e], f, acc);
+    }
+    out[((size_t)tok * H + head0 + row) * D + e] = __float2bfloat16_rn(acc / sum);
   }
 }
 
@@ -500,14 +571,17 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* blo
 int launch_tma(const void* q, const void* k_pool, const void* v_pool, long long pool_rows, const int* block_table,
                int max_blocks, const int* seq_of_token, const int* positions, void* out, float* part_o, float* part_ml,
                float scale, int window, int page_size, int N, int H, int KH, int splits, cudaStream_t stream) {
-  constexpr int D = 64;
-  constexpr int smem = 1024 + 2 * TMA_STAGES * TMA_TILE + ROWS * (D + 8) * (int)sizeof(bf16) + 2 * TMA_STAGES * 8 + 16;
-  static_assert(2 * TMA_STAGES * TMA_TILE >= WARPS * ROWS * (D + 2) * (int)sizeof(float), "the merge buffers fit the tiles");
+  constexpr int D = 64, MAX_CLUSTER = 8;
+  constexpr int smem = 1024 + 2 * TMA_STAGES * TMA_TILE + ROWS * (D + 8) * (int)sizeof(bf16) + (2 * TMA_STAGES + 1) * 8 + 16;
+  constexpr int gather_most = (MAX_CLUSTER - 1) * ROWS * (D + 2) * (int)sizeof(float);  // the other parts, in the first block
+  static_assert(2 * TMA_STAGES * TMA_TILE >= (WARPS + 1) * ROWS * (D + 2) * (int)sizeof(float), "the merge buffers fit the tiles");
   static bool configured[kMaxDevices] = {};
+  static int cluster_ok[kMaxDevices][MAX_CLUSTER + 1] = {};  // 0 unknown, 1 a cluster of that many blocks can run, -1 it cannot
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return (int)cudaErrorInvalidDevice;
   if (!configured[device]) {
-    const cudaError_t e = cudaFuncSetAttribute(decode_attention_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const cudaError_t e = cudaFuncSetAttribute(decode_attention_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               smem + gather_most);
     if (e != cudaSuccess) return (int)e;
     configured[device] = true;
   }
@@ -516,10 +590,54 @@ int launch_tma(const void* q, const void* k_pool, const void* v_pool, long long 
   if (!err) err = akas::tc::cached_map(&map_v, v_pool, (int)pool_rows, D, BK, true);
   if (err) return err;
   const int G = H / KH, row_tiles = (G + ROWS - 1) / ROWS;
-  err = launch_chained(decode_attention_tma_kernel, dim3(N, KH * row_tiles, splits), dim3((WARPS + 1) * 32), smem, stream,
-                       map_k, map_v, (const bf16*)q, block_table, max_blocks, seq_of_token, positions, (bf16*)out, part_o,
-                       part_ml, scale, window, page_size, H, KH, row_tiles, splits);
-  if (err || splits == 1) return err;
+  // The parts of a (token, KV head) as a thread-block cluster whose first block merges them, where a cluster can be
+  // that large; else every part writes to the scratch and a second kernel merges.
+  static const bool clusters_wanted = [] { const char* v = getenv("AKAS_B200_DECODE_CLUSTER_MERGE"); return !(v && v[0] == '0'); }();
+  // Only while the blocks are few (up to four per SM): with more, a cluster's blocks wait for one another to be placed
+  // and the second kernel costs less than that (64 requests: 43.1k tokens/s merged in clusters, 44.3k with the kernel).
+  static int sms[kMaxDevices] = {};
+  if (sms[device] == 0) cudaDeviceGetAttribute(&sms[device], cudaDevAttrMultiProcessorCount, device);
+  int in_cluster = clusters_wanted && splits >= 2 && splits <= MAX_CLUSTER &&
+                   (long long)N * KH * row_tiles * splits <= 4ll * sms[device] ? 1 : 0;
+  const int gather_bytes = in_cluster ? (splits - 1) * (G < ROWS ? G : ROWS) * (D + 2) * (int)sizeof(float) : 0;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(N, KH * row_tiles, splits);
+  config.blockDim = dim3((WARPS + 1) * 32);
+  config.dynamicSmemBytes = smem + gather_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  int n = 0;
+  if (chained_launches_enabled()) {
+    attribute[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (in_cluster) {
+    attribute[n].id = cudaLaunchAttributeClusterDimension;
+    attribute[n].val.clusterDim.x = 1;
+    attribute[n].val.clusterDim.y = 1;
+    attribute[n].val.clusterDim.z = splits;
+    config.attrs = attribute;
+    config.numAttrs = n + 1;
+    if (cluster_ok[device][splits] == 0) {
+      int room = 0;
+      if (cudaOccupancyMaxActiveClusters(&room, decode_attention_tma_kernel, &config) != cudaSuccess) { cudaGetLastError(); room = 0; }
+      cluster_ok[device][splits] = room > 0 ? 1 : -1;
+    }
+    if (cluster_ok[device][splits] < 0) {
+      in_cluster = 0;
+      config.dynamicSmemBytes = smem;
+    } else {
+      ++n;
+    }
+  }
+  config.attrs = attribute;
+  config.numAttrs = n;
+  if (!in_cluster && splits > 1 && (part_o == nullptr || part_ml == nullptr)) return (int)cudaErrorInvalidValue;
+  err = (int)cudaLaunchKernelEx(&config, decode_attention_tma_kernel, map_k, map_v, (const bf16*)q, block_table, max_blocks,
+                                seq_of_token, positions, (bf16*)out, part_o, part_ml, scale, window, page_size, H, KH,
+                                row_tiles, splits, in_cluster);
+  if (err || splits == 1 || in_cluster) return err;
   return launch_chained(decode_merge_bf16_kernel, dim3(N, H), dim3(64), 0, stream, (const float*)part_o,
                         (const float*)part_ml, seq_of_token, (bf16*)out, H, D, splits);
 }

@@ -842,6 +842,17 @@ def decode_splits(num_tokens: int, kv_heads: int, head_tiles: int, max_context: 
     return max(1, min(want, most, 64))
 
 
+_decode_cluster_merge = os.environ.get("AKAS_B200_DECODE_CLUSTER_MERGE", "1") != "0"
+
+
+def _merges_in_cluster(blocks: int, splits: int, head_dim: int, page_size: int) -> bool:
+    """Whether the decode attention kernel merges its key parts itself (they form a thread-block cluster: the TMA-fed
+    kernel, 2 to 8 parts, up to four blocks per SM in all) instead of leaving them to a second kernel; the rule of
+    csrc/attention_decode.cu::launch_tma."""
+    return (_decode_cluster_merge and 2 <= splits <= 8 and head_dim == 64 and page_size % 64 == 0
+            and blocks * splits <= 4 * _sm_count())
+
+
 def _decode_attention(q, n, out, k_pool, v_pool, block_table, seq_of_token, positions, scale, win, page_size, keys):
     """Split-key attention of the first ``n`` tokens of q, each the single token of its request, into out[:n]."""
     kh, d = k_pool.shape[1], k_pool.shape[3]
@@ -857,7 +868,7 @@ def _decode_attention(q, n, out, k_pool, v_pool, block_table, seq_of_token, posi
         _check(_fn("attention_decode", "akas_decode_attention_bf16_paged")(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
             _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
-            splits, _stream()), "decode_attention", kernels=2 if splits > 1 else 1)
+            splits, _stream()), "decode_attention", kernels=2 if splits > 1 and not _merges_in_cluster(n * kh * -(-group // 16), splits, d, page_size) else 1)
         return
     gt = 8 if group >= 8 else 4 if group > 2 else group
     splits = decode_splits(n, kh, -(-group // gt), keys)

@@ -573,7 +573,9 @@ def test_decoded_tokens_at_the_front_of_a_mixed_step(ops, h, kh, d, page, window
     ctx.max_context = max(contexts)
     before = cuda.launch_count
     got = cuda.paged_attention(q, k, v, bt, seq, pos, d ** -0.5, window, page, ctx)
-    assert cuda.launch_count - before == (3 if mode == "split" else 1)  # split keys, their merge, the prompt tiles
+    # split keys, their merge (a kernel of its own unless the TMA-fed kernel merges in its clusters), the prompt tiles
+    merged = d == 64 and page % 64 == 0
+    assert cuda.launch_count - before == ((2 if merged else 3) if mode == "split" else 1)
     _close(got, ref.paged_attention(q, k, v, bt, seq, pos, d ** -0.5, window, page), dtype, mode)
     assert cuda.decode_attention_status() == 0 and cuda.prefill_attention_tc_status() == 0
 
