@@ -2,8 +2,8 @@
 // tcgen05.mma.cta_group::2, float32 accumulation in the tensor memory of both SMs, epilogues fused into the read-out
 // and written by TMA.
 //
-// A thread-block cluster of two blocks (two SMs) walks output tiles of 256 tokens x BN channels (BN 256, 128 or 64:
-// the widest that still gives every pair of SMs a tile). Each block stages its own 128 token rows of x and HALF of
+// A thread-block cluster of two blocks (two SMs) walks output tiles of 256 tokens x BN channels (BN 256, 192, 128 or
+// 64: the width that finishes first by a count of rounds over the pairs and of what a stage costs, see launch_width). Each block stages its own 128 token rows of x and HALF of
 // the tile's channels of W, 32 KB a step of K at BN = 256 instead of the 48 KB a lone block needs for a 128 x 256
 // tile: a product of the pair reads the channels from both blocks' shared memory. That halves what a block writes
 // into and reads out of its shared memory per multiply-add, which is what bounds a one-block kernel (its TMA writes
@@ -53,8 +53,9 @@ enum { EPI_BF16 = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3 };
 template <int BN> struct Shape {
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, HALF_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGE_BYTES = STEPS * HALF_BYTES;  // x of both steps of K, then W of both steps
-  static constexpr int STAGES = BN == 256 ? 3 : 4;
+  static constexpr int STAGES = BN >= 192 ? 3 : 4;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 8 * STAGING + 1024;
+  static constexpr int TMEM_COLS = BN > 128 ? 512 : 2 * BN;  // two accumulators of BN columns, a power of two
 };
 
 __device__ int g_pair_status = 0;  // 0, or which bounded wait ran out last (1 producer, 2 tensor cores, 3 read-out)
@@ -166,7 +167,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {  // tensor memory of both SMs: two accumulators of BN float32 columns, 128 lanes in each block
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(2 * BN));
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(S::TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -334,7 +335,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   cluster_meet();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(S::TMEM_COLS));
   }
 }
 
@@ -447,19 +448,33 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, cudaStrea
 
 template <int EPI>
 int launch_width(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
-  // The widest tile that still gives most pairs of SMs one (a B200 has 74 pairs): narrower tiles fetch the token rows
-  // more often, so they are for products with few channels or few tokens only.
+  // The tile width that finishes first by a count of the issuing thread's cycles: rounds over the pairs of SMs (a B200
+  // has 74) times what a stage of eight products takes, which is the tensor cores' 131 cycles a product at 256 channels
+  // and in proportion for narrower tiles, but never less than the 700 cycles it costs the one thread to issue eight
+  // products and their commit. So a tile narrower than 192 channels only pays where it saves a round: measured on
+  // [2048 x 6912] . [1536 x 6912]^T, 128-channel tiles (96 tiles, two rounds) took 76 us and 192-channel tiles (64
+  // tiles, one round) 49 us (the library: 42 us). Among equals the wider tile wins (it fetches the token rows less often).
   const long long rows = (M + 2 * BM - 1) / (2 * BM);
   const int out_cols = EPI == EPI_SWIGLU ? N / 2 : N;
   const int unit = EPI == EPI_SWIGLU ? 2 : 1;  // a SwiGLU tile of BN stacked rows yields BN / 2 channels
-  if (K % 64 == 0) {
-    if (rows * ((out_cols * unit + 255) / 256) >= 56) return launch<256, EPI, true>(x, w, y, M, N, K, stream);
-    if (rows * ((out_cols * unit + 127) / 128) >= 56) return launch<128, EPI, true>(x, w, y, M, N, K, stream);
-    return launch<64, EPI, true>(x, w, y, M, N, K, stream);
+  int device = 0, sms = 148;
+  if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const long long pairs = sms / 2 > 0 ? sms / 2 : 1;
+  int best = 256;
+  long long best_cost = -1;
+  for (const int bn : {256, 192, 128, 64}) {
+    const long long tiles = rows * ((out_cols * unit + bn - 1) / bn), rounds = (tiles + pairs - 1) / pairs;
+    const long long stage = 1048ll * bn / 256 > 700 ? 1048ll * bn / 256 : 700;
+    const long long cost = rounds * stage;
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
   }
-  if (rows * ((out_cols * unit + 255) / 256) >= 56) return launch<256, EPI, false>(x, w, y, M, N, K, stream);
-  if (rows * ((out_cols * unit + 127) / 128) >= 56) return launch<128, EPI, false>(x, w, y, M, N, K, stream);
-  return launch<64, EPI, false>(x, w, y, M, N, K, stream);
+#define AKAS_PAIR_WIDTH(BN_) \
+  case BN_: return K % 64 == 0 ? launch<BN_, EPI, true>(x, w, y, M, N, K, stream) : launch<BN_, EPI, false>(x, w, y, M, N, K, stream);
+  switch (best) {
+    AKAS_PAIR_WIDTH(256) AKAS_PAIR_WIDTH(192) AKAS_PAIR_WIDTH(128) AKAS_PAIR_WIDTH(64)
+  }
+#undef AKAS_PAIR_WIDTH
+  return (int)cudaErrorInvalidValue;
 }
 
 }  // namespace
