@@ -32,6 +32,17 @@
 //                                                 element is added to once, so the sum does not depend on timing
 //              F32     y float32 [M, O]           a TMA store
 //              SWIGLU  y bfloat16 [M, F]          silu(gate) * up, a TMA store
+// Parts of K. Every block reads all token rows of x for the k it multiplies, from the L2 at the 64 bytes a cycle an SM
+// takes in; where K is long and the tile narrow (the down projection of a feed-forward: 1 MB of x beside 256 KB of
+// weights at 64 tokens) that is what the block waits for. Such a product (residual read-out only) is cut along K into
+// 2 or 4 parts with tiles that many times as wide: the blocks of a thread-block cluster take one part each for the same
+// tile, the others put their sums into their own shared memory (the ring is free by then) and send them to the first
+// block's with ONE bulk copy each (cp.async.bulk shared::cta -> shared::cluster, its bytes counted on the first block's
+// mbarrier; stores from registers into a peer's shared memory, 16 bytes a thread and rows 256 bytes apart, took 10 us
+// for 48 KB), and the first block adds the parts in the order of their numbers and hands the tile to TMA. One tile per
+// block then (the meeting place is used once). The cluster's barrier is passed twice: once so that the first block's
+// mbarrier exists before a peer's copy counts on it, once so that a peer's shared memory lives until its copy has
+// been received.
 // Every wait on an mbarrier is bounded (akas_gemm_rows_status): one that runs out sets a status word, every role
 // falls through, tensor memory is freed and the block returns; that launch's results are not valid.
 #include <math.h>
@@ -48,7 +59,7 @@ constexpr int STAGING = 2048;  // bytes of one staging tile: 32 rows x 64 bytes 
 constexpr int SMEM_LIMIT = 227 * 1024;
 enum { EPI_BF16 = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3 };
 
-__device__ int g_rows_status = 0;  // 0, or which bounded wait ran out last (1 producer, 2 tensor cores, 3 read-out)
+__device__ int g_rows_status = 0;  // 0, or which bounded wait ran out last (1 producer, 2 tensor cores, 3 read-out, 4 the parts of K)
 
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int row, int group, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -117,6 +128,21 @@ __device__ __forceinline__ void tmem_sum16(unsigned taddr, int warps, int pitch,
   }
 }
 
+__device__ __forceinline__ unsigned cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The address of a shared-memory location of block `rank` of this cluster, and a 16-byte store there.
+__device__ __forceinline__ unsigned peer_address(const void* local, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void peer_store4(unsigned address, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(address), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 struct Shape {
   int M, O, K, F;     // F: output channels of SwiGLU (O = 2F), else unused
   int RT;             // token rows a stage holds (M rounded up to 16)
@@ -128,6 +154,8 @@ struct Shape {
   int issuers;        // warps that issue products, each with accumulators of its own
   int buffers;        // sets of accumulators: 2 where a block walks several tiles, else 1
   unsigned suspend_ns;  // how long a waiting thread may sleep before it looks at its barrier again
+  int parts;          // blocks of a cluster that share a tile, one part of K each (1: no cluster)
+  int part_blocks;    // 64-wide steps of K in a part (a multiple of G)
 };
 
 template <int EPI>
@@ -138,17 +166,23 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   constexpr int HALVES = SWIGLU ? 2 : 1;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2], gathered;
   __shared__ unsigned tmem_base_s;
   __shared__ int abort_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int M = sh.M, K = sh.K, RT = sh.RT, TN = sh.tile_n, G = sh.G, stages = sh.stages;
   const int out_cols = SWIGLU ? sh.F : sh.O;
-  const int tiles = (out_cols + TN - 1) / TN, k_blocks = (K + BK - 1) / BK;
+  const int tiles = (out_cols + TN - 1) / TN;
+  // this block's part of K: 64-wide steps [kb0, kb0 + k_blocks); its place among the blocks that walk the tiles
+  const int P = sh.parts, rank = P > 1 ? (int)cluster_rank() : 0;
+  const int kb0 = rank * sh.part_blocks;
+  const int k_blocks = P > 1 ? min(sh.part_blocks, (K + BK - 1) / BK - kb0) : (K + BK - 1) / BK;
+  const int bid = (int)blockIdx.x / P, nb = (int)gridDim.x / P;
   const int steps = (k_blocks + G - 1) / G;  // stages' worth of K in a tile
   const int x_bytes = G * RT * 128, w_bytes = G * HALVES * TN * 128;  // of a stage; W as [G][gate rows, up rows][64]
   const int stage_bytes = x_bytes + w_bytes;
   unsigned char* staging = smem + (size_t)stages * stage_bytes;  // [4 warps][2][STAGING], behind the ring
+  float* gather = reinterpret_cast<float*>(staging + 8 * STAGING);  // first block of a cluster: [P - 1][RT][TN + 4] sums of the other parts
   const int acc_cols = HALVES * TN, W = sh.issuers < steps ? sh.issuers : steps;  // warps that issue at all
 
   if (tid == 0) {
@@ -160,6 +194,10 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (lane < stages) { mbar_init(&full_bar[lane], 1); mbar_init(&empty_bar[lane], 1); }
     if (lane >= 16 && lane < 18) { mbar_init(&acc_full[lane - 16], (unsigned)W); mbar_init(&acc_empty[lane - 16], 4); }
     if (lane == 18) abort_s = 0;
+    if (lane == 19) {  // the bytes of the other parts' copies are counted here (first block of a cluster)
+      mbar_init(&gathered, 1);
+      if (P > 1 && rank == 0) mbar_expect_tx(&gathered, (unsigned)((P - 1) * RT * (TN + 4) * 4));
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -170,6 +208,17 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = tmem_base_s;
+  // Every block of a cluster says that its barriers exist; who writes into the first block waits for that, at the end.
+  if (P > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  // Every thread of a cluster's block passes here once, when its own work is done: the first meeting is over by then;
+  // it arrives at the second, and in a block that sent its sums away it stays until the first block has them.
+  auto cluster_leave = [&]() {
+    if (P > 1) {
+      asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+      asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+      if (rank > 0) asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    }
+  };
   chain_release();
 
   // A bounded wait that also ends when another role has given up; nothing but the poll itself on the fast path.
@@ -189,7 +238,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   };
 
   // Loads of this block in all, and how many of them fill the ring for the first time.
-  const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int my_tiles = bid < tiles ? (tiles - bid + nb - 1) / nb : 0;
   const int total = my_tiles * steps, head = total < stages ? total : stages;
 
   if (warp == 0) {
@@ -198,13 +247,13 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       // Where the next load goes: tile, step of K within it, stage of the ring; counted up, never divided.
       struct Cursor { int tile, st, s; unsigned char* dst; };
       auto advance = [&](Cursor& c) {
-        if (++c.st == steps) { c.st = 0; c.tile += (int)gridDim.x; }
+        if (++c.st == steps) { c.st = 0; c.tile += nb; }
         c.dst += stage_bytes;
         if (++c.s == stages) { c.s = 0; c.dst = smem; }
       };
       auto load_w = [&](const Cursor& c) {
         unsigned char* dst = c.dst + x_bytes;
-        const int kb = c.st * G, row = c.tile * TN;
+        const int kb = kb0 + c.st * G, row = c.tile * TN;
         mbar_expect_tx(&full_bar[c.s], stage_bytes);
         if (sh.wide) {
           if (SWIGLU) tma_load_4d(dst, &map_w, row, kb, &full_bar[c.s]); else tma_load_3d(dst, &map_w, row, kb, &full_bar[c.s]);
@@ -216,7 +265,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
       };
       auto load_x = [&](const Cursor& c) {
-        const int kb = c.st * G;
+        const int kb = kb0 + c.st * G;
         if (sh.wide) {
           tma_load_3d(c.dst, &map_x, 0, kb, &full_bar[c.s]);
         } else {
@@ -225,7 +274,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       };
       // The ring's first filling: the weights from here, at once (no kernel writes them); the token rows from a thread
       // of the read-out warps, which has nothing else to do yet, as soon as the predecessor on the stream is done.
-      Cursor c = {(int)blockIdx.x, 0, 0, smem};
+      Cursor c = {bid, 0, 0, smem};
       for (int i = 0; i < head; ++i, advance(c)) load_w(c);
       chain_wait();
       unsigned parity = 0;  // of the "empty" barriers in this round of the ring
@@ -236,6 +285,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (c.s == stages - 1) parity ^= 1;
       }
     }
+    cluster_leave();
   } else if (warp <= ISSUERS) {
     // ------------------------------------------------------------------ tensor cores: warps 1..W, stage i to warp 1 + i % W.
     // The ring's depth is a multiple of W (the host sees to it), so a slot of the ring is always the same warp's.
@@ -252,7 +302,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       unsigned parity = 0, t = 0;
       uint64_t stage_desc = ring_desc;
       bool lost = false;
-      for (int tile = blockIdx.x; tile < tiles && !lost; tile += gridDim.x, ++t) {
+      for (int tile = bid; tile < tiles && !lost; tile += nb, ++t) {
         const unsigned acc = t % (unsigned)sh.buffers;
         if (!wait_for(&acc_empty[acc], ((t / (unsigned)sh.buffers) & 1) ^ 1, 2)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -284,16 +334,18 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         umma_commit(&acc_full[acc]);  // this warp's share of the tile is summed (every issuing warp has a stage in every tile)
       }
     }
+    cluster_leave();
   } else {
     // ------------------------------------------------------------------ read-out: the last four warps
     const int sub = warp & 3;  // the tensor-memory sub-partition (32 lanes) this warp may read
     unsigned char* stage_of_warp = staging + (size_t)sub * 2 * STAGING;
     const int row0 = sub * 32;  // this warp's 32 token rows; lane l holds row0 + l
     unsigned t = 0, stores = 0;
+    bool left = false;  // whether this thread has passed the cluster's second meeting (every thread must, once)
     chain_wait();  // the residual stream that ACC adds to is an earlier kernel's, and so are the token rows
     if (warp == THREADS / 32 - 1 && lane == 0) {  // the token rows of the ring's first filling
       for (int i = 0; i < head; ++i) {
-        const int kb = (i % steps) * G;
+        const int kb = kb0 + (i % steps) * G;
         unsigned char* dst = smem + (size_t)i * stage_bytes;
         if (sh.wide) {
           tma_load_3d(dst, &map_x, 0, kb, &full_bar[i]);
@@ -302,7 +354,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
       }
     }
-    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t) {
+    for (int tile = bid; tile < tiles; tile += nb, ++t) {
       const unsigned acc = t % (unsigned)sh.buffers;
       const int n0 = tile * TN;
       int ok = 1;
@@ -310,6 +362,61 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       if (!__shfl_sync(0xffffffffu, ok, 0)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const unsigned taddr = tmem_base + acc * W * acc_cols + ((unsigned)row0 << 16);
+      if (EPI == EPI_ACC && P > 1 && rank > 0) {
+        // A part of K that is not the first: this block's sums go into its own shared memory, [token row][TN + 4]
+        // float32 (the ring is free: every stage has been multiplied), and from there to the first block with one copy.
+        float* mine = reinterpret_cast<float*>(smem);
+        const int pitch = TN + 4;  // 16 bytes of padding a row: a warp's 16-byte stores and loads meet no bank twice
+        if (row0 < M) {  // the whole warp reads tensor memory (the loads are warp-wide); rows past RT are not kept
+#pragma unroll 1
+          for (int c = 0; c < TN; c += 16) {
+            float v[16];
+            tmem_sum16(taddr + c, W, acc_cols, v);
+            if (row0 + lane < RT) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<float4*>(mine + (size_t)(row0 + lane) * pitch + c + 4 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        fence_async_smem();
+        asm volatile("bar.sync 2, 128;" ::: "memory");  // the four read-out warps: the block's sums are in place
+        if (warp == 1 + ISSUERS && lane == 0) {
+          asm volatile("barrier.cluster.wait.acquire;" ::: "memory");  // (arrived at the start) the first block's barrier exists
+          const unsigned bytes = (unsigned)(RT * pitch * 4);
+          asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(peer_address(gather, 0) + (unsigned)(rank - 1) * bytes), "r"(smem_u32(mine)), "r"(bytes),
+                         "r"(peer_address(&gathered, 0)) : "memory");
+          asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+          asm volatile("barrier.cluster.wait.acquire;" ::: "memory");  // the first block has the sums: this block may go
+        } else {
+          cluster_leave();
+        }
+        left = true;
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        continue;
+      }
+      if (EPI == EPI_ACC && P > 1) {  // the first part: the others' sums have arrived in this block's shared memory
+        int here = 1;
+        if (lane == 0) {
+          here = 0;
+          const unsigned addr = smem_u32(&gathered);
+          for (unsigned spin = 0; spin < kSpinLimit && !here; ++spin) {
+            unsigned done;
+            asm volatile(
+                "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                : "=r"(done) : "r"(addr), "r"(0u) : "memory");
+            here = done != 0;
+            if (!here && *(volatile int*)&abort_s) break;
+          }
+          if (!here) { *(volatile int*)&abort_s = 1; atomicExch(&g_rows_status, 4); }
+        }
+        const int got = __shfl_sync(0xffffffffu, here, 0);
+        cluster_leave();  // (the peers may go: their sums are here, or are given up)
+        left = true;
+        if (!got) break;
+      }
       if (row0 < M) {
 #pragma unroll 1
         for (int c = 0; c < TN; c += 16, ++stores) {
@@ -319,6 +426,16 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           __syncwarp();
           float v[16];
           tmem_sum16(taddr + c, W, acc_cols, v);
+          if (EPI == EPI_ACC && P > 1 && row0 + lane < RT) {  // the parts in the order of their numbers
+            for (int r = 0; r < P - 1; ++r) {
+              const float4* part = reinterpret_cast<const float4*>(gather + ((size_t)r * RT + row0 + lane) * (TN + 4) + c);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float4 q = part[j];
+                v[4 * j] += q.x; v[4 * j + 1] += q.y; v[4 * j + 2] += q.z; v[4 * j + 3] += q.w;
+              }
+            }
+          }
           if (EPI == EPI_ACC || EPI == EPI_F32) {
             // row `lane` of 64 bytes, its 16-byte units XORed with bits 7-8 of the address (the 64-byte swizzle)
 #pragma unroll
@@ -355,6 +472,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
     if (lane == 0) bulk_wait_all();  // what this warp handed to TMA has been written before the block may leave
     __syncwarp();
+    if (!left) cluster_leave();  // (a wait gave up before the parts met)
   }
 
   // wind down: everyone meets, then the allocating warp frees tensor memory
@@ -442,7 +560,7 @@ int env_int(const char* name, int fallback) {
 
 // How a product is cut: the tile width that gives every SM the same number of tiles, the steps of K per stage and the
 // depth of the ring that fit the shared memory. Returns false if the kernel does not take these sizes.
-bool plan(Shape* sh, int M, int O, int K, int epilogue, int sms, int budget) {
+bool plan(Shape* sh, int M, int O, int K, int epilogue, int sms, int budget, int parts = 0) {
   const bool swiglu = epilogue == EPI_SWIGLU;
   const int out_cols = swiglu ? O / 2 : O, halves = swiglu ? 2 : 1;
   const int widest = 256 / halves;  // two accumulators of halves * tile_n columns in 512 columns of tensor memory
@@ -451,9 +569,31 @@ bool plan(Shape* sh, int M, int O, int K, int epilogue, int sms, int budget) {
   const int rounds = (out_cols + widest * sms - 1) / (widest * sms);  // tiles a block walks
   int tile_n = ((out_cols + rounds * sms - 1) / (rounds * sms) + 15) / 16 * 16;
   if (tile_n > widest) tile_n = widest;
+  const int all_blocks = (K + BK - 1) / BK;
+  // Parts of K (the residual read-out, K a multiple of 64, one tile per block): tiles `parts` times as wide, so that a
+  // block reads a part of x only. Taken where x is most of what a block reads: from K = 4,096 on, the cut that leaves
+  // a block the fewest bytes of 1, 2 and 4 (AKAS_B200_ROWS_PARTS forces one).
+  if (parts == 0) {
+    parts = 1;
+    const int forced = env_int("AKAS_B200_ROWS_PARTS", 0);
+    if (epilogue == EPI_ACC && K % 64 == 0 && rounds == 1 && (forced > 1 || (forced == 0 && K >= 4096))) {
+      long long best = (long long)(sh->RT + tile_n) * K;
+      for (int p = 2; p <= 4; p *= 2) {
+        if (forced > 1 && p != forced) continue;
+        const int wide_n = ((out_cols * p + sms - 1) / sms + 15) / 16 * 16;
+        if (wide_n > widest || ((out_cols + wide_n - 1) / wide_n) * p > sms || all_blocks < 4 * p) continue;
+        const long long bytes = (long long)(sh->RT + wide_n) * K / p;
+        if (forced > 1 || bytes * 4 <= best * 3) { best = bytes; parts = p; }
+      }
+    }
+  }
+  if (parts > 1) tile_n = ((out_cols * parts + sms - 1) / sms + 15) / 16 * 16;
   sh->tile_n = tile_n;
   sh->wide = K % 64 == 0 ? 1 : 0;
-  const int k_blocks = (K + BK - 1) / BK;
+  sh->parts = parts;
+  const int gather_bytes = parts > 1 ? (parts - 1) * sh->RT * (tile_n + 4) * (int)sizeof(float) : 0;
+  budget -= gather_bytes;
+  int k_blocks = all_blocks;  // of a part
   const int step_bytes = (sh->RT + halves * tile_n) * 128;
   // All of an SM's shared memory by default. AKAS_B200_ROWS_SMEM_KB gives a block less (and at most half of tensor
   // memory), so that a block of the next kernel on the stream can set itself up and fetch its first weights beside a
@@ -481,6 +621,12 @@ bool plan(Shape* sh, int M, int O, int K, int epilogue, int sms, int budget) {
   if (stages > cap) stages = cap;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   sh->G = g;
+  sh->part_blocks = all_blocks;
+  if (parts > 1) {  // a part: a whole number of stages, and the last part is not empty
+    sh->part_blocks = ((all_blocks + parts - 1) / parts + g - 1) / g * g;
+    if ((parts - 1) * sh->part_blocks >= all_blocks) return false;
+    k_blocks = sh->part_blocks;
+  }
   const int tiles = (out_cols + tile_n - 1) / tile_n;
   sh->buffers = tiles > sms ? 2 : 1;
   // As many issuing warps as tensor memory has accumulators for, at most one per stage of a tile. The ring's depth is
@@ -500,6 +646,31 @@ bool plan(Shape* sh, int M, int O, int K, int epilogue, int sms, int budget) {
   sh->tmem_cols = 32;
   while (sh->tmem_cols < sh->buffers * issuers * halves * tile_n) sh->tmem_cols *= 2;
   return sh->tmem_cols <= 512;
+}
+
+// The launch of a product that is not cut along K (also where a cut was planned and the device cannot place its clusters).
+template <int EPI, typename Kernel>
+int launch_uncut(Kernel kernel, const void* x, const void* w, const CUtensorMap& map_y, const Shape& sh, int M, int O,
+                 int K, int sms, cudaStream_t stream) {
+  constexpr bool SWIGLU = EPI == EPI_SWIGLU;
+  const int out_cols = SWIGLU ? O / 2 : O, halves = SWIGLU ? 2 : 1;
+  CUtensorMap map_x, map_w;
+  int err = sh.wide ? make_wide_map(&map_x, x, M, K, sh.RT, sh.G) : make_map(&map_x, x, M, K, sh.RT);
+  if (!err) err = weight_map(&map_w, w, O, K, sh.tile_n, sh.G, sh.wide, SWIGLU);
+  if (err) return err;
+  const int tiles = (out_cols + sh.tile_n - 1) / sh.tile_n, per = (tiles + sms - 1) / sms;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((tiles + per - 1) / per);
+  config.blockDim = dim3(THREADS);
+  config.dynamicSmemBytes = sh.stages * sh.G * (sh.RT + halves * sh.tile_n) * 128 + 8 * STAGING + 1024;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = chained_launches_enabled() ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_x, map_w, map_y, sh);
+  return e != cudaSuccess ? (int)e : launch_status();
 }
 
 template <int EPI>
@@ -523,7 +694,10 @@ int launch(const void* x, const void* w, void* y, int M, int O, int K, bool dry,
     }
   }
   Shape sh;
-  if (!plan(&sh, M, O, K, EPI, sms[device], budget[device])) return 3999;
+  if (!plan(&sh, M, O, K, EPI, sms[device], budget[device])) {
+    // (a cut along K that does not fit after all: the product uncut)
+    if (!plan(&sh, M, O, K, EPI, sms[device], budget[device], 1)) return 3999;
+  }
   if (dry) return 0;
   constexpr bool SWIGLU = EPI == EPI_SWIGLU;
   const int out_cols = SWIGLU ? O / 2 : O;
@@ -537,17 +711,48 @@ int launch(const void* x, const void* w, void* y, int M, int O, int K, bool dry,
   const int tiles = (out_cols + sh.tile_n - 1) / sh.tile_n;
   const int per = (tiles + sms[device] - 1) / sms[device];  // tiles per block, and as few blocks as do it in that many rounds
   const int halves = SWIGLU ? 2 : 1;
-  const int smem = sh.stages * sh.G * (sh.RT + halves * sh.tile_n) * 128 + 8 * STAGING + 1024;
+  auto smem_of = [&](const Shape& s) {
+    return s.stages * s.G * (s.RT + halves * s.tile_n) * 128 + 8 * STAGING + 1024 +
+           (s.parts > 1 ? (s.parts - 1) * s.RT * (s.tile_n + 4) * (int)sizeof(float) : 0);
+  };
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3((tiles + per - 1) / per);
+  config.gridDim = dim3(sh.parts > 1 ? tiles * sh.parts : (tiles + per - 1) / per);
   config.blockDim = dim3(THREADS);
-  config.dynamicSmemBytes = smem;
+  config.dynamicSmemBytes = smem_of(sh);
   config.stream = stream;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attribute[2];
+  int n = 0;
+  if (chained_launches_enabled()) {
+    attribute[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (sh.parts > 1) {  // the parts of a tile: a thread-block cluster, if the device can place one
+    attribute[n].id = cudaLaunchAttributeClusterDimension;
+    attribute[n].val.clusterDim.x = sh.parts;
+    attribute[n].val.clusterDim.y = 1;
+    attribute[n].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = n + 1;
+    static std::map<std::tuple<int, int, int>, int> room;  // (device, parts, shared memory) -> clusters resident at once
+    int clusters = 0;
+    {
+      std::lock_guard<std::mutex> lock(mutex);
+      const auto key = std::make_tuple(device, sh.parts, (int)config.dynamicSmemBytes);
+      if (!room.count(key)) {
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) { cudaGetLastError(); clusters = 0; }
+        room[key] = clusters;
+      }
+      clusters = room[key];
+    }
+    if (clusters * sh.parts < (int)config.gridDim.x) {  // all of a launch's clusters are resident at once, or the product goes uncut
+      if (!plan(&sh, M, O, K, EPI, sms[device], budget[device], 1)) return 3999;
+      return launch_uncut<EPI>(kernel, x, w, map_y, sh, M, O, K, sms[device], stream);
+    }
+    ++n;
+  }
   config.attrs = attribute;
-  config.numAttrs = chained_launches_enabled() ? 1 : 0;
+  config.numAttrs = n;
   const cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_x, map_w, map_y, sh);
   return e != cudaSuccess ? (int)e : launch_status();
 }

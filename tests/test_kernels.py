@@ -225,7 +225,8 @@ def test_products_on_pairs_of_sms(ops, m, k, o):
 
 
 @pytest.mark.parametrize("m,k,o", [(17, 64, 48), (64, 2048, 6144), (33, 264, 520), (128, 8192, 2048), (100, 200, 2056),
-                                   (64, 2048, 65536), (20, 1024, 40), (96, 704, 1160), (48, 128, 40000)])
+                                   (64, 2048, 65536), (20, 1024, 40), (96, 704, 1160), (48, 128, 40000), (64, 8192, 2048),
+                                   (33, 4096, 1000), (70, 6912, 1536)])
 def test_products_of_few_rows_stream_the_weights(ops, m, k, o):
     """The one-block tcgen05 kernel for 17 to 128 tokens (tiles as wide as gives every SM one; token rows past the batch
     are never loaded), all four read-outs, at inner sizes that are and are not multiples of 64 (one copy per stage, a
