@@ -20,6 +20,20 @@ def test_products_above_sixteen_tokens_run_on_the_hand_written_kernels(monkeypat
     assert {route(2048, 2048, m) for m in (bf16, f32, acc, swiglu)} == {"library"}
 
 
+def test_key_parts_of_decode_attention():
+    """Two blocks per SM's worth of (request, KV head) parts, at least two parts, at least four 64-key tiles a part."""
+    parts = cuda.decode_splits
+    assert parts(8, 8, 1, 4096) == 5 and parts(64, 8, 1, 4096) == 2 and parts(1, 8, 1, 4096) == 16
+    assert parts(8, 8, 1, 256) == 1 and parts(8, 8, 1, 700) == 3 and parts(256, 8, 1, 2304) == 2
+    assert parts(1, 1, 1, 10 ** 6) == 64
+    # the kernel merges its parts itself while the blocks are few: 8 requests yes, 64 requests no (a merge kernel then)
+    merged = cuda._merges_in_cluster
+    import unittest.mock as mock
+    with mock.patch.object(cuda, "_sm_count", return_value=148):
+        assert merged(64, 5, 64, 64) and not merged(512, 2, 64, 64) and not merged(64, 16, 64, 64)
+        assert not merged(64, 5, 128, 64) and not merged(64, 5, 64, 16)
+
+
 def test_reports_are_compared_case_by_case():
     from akas_b200.bench import case_lengths, compare_reports
 
