@@ -179,6 +179,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             bf16* __restrict__ out, float scale, int window, int page_size, int H, int KH, int R) {
   // The block has no static shared memory, so the dynamic array starts the block's window, 1024-byte aligned (the
   // swizzled tiles need that; it is checked below): with no bytes lost to alignment, two blocks fit an SM.
+  chain_release();  // a kernel after this one that was launched as its programmatic dependent may set itself up meanwhile
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_s = smem;                                   // [128 queries][128 bytes]
   unsigned char* k_s = q_s + TILE_BYTES;                       // [STAGES][128 keys][128 bytes]

@@ -95,6 +95,7 @@ short_conv_forward_run_kernel(const T* __restrict__ bcx, const float* __restrict
                               const float* __restrict__ state, const int* __restrict__ cu_seqlens,
                               const int* __restrict__ seq_of_token, const int* __restrict__ slots, T* __restrict__ out,
                               int N, int C) {
+  chain_release();  // a kernel after this one that was launched as its programmatic dependent may set itself up meanwhile
   const int t0 = blockIdx.x * TT;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (c >= C) return;
@@ -171,6 +172,7 @@ template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int C,
                                         int L) {
+  chain_release();  // a kernel after this one that was launched as its programmatic dependent may set itself up meanwhile
   const int r = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;

@@ -32,6 +32,7 @@ AKAS_API int akas_embedding(const int* tokens, const void* table, float* out, in
 template <typename TI, typename TO>
 __global__ void rmsnorm_kernel(const TI* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
                                const int* __restrict__ rows, int C, float eps, int zero_centered) {
+  chain_release();  // a kernel after this one that was launched as its programmatic dependent may set itself up meanwhile
   __shared__ float scratch[32];
   const int i = blockIdx.x;
   const TI* src = x + (size_t)(rows ? rows[i] : i) * C;
@@ -55,6 +56,7 @@ template <typename TO, int PER_THREAD>  // PER_THREAD groups of 8 elements per t
 __global__ void __launch_bounds__(256)
 rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
                     const int* __restrict__ rows, int C, float eps, int zero_centered) {
+  chain_release();  // a kernel after this one that was launched as its programmatic dependent may set itself up meanwhile
   __shared__ float scratch[32];
   const int i = blockIdx.x;
   const float* src = x + (size_t)(rows ? rows[i] : i) * C;

@@ -8,6 +8,8 @@
 // tile: a product of the pair reads the channels from both blocks' shared memory. That halves what a block writes
 // into and reads out of its shared memory per multiply-add, which is what bounds a one-block kernel (its TMA writes
 // and operand reads ask for 192 bytes a cycle of a shared memory that gives 128).
+//   The kernel is launched as a programmatic dependent of the kernel before it on the stream: it sets itself up and
+//   asks for its first weights while that kernel drains, and waits for it before it touches the token rows.
 //   warp 0   producer, in both blocks: TMA loads of the block's slice of x and of W into a ring of stages of two
 //            64-wide steps of K each: ONE copy per operand and stage (a box of two groups of 64 k from a view
 //            [K / 64][rows][64] of the matrix; starting a copy costs the issuing thread some 300 cycles whatever it
@@ -175,6 +177,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   cluster_meet();  // the peer's barriers exist and its tensor memory is allocated before anything arrives there
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = tmem_base_s;
+  chain_release();  // (programmatic dependent launch) the next kernel on the stream may set itself up beside this one
 
   auto wait_for = [&](uint64_t* bar, unsigned parity, int code) {
     if (*(volatile int*)&abort_s) return;
@@ -187,30 +190,37 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (both blocks)
     if (lane == 0) {
-      unsigned it = 0;
-      for (int tile = pair; tile < tiles; tile += pairs) {
+      // The ring's first filling asks for the weights at once (no kernel writes them) and for the token rows only when
+      // the kernel before this one on the stream is done; from then on a stage's two copies go out together.
+      const int per_tile = (k_blocks + STEPS - 1) / STEPS;  // stages of a tile
+      const int my_tiles = pair < tiles ? (tiles - pair + pairs - 1) / pairs : 0;
+      const int total = my_tiles * per_tile, head = total < STAGES ? total : STAGES;
+      auto load = [&](int i, bool weights, bool rows) {
+        const int tile = pair + (i / per_tile) * pairs, kb = (i % per_tile) * STEPS, s = i % STAGES;
         const int m0 = (tile / tiles_n) * 2 * BM + (int)rank * BM, n0 = (tile % tiles_n) * TILE_N;
         // this block's half of the tile's channels: rows of W
         const int w_row = EPI == EPI_SWIGLU ? (rank == 0 ? n0 : F + n0) : n0 + (int)rank * (BN / 2);
-        for (int kb = 0; kb < k_blocks; kb += STEPS, ++it) {
-          const int s = it % STAGES;
-          wait_for(&empty_bar[s], ((it / STAGES) & 1) ^ 1, 1);
-          if (*(volatile int*)&abort_s) break;
-          unsigned char* a = smem + (size_t)s * STAGE_BYTES;
-          const unsigned leader_full = peer_address(&full_bar[s], 0);
-          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);  // the bytes of both blocks
-          if (WIDE) {  // K is a multiple of 64: both steps of K in one copy per operand (groups past K: zeros)
-            tma_load_3d_for(a, &map_x, m0, kb, leader_full);
-            tma_load_3d_for(a + STEPS * A_BYTES, &map_w, w_row, kb, leader_full);
-          } else {
+        unsigned char* a = smem + (size_t)s * STAGE_BYTES;
+        const unsigned leader_full = peer_address(&full_bar[s], 0);
+        if (weights && rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);  // the bytes of both blocks
+        if (WIDE) {  // K is a multiple of 64: both steps of K in one copy per operand (groups past K: zeros)
+          if (rows) tma_load_3d_for(a, &map_x, m0, kb, leader_full);
+          if (weights) tma_load_3d_for(a + STEPS * A_BYTES, &map_w, w_row, kb, leader_full);
+        } else {
 #pragma unroll
-            for (int h = 0; h < STEPS; ++h) {  // a step past the end of K is filled with zeros
-              tma_load_2d_for(a + h * A_BYTES, &map_x, (kb + h) * BK, m0, leader_full);
-              tma_load_2d_for(a + STEPS * A_BYTES + h * S::B_BYTES, &map_w, (kb + h) * BK, w_row, leader_full);
-            }
+          for (int h = 0; h < STEPS; ++h) {  // a step past the end of K is filled with zeros
+            if (rows) tma_load_2d_for(a + h * A_BYTES, &map_x, (kb + h) * BK, m0, leader_full);
+            if (weights) tma_load_2d_for(a + STEPS * A_BYTES + h * S::B_BYTES, &map_w, (kb + h) * BK, w_row, leader_full);
           }
         }
+      };
+      for (int i = 0; i < head; ++i) load(i, true, false);
+      chain_wait();
+      for (int i = 0; i < head; ++i) load(i, false, true);
+      for (int i = head; i < total; ++i) {
+        wait_for(&empty_bar[i % STAGES], ((i / STAGES) & 1) ^ 1, 1);
         if (*(volatile int*)&abort_s) break;
+        load(i, true, true);
       }
     }
   } else if (warp == 1) {
@@ -250,6 +260,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const int sub = warp & 3;  // the tensor-memory sub-partition (32 lanes) this warp may read
     unsigned char* stage_of_warp = staging + (size_t)sub * 2 * STAGING;
     unsigned t = 0, stores = 0;
+    chain_wait();  // what the read-out adds to is an earlier kernel's
     for (int tile = pair; tile < tiles; tile += pairs, ++t) {
       const unsigned acc = t & 1;
       const int m0 = (tile / tiles_n) * 2 * BM + (int)rank * BM, n0 = (tile % tiles_n) * TILE_N;
@@ -435,13 +446,15 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, cudaStrea
   config.blockDim = dim3(THREADS);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attribute[1];
+  cudaLaunchAttribute attribute[2];
   attribute[0].id = cudaLaunchAttributeClusterDimension;
   attribute[0].val.clusterDim.x = 2;
   attribute[0].val.clusterDim.y = 1;
   attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = 1;
+  config.numAttrs = chained_launches_enabled() ? 2 : 1;
   const cudaError_t e = cudaLaunchKernelEx(&config, gemm_pair_kernel<BN, EPI, WIDE>, map_x, map_w, map_y, M, N, K, F);
   return e != cudaSuccess ? (int)e : launch_status();
 }
