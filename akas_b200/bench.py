@@ -98,8 +98,10 @@ def fill_requests(runner: ModelRunner, prompts: Sequence[Sequence[int]], chunk: 
     return ids
 
 
-def measure_prefill(runner: ModelRunner, prompt: Sequence[int], repeats: int = 3, warmup: int = 1) -> float:
-    """Median milliseconds to run one whole prompt and produce its first token (head and argmax included)."""
+def measure_prefill(runner: ModelRunner, prompt: Sequence[int], repeats: int = 7, warmup: int = 3) -> float:
+    """Median milliseconds to run one whole prompt and produce its first token (head and argmax included). The warm-up
+    runs also let the step function capture the prompt's shape (it does when a shape comes a third time), so the timed
+    runs are replays, as in serving where portions of one size keep coming."""
     times = []
     for i in range(warmup + repeats):
         def run():

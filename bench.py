@@ -165,7 +165,7 @@ def main():
 
         # prefill of 2,048 tokens, one request
         prompt = synthetic_prompts(1, PROMPT, model_config.vocab_size)[0]
-        pre_ms = measure_prefill(runner, prompt, repeats=5, warmup=2)
+        pre_ms = measure_prefill(runner, prompt, repeats=7, warmup=3)
         pre_flops = prefill_flops(runner, PROMPT)
         flop_peak = (pk["bf16_tflops"] if args.dtype == "bfloat16" else pk["fp32_tflops"]) * 1e12
 
