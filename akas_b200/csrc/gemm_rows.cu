@@ -287,8 +287,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
     cluster_leave();
   } else if (warp <= ISSUERS) {
-    // ------------------------------------------------------------------ tensor cores: warps 1..W, stage i to warp 1 + i % W.
-    // The ring's depth is a multiple of W (the host sees to it), so a slot of the ring is always the same warp's.
+    // ------------------------------------------------------------------ tensor cores: warps 1..W, stage i to warp 1 + i % W
     const int me = warp - 1;
     if (lane == 0 && me < W) {
       // instruction descriptor: float32 accumulate, bfloat16 A and B, both K-major, N = the tile's stacked rows, M = 128
@@ -312,8 +311,12 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         for (int st = 0; st < steps; ++st) {
           const int gs = left < G ? left : G;  // a stage's steps past the end of K hold zeros: nothing to add
           left -= gs;
+          // Every issuing warp sees every stage fill, in order, also those it leaves to the others: a warp that looked at
+          // a slot of the ring only every few fillings could ask its barrier for a phase whose parity reads "complete"
+          // before the slot has been filled at all (the phase before the first has that parity). In order, and with the
+          // producer held back by this warp's own uncommitted stage, it can never fall two fillings of a slot behind.
+          if (!wait_for(&full_bar[s], parity, 2)) { lost = true; break; }
           if (turn == me) {
-            if (!wait_for(&full_bar[s], parity, 2)) { lost = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint64_t a_desc = stage_desc, b_desc = stage_desc + x_units;
             for (int g = 0; g < gs; ++g) {
@@ -629,9 +632,7 @@ bool plan(Shape* sh, int M, int O, int K, int epilogue, int sms, int budget, int
   }
   const int tiles = (out_cols + tile_n - 1) / tile_n;
   sh->buffers = tiles > sms ? 2 : 1;
-  // As many issuing warps as tensor memory has accumulators for, at most one per stage of a tile. The ring's depth is
-  // a multiple of their number, so that a slot of the ring is always the same warp's: a warp that waited for a slot's
-  // second filling before another had seen the first would find its parity already "complete".
+  // As many issuing warps as tensor memory has accumulators for, at most one per stage of a tile or of the ring.
   const int steps = (k_blocks + g - 1) / g;
   int issuers = env_int("AKAS_B200_ROWS_ISSUERS", ISSUERS);
   if (issuers > ISSUERS) issuers = ISSUERS;
@@ -639,7 +640,6 @@ bool plan(Shape* sh, int M, int O, int K, int epilogue, int sms, int budget, int
   if (issuers > stages) issuers = stages;
   while (issuers > 1 && sh->buffers * issuers * halves * tile_n > tmem_cap) --issuers;
   if (issuers < 1) issuers = 1;
-  stages -= stages % issuers;
   sh->stages = stages;
   sh->issuers = issuers;
   sh->suspend_ns = (unsigned)env_int("AKAS_B200_ROWS_SUSPEND_NS", 200);
