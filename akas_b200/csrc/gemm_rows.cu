@@ -1,7 +1,7 @@
 // bfloat16 matrix products for 17 to 128 tokens (a decode step of many requests, a short prompt portion):
 // y[M, O] = x[M, K] . W[O, K]^T with tcgen05.mma, float32 accumulation in tensor memory, epilogues fused into the
 // read-out and written by TMA. The time of such a product is the time to read W once, so the kernel is a stream
-// of weights through as many SMs as there are: no cluster, no split of K, one block per SM.
+// of weights through as many SMs as there are, one block per SM (a long K is cut over a cluster, see "Parts of K").
 //
 // The token rows are the 128 lanes of the accumulator (rows past M are never read), the channels its columns. The
 // output is cut into tiles of TILE_N channels, TILE_N the multiple of 16 that gives every SM one tile (or two, three
@@ -19,7 +19,8 @@
 //            stage: per step of K four tcgen05.mma (M 128, N TILE_N, or 2 TILE_N for SwiGLU, whose gate and up rows lie
 //            behind one another in a stage; K 16), then a commit to the stage's "empty" barrier. Issuing a product costs
 //            its thread some 55 cycles however small the product is, which for these thin tiles is more than the tensor
-//            cores need for it: several issuing threads, each with an accumulator of its own, keep them busy. The
+//            cores need for it: several issuing threads, each with an accumulator of its own, keep them busy. Each of
+//            them waits for every stage in order, also for those it leaves to the others (see there). The
 //            operand of the token rows is read as 128 rows although only RT were loaded: the rest is whatever lies
 //            behind in shared memory, and lands in accumulator lanes that nobody reads.
 //   warps 5-8 read-out: each warp owns the 32 accumulator lanes (token rows) of its sub-partition; those whose rows lie
@@ -44,7 +45,8 @@
 // mbarrier exists before a peer's copy counts on it, once so that a peer's shared memory lives until its copy has
 // been received.
 // Every wait on an mbarrier is bounded (akas_gemm_rows_status): one that runs out sets a status word, every role
-// falls through, tensor memory is freed and the block returns; that launch's results are not valid.
+// falls through, tensor memory is freed and the block returns; that launch's results are not valid. The cluster's
+// barrier has no bounded form; every thread arrives at it without condition, or after a bounded wait of its own.
 #include <math.h>
 
 #include "tcgen05.cuh"
