@@ -199,11 +199,12 @@ def run_matrix(model_dir, config, batches=(1, 8), prompts=(2048,), generated=128
                     tokens = holder["t"]
 
                     def decode():
+                        # every step feeds the tokens that the step before picked; they stay on the device (an entry
+                        # names its place among them), as in the engine's own loop, so nothing waits for the host
                         t = tokens
+                        entries = [StepEntry(rid, (0,), (0,), source=j) for j, rid in enumerate(ids)]
                         for _ in range(generated - 1):
-                            host = t.tolist()
-                            logits = runner.step([StepEntry(rid, (host[j],), (0,)) for j, rid in enumerate(ids)])
-                            t = runner.ops.argmax(logits)
+                            t = runner.ops.argmax(runner.step(entries, previous=t))
 
                     tg_ms = _event_ms(decode)
                     for rid in ids:
