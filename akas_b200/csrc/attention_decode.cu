@@ -15,6 +15,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "qk_prep.cuh"
 #include "mma.cuh"
 #include "tcgen05.cuh"
 
@@ -271,12 +272,31 @@ __device__ __forceinline__ void peer_store(unsigned address, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(v) : "memory");
 }
 
+// The token's own q, k and v as the qkv product left them, [N, (H + 2 KH) * 64], for a kernel that does what lies
+// between that product and attention itself: the per-head RMSNorm and rotation of q (every block, for its own rows,
+// on the way into shared memory) and of k, and the write of k and v into the pages. The block that holds the last key
+// tile does the latter and puts the two rows into its tile in shared memory as well, since its TMA load may have read
+// the page before the write landed. With qkv == nullptr, q is ready and the pages hold the token already.
+struct Fresh {
+  const bf16* qkv;
+  const float* q_w;    // the norms' weights over a head (nullptr: no norm)
+  const float* k_w;
+  float eps;
+  int zero_centered;
+  const float* cos_t;  // [N, rotary / 2] each (nullptr: no rotation)
+  const float* sin_t;
+  int rotary;
+  bf16* k_pool;        // nullptr: a layer that only reads the pages; they are attended as they are
+  bf16* v_pool;
+};
+
 __global__ void __launch_bounds__((WARPS + 1) * 32)
 decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const bf16* __restrict__ q, const int* __restrict__ block_table, int max_blocks,
                             const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                             bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, float scale,
-                            int window, int page_size, int H, int KH, int row_tiles, int splits, int in_cluster) {
+                            int window, int page_size, int H, int KH, int row_tiles, int splits, int in_cluster,
+                            const Fresh fresh) {
   // in_cluster: the blocks of a (token, KV head)'s key parts form a thread-block cluster; their partial results meet in
   // the first block's shared memory and that block writes the output, instead of a second kernel over global scratch.
   using namespace akas::tc;
@@ -351,13 +371,53 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   // -------------------------------------------------------------------- consumers: warps 0..3
   auto consumers_meet = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory"); };
-  for (int c = tid; c < ROWS * CHUNKS; c += WARPS * 32) {
-    const int row = c / CHUNKS, col = (c % CHUNKS) * 8;
-    const bf16* src = q + ((size_t)tok * H + head0 + min(row, gn - 1)) * D + col;
-    cp_async16(q_s + row * STRIDE + col, src, row < gn ? 16 : 0);
+  uint4 new_row = make_uint4(0u, 0u, 0u, 0u);  // first warp, lanes 0..7: the token's k row; lanes 8..15: its v row
+  const bool holds_last = lo <= kt_last && kt_last < hi;
+  const bool patches = fresh.qkv != nullptr && fresh.k_pool != nullptr && holds_last;
+  if (fresh.qkv == nullptr) {
+    for (int c = tid; c < ROWS * CHUNKS; c += WARPS * 32) {
+      const int row = c / CHUNKS, col = (c % CHUNKS) * 8;
+      const bf16* src = q + ((size_t)tok * H + head0 + min(row, gn - 1)) * D + col;
+      cp_async16(q_s + row * STRIDE + col, src, row < gn ? 16 : 0);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+  } else {
+    static_assert(ROWS * CHUNKS == WARPS * 32, "one thread per 8 channels of the query tile");
+    const int total = H + 2 * KH, half = fresh.rotary / 2;
+    const float* cos_row = fresh.cos_t ? fresh.cos_t + (size_t)tok * half : nullptr;
+    const float* sin_row = fresh.cos_t ? fresh.sin_t + (size_t)tok * half : nullptr;
+    const bf16* token = fresh.qkv + (size_t)tok * total * D;
+    const int row = tid / CHUNKS, e0 = (tid % CHUNKS) * 8;
+    float x[8];
+    load8(token + (size_t)(head0 + min(row, gn - 1)) * D + e0, x);
+    head_norm_rotate8<CHUNKS>(x, e0, fresh.q_w, fresh.eps, fresh.zero_centered, cos_row, sin_row, fresh.rotary);
+    if (row >= gn) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = 0.f;
+    }
+    store8(q_s + row * STRIDE + e0, x);
+    if (patches && warp == 0) {  // (a whole warp: the norm and the rotation shuffle)
+      const int which = lane / CHUNKS;  // 0: k; 1: v; the others shadow k
+      load8(token + (size_t)(which == 1 ? H + KH + kvh : H + kvh) * D + e0, x);
+      float turned[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) turned[e] = x[e];
+      head_norm_rotate8<CHUNKS>(turned, e0, fresh.k_w, fresh.eps, fresh.zero_centered, cos_row, sin_row, fresh.rotary);
+      if (which != 1) {  // v goes as it is (its lanes took part in the shuffles above all the same)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = turned[e];
+      }
+      new_row = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+      if (row_tile == 0 && which < 2) {  // one block per (token, KV head) writes the pages
+        const int page = block_table[(size_t)r * max_blocks + pos / page_size];
+        if (page >= 0) {
+          bf16* pool = which == 0 ? fresh.k_pool : fresh.v_pool;
+          *reinterpret_cast<uint4*>(pool + (((size_t)page * KH + kvh) * page_size + pos % page_size) * D + e0) = new_row;
+        }
+      }
+    }
   }
-  cp_async_commit();
-  cp_async_wait<0>();
   consumers_meet();
   uint32_t qf[KS][4];
 #pragma unroll
@@ -375,9 +435,14 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   for (int kt = lo; kt < hi; ++kt) {
     const int i = kt - lo, s = i % TMA_STAGES;
     wait_for(&full_bar[s], (i / TMA_STAGES) & 1, 1);
-    const unsigned char* kt_ = k_t + s * TMA_TILE;
+    unsigned char* kt_ = k_t + s * TMA_TILE;
     unsigned char* vt_ = v_t + s * TMA_TILE;
-    if (kt == kt_last && pos % BK != BK - 1) {  // rows of V past the position: zero
+    if (kt == kt_last && (patches || pos % BK != BK - 1)) {
+      if (patches && warp == 0 && lane < 2 * CHUNKS) {  // the token's own k and v rows, whatever the load found there
+        const int p = pos % BK;
+        *reinterpret_cast<uint4*>((lane < CHUNKS ? kt_ : vt_) + p * 128 + (((lane % CHUNKS) ^ (p & 7)) << 4)) = new_row;
+      }
+      // rows of V past the position: zero
       for (int c = tid + (pos % BK + 1) * 8; c < BK * 8; c += WARPS * 32)
         *reinterpret_cast<uint4*>(vt_ + c * 16) = make_uint4(0u, 0u, 0u, 0u);
       consumers_meet();
@@ -570,7 +635,8 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* blo
 // Head size 64, pages of whole tiles: the TMA-fed kernel. pool_rows: pages x kv heads x page size.
 int launch_tma(const void* q, const void* k_pool, const void* v_pool, long long pool_rows, const int* block_table,
                int max_blocks, const int* seq_of_token, const int* positions, void* out, float* part_o, float* part_ml,
-               float scale, int window, int page_size, int N, int H, int KH, int splits, cudaStream_t stream) {
+               float scale, int window, int page_size, int N, int H, int KH, int splits, cudaStream_t stream,
+               const Fresh& fresh = Fresh{}) {
   constexpr int D = 64, MAX_CLUSTER = 8;
   constexpr int smem = 1024 + 2 * TMA_STAGES * TMA_TILE + ROWS * (D + 8) * (int)sizeof(bf16) + (2 * TMA_STAGES + 1) * 8 + 16;
   constexpr int gather_most = (MAX_CLUSTER - 1) * ROWS * (D + 2) * (int)sizeof(float);  // the other parts, in the first block
@@ -636,7 +702,7 @@ int launch_tma(const void* q, const void* k_pool, const void* v_pool, long long 
   if (!in_cluster && splits > 1 && (part_o == nullptr || part_ml == nullptr)) return (int)cudaErrorInvalidValue;
   err = (int)cudaLaunchKernelEx(&config, decode_attention_tma_kernel, map_k, map_v, (const bf16*)q, block_table, max_blocks,
                                 seq_of_token, positions, (bf16*)out, part_o, part_ml, scale, window, page_size, H, KH,
-                                row_tiles, splits, in_cluster);
+                                row_tiles, splits, in_cluster, fresh);
   if (err || splits == 1 || in_cluster) return err;
   return launch_chained(decode_merge_bf16_kernel, dim3(N, H), dim3(64), 0, stream, (const float*)part_o,
                         (const float*)part_ml, seq_of_token, (bf16*)out, H, D, splits);
@@ -697,6 +763,40 @@ AKAS_API int akas_decode_attention_bf16_paged(const void* q, const void* k_pool,
   }
   return akas_decode_attention_bf16(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, part_o,
                                     part_ml, scale, window, page_size, N, H, KH, D, splits, stream);
+}
+
+// Decode attention straight from the qkv product, [N, (H + 2 KH) * D] bfloat16: the per-head RMSNorm (q_w, k_w:
+// float32 [D], or null) and rotation (cos_t, sin_t: float32 [N, rotary / 2], or null) of q and k, the write of the
+// token's k and v rows into the pages (write == 0: a layer that only reads them) and attention, as one kernel.
+// Returns 3999 where that kernel does not take the sizes (head size 64, page size a multiple of 64, a rotary width
+// that is a multiple of 16, 16-byte aligned pointers): the caller then runs the steps as separate kernels.
+AKAS_API int akas_decode_attention_from_qkv(const void* qkv, const float* q_w, const float* k_w, float eps, int zero_centered,
+                                            const float* cos_t, const float* sin_t, int rotary, int write, void* k_pool,
+                                            void* v_pool, int pool_pages, const int* block_table, int max_blocks,
+                                            const int* seq_of_token, const int* positions, void* out, float* part_o,
+                                            float* part_ml, float scale, int window, int page_size, int N, int H, int KH,
+                                            int D, int splits, cudaStream_t stream) {
+  const long long pool_rows = (long long)pool_pages * KH * page_size;
+  if (D != 64 || page_size % BK || KH <= 0 || H % KH || splits < 1 || splits > 65535 || pool_rows <= 0 || pool_rows >= (1ll << 31) ||
+      (long long)KH * ((H / KH + ROWS - 1) / ROWS) > 65535 || rotary < 0 || rotary > D || rotary % 16 ||
+      (cos_t != nullptr && (rotary == 0 || sin_t == nullptr)) ||
+      (uintptr_t)qkv % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 16 ||
+      (uintptr_t)q_w % 16 || (uintptr_t)k_w % 16 || (uintptr_t)cos_t % 16 || (uintptr_t)sin_t % 16)
+    return 3999;
+  if (N <= 0) return 0;
+  Fresh fresh;
+  fresh.qkv = (const bf16*)qkv;
+  fresh.q_w = q_w;
+  fresh.k_w = k_w;
+  fresh.eps = eps;
+  fresh.zero_centered = zero_centered;
+  fresh.cos_t = cos_t;
+  fresh.sin_t = sin_t;
+  fresh.rotary = cos_t ? rotary : 0;
+  fresh.k_pool = write ? (bf16*)k_pool : nullptr;
+  fresh.v_pool = write ? (bf16*)v_pool : nullptr;
+  return launch_tma(nullptr, k_pool, v_pool, pool_rows, block_table, max_blocks, seq_of_token, positions, out, part_o,
+                    part_ml, scale, window, page_size, N, H, KH, splits, stream, fresh);
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -221,11 +221,13 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* blo
            const int* cu_seqlens, const int* positions, void* out, float scale, int window, int page_size, int tiles,
            int H, int KH, int R, cudaStream_t stream) {
   constexpr int smem = 4 * BK * (D + 8) * (int)sizeof(bf16);
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};  // by device ordinal: the attribute belongs to a device's copy of the kernel
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+  if (!configured[device]) {
     const cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[device] = true;
   }
   prefill_attention_kernel<D><<<dim3(H, tiles), WARPS * 32, smem, stream>>>(
       (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_seqlens, positions,

@@ -492,11 +492,13 @@ AKAS_API int akas_prefill_attention_tc(const void* q, const void* k_pool, const 
   if (head_dim != D || page_size % 64 || H % KH || tiles > 65535 || R <= 0 || N <= 0) return 3999;
   if ((uintptr_t)q % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 16) return 3999;
   if (tiles <= 0) return 0;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};  // by device ordinal: the attribute belongs to a device's copy of the kernel
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+  if (!configured[device]) {
     const cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[device] = true;
   }
   CUtensorMap map_q, map_k, map_v;
   int err = rows_map(&map_q, q, N, H * D, (long long)H * D, 128);

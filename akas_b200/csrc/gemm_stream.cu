@@ -403,14 +403,10 @@ struct Plan {
   int nt, row_tiles, k_blocks, splits, stages, smem, tmem_cols, grid;
 };
 
-int device_sms() {
-  static int sms = 0;
-  if (sms == 0) {
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  }
-  return sms;
+int device_sms(int device) {
+  static int sms[64] = {};
+  if (sms[device] == 0) cudaDeviceGetAttribute(&sms[device], cudaDevAttrMultiProcessorCount, device);
+  return sms[device];
 }
 
 // Shared memory of a block with `splits` parts of K; 0 if it does not fit with at least `least` stages.
@@ -435,10 +431,13 @@ int launch(const void* x, const int* rows, const void* norm_w, float eps, int ze
            int O, int K, bool dry, cudaStream_t stream) {
   constexpr bool SWIGLU = OUT == OUT_SWIGLU;
   auto kernel = stream_gemm_kernel<IN_NORM, OUT>;
-  static int budget = 0;  // dynamic shared memory this kernel may ask for
-  static std::map<int, int> cluster_room;  // splits -> clusters of that size that can be resident at once
+  static int budgets[64] = {};  // by device ordinal: dynamic shared memory this kernel may ask for
+  static std::map<std::pair<int, int>, int> cluster_room;  // (device, splits) -> clusters of that size resident at once
   static std::mutex mutex;
-  const int sms = device_sms();
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+  int& budget = budgets[device];
+  const int sms = device_sms(device);
   Plan p;
   p.nt = (M + 15) / 16 * 16;
   const int out_cols = SWIGLU ? O / 2 : O;
@@ -468,7 +467,8 @@ int launch(const void* x, const int* rows, const void* norm_w, float eps, int ze
       const int smem = layout(budget, M, p.nt, p.k_blocks, IN_NORM, SWIGLU, s, &p.stages);
       if (!smem) continue;
       if (s > 1) {
-        if (!cluster_room.count(s)) {
+        const auto room_key = std::make_pair(device, s);
+        if (!cluster_room.count(room_key)) {
           cudaLaunchConfig_t config = {};
           config.gridDim = dim3(s * 64);
           config.blockDim = dim3(THREADS);
@@ -482,9 +482,9 @@ int launch(const void* x, const int* rows, const void* norm_w, float eps, int ze
           config.numAttrs = 1;
           int room = 0;
           if (cudaOccupancyMaxActiveClusters(&room, kernel, &config) != cudaSuccess) { cudaGetLastError(); room = 0; }
-          cluster_room[s] = room;
+          cluster_room[room_key] = room;
         }
-        if (cluster_room[s] < p.row_tiles) continue;  // all clusters of a launch run at once
+        if (cluster_room[room_key] < p.row_tiles) continue;  // all clusters of a launch run at once
       }
       p.splits = s;
       p.smem = smem;

@@ -203,14 +203,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 template <int BN, int EPI>
 int launch(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
   constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
-  static int sms = 0;
-  if (sms == 0) {
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  static int sms_of[64] = {};  // by device ordinal: the launch attribute belongs to a device's copy of the kernel
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+  if (sms_of[device] == 0) {
     const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) { sms = 0; return (int)e; }
+    if (e != cudaSuccess) return (int)e;
+    cudaDeviceGetAttribute(&sms_of[device], cudaDevAttrMultiProcessorCount, device);
   }
+  const int sms = sms_of[device];
   const int F = N / 2;
   CUtensorMap map_x, map_w;
   int err = cached_map(&map_x, x, M, K, BM, false);

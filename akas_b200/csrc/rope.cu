@@ -9,6 +9,7 @@
 // back in place and into the key page of the token's (request, position). v heads: copy into the
 // value page. Rotation pairs channel i with i + rotary/2; channels from `rotary` on pass through.
 #include "common.cuh"
+#include "qk_prep.cuh"
 
 using namespace akas;
 
@@ -148,36 +149,9 @@ qk_norm_rope_store8_kernel(T* __restrict__ qkv, T* __restrict__ q_out, const flo
   if (!is_q && !is_k) {  // value head: copy into the page (every lane still takes part in the shuffles below)
     if (page_row) store8(page_row, x);
   }
-  const float* w = is_q ? q_w : k_w;
-  if (w != nullptr) {
-    float ss = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
-#pragma unroll
-    for (int o = TPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float inv = 1.f / sqrtf(ss / (float)D + eps);
-    float g[8];
-    load8(w + e0, g);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * (zero_centered ? 1.f + g[e] : g[e]);
-  }
-  if (cos_t != nullptr) {
-    const int half = rotary / 2, shift = half / 8;  // the partner of channel e is e +- half: `shift` threads away
-    const bool low = e0 < half, rotated = e0 < rotary;
-    const int lane = threadIdx.x & 31;
-    const int partner = rotated ? (low ? lane + shift : lane - shift) : lane;
-    float other[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) other[e] = __shfl_sync(0xffffffffu, x[e], partner);
-    if (rotated) {
-      float c[8], sn[8];
-      const int f0 = low ? e0 : e0 - half;
-      load8(cos_t + (size_t)t * half + f0, c);
-      load8(sin_t + (size_t)t * half + f0, sn);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) x[e] = low ? x[e] * c[e] - other[e] * sn[e] : other[e] * sn[e] + x[e] * c[e];
-    }
-  }
+  const int half = rotary / 2;
+  head_norm_rotate8<TPH>(x, e0, is_q ? q_w : k_w, eps, zero_centered, cos_t ? cos_t + (size_t)t * half : nullptr,
+                         cos_t ? sin_t + (size_t)t * half : nullptr, rotary);
   if (!live || (!is_q && !is_k)) return;
   if (is_q) {
     store8(q_out + (size_t)t * H * D + (size_t)hd * D + e0, x);

@@ -503,21 +503,22 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
   constexpr bool UNCUT = OUTM == OUT_SWIGLU || OUTM == OUT_CONV;  // read-outs that need a tile's whole K in one block
   if (block_smem<NT, OUTM>(K, 1) > kMaxSmemBytes && (UNCUT || block_smem<NT, OUTM>(K, MAX_KSPLIT) > kMaxSmemBytes))
     return (int)cudaErrorInvalidValue;
-  static int sms = 0;
+  static int sms_of[64] = {};  // by device ordinal, like the plans below: a launch attribute belongs to a device
   static std::mutex mutex;
-  static std::map<std::tuple<int, int>, SplitPlan> plans;  // (tiles, K) -> how the product is cut
-  static std::map<std::tuple<int, int>, int> cluster_room;  // (ksplit, smem) -> clusters resident at once
+  static std::map<std::tuple<int, int, int>, SplitPlan> plans;  // (device, tiles, K) -> how the product is cut
+  static std::map<std::tuple<int, int, int>, int> cluster_room;  // (device, ksplit, smem) -> clusters resident at once
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
   SplitPlan plan;
   {
     std::lock_guard<std::mutex> lock(mutex);
-    if (sms == 0) {
-      int device = 0;
-      cudaGetDevice(&device);
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (sms_of[device] == 0) {
       const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
-      if (e != cudaSuccess) { sms = 0; return (int)e; }
+      if (e != cudaSuccess) return (int)e;
+      cudaDeviceGetAttribute(&sms_of[device], cudaDevAttrMultiProcessorCount, device);
     }
-    const auto key = std::make_tuple(num_tiles, K);
+    const int sms = sms_of[device];
+    const auto key = std::make_tuple(device, num_tiles, K);
     auto found = plans.find(key);
     if (found == plans.end()) {
       // What the busiest SM must fetch, in bytes, if the product is cut into `ksplit` parts of K: its blocks' weights
@@ -536,7 +537,7 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
         const int per_sm = max(1, min(per_sm_cap, kMaxSmemBytes / (smem + 1024)));
         int clusters = sms * per_sm / ksplit;
         if (ksplit > 1) {
-          const auto room_key = std::make_tuple(ksplit, smem);
+          const auto room_key = std::make_tuple(device, ksplit, smem);
           if (!cluster_room.count(room_key)) {
             cudaLaunchConfig_t config = {};
             config.gridDim = dim3(ksplit * 64);

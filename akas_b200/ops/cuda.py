@@ -72,6 +72,10 @@ _SIGNATURES = {
         "akas_decode_attention_bf16_paged": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int,
                                              c_int, c_int, c_void_p],
+        "akas_decode_attention_from_qkv": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int,
+                                           c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                           c_void_p],
         "akas_decode_attention_status": [],
     },
     "gemm_tcgen05": {
@@ -878,6 +882,46 @@ def _decode_attention(q, n, out, k_pool, v_pool, block_table, seq_of_token, posi
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
         _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
         splits, _code(q), _stream()), "paged_attention_decode", kernels=2)
+
+
+# Whether a decode step's attention layers run as one kernel from the qkv product on (norm and rotation of q and k, the
+# write into the pages and attention; measured on the 1.2B shape: 6 launches fewer a step).
+fused_qkv_attention = os.environ.get("AKAS_B200_FUSED_QKV_ATTENTION", "1") != "0"
+
+
+@_flushes
+def qkv_decode_attention(qkv, heads, kv_heads, head_dim, q_weight, k_weight, eps, zero_centered, cos, sin, k_pool, v_pool,
+                         block_table, seq_of_token, positions, scale, window, page_size, ctx, write=True):
+    """``paged_attention(qk_norm_rope_store(qkv, ...), ...)`` for a decode step (every token the single token of its
+    request) in one launch, or None where the fused kernel does not take the sizes or the dtype (the caller then runs
+    the two by themselves). With ``write=False`` the pages are read as they are and nothing is written."""
+    if not fused_qkv_attention or qkv.dtype != torch.bfloat16 or head_dim != 64 or page_size % 64 or k_pool.dtype != torch.bfloat16:
+        return None
+    n = qkv.shape[0]
+    _dense(qkv, "qkv")
+    if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+        raise ValueError("qkv width does not match (heads + 2 kv_heads) * head_dim")
+    rotary = 2 * cos.shape[1] if cos is not None else 0
+    if rotary % 16:
+        return None
+    win = int(window) if window else 0
+    group = heads // kv_heads
+    splits = decode_splits(n, kv_heads, -(-group // 16), win if win else ctx.max_context)
+    merged = splits == 1 or _merges_in_cluster(n * kv_heads * -(-group // 16), splits, head_dim, page_size)
+    out = torch.empty((n, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((n, heads, splits, head_dim), dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=qkv.device)
+    err = _fn("attention_decode", "akas_decode_attention_from_qkv")(
+        _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), int(bool(zero_centered)), _ptr(cos), _ptr(sin), rotary,
+        int(bool(write)), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table), block_table.shape[1],
+        _ptr(seq_of_token), _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n,
+        heads, kv_heads, head_dim, splits, _stream())
+    if err == 3999:
+        return None
+    _check(err, "decode attention from qkv", kernels=1 if merged else 2)
+    return out
 
 
 def _leading_single_tokens(ctx) -> int:

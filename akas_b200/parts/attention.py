@@ -72,6 +72,17 @@ class Attention(Mixer):
         if self.position is not None and fused:
             cos, sin = self.position.tables(ctx)
         norm = self.q_norm.spec if self.q_norm is not None else None
+        if fused and ctx.decode_only and hasattr(ops, "qkv_decode_attention"):
+            # a decode step: everything between the qkv product and the output product as one kernel, where there is one
+            out = ops.qkv_decode_attention(
+                qkv, s.num_heads, s.num_kv_heads, s.head_dim,
+                self.q_norm.weight if norm else None, self.k_norm.weight if norm else None,
+                norm.eps if norm else 0.0, bool(norm and norm.zero_centered), cos, sin, cache.k, cache.v,
+                ctx.block_table(cache.group), ctx.seq_of_token, ctx.positions, self.scale, s.window, cache.page_size,
+                ctx, write=write,
+            )
+            if out is not None:
+                return project(self.rt, out, self.w_out, residual=residual)
         store = write and fused
         q = ops.qk_norm_rope_store(
             qkv, s.num_heads, s.num_kv_heads, s.head_dim,

@@ -647,6 +647,56 @@ def test_paged_attention_decode_split(ops, dtype, h, kh, d, page, window):
     assert torch.equal(got[-2:], torch.zeros_like(got[-2:]))
 
 
+@pytest.mark.parametrize("h,kh,page,window,rot,norm", [
+    (32, 8, 64, None, 64, True), (24, 1, 128, 300, 32, True), (4, 4, 256, None, 64, False), (8, 2, 64, 1000, 16, True),
+    (6, 2, 64, None, 0, True),
+])
+def test_decode_attention_from_the_qkv_product(ops, h, kh, page, window, rot, norm):
+    """Norm and rotation of q and k, the write into the pages and split-key attention as one kernel, against the two
+    kernels that do the same: every bit of the output and of the pages. The page rows that the step's own tokens go to
+    are poisoned beforehand, so a block that attended to what its load found there instead of the token would show;
+    24 heads over one key/value head make two tiles of query rows, of which only the first writes the pages."""
+    cuda, ref = ops
+    d, dtype = 64, torch.bfloat16
+    contexts = [1, 2, 33, 700, 1500, 257, 64, 128, 65]
+    cu, seq = _batch([1] * len(contexts), pad=2)
+    pos = torch.tensor([c - 1 for c in contexts] + [0, 0], dtype=torch.int32, device=DEV)
+    n = pos.numel()
+    pages = sum(-(-c // page) for c in contexts) + 3
+    bt = _tables(contexts, page, pages, 6)
+    k0, v0 = _pools(pages, kh, page, d, dtype, 50)
+    for r, context in enumerate(contexts):
+        last = int(bt[r, (context - 1) // page])
+        k0[last, :, (context - 1) % page:] = float("nan")
+        v0[last, :, (context - 1) % page:] = float("nan")
+    qkv = _rand((n, (h + 2 * kh) * d), dtype, 20)
+    qw, kw = (_rand((d,), torch.float32, 21) + 1, _rand((d,), torch.float32, 22) + 1) if norm else (None, None)
+    cos = sin = None
+    if rot:
+        inv = (torch.tensor(1e4, dtype=torch.float64) ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).to(DEV)
+        cos, sin = ref.rope_tables(pos, inv)
+    scale, step = d ** -0.5, _Decode(max(contexts))
+    prep = (h, kh, d, qw, kw, 1e-5, False, cos, sin)
+    k1, v1, k2, v2 = k0.clone(), v0.clone(), k0.clone(), v0.clone()
+    q = cuda.qk_norm_rope_store(qkv.clone(), *prep, k1, v1, bt, seq, pos, page)
+    want = cuda.paged_attention(q, k1, v1, bt, seq, pos, scale, window, page, step)
+    got = cuda.qkv_decode_attention(qkv.clone(), *prep, k2, v2, bt, seq, pos, scale, window, page, step)
+    assert got is not None and cuda.decode_attention_status() == 0
+    assert torch.equal(got, want)
+    live = torch.ones_like(k1, dtype=torch.bool)
+    for r, context in enumerate(contexts):  # (what lies past a request's end stays poisoned)
+        live[int(bt[r, (context - 1) // page]), :, context % page if context % page else page:] = False
+    assert torch.equal(k1[live], k2[live]) and torch.equal(v1[live], v2[live])
+    assert not torch.isnan(k2[live]).any()
+    _close(got, ref.paged_attention(q, k1, v1, bt, seq, pos, scale, window, page), dtype, "against the plain statement")
+    # a layer that only reads the pages: nothing written, the pages attended as they are
+    q = cuda.qk_norm_rope_store(qkv.clone(), *prep, None, None, bt, seq, pos, page)
+    want = cuda.paged_attention(q, k1, v1, bt, seq, pos, scale, window, page, step)
+    before = k1.clone()
+    got = cuda.qkv_decode_attention(qkv.clone(), *prep, k1, v1, bt, seq, pos, scale, window, page, step, write=False)
+    assert torch.equal(got, want) and torch.equal(k1[live], before[live])
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_one_far_key(ops, dtype):
     """One key among a thousand, far back and in a page of its own, is made to dominate: random values
