@@ -76,6 +76,11 @@ _SIGNATURES = {
                                            c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_void_p],
+        "akas_decode_attention_items": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int,
+                                        c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_void_p],
+        "akas_decode_attention_items_places": [c_int, c_int],
         "akas_decode_attention_status": [],
     },
     "gemm_tcgen05": {
@@ -832,6 +837,7 @@ def prefill_attention_tc_status() -> int:
 
 
 _DECODE_BLOCKS = int(os.environ.get("AKAS_B200_DECODE_BLOCKS", "300"))
+_DECODE_SPLITS = int(os.environ.get("AKAS_B200_DECODE_SPLITS", "0"))  # a number of key parts for every step, for measurements
 
 
 def decode_splits(num_tokens: int, kv_heads: int, head_tiles: int, max_context: int) -> int:
@@ -841,7 +847,7 @@ def decode_splits(num_tokens: int, kv_heads: int, head_tiles: int, max_context: 
     in 4 to 5 parts, 0.861 ms a step against 0.888 ms in 16), two parts even where the requests alone give that many
     (64 requests: 44.8k tokens/s in 2 parts, 43.4k in 1, 44.4k in 4), and at least four 64-key tiles per part."""
     blocks = max(1, num_tokens * kv_heads * head_tiles)
-    want = max(-(-_DECODE_BLOCKS // blocks), 2)
+    want = _DECODE_SPLITS or max(-(-_DECODE_BLOCKS // blocks), 2)
     most = max(1, -(-max_context // 256))
     return max(1, min(want, most, 64))
 
@@ -857,6 +863,36 @@ def _merges_in_cluster(blocks: int, splits: int, head_dim: int, page_size: int) 
             and blocks * splits <= 4 * _sm_count())
 
 
+# Decode attention by blocks that walk the step's items instead of a block per item: "auto" (where a block per item
+# would come to more blocks than the GPU holds at once: alone and with a cold L2, 64 requests of 2,048 keys take 50 us
+# against 58 us), "0" never, "1" wherever the kernel takes the sizes.
+decode_items = os.environ.get("AKAS_B200_DECODE_ITEMS", "auto")
+if decode_items not in ("auto", "0", "1"):
+    raise ValueError(f"AKAS_B200_DECODE_ITEMS must be auto, 0 or 1, got {decode_items!r}")
+_items_places_cache = {}
+
+
+def _items_places(heads: int, kv_heads: int) -> int:
+    key = (torch.cuda.current_device(), heads // kv_heads)
+    if key not in _items_places_cache:
+        _items_places_cache[key] = int(_fn("attention_decode", "akas_decode_attention_items_places")(heads, kv_heads))
+    return _items_places_cache[key]
+
+
+def decode_plan(num_tokens: int, heads: int, kv_heads: int, head_dim: int, page_size: int, keys: int, dtype):
+    """(key parts, whether the blocks walk the items) for a decode step's attention, from sizes known on the host."""
+    head_tiles = -(-(heads // kv_heads) // 16)
+    splits = decode_splits(num_tokens, kv_heads, head_tiles, keys)
+    if dtype != torch.bfloat16 or head_dim != 64 or page_size % 64 or decode_items == "0":
+        return splits, False
+    blocks = num_tokens * kv_heads * head_tiles
+    if decode_items == "auto" and blocks * splits <= 3 * _sm_count():
+        return splits, False
+    # (the same parts: measured at 64 requests of 2,048 keys, 48.1k tokens/s in 2 parts, 47.3k in 3, 46.4k in 6 and
+    # 44.3k in 11 against 47.2k with a block per item: what an item costs beside its tiles is not hidden by the ring)
+    return splits, _items_places(heads, kv_heads) > 0
+
+
 def _decode_attention(q, n, out, k_pool, v_pool, block_table, seq_of_token, positions, scale, win, page_size, keys):
     """Split-key attention of the first ``n`` tokens of q, each the single token of its request, into out[:n]."""
     kh, d = k_pool.shape[1], k_pool.shape[3]
@@ -864,11 +900,23 @@ def _decode_attention(q, n, out, k_pool, v_pool, block_table, seq_of_token, posi
     group = heads // kh
     if q.dtype == torch.bfloat16 and d in (16, 32, 64, 128):
         # tensor-core kernel: the query heads of a group are the rows of one tile
-        splits = decode_splits(n, kh, -(-group // 16), keys)
+        splits, walks = decode_plan(n, heads, kh, d, page_size, keys, q.dtype)
         part_o = part_ml = None
         if splits > 1:
             part_o = torch.empty((n, heads, splits, d), dtype=torch.float32, device=q.device)
             part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
+        if walks:
+            err = _fn("attention_decode", "akas_decode_attention_items")(
+                _ptr(q), None, None, None, 0.0, 0, None, None, 0, 0, _ptr(k_pool), _ptr(v_pool), k_pool.shape[0],
+                _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions), _ptr(out), _ptr(part_o),
+                _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d, splits, _stream())
+            if err != 3999:
+                _check(err, "decode_attention (items)", kernels=2 if splits > 1 else 1)
+                return
+            splits = decode_splits(n, kh, -(-group // 16), keys)  # (pointers that the kernel does not take)
+            if splits > 1:
+                part_o = torch.empty((n, heads, splits, d), dtype=torch.float32, device=q.device)
+                part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
         _check(_fn("attention_decode", "akas_decode_attention_bf16_paged")(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
             _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n, heads, kh, d,
@@ -906,18 +954,21 @@ def qkv_decode_attention(qkv, heads, kv_heads, head_dim, q_weight, k_weight, eps
         return None
     win = int(window) if window else 0
     group = heads // kv_heads
-    splits = decode_splits(n, kv_heads, -(-group // 16), win if win else ctx.max_context)
-    merged = splits == 1 or _merges_in_cluster(n * kv_heads * -(-group // 16), splits, head_dim, page_size)
+    splits, walks = decode_plan(n, heads, kv_heads, head_dim, page_size, win if win else ctx.max_context, qkv.dtype)
+    merged = splits == 1 or (not walks and _merges_in_cluster(n * kv_heads * -(-group // 16), splits, head_dim, page_size))
     out = torch.empty((n, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     part_o = part_ml = None
     if splits > 1:
         part_o = torch.empty((n, heads, splits, head_dim), dtype=torch.float32, device=qkv.device)
         part_ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=qkv.device)
-    err = _fn("attention_decode", "akas_decode_attention_from_qkv")(
-        _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), int(bool(zero_centered)), _ptr(cos), _ptr(sin), rotary,
-        int(bool(write)), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table), block_table.shape[1],
-        _ptr(seq_of_token), _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n,
-        heads, kv_heads, head_dim, splits, _stream())
+    prep = (_ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), int(bool(zero_centered)), _ptr(cos), _ptr(sin), rotary,
+            int(bool(write)), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table), block_table.shape[1],
+            _ptr(seq_of_token), _ptr(positions), _ptr(out), _ptr(part_o), _ptr(part_ml), float(scale), win, page_size, n,
+            heads, kv_heads, head_dim, splits, _stream())
+    if walks:
+        err = _fn("attention_decode", "akas_decode_attention_items")(None, *prep)
+    else:
+        err = _fn("attention_decode", "akas_decode_attention_from_qkv")(*prep)
     if err == 3999:
         return None
     _check(err, "decode attention from qkv", kernels=1 if merged else 2)

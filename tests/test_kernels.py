@@ -623,10 +623,13 @@ class _Decode:
     (4, 2, 16, 16, None), (3, 1, 32, 8, None), (32, 8, 64, 64, None), (6, 1, 48, 8, 300), (16, 2, 128, 32, None),
     (24, 1, 64, 16, None), (5, 5, 256, 64, None), (8, 2, 64, 128, 300), (4, 4, 64, 256, None), (32, 8, 64, 64, 1000),
 ])
-def test_paged_attention_decode_split(ops, dtype, h, kh, d, page, window):
-    """Split-key decode attention; head size 64 with pages of 64 keys or more takes the TMA-fed kernel in bfloat16.
+@pytest.mark.parametrize("items", ["auto", "1"])
+def test_paged_attention_decode_split(ops, dtype, h, kh, d, page, window, items, monkeypatch):
+    """Split-key decode attention; head size 64 with pages of 64 keys or more takes the TMA-fed kernels in bfloat16:
+    a block per (token, KV head, key part), or (items "1") a fixed number of blocks that walk those items.
     What the pages hold past the end of a request is poisoned: it must not be looked at."""
     cuda, ref = ops
+    monkeypatch.setattr(cuda, "decode_items", items)
     contexts = [1, 2, 33, 700, 1500, 257, 64, 128]
     cu, seq = _batch([1] * len(contexts), pad=2)
     pos = torch.tensor([c - 1 for c in contexts] + [0, 0], dtype=torch.int32, device=DEV)
@@ -651,12 +654,15 @@ def test_paged_attention_decode_split(ops, dtype, h, kh, d, page, window):
     (32, 8, 64, None, 64, True), (24, 1, 128, 300, 32, True), (4, 4, 256, None, 64, False), (8, 2, 64, 1000, 16, True),
     (6, 2, 64, None, 0, True),
 ])
-def test_decode_attention_from_the_qkv_product(ops, h, kh, page, window, rot, norm):
+@pytest.mark.parametrize("items", ["auto", "1"])
+def test_decode_attention_from_the_qkv_product(ops, h, kh, page, window, rot, norm, items, monkeypatch):
     """Norm and rotation of q and k, the write into the pages and split-key attention as one kernel, against the two
     kernels that do the same: every bit of the output and of the pages. The page rows that the step's own tokens go to
     are poisoned beforehand, so a block that attended to what its load found there instead of the token would show;
-    24 heads over one key/value head make two tiles of query rows, of which only the first writes the pages."""
+    24 heads over one key/value head make two tiles of query rows, of which only the first writes the pages. With
+    items "1" both sides run on the kernel whose blocks walk the items."""
     cuda, ref = ops
+    monkeypatch.setattr(cuda, "decode_items", items)
     d, dtype = 64, torch.bfloat16
     contexts = [1, 2, 33, 700, 1500, 257, 64, 128, 65]
     cu, seq = _batch([1] * len(contexts), pad=2)
@@ -695,6 +701,34 @@ def test_decode_attention_from_the_qkv_product(ops, h, kh, page, window, rot, no
     before = k1.clone()
     got = cuda.qkv_decode_attention(qkv.clone(), *prep, k1, v1, bt, seq, pos, scale, window, page, step, write=False)
     assert torch.equal(got, want) and torch.equal(k1[live], before[live])
+
+
+def test_decode_attention_with_more_items_than_blocks(ops):
+    """96 requests of 8 key/value heads with contexts from 1 to 3,000 keys: more (token, KV head, key part) items than
+    blocks fit the GPU, so the blocks walk them (several rounds, the ring of tiles running on from item to item, empty
+    parts and padding tokens among them)."""
+    cuda, ref = ops
+    h, kh, d, page, dtype = 32, 8, 64, 64, torch.bfloat16
+    g = torch.Generator().manual_seed(5)
+    contexts = [1, 2, 63, 64, 65, 3000] + torch.randint(1, 2500, (90,), generator=g).tolist()
+    cu, seq = _batch([1] * len(contexts), pad=3)
+    pos = torch.tensor([c - 1 for c in contexts] + [0, 0, 0], dtype=torch.int32, device=DEV)
+    pages = sum(-(-c // page) for c in contexts) + 3
+    bt = _tables(contexts, page, pages, 6)
+    k, v = _pools(pages, kh, page, d, dtype, 50)
+    for r, context in enumerate(contexts):
+        if context % page:
+            last = int(bt[r, (context - 1) // page])
+            k[last, :, context % page:] = float("nan")
+            v[last, :, context % page:] = float("nan")
+    q = _rand((pos.numel(), h * d), dtype, 52)
+    step = _Decode(max(contexts))
+    assert cuda.decode_plan(len(contexts) + 3, h, kh, d, page, step.max_context, dtype)[1]
+    want = ref.paged_attention(q, k, v, bt, seq, pos, d ** -0.5, None, page)
+    got = cuda.paged_attention(q, k, v, bt, seq, pos, d ** -0.5, None, page, step)
+    _close(got, want, dtype, "walking the items")
+    assert cuda.decode_attention_status() == 0
+    assert torch.equal(got[-3:], torch.zeros_like(got[-3:]))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
