@@ -145,7 +145,7 @@ __device__ __forceinline__ void cluster_meet() {
 }
 
 template <int NT, int IN, int OUT>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __restrict__ x_, const int* __restrict__ rows,
                    const float* __restrict__ norm_w, float eps, int zero_centered, void* __restrict__ y_, int M, int O,
                    int K, int num_tiles, int ksplit, const ConvTail tail) {
@@ -159,7 +159,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
   float* peer_ss = peer + (ksplit > 1 ? (ksplit - 1) * SPLIT_TILES * NT * 128 : 0);  // [ksplit - 1][NT * 8]
   bf16* xs = reinterpret_cast<bf16*>(peer_ss + (ksplit > 1 ? (ksplit - 1) * NT * 8 : 0));  // [NT * 8][XS]: activations
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], gathered;
-  __shared__ float ss_s[NT * 8];
+  __shared__ float ss_s[CONSUMERS][NT * 8];  // sums of x^2 per token, one part per consumer warp (added in warp order)
   __shared__ int abort_s;  // set by the first wait that runs out; from then on nobody waits on an mbarrier
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int F = O / 2;  // swiglu only: O is the stacked height 2F
@@ -229,8 +229,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
   } else {
     // ---------------------------------------------------------------- consumers
     const int g = lane >> 2, t = lane & 3;
-    chain_wait();  // from here on the kernel reads what its predecessor wrote
     if (IN == IN_BF16) {
+      chain_wait();  // from here on the kernel reads what its predecessor wrote
       const int per_row = k_len / 8;
       for (int i = tid; i < NT * 8 * per_row; i += CONSUMERS * 32) {  // all copies in flight together
         const int m = i / per_row, col = (i % per_row) * 8;
@@ -240,31 +240,73 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
       cp_async_commit();
       cp_async_wait<0>();
     } else {
-      // float32 residual rows -> bf16(x * norm weight); each warp owns tokens warp, warp + 8 and sums x^2
-      for (int m = warp; m < NT * 8; m += CONSUMERS) {
-        float ss = 0.f;
-        bf16* dst = xs + (size_t)m * XS;
-        if (m < M) {
-          const float* src = (const float*)x_ + (size_t)(rows ? rows[m] : m) * K + k0;
-#pragma unroll 8
-          for (int k = lane * 4; k < k_len; k += 128) {
-            const float4 v = *reinterpret_cast<const float4*>(src + k);
-            float4 w = *reinterpret_cast<const float4*>(norm_w + k0 + k);
-            if (zero_centered) { w.x += 1.f; w.y += 1.f; w.z += 1.f; w.w += 1.f; }
-            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-            uint2 packed;
-            packed.x = pack_bf16(v.x * w.x, v.y * w.y);
-            packed.y = pack_bf16(v.z * w.z, v.w * w.w);
-            *reinterpret_cast<uint2*>(dst + k) = packed;
+      // float32 residual rows -> bf16(x * norm weight), with the sum of x^2 on the way. A warp takes 128-float blocks
+      // of k (blocks warp, warp + 8, ...) for every token, two blocks a pass: the pass's 16 loads per lane (8 tokens x
+      // 2 blocks) are all in flight at once, so a pass costs one trip to the L2, and the first pass's norm weights
+      // are fetched before the kernel waits for its predecessor (they depend on nothing).
+      constexpr int PER = 2;
+      const int kblocks = (k_len + 127) / 128;
+      float4 wv[PER];
+#pragma unroll
+      for (int p = 0; p < PER; ++p) {
+        const int k = (warp + CONSUMERS * p) * 128 + lane * 4;
+        wv[p] = k < k_len ? *reinterpret_cast<const float4*>(norm_w + k0 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      chain_wait();  // from here on the kernel reads what its predecessor wrote
+#pragma unroll 1
+      for (int half = 0; half < NT; ++half) {  // 8 tokens at a time
+        float ss[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss[i] = 0.f;
+        for (int b0 = warp; b0 < kblocks; b0 += CONSUMERS * PER) {
+          if (b0 != warp || half > 0) {
+#pragma unroll
+            for (int p = 0; p < PER; ++p) {
+              const int k = (b0 + CONSUMERS * p) * 128 + lane * 4;
+              wv[p] = k < k_len ? *reinterpret_cast<const float4*>(norm_w + k0 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
           }
-          ss = warp_sum(ss);
-        } else {
-          for (int k = lane * 4; k < k_len; k += 128) *reinterpret_cast<uint2*>(dst + k) = make_uint2(0u, 0u);
+          float4 v[PER][8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int m = half * 8 + i;
+            const float* src = (const float*)x_ + (size_t)(m < M ? (rows ? rows[m] : m) : 0) * K + k0;
+#pragma unroll
+            for (int p = 0; p < PER; ++p) {
+              const int k = (b0 + CONSUMERS * p) * 128 + lane * 4;
+              v[p][i] = m < M && k < k_len ? *reinterpret_cast<const float4*>(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+#pragma unroll
+          for (int p = 0; p < PER; ++p) {
+            const int k = (b0 + CONSUMERS * p) * 128 + lane * 4;
+            float4 w = wv[p];
+            if (zero_centered) { w.x += 1.f; w.y += 1.f; w.z += 1.f; w.w += 1.f; }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 a = v[p][i];
+              ss[i] = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, fmaf(a.w, a.w, ss[i]))));
+              uint2 packed;
+              packed.x = pack_bf16(a.x * w.x, a.y * w.y);
+              packed.y = pack_bf16(a.z * w.z, a.w * w.w);
+              if (k < k_len) *reinterpret_cast<uint2*>(xs + (size_t)(half * 8 + i) * XS + k) = packed;
+            }
+          }
         }
-        if (lane == 0) ss_s[m] = ss;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float total = warp_sum(ss[i]);
+          if (lane == 0) ss_s[warp][half * 8 + i] = total;
+        }
       }
     }
     consumer_barrier();  // the activations are in shared memory for every consumer warp
+    auto sum_sq = [&](int m) {
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < CONSUMERS; ++w) total += ss_s[w][m];
+      return total;
+    };
 
     // Where this thread's 16 bytes of weight rows g and g + 8 lie inside a stage: group of 64 k, row, and the 16-byte
     // unit (slice & 1) * 4 + t XOR g of the 128-byte swizzle. One box holds 16 rows to a group of k, SwiGLU's two boxes
@@ -343,7 +385,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           continue;
         }
         if (IN == IN_NORM) {
-          const float inv = 1.f / sqrtf(ss_s[m] / (float)K + eps);
+          const float inv = 1.f / sqrtf(sum_sq(m) / (float)K + eps);
           v *= inv;
           u *= inv;
           xv *= inv;
@@ -396,7 +438,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
       if (rank > 0) {
         const unsigned to = peer_address(peer, 0) + (unsigned)((rank - 1) * SPLIT_TILES * NT * 128 * 4);
         for (int i = tid; i < count; i += CONSUMERS * 32) peer_store(to + (unsigned)i * 4u, part[i]);
-        if (IN == IN_NORM && tid < NT * 8) peer_store(peer_address(peer_ss, 0) + (unsigned)(((rank - 1) * NT * 8 + tid) * 4), ss_s[tid]);
+        if (IN == IN_NORM && tid < NT * 8) peer_store(peer_address(peer_ss, 0) + (unsigned)(((rank - 1) * NT * 8 + tid) * 4), sum_sq(tid));
         consumer_barrier();  // all of this block's sums are on their way; one thread tells the first block
         if (tid == 0) {
           asm volatile("fence.acq_rel.cluster;" ::: "memory");
@@ -413,7 +455,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
             const int j = e / 128, row = (e % 128) / 8, tok = e % 8;
             const int m = 8 * j + tok, o = (first_tile + tl * tile_step) * 16 + row;
             if (m >= M || o >= O) continue;
-            float v = part[i], ss = IN == IN_NORM ? ss_s[m] : 0.f;
+            float v = part[i], ss = IN == IN_NORM ? sum_sq(m) : 0.f;
             for (int r = 0; r < ksplit - 1; ++r) {  // in rank order
               v += peer[(r * SPLIT_TILES + tl) * NT * 128 + e];
               if (IN == IN_NORM) ss += peer_ss[r * NT * 8 + m];
