@@ -160,6 +160,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
   bf16* xs = reinterpret_cast<bf16*>(peer_ss + (ksplit > 1 ? (ksplit - 1) * NT * 8 : 0));  // [NT * 8][XS]: activations
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], gathered;
   __shared__ float ss_s[CONSUMERS][NT * 8];  // sums of x^2 per token, one part per consumer warp (added in warp order)
+  __shared__ int slot_s[NT * 8];  // convolution read-out: the state row of each token's request, or -1
   __shared__ int abort_s;  // set by the first wait that runs out; from then on nobody waits on an mbarrier
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int F = O / 2;  // swiglu only: O is the stacked height 2F
@@ -229,13 +230,19 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
   } else {
     // ---------------------------------------------------------------- consumers
     const int g = lane >> 2, t = lane & 3;
+    if (OUT == OUT_CONV && tid < NT * 8) {
+      // which request a token belongs to and where its state lies is what the host wrote for this step: looked up while
+      // the kernel ahead is still at work, not once per tile in the read-out (two loads, one after the other)
+      const int r = tid < M ? tail.seq_of_token[tid] : -1;
+      slot_s[tid] = r >= 0 ? tail.slots[r] : -1;
+    }
     if (IN == IN_BF16) {
       chain_wait();  // from here on the kernel reads what its predecessor wrote
-      const int per_row = k_len / 8;
-      for (int i = tid; i < NT * 8 * per_row; i += CONSUMERS * 32) {  // all copies in flight together
-        const int m = i / per_row, col = (i % per_row) * 8;
+#pragma unroll
+      for (int m = 0; m < NT * 8; ++m) {  // all copies in flight together
         const size_t src = m < M ? (size_t)(rows ? rows[m] : m) : 0;
-        cp_async16(xs + (size_t)m * XS + col, (const bf16*)x_ + src * K + k0 + col, m < M ? 16 : 0);
+        for (int col = tid * 8; col < k_len; col += CONSUMERS * 32 * 8)
+          cp_async16(xs + (size_t)m * XS + col, (const bf16*)x_ + src * K + k0 + col, m < M ? 16 : 0);
       }
       cp_async_commit();
       cp_async_wait<0>();
@@ -366,8 +373,14 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           acc_x[j][0] = acc_x[j][1] = acc_x[j][2] = acc_x[j][3] = 0.f;
         }
       }
-      consumer_barrier();
       constexpr int per_tile = BOXES8 ? 64 : 128;  // (row, token) pairs per n-block
+      static_assert(2 * 128 <= CONSUMERS * 32, "a thread reads out at most one (row, token) pair of a tile");
+      float before = 0.f;  // the residual stream's value, on its way while the sums meet
+      if (OUT == OUT_ACC && ksplit == 1 && tid < NT * per_tile) {
+        const int m = 8 * (tid / per_tile) + tid % 8, o = tile * 16 + (tid % per_tile) / 8;
+        if (m < M && o < O) before = ((const float*)y_)[(size_t)m * O + o];
+      }
+      consumer_barrier();
       for (int i = tid; i < NT * per_tile; i += CONSUMERS * 32) {
         const int j = i / per_tile, row = (i % per_tile) / 8, tok = i % 8;
         const int m = 8 * j + tok;
@@ -394,8 +407,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           // v, u, xv: the B, C and x parts of channel c for token m, rounded as the projection's own read-out would
           const int C = O / 3, c = tile * 8 + row, L = tail.L;
           if (c >= C) continue;
-          const int r = tail.seq_of_token[m];
-          const int slot = r >= 0 ? tail.slots[r] : -1;
+          const int slot = slot_s[m];
           bf16* out = (bf16*)y_ + (size_t)m * C + c;
           if (slot < 0) {
             *out = __float2bfloat16_rn(0.f);
@@ -423,7 +435,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           const size_t at = (size_t)m * O + o;
           if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
           else if (OUT == OUT_F32) ((float*)y_)[at] = v;
-          else ((float*)y_)[at] += v;
+          else ((float*)y_)[at] = before + v;
         }
       }
       consumer_barrier();  // `red` is free again before the next tile's sums are written
@@ -445,12 +457,27 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_address(&gathered, 0)) : "memory");
         }
       } else {
+        constexpr int MOST = (SPLIT_TILES * NT * 128 + CONSUMERS * 32 - 1) / (CONSUMERS * 32);  // pairs a thread writes
+        float before[MOST];  // the residual stream's values, fetched while the other parts are on their way
+#pragma unroll
+        for (int n = 0; n < MOST; ++n) {
+          before[n] = 0.f;
+          const int i = tid + n * CONSUMERS * 32;
+          if (OUT == OUT_ACC && i < count) {
+            const int tl = i / (NT * 128), e = i % (NT * 128);
+            const int m = 8 * (e / 128) + e % 8, o = (first_tile + tl * tile_step) * 16 + (e % 128) / 8;
+            if (m < M && o < O) before[n] = ((const float*)y_)[(size_t)m * O + o];
+          }
+        }
         if (!*(volatile int*)&abort_s && !mbar_wait_cluster(&gathered, 0)) {
           *(volatile int*)&abort_s = 1;
           if (lane == 0) atomicExch(&g_skinny_status, 3);
         }
         if (!*(volatile int*)&abort_s) {
-          for (int i = tid; i < count; i += CONSUMERS * 32) {
+#pragma unroll
+          for (int n = 0; n < MOST; ++n) {
+            const int i = tid + n * CONSUMERS * 32;
+            if (i >= count) continue;
             const int tl = i / (NT * 128), e = i % (NT * 128);
             const int j = e / 128, row = (e % 128) / 8, tok = e % 8;
             const int m = 8 * j + tok, o = (first_tile + tl * tile_step) * 16 + row;
@@ -464,7 +491,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
             const size_t at = (size_t)m * O + o;
             if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
             else if (OUT == OUT_F32) ((float*)y_)[at] = v;
-            else ((float*)y_)[at] += v;
+            else ((float*)y_)[at] = before[n] + v;
           }
         }
       }
