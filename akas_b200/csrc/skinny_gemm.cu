@@ -380,6 +380,23 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
         const int m = 8 * (tid / per_tile) + tid % 8, o = tile * 16 + (tid % per_tile) / 8;
         if (m < M && o < O) before = ((const float*)y_)[(size_t)m * O + o];
       }
+      // The convolution's taps, bias and state rows of this thread's (channel, token), likewise (up to 4 taps; longer
+      // ones are read where they are used).
+      constexpr int TAPS = 4;
+      float taps_r[TAPS] = {0.f, 0.f, 0.f, 0.f}, hist_r[TAPS - 1] = {0.f, 0.f, 0.f}, bias_r = 0.f;
+      if (OUT == OUT_CONV && tail.L <= TAPS && tid < NT * per_tile) {
+        const int m = 8 * (tid / per_tile) + tid % 8, C = O / 3, c = tile * 8 + (tid % per_tile) / 8;
+        const int slot = m < M ? slot_s[m] : -1;
+        if (slot >= 0 && c < C) {
+          const float* hist = tail.state + (size_t)slot * (tail.L - 1) * C + c;
+#pragma unroll
+          for (int l = 0; l < TAPS; ++l) {
+            if (l < tail.L) taps_r[l] = tail.taps[(size_t)c * tail.L + l];
+            if (l < tail.L - 1) hist_r[l] = hist[(size_t)l * C];
+          }
+          if (tail.bias) bias_r = tail.bias[c];
+        }
+      }
       consumer_barrier();
       for (int i = tid; i < NT * per_tile; i += CONSUMERS * 32) {
         const int j = i / per_tile, row = (i % per_tile) / 8, tok = i % 8;
@@ -417,14 +434,30 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           const float uu = bq * xq;
           float* hist = tail.state + (size_t)slot * (L - 1) * C + c;
           float sum = 0.f;
-          for (int l = 0; l < L - 1; ++l) {
-            const float h = hist[(size_t)l * C];
-            sum = fmaf(h, tail.taps[(size_t)c * L + l], sum);
-            if (l > 0 && tail.write) hist[(size_t)(l - 1) * C] = h;
+          if (L <= TAPS) {  // (everything is in registers already)
+#pragma unroll
+            for (int l = 0; l < TAPS - 1; ++l) {
+              if (l < L - 1) {
+                sum = fmaf(hist_r[l], taps_r[l], sum);
+                if (l > 0 && tail.write) hist[(size_t)(l - 1) * C] = hist_r[l];
+              }
+            }
+            float last = taps_r[0];
+#pragma unroll
+            for (int l = 1; l < TAPS; ++l) last = l == L - 1 ? taps_r[l] : last;
+            sum = fmaf(uu, last, sum);
+            if (tail.write) hist[(size_t)(L - 2) * C] = uu;
+            if (tail.bias) sum += bias_r;
+          } else {
+            for (int l = 0; l < L - 1; ++l) {
+              const float h = hist[(size_t)l * C];
+              sum = fmaf(h, tail.taps[(size_t)c * L + l], sum);
+              if (l > 0 && tail.write) hist[(size_t)(l - 1) * C] = h;
+            }
+            sum = fmaf(uu, tail.taps[(size_t)c * L + L - 1], sum);
+            if (tail.write) hist[(size_t)(L - 2) * C] = uu;
+            if (tail.bias) sum += tail.bias[c];
           }
-          sum = fmaf(uu, tail.taps[(size_t)c * L + L - 1], sum);
-          if (tail.write) hist[(size_t)(L - 2) * C] = uu;
-          if (tail.bias) sum += tail.bias[c];
           *out = __float2bfloat16_rn(cq * sum);
         } else if (OUT == OUT_SWIGLU) {
           const int f = tile * 8 + row;
