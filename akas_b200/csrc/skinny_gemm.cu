@@ -625,9 +625,11 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
     if (found == plans.end()) {
       // What the busiest SM must fetch, in bytes, if the product is cut into `ksplit` parts of K: its blocks' weights
       // and activations. A cut costs an exchange at the end that grows with the number of parts, counted as the
-      // bytes the SM could have fetched meanwhile (12 KB a part); an SM with a single block streams about 30 % slower
-      // than one with two. On the 1.2B shape this picks 4 parts for the down projection, which measured best among
-      // 1, 2, 4 and 8 parts: 0.950 ms a decode step against 1.035, 1.10 and 0.965.
+      // bytes the SM could have fetched meanwhile (30 KB a part; AKAS_B200_SKINNY_PART_COST sets another figure); an
+      // SM with a single block streams about 30 % slower than one with two. On the 1.2B shape this cuts only the down
+      // projection (4 parts) and leaves the out and qkv projections whole. Measured, a decode step of 8 requests:
+      // 0.811 ms at 6 KB a part, 0.757 at 12 KB (out projection in 2 parts, qkv in 4), 0.740 at 30 KB, 0.742 at 60 KB
+      // (nothing cut).
       const int chunks = (K + KC - 1) / KC;
       long long best = -1;
       plan = SplitPlan{1, 0, 0};
@@ -668,7 +670,8 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
         const long long part_k = (long long)(chunks + ksplit - 1) / ksplit * KC;
         long long fetched = on_busiest_sm * (rounds * 16 * part_k * 2 + NT * 8 * part_k * 2);
         if (on_busiest_sm == 1) fetched += fetched * 3 / 10;  // one ring per SM keeps too few bytes in flight
-        if (ksplit > 1) fetched += 12000 * ksplit;
+        static const int part_cost = [] { const char* v = getenv("AKAS_B200_SKINNY_PART_COST"); return v ? atoi(v) : 30000; }();
+        if (ksplit > 1) fetched += (long long)part_cost * ksplit;
         if (best < 0 || fetched < best) {
           best = fetched;
           plan = SplitPlan{ksplit, blocks, smem};
