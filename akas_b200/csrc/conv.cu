@@ -201,20 +201,51 @@ __global__ void short_conv_decode_kernel(const T* __restrict__ bcx, const float*
                                          const float* __restrict__ bias, float* __restrict__ state,
                                          const int* __restrict__ seq_of_token, const int* __restrict__ slots,
                                          T* __restrict__ out, int C, int L, int write) {
+  constexpr int FEW = 4;  // up to this many taps everything is fetched at once: one trip to memory, not one per tap
   chain_release();
-  chain_wait();
   const int t = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+  // What the host wrote for this step (which request, which state row) and the weights do not wait for the kernel ahead.
   const int r = seq_of_token[t];
   const int slot = r >= 0 ? slots[r] : -1;
+  float tap[FEW] = {0.f, 0.f, 0.f, 0.f}, add = 0.f;
+  if (c < C && L <= FEW) {
+#pragma unroll
+    for (int i = 0; i < FEW; ++i)
+      if (i < L) tap[i] = taps[(size_t)c * L + i];
+    if (bias) add = bias[c];
+  }
+  chain_wait();
+  if (c >= C) return;
   if (slot < 0) {
     out[(size_t)t * C + c] = from_f32<T>(0.f);
     return;
   }
   const T* row = bcx + (size_t)t * 3 * C;
-  const float u = to_f32(row[c]) * to_f32(row[2 * C + c]);
   float* hist = state + (size_t)slot * (L - 1) * C + c;
+  if (L <= FEW) {
+    float h[FEW - 1] = {0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < FEW - 1; ++i)
+      if (i < L - 1) h[i] = hist[(size_t)i * C];
+    const float b = to_f32(row[c]), gate = to_f32(row[C + c]), x = to_f32(row[2 * C + c]);
+    const float u = b * x;
+    float acc = 0.f, last = tap[0];
+#pragma unroll
+    for (int i = 0; i < FEW - 1; ++i) {
+      if (i < L - 1) {
+        acc = fmaf(h[i], tap[i], acc);
+        if (i > 0 && write) hist[(size_t)(i - 1) * C] = h[i];
+      }
+      last = i + 1 == L - 1 ? tap[i + 1] : last;
+    }
+    acc = fmaf(u, last, acc);
+    if (write) hist[(size_t)(L - 2) * C] = u;
+    if (bias) acc += add;
+    out[(size_t)t * C + c] = from_f32<T>(gate * acc);
+    return;
+  }
+  const float u = to_f32(row[c]) * to_f32(row[2 * C + c]);
   float acc = 0.f;
   for (int i = 0; i < L - 1; ++i) {
     const float h = hist[(size_t)i * C];

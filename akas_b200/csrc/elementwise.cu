@@ -60,16 +60,20 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, TO
   __shared__ float scratch[32];
   const int i = blockIdx.x;
   const float* src = x + (size_t)(rows ? rows[i] : i) * C;
-  float v[PER_THREAD][8];
+  float v[PER_THREAD][8], g[PER_THREAD][8];
   float ss = 0.f;
 #pragma unroll
-  for (int p = 0; p < PER_THREAD; ++p) {
+  for (int p = 0; p < PER_THREAD; ++p) {  // the row and the weights in one trip to memory
     const int c = (p * 256 + threadIdx.x) * 8;
     if (c < C) {
       const float4 a = *reinterpret_cast<const float4*>(src + c);
       const float4 b = *reinterpret_cast<const float4*>(src + c + 4);
+      const float4 wa = *reinterpret_cast<const float4*>(w + c);
+      const float4 wb = *reinterpret_cast<const float4*>(w + c + 4);
       v[p][0] = a.x; v[p][1] = a.y; v[p][2] = a.z; v[p][3] = a.w;
       v[p][4] = b.x; v[p][5] = b.y; v[p][6] = b.z; v[p][7] = b.w;
+      g[p][0] = wa.x; g[p][1] = wa.y; g[p][2] = wa.z; g[p][3] = wa.w;
+      g[p][4] = wb.x; g[p][5] = wb.y; g[p][6] = wb.z; g[p][7] = wb.w;
 #pragma unroll
       for (int e = 0; e < 8; ++e) ss = fmaf(v[p][e], v[p][e], ss);
     }
@@ -81,12 +85,9 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, TO
   for (int p = 0; p < PER_THREAD; ++p) {
     const int c = (p * 256 + threadIdx.x) * 8;
     if (c < C) {
-      const float4 wa = *reinterpret_cast<const float4*>(w + c);
-      const float4 wb = *reinterpret_cast<const float4*>(w + c + 4);
-      const float g[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
       float o[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) o[e] = v[p][e] * inv * (zero_centered ? 1.f + g[e] : g[e]);
+      for (int e = 0; e < 8; ++e) o[e] = v[p][e] * inv * (zero_centered ? 1.f + g[p][e] : g[p][e]);
       store8(dst + c, o);
     }
   }
