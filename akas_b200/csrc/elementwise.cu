@@ -59,21 +59,30 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, TO
   chain_release();  // a kernel after this one that was launched as its programmatic dependent may set itself up meanwhile
   __shared__ float scratch[32];
   const int i = blockIdx.x;
-  const float* src = x + (size_t)(rows ? rows[i] : i) * C;
+  // the weights and (what the host wrote for this step) the row's number do not wait for the kernel ahead
+  const size_t row = rows ? rows[i] : i;
   float v[PER_THREAD][8], g[PER_THREAD][8];
+#pragma unroll
+  for (int p = 0; p < PER_THREAD; ++p) {
+    const int c = (p * 256 + threadIdx.x) * 8;
+    if (c < C) {
+      const float4 wa = *reinterpret_cast<const float4*>(w + c);
+      const float4 wb = *reinterpret_cast<const float4*>(w + c + 4);
+      g[p][0] = wa.x; g[p][1] = wa.y; g[p][2] = wa.z; g[p][3] = wa.w;
+      g[p][4] = wb.x; g[p][5] = wb.y; g[p][6] = wb.z; g[p][7] = wb.w;
+    }
+  }
+  chain_wait();
+  const float* src = x + row * C;
   float ss = 0.f;
 #pragma unroll
-  for (int p = 0; p < PER_THREAD; ++p) {  // the row and the weights in one trip to memory
+  for (int p = 0; p < PER_THREAD; ++p) {
     const int c = (p * 256 + threadIdx.x) * 8;
     if (c < C) {
       const float4 a = *reinterpret_cast<const float4*>(src + c);
       const float4 b = *reinterpret_cast<const float4*>(src + c + 4);
-      const float4 wa = *reinterpret_cast<const float4*>(w + c);
-      const float4 wb = *reinterpret_cast<const float4*>(w + c + 4);
       v[p][0] = a.x; v[p][1] = a.y; v[p][2] = a.z; v[p][3] = a.w;
       v[p][4] = b.x; v[p][5] = b.y; v[p][6] = b.z; v[p][7] = b.w;
-      g[p][0] = wa.x; g[p][1] = wa.y; g[p][2] = wa.z; g[p][3] = wa.w;
-      g[p][4] = wb.x; g[p][5] = wb.y; g[p][6] = wb.z; g[p][7] = wb.w;
 #pragma unroll
       for (int e = 0; e < 8; ++e) ss = fmaf(v[p][e], v[p][e], ss);
     }
@@ -98,11 +107,10 @@ AKAS_API int akas_rmsnorm(const void* x, const float* w, void* y, const int* row
   if (M <= 0) return 0;
   if (in_dtype == AKAS_F32 && C % 8 == 0 && C >= 1024 && C <= 8192 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
 #define AKAS_ROWS(TO, P) \
-  rmsnorm_rows_kernel<TO, P><<<M, 256, 0, stream>>>((const float*)x, w, (TO*)y, rows, C, eps, zero_centered)
+  return launch_chained(rmsnorm_rows_kernel<TO, P>, dim3(M), dim3(256), 0, stream, (const float*)x, w, (TO*)y, rows, C, eps, zero_centered)
     if (out_dtype == AKAS_F32) { if (C <= 2048) AKAS_ROWS(float, 1); else if (C <= 4096) AKAS_ROWS(float, 2); else AKAS_ROWS(float, 4); }
     else { if (C <= 2048) AKAS_ROWS(bf16, 1); else if (C <= 4096) AKAS_ROWS(bf16, 2); else AKAS_ROWS(bf16, 4); }
 #undef AKAS_ROWS
-    return launch_status();
   }
   const int threads = C >= 2048 ? 512 : C >= 512 ? 256 : 128;
 #define AKAS_NORM(TI, TO) \
