@@ -199,9 +199,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (tile < tiles) break;
     tile -= tiles;
   }
-  if (r >= R) return;  // the grid is sized for 64-token tiles: more blocks than 128-token tiles
+  if (r >= R) {  // the grid is sized for 64-token tiles: more blocks than 128-token tiles
+    chain_wait();
+    return;
+  }
   if (smem_u32(smem) & 1023u) {  // never seen; the tiles' swizzle would be wrong
     if (threadIdx.x == 0) atomicExch(&g_attention_status, 9);
+    chain_wait();
     return;
   }
   const int head = blockIdx.x, kvh = head / (H / KH);
@@ -237,6 +241,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = tmem_base_s;
+  // Up to here the block has read what the host wrote for the step (lengths, positions) and set itself up; the queries
+  // and the pages are the work of the kernel ahead.
+  chain_wait();
 
   auto wait_for = [&](uint64_t* bar, unsigned parity, int code) {
     if (*(volatile int*)&abort_s) return;
@@ -505,9 +512,8 @@ AKAS_API int akas_prefill_attention_tc(const void* q, const void* k_pool, const 
   if (!err) err = rows_map(&map_k, k_pool, pool_rows, D, D, 64);
   if (!err) err = rows_map(&map_v, v_pool, pool_rows, D, D, 64);
   if (err) return err;
-  prefill_attention_tc_kernel<<<dim3(H, tiles), THREADS, SMEM_BYTES, stream>>>(
-      map_q, map_k, map_v, block_table, max_blocks, cu_seqlens, positions, (bf16*)out, scale, window, page_size, H, KH, R);
-  return launch_status();
+  return launch_chained(prefill_attention_tc_kernel, dim3(H, tiles), dim3(THREADS), SMEM_BYTES, stream,
+                        map_q, map_k, map_v, block_table, max_blocks, cu_seqlens, positions, (bf16*)out, scale, window, page_size, H, KH, R);
 }
 
 // 0 if no bounded wait of the kernel has ever run out on the current device (1: producer, 2: tensor cores,

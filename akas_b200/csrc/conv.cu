@@ -96,6 +96,7 @@ short_conv_forward_run_kernel(const T* __restrict__ bcx, const float* __restrict
                               const int* __restrict__ seq_of_token, const int* __restrict__ slots, T* __restrict__ out,
                               int N, int C) {
   chain_release();  // a kernel after this one that was launched as its programmatic dependent may set itself up meanwhile
+  chain_wait();
   const int t0 = blockIdx.x * TT;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (c >= C) return;
@@ -173,6 +174,7 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, float* __rest
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int C,
                                         int L) {
   chain_release();  // a kernel after this one that was launched as its programmatic dependent may set itself up meanwhile
+  chain_wait();
   const int r = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
@@ -284,18 +286,20 @@ AKAS_API int akas_short_conv(const void* bcx, const float* taps, const float* bi
   constexpr int TT = 4;
   const dim3 run((N + TT - 1) / TT, (C / 8 + threads - 1) / threads);
   const bool runs = wide && N >= 256 && L >= 2 && L <= 4 && (uintptr_t)taps % 16 == 0;
+  // (both kernels as programmatic dependents; the state kernel writes what the run kernel ahead of it reads, after its wait)
 #define AKAS_CONV_RUN(T, TAPS)                                                                                        \
-  short_conv_forward_run_kernel<T, TAPS, TT><<<run, threads, 0, stream>>>((const T*)bcx, taps, bias, state, cu_seqlens, \
-                                                                          seq_of_token, slots, (T*)out, N, C)
+  err = launch_chained(short_conv_forward_run_kernel<T, TAPS, TT>, run, dim3(threads), 0, stream, (const T*)bcx, taps, \
+                       bias, (const float*)state, cu_seqlens, seq_of_token, slots, (T*)out, N, C)
   if (runs) {
+    int err = 0;
     if (dtype == AKAS_F32) {
       if (L == 2) AKAS_CONV_RUN(float, 2); else if (L == 3) AKAS_CONV_RUN(float, 3); else AKAS_CONV_RUN(float, 4);
-      if (write) short_conv_state_kernel<float><<<upd, threads, 0, stream>>>((const float*)bcx, state, cu_seqlens, slots, C, L);
+      if (!err && write) err = launch_chained(short_conv_state_kernel<float>, upd, dim3(threads), 0, stream, (const float*)bcx, state, cu_seqlens, slots, C, L);
     } else {
       if (L == 2) AKAS_CONV_RUN(bf16, 2); else if (L == 3) AKAS_CONV_RUN(bf16, 3); else AKAS_CONV_RUN(bf16, 4);
-      if (write) short_conv_state_kernel<bf16><<<upd, threads, 0, stream>>>((const bf16*)bcx, state, cu_seqlens, slots, C, L);
+      if (!err && write) err = launch_chained(short_conv_state_kernel<bf16>, upd, dim3(threads), 0, stream, (const bf16*)bcx, state, cu_seqlens, slots, C, L);
     }
-    return launch_status();
+    return err;
   }
 #undef AKAS_CONV_RUN
   if (dtype == AKAS_F32) {
