@@ -34,6 +34,32 @@ def test_key_parts_of_decode_attention():
         assert not merged(64, 5, 128, 64) and not merged(64, 5, 64, 16)
 
 
+def test_plan_of_decode_attention():
+    """Key parts and which kernel: a block per (token, KV head, key part) while that is at most three blocks per SM, a
+    fixed number of blocks that walk those items beyond; up to 8 parts that meet inside their cluster where a part stays
+    within 8 tiles, rather than more parts and a merge kernel."""
+    import unittest.mock as mock
+
+    import torch
+
+    plan = cuda.decode_plan
+    bf16 = torch.bfloat16
+    with mock.patch.object(cuda, "_sm_count", return_value=148), mock.patch.object(cuda, "_items_places", return_value=592):
+        assert plan(8, 32, 8, 64, 64, 4096, bf16) == (5, False)
+        assert plan(1, 32, 8, 64, 64, 4096, bf16) == (8, False)         # 16 parts would need a merge kernel
+        assert plan(1, 32, 8, 64, 64, 30000, bf16) == (38, False)       # long parts: as many as fill the GPU
+        assert plan(64, 32, 8, 64, 64, 4096, bf16) == (2, True)         # 1,024 items for 444 places
+        assert plan(32, 32, 8, 64, 64, 4096, bf16) == (2, True)
+        assert plan(16, 32, 8, 64, 64, 4096, bf16) == (3, False)
+        assert plan(64, 32, 8, 128, 64, 4096, bf16) == (2, False)       # the TMA-fed kernels take head size 64 only
+        assert plan(64, 32, 8, 64, 16, 4096, bf16) == (2, False)        # and pages of whole 64-key tiles
+        assert plan(64, 32, 8, 64, 64, 4096, torch.float32) == (2, False)
+        with mock.patch.object(cuda, "decode_items", "0"):
+            assert plan(64, 32, 8, 64, 64, 4096, bf16) == (2, False)
+    with mock.patch.object(cuda, "_sm_count", return_value=148), mock.patch.object(cuda, "_items_places", return_value=0):
+        assert plan(64, 32, 8, 64, 64, 4096, bf16) == (2, False)        # the kernel cannot run on this device
+
+
 def test_reports_are_compared_case_by_case():
     from akas_b200.bench import case_lengths, compare_reports
 
