@@ -890,7 +890,11 @@ def decode_plan(num_tokens: int, heads: int, kv_heads: int, head_dim: int, page_
         # up to 8 tiles a part: 8 parts that meet inside their cluster, rather than more parts and a kernel that merges
         # them (one request of 2,048 keys: 1,495 against 1,478 tokens/s)
         splits = 8
-    if decode_items == "auto" and blocks * splits <= 3 * _sm_count():
+    if decode_items == "auto" and not 3 * _sm_count() < blocks * splits <= 8 * _sm_count():
+        # up to three blocks per SM all run at once; far more than the GPU holds are spread well by the hardware as they
+        # come (128 requests of 8,192 keys: 40.1k tokens/s with a block per item, 37.7k with blocks that walk them,
+        # whose items are dealt out beforehand); in between, the last round would run part empty (32 requests: 24.5k
+        # against 25.9k, at 8,192 keys 18.3k against 20.4k)
         return splits, False
     # (the same parts: measured at 64 requests of 2,048 keys, 48.1k tokens/s in 2 parts, 47.3k in 3, 46.4k in 6 and
     # 44.3k in 11 against 47.2k with a block per item: what an item costs beside its tiles is not hidden by the ring)

@@ -51,6 +51,7 @@ def test_plan_of_decode_attention():
         assert plan(64, 32, 8, 64, 64, 4096, bf16) == (2, True)         # 1,024 items for 444 places
         assert plan(32, 32, 8, 64, 64, 4096, bf16) == (2, True)
         assert plan(16, 32, 8, 64, 64, 4096, bf16) == (3, False)
+        assert plan(128, 32, 8, 64, 64, 8192, bf16) == (2, False)       # 2,048 blocks: the hardware spreads them as they come
         assert plan(64, 32, 8, 128, 64, 4096, bf16) == (2, False)       # the TMA-fed kernels take head size 64 only
         assert plan(64, 32, 8, 64, 16, 4096, bf16) == (2, False)        # and pages of whole 64-key tiles
         assert plan(64, 32, 8, 64, 64, 4096, torch.float32) == (2, False)
