@@ -703,32 +703,34 @@ def test_decode_attention_from_the_qkv_product(ops, h, kh, page, window, rot, no
     assert torch.equal(got, want) and torch.equal(k1[live], before[live])
 
 
-def test_decode_attention_with_more_items_than_blocks(ops):
-    """96 requests of 8 key/value heads with contexts from 1 to 3,000 keys: more (token, KV head, key part) items than
-    blocks fit the GPU, so the blocks walk them (several rounds, the ring of tiles running on from item to item, empty
-    parts and padding tokens among them)."""
+def test_decode_attention_with_more_items_than_blocks(ops, monkeypatch):
+    """66 requests of 8 key/value heads with contexts from 1 to 3,000 keys: more (token, KV head, key part) items than
+    blocks fit the GPU, so the blocks walk them (two rounds, the ring of tiles running on from item to item, empty
+    parts and padding tokens among them); then 130 requests with the walking kernel asked for (four rounds)."""
     cuda, ref = ops
     h, kh, d, page, dtype = 32, 8, 64, 64, torch.bfloat16
     g = torch.Generator().manual_seed(5)
-    contexts = [1, 2, 63, 64, 65, 3000] + torch.randint(1, 2500, (90,), generator=g).tolist()
-    cu, seq = _batch([1] * len(contexts), pad=3)
-    pos = torch.tensor([c - 1 for c in contexts] + [0, 0, 0], dtype=torch.int32, device=DEV)
-    pages = sum(-(-c // page) for c in contexts) + 3
-    bt = _tables(contexts, page, pages, 6)
-    k, v = _pools(pages, kh, page, d, dtype, 50)
-    for r, context in enumerate(contexts):
-        if context % page:
-            last = int(bt[r, (context - 1) // page])
-            k[last, :, context % page:] = float("nan")
-            v[last, :, context % page:] = float("nan")
-    q = _rand((pos.numel(), h * d), dtype, 52)
-    step = _Decode(max(contexts))
-    assert cuda.decode_plan(len(contexts) + 3, h, kh, d, page, step.max_context, dtype)[1]
-    want = ref.paged_attention(q, k, v, bt, seq, pos, d ** -0.5, None, page)
-    got = cuda.paged_attention(q, k, v, bt, seq, pos, d ** -0.5, None, page, step)
-    _close(got, want, dtype, "walking the items")
-    assert cuda.decode_attention_status() == 0
-    assert torch.equal(got[-3:], torch.zeros_like(got[-3:]))
+    for extra, items in ((60, "auto"), (124, "1")):
+        monkeypatch.setattr(cuda, "decode_items", items)
+        contexts = [1, 2, 63, 64, 65, 3000] + torch.randint(1, 2500, (extra,), generator=g).tolist()
+        cu, seq = _batch([1] * len(contexts), pad=3)
+        pos = torch.tensor([c - 1 for c in contexts] + [0, 0, 0], dtype=torch.int32, device=DEV)
+        pages = sum(-(-c // page) for c in contexts) + 3
+        bt = _tables(contexts, page, pages, 6)
+        k, v = _pools(pages, kh, page, d, dtype, 50)
+        for r, context in enumerate(contexts):
+            if context % page:
+                last = int(bt[r, (context - 1) // page])
+                k[last, :, context % page:] = float("nan")
+                v[last, :, context % page:] = float("nan")
+        q = _rand((pos.numel(), h * d), dtype, 52)
+        step = _Decode(max(contexts))
+        assert cuda.decode_plan(len(contexts) + 3, h, kh, d, page, step.max_context, dtype)[1]
+        want = ref.paged_attention(q, k, v, bt, seq, pos, d ** -0.5, None, page)
+        got = cuda.paged_attention(q, k, v, bt, seq, pos, d ** -0.5, None, page, step)
+        _close(got, want, dtype, "walking the items")
+        assert cuda.decode_attention_status() == 0
+        assert torch.equal(got[-3:], torch.zeros_like(got[-3:]))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
