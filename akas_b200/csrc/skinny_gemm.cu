@@ -148,7 +148,7 @@ template <int NT, int IN, int OUT>
 __global__ void __launch_bounds__(THREADS, 2)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __restrict__ x_, const int* __restrict__ rows,
                    const float* __restrict__ norm_w, float eps, int zero_centered, void* __restrict__ y_, int M, int O,
-                   int K, int num_tiles, int ksplit, const ConvTail tail) {
+                   int K, int num_tiles, int ksplit, int groups, ConvTail tail) {
   constexpr int STAGES = Ring<OUT>::DEPTH, STAGE_BYTES = Ring<OUT>::BYTES, RT = Ring<OUT>::ROWS;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);  // [STAGES][STAGE_BYTES]
@@ -170,7 +170,21 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
   const int chunk0 = all_chunks * rank / ksplit, chunks = all_chunks * (rank + 1) / ksplit - chunk0;
   const int k0 = chunk0 * KC, k_len = min(K, (chunk0 + chunks) * KC) - k0;
   const int XS = ((all_chunks + ksplit - 1) / ksplit) * KC + 32;
-  const int first_tile = (int)blockIdx.x / ksplit, tile_step = (int)gridDim.x / ksplit;  // of this block's cluster
+  // Token groups (9 to 16 tokens on the kernel for 8): every row tile is the work of `groups` blocks (clusters), one per
+  // group of NT * 8 tokens, that run side by side and read the same weights, the second one mostly from the L2. A
+  // block's group is fixed (the host makes the number of clusters a multiple of `groups`); from here on it sees only
+  // its own tokens.
+  const int item0 = (int)blockIdx.x / ksplit, item_step = (int)gridDim.x / ksplit;  // of this block's cluster
+  const int first_tile = item0 / groups, tile_step = item_step / groups;
+  if (groups > 1) {
+    const int m0 = (item0 % groups) * NT * 8;
+    if (rows) rows += m0;
+    else x_ = IN == IN_NORM ? (const void*)((const float*)x_ + (size_t)m0 * K) : (const void*)((const bf16*)x_ + (size_t)m0 * K);
+    const size_t width = OUT == OUT_SWIGLU ? O / 2 : OUT == OUT_CONV ? O / 3 : O;
+    y_ = OUT == OUT_F32 || OUT == OUT_ACC ? (void*)((float*)y_ + m0 * width) : (void*)((bf16*)y_ + m0 * width);
+    if (OUT == OUT_CONV) tail.seq_of_token += m0;
+    M = max(0, min(M - m0, NT * 8));
+  }
   const int my_tiles = first_tile < num_tiles ? (num_tiles - first_tile + tile_step - 1) / tile_step : 0;
   const int items = my_tiles * chunks;  // this block's work: the chunks of its row tiles, in order
 
@@ -600,14 +614,14 @@ struct SplitPlan {
 
 template <int NT, int IN, int OUTM>
 int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
-               const void* W, void* y, int M, int O, int K, const ConvTail& tail, cudaStream_t stream) {
+               const void* W, void* y, int M, int O, int K, const ConvTail& tail, int groups, cudaStream_t stream) {
   auto kernel = skinny_gemm_kernel<NT, IN, OUTM>;
   constexpr bool UNCUT = OUTM == OUT_SWIGLU || OUTM == OUT_CONV;  // read-outs that need a tile's whole K in one block
   if (block_smem<NT, OUTM>(K, 1) > kMaxSmemBytes && (UNCUT || block_smem<NT, OUTM>(K, MAX_KSPLIT) > kMaxSmemBytes))
     return (int)cudaErrorInvalidValue;
   static int sms_of[64] = {};  // by device ordinal, like the plans below: a launch attribute belongs to a device
   static std::mutex mutex;
-  static std::map<std::tuple<int, int, int>, SplitPlan> plans;  // (device, tiles, K) -> how the product is cut
+  static std::map<std::tuple<int, int, int, int>, SplitPlan> plans;  // (device, tiles, token groups, K) -> how the product is cut
   static std::map<std::tuple<int, int, int>, int> cluster_room;  // (device, ksplit, smem) -> clusters resident at once
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
@@ -620,7 +634,7 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
       cudaDeviceGetAttribute(&sms_of[device], cudaDevAttrMultiProcessorCount, device);
     }
     const int sms = sms_of[device];
-    const auto key = std::make_tuple(device, num_tiles, K);
+    const auto key = std::make_tuple(device, num_tiles, groups, K);
     auto found = plans.find(key);
     if (found == plans.end()) {
       // What the busiest SM must fetch, in bytes, if the product is cut into `ksplit` parts of K: its blocks' weights
@@ -661,11 +675,13 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
           clusters = min(clusters, cluster_room[room_key]);
           if (clusters < 1) continue;
         }
-        clusters = min(clusters, num_tiles);
-        // every cluster gets the same number of row tiles (to within one)
-        const int rounds = (num_tiles + clusters - 1) / clusters;
+        // every row tile is the work of `groups` clusters (one per group of tokens) that run side by side: the
+        // clusters come in sets of that many, and every set gets the same number of row tiles (to within one)
+        int sets = min(max(1, clusters / groups), num_tiles);
+        const int rounds = (num_tiles + sets - 1) / sets;
         if (ksplit > 1 && rounds > SPLIT_TILES) continue;
-        clusters = (num_tiles + rounds - 1) / rounds;
+        sets = (num_tiles + rounds - 1) / rounds;
+        clusters = sets * groups;
         const int blocks = clusters * ksplit, on_busiest_sm = (blocks + sms - 1) / sms;
         const long long part_k = (long long)(chunks + ksplit - 1) / ksplit * KC;
         long long fetched = on_busiest_sm * (rounds * 16 * part_k * 2 + NT * 8 * part_k * 2);
@@ -707,21 +723,21 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
   }
   config.attrs = attribute;
   config.numAttrs = n;
-  return (int)cudaLaunchKernelEx(&config, kernel, map, x, rows, norm_w, eps, zero_centered, y, M, O, K, num_tiles, plan.ksplit, tail);
+  return (int)cudaLaunchKernelEx(&config, kernel, map, x, rows, norm_w, eps, zero_centered, y, M, O, K, num_tiles, plan.ksplit, groups, tail);
 }
 
 template <int NT, int IN>
 int launch_out(int out_mode, const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
-               const void* W, void* y, int M, int O, int K, const ConvTail& tail, cudaStream_t stream) {
+               const void* W, void* y, int M, int O, int K, const ConvTail& tail, int groups, cudaStream_t stream) {
   const int tiles = (O + 15) / 16;
   switch (out_mode) {
-    case OUT_BF16: return launch_one<NT, IN, OUT_BF16>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
-    case OUT_F32: return launch_one<NT, IN, OUT_F32>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
-    case OUT_ACC: return launch_one<NT, IN, OUT_ACC>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+    case OUT_BF16: return launch_one<NT, IN, OUT_BF16>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, groups, stream);
+    case OUT_F32: return launch_one<NT, IN, OUT_F32>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, groups, stream);
+    case OUT_ACC: return launch_one<NT, IN, OUT_ACC>(tiles, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, groups, stream);
     case OUT_SWIGLU:
-      return launch_one<NT, IN, OUT_SWIGLU>((O / 2 + 7) / 8, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+      return launch_one<NT, IN, OUT_SWIGLU>((O / 2 + 7) / 8, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, groups, stream);
     case OUT_CONV:
-      return launch_one<NT, IN, OUT_CONV>((O / 3 + 7) / 8, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+      return launch_one<NT, IN, OUT_CONV>((O / 3 + 7) / 8, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, groups, stream);
     default: return (int)cudaErrorInvalidValue;
   }
 }
@@ -737,12 +753,17 @@ static int skinny_dispatch(const void* x, const int* rows, const float* norm_w, 
   if (M > 16 || K <= 0 || K % 64 || (out_mode == OUT_SWIGLU && O % 2) || (out_mode == OUT_CONV && O % 3)) return (int)cudaErrorInvalidValue;
   if (in_mode == IN_NORM && norm_w == nullptr) return (int)cudaErrorInvalidValue;
   if ((uintptr_t)W % 16 || (uintptr_t)x % 16) return (int)cudaErrorInvalidValue;  // TMA and 16-byte loads
-  if (M <= 8) {
-    if (in_mode == IN_BF16) return launch_out<1, IN_BF16>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
-    return launch_out<1, IN_NORM>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+  // 9 to 16 tokens: as two groups of 8 on the kernel for 8, whose blocks then come in pairs that read the same weights
+  // (the second mostly from the L2), rather than on the kernel for 16, whose activations leave room for one block per
+  // SM only (AKAS_B200_SKINNY_GROUPS=0: that kernel).
+  static const bool in_groups = [] { const char* v = getenv("AKAS_B200_SKINNY_GROUPS"); return !(v && v[0] == '0'); }();
+  if (M <= 8 || in_groups) {
+    const int groups = M <= 8 ? 1 : 2;
+    if (in_mode == IN_BF16) return launch_out<1, IN_BF16>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, groups, stream);
+    return launch_out<1, IN_NORM>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, groups, stream);
   }
-  if (in_mode == IN_BF16) return launch_out<2, IN_BF16>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
-  return launch_out<2, IN_NORM>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, stream);
+  if (in_mode == IN_BF16) return launch_out<2, IN_BF16>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, 1, stream);
+  return launch_out<2, IN_NORM>(out_mode, x, rows, norm_w, eps, zero_centered, W, y, M, O, K, tail, 1, stream);
 }
 
 AKAS_API int akas_skinny_gemm(const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
