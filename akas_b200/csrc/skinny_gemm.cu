@@ -144,11 +144,11 @@ __device__ __forceinline__ void cluster_meet() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-template <int NT, int IN, int OUT>
+template <int NT, int IN, int OUT, bool GROUPED>
 __global__ void __launch_bounds__(THREADS, 2)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __restrict__ x_, const int* __restrict__ rows,
                    const float* __restrict__ norm_w, float eps, int zero_centered, void* __restrict__ y_, int M, int O,
-                   int K, int num_tiles, int ksplit, int groups, ConvTail tail) {
+                   int K, int num_tiles, int ksplit, int groups, const ConvTail tail) {
   constexpr int STAGES = Ring<OUT>::DEPTH, STAGE_BYTES = Ring<OUT>::BYTES, RT = Ring<OUT>::ROWS;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);  // [STAGES][STAGE_BYTES]
@@ -174,15 +174,18 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
   // group of NT * 8 tokens, that run side by side and read the same weights, the second one mostly from the L2. A
   // block's group is fixed (the host makes the number of clusters a multiple of `groups`); from here on it sees only
   // its own tokens.
+  // (GROUPED is a template argument so that the kernel for a single group keeps its registers: with the group's offsets
+  // computed in every instance the staging of the normed rows spilled)
   const int item0 = (int)blockIdx.x / ksplit, item_step = (int)gridDim.x / ksplit;  // of this block's cluster
-  const int first_tile = item0 / groups, tile_step = item_step / groups;
-  if (groups > 1) {
+  const int first_tile = GROUPED ? item0 / groups : item0, tile_step = GROUPED ? item_step / groups : item_step;
+  const int* token_request = tail.seq_of_token;
+  if (GROUPED) {
     const int m0 = (item0 % groups) * NT * 8;
     if (rows) rows += m0;
     else x_ = IN == IN_NORM ? (const void*)((const float*)x_ + (size_t)m0 * K) : (const void*)((const bf16*)x_ + (size_t)m0 * K);
     const size_t width = OUT == OUT_SWIGLU ? O / 2 : OUT == OUT_CONV ? O / 3 : O;
     y_ = OUT == OUT_F32 || OUT == OUT_ACC ? (void*)((float*)y_ + m0 * width) : (void*)((bf16*)y_ + m0 * width);
-    if (OUT == OUT_CONV) tail.seq_of_token += m0;
+    if (OUT == OUT_CONV) token_request += m0;
     M = max(0, min(M - m0, NT * 8));
   }
   const int my_tiles = first_tile < num_tiles ? (num_tiles - first_tile + tile_step - 1) / tile_step : 0;
@@ -247,7 +250,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
     if (OUT == OUT_CONV && tid < NT * 8) {
       // which request a token belongs to and where its state lies is what the host wrote for this step: looked up while
       // the kernel ahead is still at work, not once per tile in the read-out (two loads, one after the other)
-      const int r = tid < M ? tail.seq_of_token[tid] : -1;
+      const int r = tid < M ? token_request[tid] : -1;
       slot_s[tid] = r >= 0 ? tail.slots[r] : -1;
     }
     if (IN == IN_BF16) {
@@ -615,7 +618,7 @@ struct SplitPlan {
 template <int NT, int IN, int OUTM>
 int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_w, float eps, int zero_centered,
                const void* W, void* y, int M, int O, int K, const ConvTail& tail, int groups, cudaStream_t stream) {
-  auto kernel = skinny_gemm_kernel<NT, IN, OUTM>;
+  auto kernel = groups > 1 ? skinny_gemm_kernel<NT, IN, OUTM, true> : skinny_gemm_kernel<NT, IN, OUTM, false>;
   constexpr bool UNCUT = OUTM == OUT_SWIGLU || OUTM == OUT_CONV;  // read-outs that need a tile's whole K in one block
   if (block_smem<NT, OUTM>(K, 1) > kMaxSmemBytes && (UNCUT || block_smem<NT, OUTM>(K, MAX_KSPLIT) > kMaxSmemBytes))
     return (int)cudaErrorInvalidValue;
@@ -629,7 +632,9 @@ int launch_one(int num_tiles, const void* x, const int* rows, const float* norm_
   {
     std::lock_guard<std::mutex> lock(mutex);
     if (sms_of[device] == 0) {
-      const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
+      cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT, IN, OUTM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(skinny_gemm_kernel<NT, IN, OUTM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
       if (e != cudaSuccess) return (int)e;
       cudaDeviceGetAttribute(&sms_of[device], cudaDevAttrMultiProcessorCount, device);
     }
